@@ -1,0 +1,296 @@
+// Grouped-query attention over the paged cache, for prompt portions and decoded tokens alike.
+//
+// A step's token rows are cut into query blocks: up to `bq` consecutive rows of ONE request.  The
+// keys are cut into splits of `split` positions at absolute boundaries (0, split, 2*split, ...).
+// One CTA takes (query block, kv head, split): it streams that split's keys and values once for all
+// query heads of the group (the reference's per-KV-group variant, attn_neon.h:130-175) and keeps,
+// for every (row, head), a running maximum, a running sum and an unnormalised output.  It writes
+// them as a partial result; `attention_merge` joins the partials of a row in split order.
+//
+// The math of one (row, head) is that of qwen_infer.c:1538-1543: s_t = (q . K_t) * scale for the
+// visible t (t <= position, and t > position - window when there is a window), softmax with the
+// maximum subtracted, o = sum_t p_t V_t.  Everything is float.  Because tiles and splits start at
+// absolute positions and a row never shares an accumulator with another row, the result of a row
+// does not depend on how the step was cut or on what else is in the batch.
+#include "common.cuh"
+
+namespace bg {
+
+constexpr int ATT_THREADS = 256;
+constexpr int ATT_WARPS = ATT_THREADS / 32;
+constexpr int ATT_MAX_DPL = 8;      // head_dim <= 256: at most 8 output features per lane
+
+struct AttnParams {
+    const void* q;          // [T, nh, hd] with row stride q_stride (elements)
+    int q_stride;
+    const void* kv_pool;    // [num_pages][2][nkv][page_size][hd]
+    int num_pages, page_size;
+    const int* block_table; // [B, max_pages]
+    int max_pages;
+    const int* positions;   // [T]
+    const int* qblk;        // [n_qblk][3] = (request, first row, number of rows)
+    float* part_o;          // [T*nh][max_splits][hd]
+    float* part_ml;         // [T*nh][max_splits][2]
+    int max_splits;
+    int nh, nkv, hd, group;
+    int window;             // 0: none
+    int split;              // keys per split
+    int tile;               // keys per shared-memory tile (32 or 64), divides split
+    int bq;                 // rows per query block (upper bound)
+    float scale;
+    unsigned* status;
+};
+
+template <typename TQ, typename TC>
+__global__ void __launch_bounds__(ATT_THREADS)
+attention_partial_kernel(AttnParams p) {
+    extern __shared__ float smem[];
+    const int hd = p.hd, group = p.group;
+    const int kstride = hd + 1;
+    const int n_rows_max = p.bq * group;
+    float* q_s = smem;                                   // [n_rows_max][hd]
+    float* acc_s = q_s + (size_t)n_rows_max * hd;        // [n_rows_max][hd]
+    float* k_s = acc_s + (size_t)n_rows_max * hd;        // [tile][hd+1]
+    float* v_s = k_s + (size_t)p.tile * kstride;         // [tile][hd]
+    float* m_s = v_s + (size_t)p.tile * hd;              // [n_rows_max]
+    float* l_s = m_s + n_rows_max;                       // [n_rows_max]
+    long long* base_s = (long long*)(l_s + n_rows_max);   // [tile] element offsets (the float count before it is even)
+
+    const int qb = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+    const int req = p.qblk[qb * 3 + 0], row0 = p.qblk[qb * 3 + 1], nq = p.qblk[qb * 3 + 2];
+    if (nq <= 0) return;
+    const int pos_first = p.positions[row0];
+    const int pos_last = p.positions[row0 + nq - 1];
+    const int lo_first = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int k_begin = max(sp * p.split, lo_first);
+    const int k_end = min((sp + 1) * p.split, pos_last + 1);       // exclusive
+    if (k_begin >= k_end) return;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_rows = nq * group;
+    const TQ* q = (const TQ*)p.q;
+    for (int idx = tid; idx < n_rows * hd; idx += ATT_THREADS) {
+        int r = idx / hd, d = idx - r * hd;
+        int qi = r / group, g = r - qi * group;
+        q_s[idx] = to_float(q[(size_t)(row0 + qi) * p.q_stride + (size_t)(kvh * group + g) * hd + d]);
+        acc_s[idx] = 0.0f;
+    }
+    for (int r = tid; r < n_rows; r += ATT_THREADS) { m_s[r] = -INFINITY; l_s[r] = 0.0f; }
+
+    const TC* pool = (const TC*)p.kv_pool;
+    const size_t page_elems = (size_t)2 * p.nkv * p.page_size * hd;
+    const size_t v_off = (size_t)p.nkv * p.page_size * hd;
+    const int tile = p.tile;
+    const int t_first = (k_begin / tile) * tile;
+
+    for (int t0 = t_first; t0 < k_end; t0 += tile) {
+        __syncthreads();
+        // element offset of each key's K row in the pool, or -1 for a key outside [k_begin, k_end)
+        for (int j = tid; j < tile; j += ATT_THREADS) {
+            int key = t0 + j;
+            long long off = -1;
+            if (key >= k_begin && key < k_end) {
+                int page = p.block_table[(size_t)req * p.max_pages + key / p.page_size];
+                if (page < 0 || page >= p.num_pages) {
+                    if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE);
+                } else {
+                    off = (long long)((size_t)page * page_elems + ((size_t)kvh * p.page_size + key % p.page_size) * hd);
+                }
+            }
+            base_s[j] = off;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < tile * hd; idx += ATT_THREADS) {
+            int j = idx / hd, d = idx - j * hd;
+            long long off = base_s[j];
+            float kv = 0.0f, vv = 0.0f;
+            if (off >= 0) { kv = to_float(pool[off + d]); vv = to_float(pool[off + v_off + d]); }
+            k_s[j * kstride + d] = kv;
+            v_s[j * hd + d] = vv;
+        }
+        __syncthreads();
+
+        for (int r = warp; r < n_rows; r += ATT_WARPS) {
+            const int qi = r / group;
+            const int pos = p.positions[row0 + qi];
+            const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+            const float* qr = q_s + (size_t)r * hd;
+            float s[2];
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                s[c] = -INFINITY;
+                int j = c * 32 + lane;
+                if (j < tile) {
+                    int key = t0 + j;
+                    if (key >= lo && key <= pos && key >= k_begin && key < k_end && base_s[j] >= 0) {
+                        const float* kr = k_s + j * kstride;
+                        float dot = 0.0f;
+                        for (int d = 0; d < hd; ++d) dot = fmaf(qr[d], kr[d], dot);
+                        s[c] = dot * p.scale;
+                    }
+                }
+                tmax = fmaxf(tmax, s[c]);
+            }
+            tmax = warp_max(tmax);
+            if (tmax == -INFINITY) continue;            // no visible key of this tile for this row
+            const float m_old = m_s[r];
+            const float m_new = fmaxf(m_old, tmax);
+            const float corr = (m_old == -INFINITY) ? 0.0f : expf(m_old - m_new);
+            float psum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                s[c] = (s[c] == -INFINITY) ? 0.0f : expf(s[c] - m_new);
+                psum += s[c];
+            }
+            psum = warp_sum(psum);
+            float acc[ATT_MAX_DPL];
+            float* ar = acc_s + (size_t)r * hd;
+#pragma unroll
+            for (int i = 0; i < ATT_MAX_DPL; ++i) {
+                int d = i * 32 + lane;
+                acc[i] = (d < hd) ? ar[d] * corr : 0.0f;
+            }
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                if (c * 32 >= tile) break;
+                for (int jj = 0; jj < 32; ++jj) {
+                    float pj = __shfl_sync(0xffffffffu, s[c], jj);
+                    if (pj != 0.0f) {
+                        const float* vr = v_s + (c * 32 + jj) * hd;
+#pragma unroll
+                        for (int i = 0; i < ATT_MAX_DPL; ++i) {
+                            int d = i * 32 + lane;
+                            if (d < hd) acc[i] = fmaf(pj, vr[d], acc[i]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < ATT_MAX_DPL; ++i) {
+                int d = i * 32 + lane;
+                if (d < hd) ar[d] = acc[i];
+            }
+            if (lane == 0) { m_s[r] = m_new; l_s[r] = l_s[r] * corr + psum; }
+        }
+    }
+    __syncthreads();
+    // partial results, only for rows that see at least one key of this split
+    for (int r = warp; r < n_rows; r += ATT_WARPS) {
+        const int qi = r / group, g = r - qi * group;
+        const int pos = p.positions[row0 + qi];
+        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        if (pos < sp * p.split || lo >= (sp + 1) * p.split) continue;
+        const size_t prow = ((size_t)(row0 + qi) * p.nh + (size_t)kvh * group + g) * p.max_splits + sp;
+        for (int d = lane; d < hd; d += 32) p.part_o[prow * hd + d] = acc_s[(size_t)r * hd + d];
+        if (lane == 0) { p.part_ml[prow * 2 + 0] = m_s[r]; p.part_ml[prow * 2 + 1] = l_s[r]; }
+    }
+}
+
+// out[t, h, :] = sum_s o_s * exp(m_s - m) / sum_s l_s * exp(m_s - m), over the splits the row sees,
+// in split order.  One warp per (row, head).
+template <typename TO>
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
+                                       int T, int nh, int hd, int max_splits, int split, int window) {
+    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= T * nh) return;
+    const int t = w / nh, h = w - t * nh;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int s_lo = lo / split, s_hi = pos / split;
+    const size_t prow = (size_t)w * max_splits;
+    float m = -INFINITY;
+    for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, part_ml[(prow + s) * 2]);
+    float l = 0.0f;
+    float acc[ATT_MAX_DPL];
+#pragma unroll
+    for (int i = 0; i < ATT_MAX_DPL; ++i) acc[i] = 0.0f;
+    for (int s = s_lo; s <= s_hi; ++s) {
+        const float ms = part_ml[(prow + s) * 2];
+        const float f = (ms == -INFINITY) ? 0.0f : expf(ms - m);
+        l = fmaf(part_ml[(prow + s) * 2 + 1], f, l);
+        const float* po = part_o + (prow + s) * hd;
+#pragma unroll
+        for (int i = 0; i < ATT_MAX_DPL; ++i) {
+            int d = i * 32 + lane;
+            if (d < hd) acc[i] = fmaf(po[d], f, acc[i]);
+        }
+    }
+    const float inv = 1.0f / l;
+    TO* o = out + (size_t)t * out_stride + (size_t)h * hd;
+#pragma unroll
+    for (int i = 0; i < ATT_MAX_DPL; ++i) {
+        int d = i * 32 + lane;
+        if (d < hd) o[d] = from_float<TO>(acc[i] * inv);
+    }
+}
+
+}  // namespace bg
+
+using namespace bg;
+
+static size_t attention_smem_bytes(int bq, int group, int hd, int tile) {
+    size_t rows = (size_t)bq * group;
+    size_t floats = rows * hd * 2 + (size_t)tile * (hd + 1) + (size_t)tile * hd + rows * 2;
+    return floats * sizeof(float) + (size_t)tile * sizeof(long long) + 8;
+}
+
+// Rows per query block and keys per tile that fit the shared memory of one CTA for these sizes.
+// Returns 0 and fills bq and tile, or BG_ERR_UNSUPPORTED.
+extern "C" int bg_attention_plan(int group, int hd, int* bq_out, int* tile_out) {
+    if (hd <= 0 || hd > 32 * ATT_MAX_DPL || group <= 0) return BG_ERR_UNSUPPORTED;
+    const size_t limit = 200 * 1024;
+    for (int tile = 64; tile >= 32; tile >>= 1) {
+        for (int bq = 16; bq >= 1; bq >>= 1) {
+            if (attention_smem_bytes(bq, group, hd, tile) <= limit) { *bq_out = bq; *tile_out = tile; return BG_OK; }
+        }
+    }
+    return BG_ERR_UNSUPPORTED;
+}
+
+extern "C" int bg_attention_partial(const void* q, int q_dtype, int q_stride, const void* kv_pool, int cache_dtype,
+                                    int num_pages, int page_size, const int* block_table, int max_pages,
+                                    const int* positions, const int* qblk, int n_qblk, float* part_o, float* part_ml,
+                                    int max_splits, int n_splits_launch, int nh, int nkv, int hd, int window, int split,
+                                    int tile, int bq, float scale, unsigned* status, cudaStream_t stream) {
+    if (n_qblk <= 0 || n_splits_launch <= 0) return BG_OK;
+    if (nh % nkv != 0 || hd > 32 * ATT_MAX_DPL || (tile != 32 && tile != 64) || split % tile != 0) return BG_ERR_SHAPE;
+    if (n_splits_launch > max_splits || n_splits_launch > 65535 || nkv > 65535) return BG_ERR_SHAPE;
+    AttnParams p;
+    p.q = q; p.q_stride = q_stride; p.kv_pool = kv_pool; p.num_pages = num_pages; p.page_size = page_size;
+    p.block_table = block_table; p.max_pages = max_pages; p.positions = positions; p.qblk = qblk;
+    p.part_o = part_o; p.part_ml = part_ml; p.max_splits = max_splits; p.nh = nh; p.nkv = nkv; p.hd = hd;
+    p.group = nh / nkv; p.window = window; p.split = split; p.tile = tile; p.bq = bq; p.scale = scale; p.status = status;
+    size_t smem = attention_smem_bytes(bq, p.group, hd, tile);
+    if (smem > 227 * 1024) return BG_ERR_UNSUPPORTED;
+    dim3 grid(n_qblk, nkv, n_splits_launch);
+#define BG_ATT_LAUNCH(TQ, TC)                                                                              \
+    do {                                                                                                   \
+        auto kern = attention_partial_kernel<TQ, TC>;                                                      \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return (int)e;                                                               \
+        kern<<<grid, ATT_THREADS, smem, stream>>>(p);                                                      \
+    } while (0)
+    if (q_dtype == BG_DTYPE_F32 && cache_dtype == BG_DTYPE_F32) BG_ATT_LAUNCH(float, float);
+    else if (q_dtype == BG_DTYPE_BF16 && cache_dtype == BG_DTYPE_BF16) BG_ATT_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (q_dtype == BG_DTYPE_F32 && cache_dtype == BG_DTYPE_BF16) BG_ATT_LAUNCH(float, __nv_bfloat16);
+    else if (q_dtype == BG_DTYPE_BF16 && cache_dtype == BG_DTYPE_F32) BG_ATT_LAUNCH(__nv_bfloat16, float);
+    else return BG_ERR_DTYPE;
+#undef BG_ATT_LAUNCH
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, const int* positions, void* out,
+                                  int out_dtype, int out_stride, int T, int nh, int hd, int max_splits, int split,
+                                  int window, cudaStream_t stream) {
+    if (T <= 0) return BG_OK;
+    long long warps = (long long)T * nh;
+    unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+    BG_DISPATCH_DTYPE(out_dtype, TO, attention_merge_kernel<TO><<<blocks, 256, 0, stream>>>(
+        part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}

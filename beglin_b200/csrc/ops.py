@@ -1,0 +1,277 @@
+"""Python faces of the CUDA kernels: each takes torch tensors on a CUDA device, checks what the
+kernel assumes (types, shapes, contiguity), and launches on torch's current stream.
+
+There is no other implementation behind these functions.  If the library cannot be built or
+loaded, or a tensor is not on a CUDA device, they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+STATUS_BAD_TOKEN, STATUS_BAD_PAGE, STATUS_TIMEOUT = 1, 2, 4
+
+_c_int, _c_float, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+_SIGNATURES = {
+    "bg_embed_gather": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "bg_add_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_void_p,
+                       _c_int, _c_int, _c_int, _c_void_p],
+    "bg_add_residual": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
+    "bg_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_rope_table": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+    "bg_rope_kv_append": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "bg_attention_plan": [_c_int, _c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
+    "bg_attention_partial": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int,
+                             _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+    "bg_attention_merge": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                           _c_int, _c_int, _c_int, _c_void_p],
+    "bg_gemm_f32_nt": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_void_p],
+    "bg_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+}
+
+_lib = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        handle = _build.load()
+        for name, argtypes in _SIGNATURES.items():
+            try:
+                fn = getattr(handle, name)
+            except AttributeError as e:
+                raise KernelError(f"the kernel library lacks '{name}'") from e
+            fn.argtypes = argtypes
+            fn.restype = _c_int
+        _lib = handle
+    return _lib
+
+
+def available() -> bool:
+    """True when a CUDA device is present.  (The library itself builds without one.)"""
+    return torch.cuda.is_available()
+
+
+_ARG_ERRORS = {-1: "unsupported element type", -2: "unsupported shape", -3: "misaligned tensor",
+               -4: "sizes that this kernel does not take"}
+
+
+def _check(rc: int, name: str) -> None:
+    if rc == 0:
+        return
+    if rc < 0:
+        raise KernelError(f"{name}: refused: {_ARG_ERRORS.get(rc, rc)}")
+    raise KernelError(f"{name}: CUDA error {rc} at launch")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"tensors must be float32 or bfloat16, got {t.dtype}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("beglin_b200 kernels run on a CUDA device only; got a tensor on " + str(t.device))
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _i32(t: torch.Tensor, what: str) -> None:
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{what} must be a contiguous int32 tensor")
+
+
+def new_status(device) -> torch.Tensor:
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def raise_on_status(status: torch.Tensor) -> None:
+    """Read the status word (this waits for the device) and raise if a kernel recorded a fault."""
+    v = int(status.item())
+    if v == 0:
+        return
+    status.zero_()
+    what = []
+    if v & STATUS_BAD_TOKEN:
+        what.append("a token id outside the vocabulary")
+    if v & STATUS_BAD_PAGE:
+        what.append("a block-table entry outside the page pool")
+    if v & STATUS_TIMEOUT:
+        what.append("a bounded wait inside a kernel ran out")
+    raise KernelError("a kernel recorded: " + "; ".join(what or [f"status {v}"]))
+
+
+# ------------------------------------------------------------------------------------------------
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor]) -> None:
+    _cuda(table, ids, out)
+    _i32(ids, "ids")
+    T, d = ids.numel(), table.shape[1]
+    if out.dtype != torch.float32 or tuple(out.shape) != (T, d) or not out.is_contiguous() or not table.is_contiguous():
+        raise KernelError("embed_gather: out must be contiguous float32 [T, d] and the table contiguous")
+    _check(lib().bg_embed_gather(_p(table), _dt(table), _p(ids), _p(out), T, d, table.shape[0], _p(status), _stream()),
+           "embed_gather")
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None, update: bool = True) -> None:
+    """v = x[s] (+ delta[s]); x[s] = v when update; out[r] = rmsnorm(v) * weight, s = rows[r] or r."""
+    _cuda(x, delta, weight, out, rows)
+    d = x.shape[1]
+    n = rows.numel() if rows is not None else x.shape[0]
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or not weight.is_contiguous():
+        raise KernelError("add_rmsnorm: x must be contiguous float32; out and weight contiguous")
+    if tuple(out.shape) != (n, d) or weight.numel() != d:
+        raise KernelError(f"add_rmsnorm: out is {tuple(out.shape)}, expected {(n, d)}; weight has {weight.numel()} of {d}")
+    if delta is not None and (tuple(delta.shape) != tuple(x.shape) or not delta.is_contiguous()):
+        raise KernelError("add_rmsnorm: delta must be contiguous and shaped like x")
+    if rows is not None:
+        _i32(rows, "rows")
+    _check(lib().bg_add_rmsnorm(_p(x), _p(delta), _dt(delta) if delta is not None else F32, _p(weight), _dt(weight),
+                                float(eps), _p(out), _dt(out), _p(rows), n, d, 1 if update else 0, _stream()),
+           "add_rmsnorm")
+
+
+def add_residual(x: torch.Tensor, delta: torch.Tensor) -> None:
+    _cuda(x, delta)
+    if x.dtype != torch.float32 or x.shape != delta.shape or not x.is_contiguous() or not delta.is_contiguous():
+        raise KernelError("add_residual: x must be contiguous float32 and delta shaped like it")
+    _check(lib().bg_add_residual(_p(x), _p(delta), _dt(delta), x.numel(), _stream()), "add_residual")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, im + i]."""
+    _cuda(gate_up, out)
+    rows, two_im = gate_up.shape
+    im = two_im // 2
+    if two_im != 2 * im or tuple(out.shape) != (rows, im) or out.dtype != gate_up.dtype:
+        raise KernelError("swiglu: gate_up must be [rows, 2*im] and out [rows, im] of the same type")
+    if not gate_up.is_contiguous() or not out.is_contiguous():
+        raise KernelError("swiglu: tensors must be contiguous")
+    _check(lib().bg_swiglu(_p(gate_up), _p(out), _dt(out), rows, im, _stream()), "swiglu")
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = (cos, sin)(positions[t] * inv_freq[i]); out is float32 [T, half, 2]."""
+    _cuda(positions, inv_freq, out)
+    _i32(positions, "positions")
+    T, half = positions.numel(), inv_freq.numel()
+    if inv_freq.dtype != torch.float32 or out.dtype != torch.float32 or tuple(out.shape) != (T, half, 2) \
+            or not out.is_contiguous() or not inv_freq.is_contiguous():
+        raise KernelError("rope_table: inv_freq float32 [half], out contiguous float32 [T, half, 2]")
+    _check(lib().bg_rope_table(_p(positions), _p(inv_freq), _p(out), T, half, _stream()), "rope_table")
+
+
+def rope_kv_append(qkv: torch.Tensor, n_rows: int, nh: int, nkv: int, hd: int, rot: int, interleaved: bool,
+                   cos_sin: Optional[torch.Tensor], positions: torch.Tensor, row_req: torch.Tensor,
+                   block_table: torch.Tensor, kv_pool: Optional[torch.Tensor], page_size: int,
+                   status: Optional[torch.Tensor]) -> None:
+    """Rotate q (and k) of rows [q | k | v] in place and store k, v into kv_pool
+    [num_pages, 2, nkv, page_size, hd] through the block table [B, max_pages]."""
+    _cuda(qkv, cos_sin, positions, row_req, block_table, kv_pool)
+    _i32(positions, "positions"); _i32(row_req, "row_req"); _i32(block_table, "block_table")
+    width = qkv.shape[1]
+    need = nh * hd + (2 * nkv * hd if kv_pool is not None else 0)
+    if qkv.stride(1) != 1 or width < need:
+        raise KernelError(f"rope_kv_append: rows of {width} features cannot hold q, k, v ({need})")
+    num_pages = 0
+    if kv_pool is not None:
+        if tuple(kv_pool.shape[1:]) != (2, nkv, page_size, hd) or not kv_pool.is_contiguous():
+            raise KernelError(f"rope_kv_append: kv_pool is {tuple(kv_pool.shape)}, expected [pages, 2, {nkv}, {page_size}, {hd}]")
+        num_pages = kv_pool.shape[0]
+    if rot > 0 and (cos_sin is None or cos_sin.shape[0] < n_rows or cos_sin.shape[1] != rot // 2 or cos_sin.dtype != torch.float32):
+        raise KernelError("rope_kv_append: cos_sin must be float32 [T, rot/2, 2]")
+    _check(lib().bg_rope_kv_append(_p(qkv), _dt(qkv), qkv.stride(0), _p(cos_sin), _p(positions), _p(row_req),
+                                   _p(block_table), block_table.shape[1], _p(kv_pool),
+                                   _dt(kv_pool) if kv_pool is not None else F32, num_pages, page_size, n_rows,
+                                   nh, nkv, hd, rot, 1 if interleaved else 0, _p(status), _stream()),
+           "rope_kv_append")
+
+
+def attention_plan(group: int, hd: int) -> Tuple[int, int]:
+    """(rows per query block, keys per tile) that fit one CTA's shared memory for these sizes."""
+    bq, tile = _c_int(0), _c_int(0)
+    rc = lib().bg_attention_plan(group, hd, ctypes.byref(bq), ctypes.byref(tile))
+    if rc != 0:
+        raise KernelError(f"attention: head_dim {hd} with {group} query heads per kv head is not supported "
+                          "(head_dim must be at most 256)")
+    return bq.value, tile.value
+
+
+def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table: torch.Tensor,
+              positions: torch.Tensor, qblk: torch.Tensor, n_qblk: int, part_o: torch.Tensor, part_ml: torch.Tensor,
+              max_splits: int, n_splits: int, n_rows: int, nh: int, nkv: int, hd: int, window: int, split: int,
+              tile: int, bq: int, scale: float, out: torch.Tensor, status: Optional[torch.Tensor]) -> None:
+    """Paged grouped-query attention of a step's rows; out is [T, nh*hd]."""
+    _cuda(q, kv_pool, block_table, positions, qblk, part_o, part_ml, out)
+    _i32(positions, "positions"); _i32(block_table, "block_table"); _i32(qblk, "qblk")
+    num_pages, two, nkv_, page_size, hd_ = kv_pool.shape
+    if (two, nkv_, hd_) != (2, nkv, hd) or not kv_pool.is_contiguous():
+        raise KernelError(f"attention: kv_pool is {tuple(kv_pool.shape)}, expected [pages, 2, {nkv}, page, {hd}]")
+    if part_o.dtype != torch.float32 or part_ml.dtype != torch.float32:
+        raise KernelError("attention: partial buffers must be float32")
+    if part_o.numel() < n_rows * nh * max_splits * hd or part_ml.numel() < n_rows * nh * max_splits * 2:
+        raise KernelError("attention: partial buffers are too small for this step")
+    if out.stride(1) != 1 or out.shape[1] < nh * hd or out.shape[0] < n_rows:
+        raise KernelError("attention: out must be [T, nh*hd] with unit inner stride")
+    L = lib()
+    _check(L.bg_attention_partial(_p(q), _dt(q), q_stride, _p(kv_pool), _dt(kv_pool), num_pages, page_size,
+                                  _p(block_table), block_table.shape[1], _p(positions), _p(qblk), n_qblk,
+                                  _p(part_o), _p(part_ml), max_splits, n_splits, nh, nkv, hd, window, split, tile, bq,
+                                  float(scale), _p(status), _stream()), "attention_partial")
+    _check(L.bg_attention_merge(_p(part_o), _p(part_ml), _p(positions), _p(out), _dt(out), out.stride(0), n_rows, nh,
+                                hd, max_splits, split, window, _stream()), "attention_merge")
+
+
+def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                accumulate: bool = False) -> None:
+    """out[M, N] (+)= a[M, K] @ w[N, K]^T (+ bias), all float32, CUDA cores only."""
+    _cuda(a, w, bias, out)
+    for t in (a, w, out) + ((bias,) if bias is not None else ()):
+        if t.dtype != torch.float32:
+            raise KernelError("gemm_f32_nt takes float32 tensors")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N or a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"gemm_f32_nt: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not fit")
+    if bias is not None and (bias.numel() != N or not bias.is_contiguous()):
+        raise KernelError("gemm_f32_nt: bias must have one value per output feature")
+    _check(lib().bg_gemm_f32_nt(_p(a), a.stride(0), _p(w), w.stride(0), _p(bias), _p(out), out.stride(0), M, N, K,
+                                1 if accumulate else 0, _stream()), "gemm_f32_nt")
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],
+           out: torch.Tensor) -> None:
+    """out[r] = first argmax of logits[r] when temperature[r] <= 0 (or temperature is None), else the
+    index where the cumulative softmax(logits[r] / temperature[r]) first exceeds uniform[r]."""
+    _cuda(logits, temperature, uniform, out)
+    n, V = logits.shape
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise KernelError("sample: logits must be contiguous float32 [n, V]")
+    _i32(out, "out")
+    for t in (temperature, uniform):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+            raise KernelError("sample: temperature and uniform must be float32 [n]")
+    _check(lib().bg_sample(_p(logits), n, V, _p(temperature), _p(uniform), _p(out), _stream()), "sample")

@@ -1,0 +1,106 @@
+"""A decoder put together from a `ModelSpec`: embedding, the layers' blocks in the spec's run order,
+final norm and head.  The class knows no architecture; which parts run and with which sizes is the
+spec's business, and which tensors they get is decided by name.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..csrc import ops
+from ..parts import registry
+from ..parts.context import BuildContext
+from ..parts.linear import Linear
+from ..parts.spec import ModelSpec
+from ..weights.loader import layer_roles
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
+        """`tensors` maps checkpoint names to tensors (any device) in their stored types."""
+        import beglin_b200.parts  # noqa: F401
+        self.spec, self.ctx = spec, ctx
+        if ctx.status is None:
+            ctx.status = ops.new_status(ctx.device)
+        self.embed = ctx.matrix(tensors[spec.embed_name])
+        self.blocks = []
+        self.mixers = []
+        for layer in spec.layers:
+            parts = {}
+            for prefix, cls, pspec in (
+                    ("mixer_norm", registry.norm_class(layer.mixer_norm.kind), layer.mixer_norm),
+                    ("mixer", registry.mixer_class(layer.mixer.kind), layer.mixer),
+                    ("feed_forward_norm", registry.norm_class(layer.feed_forward_norm.kind), layer.feed_forward_norm),
+                    ("feed_forward", registry.feed_forward_class(layer.feed_forward.kind), layer.feed_forward)):
+                mine = {}
+                for role in cls.expected_tensors(pspec):
+                    name = layer.names[f"{prefix}.{role.name}"]
+                    if name in tensors:
+                        mine[role.name] = tensors[name]
+                parts[prefix] = cls(pspec, mine, ctx)
+            self.mixers.append(parts["mixer"])
+            self.blocks.append(registry.block_class(layer.block)(parts["mixer_norm"], parts["mixer"],
+                                                                 parts["feed_forward_norm"], parts["feed_forward"]))
+        self.final_norm = registry.norm_class(spec.final_norm.kind)(
+            spec.final_norm, {"weight": tensors[spec.final_norm_name]}, ctx)
+        if spec.head_name is None:
+            self.head = Linear(self.embed, None, ctx)      # ctx.matrix is a no-op on the table: one copy
+        else:
+            self.head = Linear(tensors[spec.head_name], None, ctx)
+
+    # ------------------------------------------------------------------ cache
+    def cache_needs(self) -> List[Optional[object]]:
+        """The cache need of every stage of the run order (None for a stage that reads another's)."""
+        needs = []
+        for stage in self.spec.order:
+            layer = self.spec.layers[stage.layer]
+            cls = registry.mixer_class(layer.mixer.kind)
+            need = cls.cache_need(layer.mixer)
+            if stage.cache is not None:
+                need = None
+            needs.append(need)
+        return needs
+
+    def weight_bytes(self) -> int:
+        """Bytes of every weight a step reads once (the tied head counted once)."""
+        seen, total = set(), 0
+
+        def add(t):
+            nonlocal total
+            if t is not None and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+
+        def walk(obj, depth=0):
+            if isinstance(obj, torch.Tensor):
+                add(obj)
+            elif depth < 3 and hasattr(obj, "__dict__"):
+                for k, v in vars(obj).items():
+                    if k in ("ctx", "spec", "bias_c", "embed"):
+                        continue
+                    walk(v, depth + 1)
+
+        for b in self.blocks:
+            for part in vars(b).values():
+                walk(part)
+        walk(self.final_norm)
+        walk(self.head)
+        return total
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, batch, cache) -> Optional[torch.Tensor]:
+        """Run the batch's rows through every stage, from and into `cache`; return float logits
+        [wanted rows, vocab], or None when no row's logits are wanted (the head is skipped then, as
+        qwen_infer.c:2145 skips it)."""
+        x = torch.empty((batch.n_rows, self.spec.hidden), dtype=torch.float32, device=self.ctx.device)
+        ops.embed_gather(self.embed, batch.token_ids, x, self.ctx.status)
+        pending = None
+        for si, stage in enumerate(self.spec.order):
+            owner = si if stage.cache is None else stage.cache
+            view = cache.view(owner, batch) if owner in cache.stage_group else None
+            pending = self.blocks[stage.layer].forward(x, pending, batch, view)
+        if batch.n_logit_rows == 0:
+            return None
+        h = self.final_norm.add_norm(x, pending, rows=batch.logit_rows, update=False)
+        return self.head(h, out_dtype=torch.float32)

@@ -1,0 +1,85 @@
+"""Grouped-query attention over the paged cache (the reference's attention, qwen_infer.c:1451-1548
+for one token and :2075-2136 for a ragged batch).
+
+Per step: one product for q, k and v together (the reference concatenates the three matrices and
+their biases at load time too, qwen_infer.c:1316-1367), rotation of q and k fused with the append
+of k and v to the pages, attention of every row over the pages of its own request, and the output
+product.  All rows' keys and values are in the cache before any row's attention runs
+(qwen_infer.c:2017-2023), which is what makes a prompt portion causal.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..csrc import ops
+from .cache_need import PagedKVNeed, PagedKVView
+from .context import BuildContext
+from .linear import Linear
+from .registry import register_mixer
+from .rope import shared_position
+from .spec import AttentionSpec, TensorRole
+
+
+@register_mixer("gqa_attention")
+class GQAAttention:
+    @staticmethod
+    def expected_tensors(spec: AttentionSpec) -> List[TensorRole]:
+        qd, kvd = spec.n_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
+        roles = [TensorRole("q_proj.weight", (qd, spec.hidden), True, True),
+                 TensorRole("o_proj.weight", (spec.hidden, qd), True, True)]
+        if spec.own_kv:
+            roles += [TensorRole("k_proj.weight", (kvd, spec.hidden), True, True),
+                      TensorRole("v_proj.weight", (kvd, spec.hidden), True, True)]
+        if spec.qkv_bias:
+            roles.append(TensorRole("q_proj.bias", (qd,)))
+            if spec.own_kv:
+                roles += [TensorRole("k_proj.bias", (kvd,)), TensorRole("v_proj.bias", (kvd,))]
+        if spec.out_bias:
+            roles.append(TensorRole("o_proj.bias", (spec.hidden,)))
+        return roles
+
+    @staticmethod
+    def cache_need(spec: AttentionSpec) -> Optional[PagedKVNeed]:
+        if not spec.own_kv:
+            return None
+        return PagedKVNeed(spec.n_kv_heads, spec.head_dim, spec.window)
+
+    def __init__(self, spec: AttentionSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
+        if spec.n_heads % spec.n_kv_heads:
+            raise ValueError(f"{spec.n_heads} query heads are not a multiple of {spec.n_kv_heads} kv heads")
+        if spec.head_dim % 2 or spec.head_dim > 256:
+            raise ValueError(f"head_dim={spec.head_dim} must be even and at most 256")
+        self.spec, self.ctx = spec, ctx
+        self.nh, self.nkv, self.hd = spec.n_heads, spec.n_kv_heads, spec.head_dim
+        self.qd, self.kvd = self.nh * self.hd, self.nkv * self.hd
+        names = ["q_proj"] + (["k_proj", "v_proj"] if spec.own_kv else [])
+        w = torch.cat([tensors[n + ".weight"] for n in names], dim=0)
+        b = torch.cat([tensors[n + ".bias"].float() for n in names], dim=0) if spec.qkv_bias else None
+        self.qkv = Linear(w, b, ctx)
+        self.o_proj = Linear(tensors["o_proj.weight"], tensors.get("o_proj.bias") if spec.out_bias else None, ctx)
+        self.position = shared_position(spec.position, ctx)
+        scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(float(self.hd))
+        self.scale = float(np.float32(scale))
+        self.bq, self.tile = ops.attention_plan(self.nh // self.nkv, self.hd)
+        self.window = int(spec.window) if spec.window else 0
+
+    def forward(self, h: torch.Tensor, batch, cache: PagedKVView) -> torch.Tensor:
+        T = batch.n_rows
+        qkv = self.qkv(h)
+        ops.rope_kv_append(qkv, T, self.nh, self.nkv, self.hd, self.position.rotary_dim, self.position.interleaved,
+                           self.position.table(batch), batch.positions, batch.row_req, cache.block_table,
+                           cache.pool if self.spec.own_kv else None, cache.page_size, self.ctx.status)
+        split = self.ctx.kv_split
+        n_splits = batch.max_position // split + 1
+        qblk, n_qblk = batch.query_blocks(self.bq)
+        part_o = torch.empty((T * self.nh * n_splits, self.hd), dtype=torch.float32, device=h.device)
+        part_ml = torch.empty((T * self.nh * n_splits, 2), dtype=torch.float32, device=h.device)
+        out = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=h.device)
+        ops.attention(qkv, qkv.stride(0), cache.pool, cache.block_table, batch.positions, qblk, n_qblk, part_o,
+                      part_ml, n_splits, n_splits, T, self.nh, self.nkv, self.hd, self.window, split, self.tile,
+                      self.bq, self.scale, out, self.ctx.status)
+        return self.o_proj(out)

@@ -1,0 +1,74 @@
+"""Random weights for a configuration: in memory, or as a model folder (config.json and
+model.safetensors) that every loader of the framework reads like a downloaded one.
+
+Matrices and biases are N(0, std) and N(0, bias_std); norm weights are 1 + N(0, norm_std).  Each
+tensor has a generator of its own, seeded from (seed, tensor name), so the values do not depend on
+the order or on which other tensors exist.  The reference has no such mode in its engine; its tests
+write a seeded three-tensor fixture (tests/regression/mk_tiny_st.py:21-45).
+"""
+from __future__ import annotations
+
+import json
+import os
+import zlib
+from typing import Dict, Optional
+
+import torch
+
+from ..parts.spec import ModelSpec
+from .loader import expected_tensors
+from .safetensors_io import write_safetensors
+
+
+def _kind(name: str) -> str:
+    if name.endswith("bias"):
+        return "bias"
+    if "norm" in name.rsplit(".", 2)[-2] or name.endswith("norm.weight"):
+        return "norm"
+    return "matrix"
+
+
+def random_tensors(spec: ModelSpec, seed: int, std: float = 0.02, bias_std: Optional[float] = None,
+                   norm_std: float = 0.02, dtype: torch.dtype = torch.bfloat16,
+                   device: str = "cpu") -> Dict[str, torch.Tensor]:
+    bias_std = std if bias_std is None else bias_std
+    out: Dict[str, torch.Tensor] = {}
+    for name, role in expected_tensors(spec).items():
+        gen = torch.Generator(device=device)
+        gen.manual_seed((int(seed) * 1000003 + zlib.crc32(name.encode())) % (2**63))
+        kind = "matrix" if role.matrix else _kind(name)
+        if role.matrix and device != "cpu" and len(role.shape) == 2 and role.shape[0] * role.shape[1] > (1 << 26):
+            # large tables are filled in row blocks so the float32 draw never doubles their footprint
+            t = torch.empty(role.shape, dtype=dtype, device=device)
+            step = max(1, (1 << 26) // role.shape[1])
+            for r0 in range(0, role.shape[0], step):
+                r1 = min(role.shape[0], r0 + step)
+                t[r0:r1] = (torch.randn((r1 - r0, role.shape[1]), generator=gen, device=device) * std).to(dtype)
+            out[name] = t
+            continue
+        x = torch.randn(role.shape, generator=gen, dtype=torch.float32, device=device)
+        if kind == "norm":
+            x = 1.0 + norm_std * x
+        elif kind == "bias":
+            x = bias_std * x
+        else:
+            x = std * x
+        out[name] = x.to(dtype)
+    return out
+
+
+def write_random_model(folder: str, config_json: dict, seed: int, std: float = 0.02,
+                       bias_std: Optional[float] = None, norm_std: float = 0.02,
+                       dtype: torch.dtype = torch.bfloat16) -> str:
+    """Write `folder`/config.json and `folder`/model.safetensors for the configuration given as
+    config.json keys.  Returns the folder."""
+    from ..config import load_config
+    arch, cfg = load_config(dict(config_json))
+    spec = arch.build_spec(cfg)
+    tensors = random_tensors(spec, seed, std, bias_std, norm_std, dtype)
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(config_json, f, indent=1)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors,
+                      metadata={"format": "pt", "seed": str(seed)})
+    return folder

@@ -1,0 +1,84 @@
+"""Tiny configurations, model folders and comparison helpers shared by the tests."""
+import os
+import sys
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "plain"))
+import qwen2_plain as plain  # noqa: E402
+
+# Tolerances, relative to the largest reference logit of the comparison.  float32 against the
+# float64 oracle; bfloat16 (weights, activations and cache rounded to 8 bits of mantissa).
+TOL_F32 = 1e-4
+TOL_BF16 = 4e-2
+
+# Three tiny configurations that differ in every size and option: heads and groups (2 per kv head,
+# MQA with 3, one per kv head), head size (16, 32, and 48 given apart from hidden/heads), width and
+# vocabulary that are no powers of two, layers, eps, theta, tying, window and frequency scaling.
+TINY_A = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "intermediate_size": 128, "vocab_size": 256, "rope_theta": 10000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True, "max_position_embeddings": 128, "use_sliding_window": False,
+    "hidden_act": "silu",
+}
+TINY_B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 3, "num_key_value_heads": 1,
+    "intermediate_size": 200, "vocab_size": 384, "rope_theta": 1000000.0, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "max_position_embeddings": 256, "use_sliding_window": False,
+}
+TINY_C = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 80, "num_attention_heads": 5, "num_key_value_heads": 5,
+    "head_dim": 48, "intermediate_size": 112, "vocab_size": 300, "rope_theta": 500000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 512,
+    "use_sliding_window": True, "sliding_window": 24, "max_window_layers": 1,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64},
+}
+TINY = {"A": (TINY_A, dict(std=0.02, bias_std=0.02), 8),
+        "B": (TINY_B, dict(std=0.02, bias_std=0.05), 16),
+        "C": (TINY_C, dict(std=0.05, bias_std=0.05), 16)}     # name -> (config, init, page size)
+
+
+def make_model(root, name, seed=0, dtype=torch.float32, config=None, **init):
+    """Write a model folder with random weights under `root` and return its path."""
+    from beglin_b200.weights import write_random_model
+    cfg, base_init, _ = TINY[name] if config is None else (config, {}, None)
+    kw = dict(base_init)
+    kw.update(init)
+    folder = os.path.join(str(root), f"{name}_{seed}_{str(dtype).split('.')[-1]}")
+    if not os.path.exists(os.path.join(folder, "model.safetensors")):
+        write_random_model(folder, cfg, seed, dtype=dtype, **kw)
+    return folder
+
+
+_PLAIN_CACHE = {}
+
+
+def plain_model(folder):
+    if folder not in _PLAIN_CACHE:
+        _PLAIN_CACHE[folder] = plain.read_folder(folder, torch.float64)
+    return _PLAIN_CACHE[folder]
+
+
+def plain_logits(folder, ids):
+    """float64 logits [T, vocab] of the whole sequence from the plain implementation."""
+    cfg, w = plain_model(folder)
+    key = (folder, tuple(ids))
+    if key not in _PLAIN_CACHE:
+        _PLAIN_CACHE[key] = plain.forward(cfg, w, list(ids))
+    return _PLAIN_CACHE[key]
+
+
+def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    want = want.to(torch.float64).cpu()
+    got = got.to(torch.float64).cpu()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+def seeded_ids(n, vocab, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
