@@ -1,0 +1,172 @@
+"""The command line in the reference's manner: `qwen_infer <mode> <N>` with everything else in
+environment variables (qwen_infer.c:20108-20128).
+
+Modes kept: `greedy` (default; N new tokens, default 32, no stop on EOS, output `greedy: id id ...`,
+qwen_infer.c:20412-20429), `bench` (prefill, 8 warm-up tokens, N timed decode tokens, best of 3,
+output `tok_s ... ms_tok ...`, :20430-20462), `dump` (last logits of the prompt to a file,
+:20405-20411) and `cbatch` (continuous batching over prompts cut from the loaded one, output one
+`cbatch req...` line per request and an `agg_tok_s` line, :20611-20912).
+
+Variables kept, with the reference's meanings: QWEN_BASE (here: the model folder with config.json
+and model.safetensors), QWEN_PROMPT (file of little-endian int32 token ids; default
+<QWEN_BASE>/ref/prompt_ids.i32), QWEN_SAFETENSORS_MAXSEQ (context cap, default 2048), QWEN_BATCH
+(live requests, default 8), QWEN_CB_REQS (default 12), QWEN_CB_REPS (default 3),
+QWEN_CB_PREFILL_BUDGET (prompt tokens per step, default 16), QWEN_CB_STOP_EXTRA (an extra stop id).
+Added: QWEN_DTYPE (bf16 | fp32, default bf16), QWEN_TEMPERATURE and QWEN_SEED (sampling),
+QWEN_PAGE_SIZE (default 16), QWEN_NUM_PAGES, QWEN_RANDOM (a seed: write random weights for
+<QWEN_BASE>/config.json first, if the folder has no model.safetensors), QWEN_DUMP_DIR.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+from typing import List
+
+import numpy as np
+
+
+def _env_int(name: str, default: int) -> int:
+    v = os.environ.get(name)
+    return int(v) if v else default
+
+
+def _err(msg: str) -> int:
+    print(f"FATAL: {msg}", file=sys.stderr)
+    return 1
+
+
+def load_ids(path: str, limit: int) -> List[int]:
+    """Raw little-endian int32 ids (qwen_infer.c:2168-2170)."""
+    return np.fromfile(path, dtype="<i4")[:limit].astype(np.int64).tolist()
+
+
+def main(argv: List[str]) -> int:
+    mode = argv[1] if len(argv) > 1 else "greedy"
+    n_gen = int(argv[2]) if len(argv) > 2 else 32
+    if mode in ("-h", "--help"):
+        print(__doc__)
+        return 0
+    if mode not in ("greedy", "bench", "dump", "cbatch"):
+        return _err(f"unknown mode '{mode}'; modes: greedy, bench, dump, cbatch")
+    base = os.environ.get("QWEN_BASE")
+    if not base:
+        return _err("QWEN_BASE is not set (the model folder with config.json and model.safetensors)")
+    if not os.path.exists(os.path.join(base, "config.json")):
+        return _err(f"{base}: no arch config (config.json) found")
+
+    import torch
+    from .engine.engine import Engine
+    from .csrc import ops
+
+    maxseq = _env_int("QWEN_SAFETENSORS_MAXSEQ", 2048)
+    dtype = os.environ.get("QWEN_DTYPE", "bf16")
+    page = _env_int("QWEN_PAGE_SIZE", 16)
+    batch = max(1, _env_int("QWEN_BATCH", 8))
+    seed_random = os.environ.get("QWEN_RANDOM")
+    if seed_random and not os.path.exists(os.path.join(base, "model.safetensors")) \
+            and not os.path.exists(os.path.join(base, "model.safetensors.index.json")):
+        import json
+        from .weights import write_random_model
+        with open(os.path.join(base, "config.json")) as f:
+            cfg_json = json.load(f)
+        print(f"[engine] writing random weights (seed {seed_random}) to {base}", file=sys.stderr)
+        write_random_model(base, cfg_json, int(seed_random),
+                           dtype=torch.float32 if dtype in ("fp32", "float32") else torch.bfloat16)
+
+    prompt_path = os.environ.get("QWEN_PROMPT") or os.path.join(base, "ref", "prompt_ids.i32")
+    try:
+        prompt = load_ids(prompt_path, maxseq)
+    except OSError as e:
+        return _err(f"could not read prompt ids from {prompt_path} ({e.strerror})")
+    if len(prompt) < 1:
+        return _err(f"no prompt ids (np={len(prompt)})")
+
+    live = batch if mode == "cbatch" else 1
+    num_pages = _env_int("QWEN_NUM_PAGES", live * -(-maxseq // page))
+    try:
+        eng = Engine.from_folder(base, dtype=dtype, max_tokens=num_pages * page, page_size=page,
+                                 max_requests=live, max_context=maxseq)
+    except Exception as e:                                   # one line, as the reference's FATALs
+        return _err(str(e))
+    cfg = eng.config
+    print(f"[engine] arch config ({base}): NL={cfg.num_hidden_layers} NH={cfg.num_attention_heads} "
+          f"NKV={cfg.num_key_value_heads} D={cfg.hidden_size} HD={cfg.head_dim} IM={cfg.intermediate_size} "
+          f"VOCAB={cfg.vocab_size} THETA={cfg.rope_theta:.1f} EPS={cfg.rms_norm_eps:g} MAXSEQ={maxseq} "
+          f"QKV_BIAS={int(cfg.qkv_bias)} GROUP={cfg.num_attention_heads // cfg.num_key_value_heads} "
+          f"DTYPE={dtype}", file=sys.stderr)
+    temperature = float(os.environ.get("QWEN_TEMPERATURE", "0"))
+    seed = _env_int("QWEN_SEED", 0)
+
+    if mode == "dump":
+        logits = eng.step([("dump", prompt, [len(prompt) - 1])], end=["dump"])
+        out_dir = os.environ.get("QWEN_DUMP_DIR") or os.path.join(base, "results")
+        os.makedirs(out_dir, exist_ok=True)
+        logits[0].cpu().numpy().astype("<f4").tofile(os.path.join(out_dir, "c_logits_last.f32"))
+        print(f"[engine] dumped, argmax={int(eng.sampler.greedy(logits)[0])}", file=sys.stderr)
+        return 0
+
+    if mode == "greedy":
+        room = maxseq - len(prompt)
+        out = eng.generate([prompt], max_new_tokens=min(n_gen, max(room, 0) + 1), temperature=temperature,
+                           seed=seed, stop_ids=())[0]
+        print("greedy:" + "".join(f" {t}" for t in out))
+        return 0
+
+    if mode == "bench":
+        N = n_gen
+        if len(prompt) + 8 + N >= maxseq:
+            old, N = N, maxseq - len(prompt) - 8 - 1
+            if N < 1:
+                return _err(f"prompt too long for bench (np={len(prompt)})")
+            print(f"[bench] N clamped {old}->{N} to fit MAXSEQ={maxseq}", file=sys.stderr)
+        best = float("inf")
+        for _ in range(3):
+            logits = eng.step([("b", prompt, [len(prompt) - 1])])
+            tok = eng.sampler.greedy(logits)
+            for _ in range(8):
+                logits = eng.step([("b", [int(tok[0])], [0])])
+                tok = eng.sampler.greedy(logits)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(N):
+                logits = eng.step([("b", [int(tok[0])], [0])], check=False)
+                tok = eng.sampler.greedy(logits)
+            torch.cuda.synchronize()
+            best = min(best, time.perf_counter() - t0)
+            eng.release("b")
+        ms = best / N * 1e3
+        print(f"[bench] {dtype} N={N} pos~{len(prompt) + 8}: {ms:.3f} ms/tok = {1000.0 / ms:.2f} tok/s", file=sys.stderr)
+        print(f"tok_s {1000.0 / ms:.3f} ms_tok {ms:.2f}")
+        return 0
+
+    # cbatch: prompts cut from the loaded one, lengths 4..40 and token limits spread as in the reference
+    R = max(1, _env_int("QWEN_CB_REQS", 12))
+    reps = max(1, _env_int("QWEN_CB_REPS", 3))
+    budget = max(1, _env_int("QWEN_CB_PREFILL_BUDGET", 16))
+    stop_extra = _env_int("QWEN_CB_STOP_EXTRA", -1)
+    spread = n_gen if n_gen > 1 else 27
+    plen = [min(len(prompt), 4 + (r * 13) % 37) for r in range(R)]
+    maxnew = [6 + (r * 7) % spread for r in range(R)]
+    stops = tuple(eng.spec.eos_ids) + ((stop_extra,) if stop_extra >= 0 else ())
+    best_wall, first, identical, reqs = float("inf"), None, True, None
+    for _ in range(reps):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        reqs = eng.generate([prompt[:n] for n in plen], max_new_tokens=maxnew, temperature=temperature, seed=seed,
+                            stop_ids=stops, max_batch=batch, prefill_budget=budget, return_requests=True)
+        torch.cuda.synchronize()
+        best_wall = min(best_wall, time.perf_counter() - t0)
+        outs = [r.output for r in reqs]
+        if first is None:
+            first = outs
+        elif outs != first:
+            identical = False
+    tot = sum(len(r.output) for r in reqs)
+    for i, r in enumerate(reqs):
+        print(f"cbatch req{i} plen {plen[i]} maxnew {maxnew[i]} nout {len(r.output)}:" + "".join(f" {t}" for t in r.output))
+    c = eng.last_counters
+    print(f"agg_tok_s {tot / best_wall:.3f} wall_s {best_wall:.3f} B {batch} R {R} tok {tot} reps_identical "
+          f"{int(identical)} mixed 1 steps {c.steps} msteps {c.mixed_steps} pfonly {c.prefill_only_steps} "
+          f"pf_cols {c.prefill_rows} preemptions {c.preemptions}")
+    return 0

@@ -80,11 +80,36 @@ def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -
     return y
 
 
-def rope_angles(positions: Sequence[int], rot: int, theta: float, dtype) -> torch.Tensor:
-    """ang[p, i] = pos * theta^(-2i/rot) for i < rot/2 (qwen_infer.c:791-794; the per-frequency
-    scale s_i is 1 when config.json has no rope_scaling, :757-764)."""
+def frequency_scale(cfg: dict, rot: int) -> Optional[torch.Tensor]:
+    """The per-frequency ratio s_i of config.json's rope_scaling of rope_type "llama3"
+    (rope_llama3_scale.h:18-28); None (all ones) without that key (qwen_infer.c:757-764)."""
+    rs = cfg.get("rope_scaling")
+    if not rs:
+        return None
+    theta = float(cfg["rope_theta"])
+    factor, low, high = float(rs["factor"]), float(rs["low_freq_factor"]), float(rs["high_freq_factor"])
+    orig = float(rs["original_max_position_embeddings"])
+    out = []
+    for i in range(rot // 2):
+        inv = theta ** (-(2.0 * i) / rot)
+        wavelen = 2.0 * math.pi / inv
+        if wavelen > orig / low:
+            out.append(1.0 / factor)
+        elif wavelen < orig / high:
+            out.append(1.0)
+        else:
+            smooth = (orig / wavelen - low) / (high - low)
+            out.append((1.0 - smooth) / factor + smooth)
+    return torch.tensor(out, dtype=torch.float64)
+
+
+def rope_angles(positions: Sequence[int], rot: int, theta: float, dtype,
+                scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """ang[p, i] = pos * theta^(-2i/rot) * s_i for i < rot/2 (qwen_infer.c:791-794)."""
     i = torch.arange(rot // 2, dtype=torch.float64)
     inv = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -(2.0 * i) / rot)
+    if scale is not None:
+        inv = inv * scale
     pos = torch.as_tensor(list(positions), dtype=torch.float64)
     return (pos[:, None] * inv[None, :]).to(dtype)
 
@@ -149,7 +174,7 @@ def mlp(h: torch.Tensor, wg, wu, wd) -> torch.Tensor:
 
 
 def attention_block(h, w: Dict[str, torch.Tensor], prefix: str, sz: dict, theta: float,
-                    window: Optional[int], fast: bool) -> torch.Tensor:
+                    window: Optional[int], fast: bool, scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q,k,v with bias, RoPE on q and k after the bias, attention, o_proj without bias
     (qwen_infer.c:1451-1465, :1548)."""
     T = h.shape[0]
@@ -159,7 +184,7 @@ def attention_block(h, w: Dict[str, torch.Tensor], prefix: str, sz: dict, theta:
     q = q.reshape(T, sz["nh"], sz["hd"])
     k = k.reshape(T, sz["nkv"], sz["hd"])
     v = v.reshape(T, sz["nkv"], sz["hd"])
-    ang = rope_angles(range(T), sz["hd"], theta, h.dtype)
+    ang = rope_angles(range(T), sz["hd"], theta, h.dtype, scale)
     q = rope_split_half(q, ang)
     k = rope_split_half(k, ang)
     fn = attention_fast if fast else attention
@@ -173,7 +198,8 @@ def decoder_layer(x, w, layer: int, cfg: dict, sz: dict, fast: bool) -> torch.Te
     p = f"model.layers.{layer}."
     eps = cfg["rms_norm_eps"]
     h = rmsnorm(x, w[p + "input_layernorm.weight"], eps)
-    x = x + attention_block(h, w, p + "self_attn.", sz, cfg["rope_theta"], layer_window(cfg, layer), fast)
+    x = x + attention_block(h, w, p + "self_attn.", sz, cfg["rope_theta"], layer_window(cfg, layer), fast,
+                            frequency_scale(cfg, sz["hd"]))
     h = rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps)
     x = x + mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
     return x

@@ -1,0 +1,135 @@
+"""Generation through the entry points: greedy against the plain implementation, temperature
+sampling reproducible and independent of the batch, few pages (preemption and recomputation), and
+the command line."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TINY, TOL_BF16, make_model, plain, plain_logits, plain_model, seeded_ids
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def engine(folder, dtype, **kw):
+    from beglin_b200 import Engine
+    args = dict(dtype=dtype, max_tokens=512, page_size=8, max_requests=4)
+    args.update(kw)
+    return Engine.from_folder(folder, **args)
+
+
+def test_greedy_float32_equals_plain(model_root):
+    """Tiny A: prompts of 5 and 11 tokens, 8 greedy steps each."""
+    folder = make_model(model_root, "A", seed=3, dtype=torch.float32)
+    cfg, w = plain_model(folder)
+    prompts = [seeded_ids(5, 256, 1), seeded_ids(11, 256, 2)]
+    want = [plain.greedy_generate(cfg, w, p, 8) for p in prompts]
+    eng = engine(folder, "float32")
+    assert eng.generate(prompts, max_new_tokens=8, stop_ids=()) == want
+    # one at a time gives the same
+    assert [eng.generate([p], max_new_tokens=8, stop_ids=())[0] for p in prompts] == want
+    assert not eng.cache.live() and eng.cache.free_pages() == eng.cache.num_pages
+
+
+def test_greedy_bfloat16_follows_plain_up_to_near_ties(model_root):
+    folder = make_model(model_root, "B", seed=3, dtype=torch.bfloat16)
+    prompts = [seeded_ids(9, 384, 4), seeded_ids(20, 384, 5)]
+    eng = engine(folder, "bfloat16", page_size=16)
+    outs = eng.generate(prompts, max_new_tokens=8, stop_ids=())
+    for p, out in zip(prompts, outs):
+        assert len(out) == 8
+        logits = plain_logits(folder, p + out)           # teacher-forced with the engine's own tokens
+        for k, tok in enumerate(out):
+            row = logits[len(p) + k - 1]
+            assert float(row.max() - row[tok]) <= 2 * TOL_BF16 * float(row.abs().max()), (k, tok)
+
+
+def test_temperature_is_reproducible_independent_of_batch_and_follows_the_distribution(model_root):
+    """Tiny B: three requests (7, 19, 33 tokens) cut into portions of 4, 8 or 16 beside decoded
+    tokens, temperature 0.8, fixed seed."""
+    from beglin_b200.sampling import uniform
+    folder = make_model(model_root, "B", seed=3, dtype=torch.float32)
+    prompts = [seeded_ids(n, 384, 10 + n) for n in (7, 19, 33)]
+    eng = engine(folder, "float32", page_size=16)
+    runs = [eng.generate(prompts, max_new_tokens=10, temperature=0.8, seed=42, stop_ids=(), prefill_budget=b)
+            for b in (4, 8, 16)]
+    assert runs[0] == runs[1] == runs[2]
+    assert eng.generate(prompts, max_new_tokens=10, temperature=0.8, seed=43, stop_ids=()) != runs[0]
+    alone = eng.generate([prompts[1]], max_new_tokens=10, temperature=0.8, seed=42, stop_ids=())[0]
+    # request keys are the prompt's index: alone it is index 0, so only its own draw order matters
+    assert len(alone) == 10
+    for i, (p, out) in enumerate(zip(prompts, runs[0])):
+        logits = plain_logits(folder, p + out)
+        for k, tok in enumerate(out):
+            cdf = plain.temperature_cdf(logits[len(p) + k - 1], 0.8)
+            u = uniform(42, i, k)
+            lo = 0.0 if tok == 0 else float(cdf[tok - 1])
+            assert lo - 1e-4 <= u <= float(cdf[tok]) + 1e-4, (i, k, tok)
+
+
+def test_stop_ids_and_token_limits(model_root):
+    folder = make_model(model_root, "A", seed=3, dtype=torch.float32)
+    eng = engine(folder, "float32")
+    p = seeded_ids(6, 256, 7)
+    full = eng.generate([p], max_new_tokens=12, stop_ids=())[0]
+    stop = full[4]
+    cut = eng.generate([p], max_new_tokens=12, stop_ids=(stop,))[0]
+    assert cut == full[:full.index(stop) + 1]                      # the stop token is recorded
+    assert eng.generate([p, p], max_new_tokens=[3, 0], stop_ids=()) == [full[:3], []]
+
+
+def test_few_pages_preempt_and_recompute_to_the_same_tokens(model_root):
+    folder = make_model(model_root, "A", seed=3, dtype=torch.float32)
+    prompts = [seeded_ids(n, 256, 30 + n) for n in (20, 17, 25, 9)]
+    roomy = engine(folder, "float32", max_tokens=512)
+    want = roomy.generate(prompts, max_new_tokens=20, stop_ids=())
+    tight = engine(folder, "float32", max_tokens=96)               # 12 pages of 8 for four requests of ~40
+    got = tight.generate(prompts, max_new_tokens=20, stop_ids=(), return_requests=True)
+    assert [r.output for r in got] == want
+    assert tight.last_counters.preemptions >= 1
+    assert all(r.finish_reason == "length" for r in got)
+    tight.cache.check()
+    assert tight.cache.free_pages() == tight.cache.num_pages
+
+
+def test_missing_gpu_or_bad_dtype_fail_loudly(model_root):
+    from beglin_b200 import Engine
+    folder = make_model(model_root, "A", seed=3, dtype=torch.float32)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        Engine.from_folder(folder, device="cpu")
+    with pytest.raises(ValueError, match="dtype"):
+        Engine.from_folder(folder, dtype="float16")
+
+
+def test_command_line_greedy_and_cbatch(model_root, tmp_path):
+    folder = make_model(model_root, "A", seed=3, dtype=torch.float32)
+    cfg, w = plain_model(folder)
+    prompt = seeded_ids(40, 256, 8)
+    ids = tmp_path / "prompt.i32"
+    np.asarray(prompt, dtype="<i4").tofile(ids)
+    env = dict(os.environ, QWEN_BASE=folder, QWEN_PROMPT=str(ids), QWEN_DTYPE="fp32", QWEN_SAFETENSORS_MAXSEQ="128",
+               QWEN_PAGE_SIZE="8")
+    exe = [sys.executable, os.path.join(ROOT, "bin", "qwen_infer")]
+    r = subprocess.run(exe + ["greedy", "6"], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    want = plain.greedy_generate(cfg, w, prompt, 6)
+    assert r.stdout.strip() == "greedy:" + "".join(f" {t}" for t in want)
+    assert "[engine] arch config" in r.stderr and "NL=2" in r.stderr
+    r = subprocess.run(exe + ["cbatch", "5"], env=dict(env, QWEN_CB_REQS="6", QWEN_BATCH="3", QWEN_CB_REPS="2",
+                                                        QWEN_CB_PREFILL_BUDGET="8"),
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = r.stdout.strip().splitlines()
+    assert len(lines) == 7 and lines[-1].startswith("agg_tok_s ") and "reps_identical 1" in lines[-1]
+    plen = [min(40, 4 + (i * 13) % 37) for i in range(6)]
+    maxnew = [6 + (i * 7) % 5 for i in range(6)]
+    for i, line in enumerate(lines[:6]):
+        head, toks = line.split(":")
+        assert head == f"cbatch req{i} plen {plen[i]} maxnew {maxnew[i]} nout {maxnew[i]}"
+        assert [int(t) for t in toks.split()] == plain.greedy_generate(cfg, w, prompt[:plen[i]], maxnew[i])
+    r = subprocess.run(exe + ["greedy"], env=dict(env, QWEN_BASE=str(tmp_path)), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 1 and "FATAL" in r.stderr and "arch config" in r.stderr

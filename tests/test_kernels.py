@@ -1,0 +1,305 @@
+"""Each CUDA kernel alone against a plain PyTorch reference of the same operation, at sizes other
+than the engine's: head sizes in steps of 16, odd numbers of heads and groups, widths that are no
+powers of two, pages in shuffled order with poisoned free pages."""
+import math
+
+import pytest
+import torch
+
+from helpers import plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from beglin_b200.csrc import ops as o
+    o.lib()
+    return o
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_gather(ops, dtype):
+    table = rnd(301, 72, dtype=dtype, seed=1)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = torch.full((5, 72), float("nan"), device=DEV)
+    status = ops.new_status(DEV)
+    ops.embed_gather(table, ids, out, status)
+    assert torch.equal(out, table.float()[ids.long()])
+    ops.raise_on_status(status)
+    bad = torch.tensor([3, 301], dtype=torch.int32, device=DEV)
+    out2 = torch.empty((2, 72), device=DEV)
+    ops.embed_gather(table, bad, out2, status)
+    with pytest.raises(ops.KernelError, match="vocabulary"):
+        ops.raise_on_status(status)
+    assert torch.equal(out2[1], torch.zeros(72, device=DEV))
+
+
+@pytest.mark.parametrize("d", [64, 1536, 100, 5000])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(ops, d, out_dtype):
+    T, eps = 7, 1e-5
+    x = rnd(T, d, seed=2)
+    delta = rnd(T, d, dtype=out_dtype, seed=3)
+    w = (1 + 0.1 * rnd(d, seed=4)).to(out_dtype if out_dtype == torch.bfloat16 else torch.float32)
+    want_x = x.double() + delta.double()
+    want = plain.rmsnorm(want_x, w.double(), eps)
+    x1 = x.clone()
+    out = torch.empty((T, d), dtype=out_dtype, device=DEV)
+    ops.add_rmsnorm(x1, delta, w, eps, out)
+    assert (x1.double() - want_x).abs().max() < 1e-6
+    tol = 1e-5 if out_dtype == torch.float32 else 1e-2
+    assert (out.double() - want).abs().max() < tol * want.abs().max()
+    # without an addend x is left alone; with rows only those rows are normed and x is not updated
+    x2 = x.clone()
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+    out2 = torch.empty((3, d), dtype=out_dtype, device=DEV)
+    ops.add_rmsnorm(x2, delta, w, eps, out2, rows=rows, update=False)
+    assert torch.equal(x2, x)
+    assert torch.equal(out2, out[rows.long()])
+    out3 = torch.empty((T, d), dtype=out_dtype, device=DEV)
+    ops.add_rmsnorm(x2, None, w, eps, out3)
+    want3 = plain.rmsnorm(x.double(), w.double(), eps)
+    assert (out3.double() - want3).abs().max() < tol * want3.abs().max() and torch.equal(x2, x)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(ops, dtype):
+    gu = rnd(5, 2 * 203, dtype=dtype, seed=5, scale=3.0)
+    out = torch.empty((5, 203), dtype=dtype, device=DEV)
+    ops.swiglu(gu, out)
+    want = plain.swiglu(gu[:, :203].double(), gu[:, 203:].double())
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    assert (out.double() - want).abs().max() <= tol * want.abs().max()
+
+
+def test_gemm_f32_is_true_float_and_row_invariant(ops):
+    M, N, K = 37, 203, 301
+    a = rnd(M, K, seed=6)
+    w = rnd(N, K, seed=7)
+    b = rnd(N, seed=8)
+    out = torch.empty((M, N), device=DEV)
+    ops.gemm_f32_nt(a, w, b, out)
+    want = a.double() @ w.double().t() + b.double()
+    assert (out.double() - want).abs().max() < 2e-6 * want.abs().max() * math.sqrt(K)
+    # a value that tf32 (10 mantissa bits) cannot hold must survive
+    a2 = torch.zeros((1, 16), device=DEV); w2 = torch.zeros((1, 16), device=DEV)
+    a2[0, 0] = 1.0 + 2.0 ** -20; w2[0, 0] = 1.0
+    o2 = torch.empty((1, 1), device=DEV)
+    ops.gemm_f32_nt(a2, w2, None, o2)
+    assert float(o2) == 1.0 + 2.0 ** -20
+    # a row's result does not depend on the rows around it
+    one = torch.empty((1, N), device=DEV)
+    ops.gemm_f32_nt(a[11:12].contiguous(), w, b, one)
+    assert torch.equal(one[0], out[11])
+    acc = out.clone()
+    ops.gemm_f32_nt(a, w, None, acc, accumulate=True)
+    assert (acc.double() - (2 * want - b.double())).abs().max() < 1e-4
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_table_and_kv_append(ops, interleaved, dtype):
+    nh, nkv, hd, rot, page, T = 3, 2, 48, 32, 8, 6
+    theta = 50000.0
+    positions = torch.tensor([9, 10, 11, 0, 40, 7], dtype=torch.int32, device=DEV)
+    row_req = torch.tensor([0, 0, 0, 1, 2, 1], dtype=torch.int32, device=DEV)
+    i = torch.arange(rot // 2, dtype=torch.float64)
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -(2 * i) / rot).float().to(DEV)
+    table = torch.empty((T, rot // 2, 2), device=DEV)
+    ops.rope_table(positions, inv, table)
+    ang = positions.double()[:, None].cpu() * inv.double().cpu()[None, :]
+    assert (table[..., 0].cpu().double() - torch.cos(ang)).abs().max() < 2e-5   # float angle at position 40
+    assert (table[..., 1].cpu().double() - torch.sin(ang)).abs().max() < 2e-5
+    width = (nh + 2 * nkv) * hd
+    qkv = rnd(T, width, dtype=dtype, seed=9)
+    orig = qkv.clone()
+    n_pages = 10
+    bt = torch.full((3, 8), -1, dtype=torch.int32, device=DEV)
+    bt[0, :2] = torch.tensor([4, 7]); bt[1, :1] = torch.tensor([2]); bt[2, :6] = torch.tensor([9, 0, 1, 3, 5, 6])
+    pool = torch.full((n_pages, 2, nkv, page, hd), float("nan"), dtype=dtype, device=DEV)
+    status = ops.new_status(DEV)
+    ops.rope_kv_append(qkv, T, nh, nkv, hd, rot, interleaved, table, positions, row_req, bt, pool, page, status)
+    ops.raise_on_status(status)
+
+    def rotate(v, t):        # v [heads, hd] float64
+        c, s = table[t, :, 0].double().cpu(), table[t, :, 1].double().cpu()
+        out = v.clone()
+        if interleaved:
+            a, b = v[:, 0:rot:2], v[:, 1:rot:2]
+            out[:, 0:rot:2] = a * c - b * s
+            out[:, 1:rot:2] = b * c + a * s
+        else:
+            a, b = v[:, :rot // 2], v[:, rot // 2:rot]
+            out[:, :rot // 2] = a * c - b * s
+            out[:, rot // 2:rot] = b * c + a * s
+        return out
+
+    tol = 1e-6 if dtype == torch.float32 else 2e-2
+    written = set()
+    for t in range(T):
+        o = orig[t].double().cpu()
+        q = rotate(o[:nh * hd].reshape(nh, hd), t)
+        k = rotate(o[nh * hd:(nh + nkv) * hd].reshape(nkv, hd), t)
+        v = o[(nh + nkv) * hd:].reshape(nkv, hd)
+        assert (qkv[t, :nh * hd].double().cpu().reshape(nh, hd) - q).abs().max() < tol * 4
+        p = int(positions[t]); pg = int(bt[int(row_req[t]), p // page]); sl = p % page
+        assert (pool[pg, 0, :, sl].double().cpu() - k).abs().max() < tol * 4
+        assert (pool[pg, 1, :, sl].double().cpu() - v).abs().max() < tol * 4
+        written.add((pg, sl))
+        assert torch.equal(qkv[t, nh * hd:], orig[t, nh * hd:])        # k and v rows themselves are not touched
+    finite = torch.isfinite(pool[:, 0, 0, :, 0].float()).cpu()
+    assert {(int(a), int(b)) for a, b in finite.nonzero()} == written   # nothing else was written
+    # a page outside the pool is recorded, not written
+    bt[1, 0] = 99
+    ops.rope_kv_append(orig.clone(), T, nh, nkv, hd, rot, interleaved, table, positions, row_req, bt, pool, page, status)
+    with pytest.raises(ops.KernelError, match="page"):
+        ops.raise_on_status(status)
+
+
+def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64):
+    """Three requests in one step: a long prompt portion on top of earlier context, a decoded token
+    far into a long context, and a fresh short prompt.  Pages are handed out in shuffled order and
+    everything not held is poison."""
+    torch.manual_seed(seed)
+    group = nh // nkv
+    ctx = [(37, 21), (150, 1), (0, 5)]               # (positions already in the cache, new rows)
+    total = [c + n for c, n in ctx]
+    n_pages_each = [-(-t // page) for t in total]
+    n_pages = sum(n_pages_each) + 5
+    perm = torch.randperm(n_pages).tolist()
+    max_pages = max(n_pages_each) + 2
+    bt = torch.full((3, max_pages), -1, dtype=torch.int32)
+    pool = torch.full((n_pages, 2, nkv, page, hd), float("nan"), dtype=dtype)
+    ks, vs, qs = [], [], []
+    it = iter(perm)
+    for r, t in enumerate(total):
+        k = torch.randn(t, nkv, hd) * 0.7
+        v = torch.randn(t, nkv, hd)
+        k, v = k.to(dtype), v.to(dtype)
+        ks.append(k); vs.append(v)
+        for pi in range(n_pages_each[r]):
+            pg = next(it)
+            bt[r, pi] = pg
+            n = min(page, t - pi * page)
+            pool[pg, 0, :, :n] = k[pi * page:pi * page + n].transpose(0, 1)
+            pool[pg, 1, :, :n] = v[pi * page:pi * page + n].transpose(0, 1)
+    rows = sum(n for _, n in ctx)
+    q = (torch.randn(rows, nh, hd) * 0.7).to(dtype)
+    # make one far key stand out for the decoded token: its score dominates unless it is missed
+    far = 3
+    q[21, :, :] = 0; q[21, :, 0] = 8.0
+    ks[1][far, :, 0] = 8.0
+    pool[int(bt[1, far // page]), 0, :, far % page, 0] = 8.0
+    positions, row_req, qblk = [], [], []
+    bq, tile = ops.attention_plan(group, hd)
+    r0 = 0
+    for r, (c, n) in enumerate(ctx):
+        positions += list(range(c, c + n)); row_req += [r] * n
+        for b in range(0, n, bq):
+            qblk.append((r, r0 + b, min(bq, n - b)))
+        r0 += n
+    positions_t = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    qblk_t = torch.tensor(qblk, dtype=torch.int32, device=DEV)
+    n_splits = max(positions) // split + 1
+    part_o = torch.full((rows * nh * n_splits, hd), float("nan"), device=DEV)
+    part_ml = torch.full((rows * nh * n_splits, 2), float("nan"), device=DEV)
+    out = torch.full((rows, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    status = ops.new_status(DEV)
+    qd = q.reshape(rows, nh * hd).to(DEV).contiguous()
+    scale = 1.0 / math.sqrt(hd)
+    ops.attention(qd, qd.stride(0), pool.to(DEV), bt.to(DEV), positions_t, qblk_t, len(qblk), part_o, part_ml,
+                  n_splits, n_splits, rows, nh, nkv, hd, window or 0, split, tile, bq, scale, out, status)
+    ops.raise_on_status(status)
+    # reference: every request's rows against its whole key/value sequence
+    want = torch.empty(rows, nh * hd, dtype=torch.float64)
+    r0 = 0
+    for r, (c, n) in enumerate(ctx):
+        t = total[r]
+        qfull = torch.zeros(t, nh, hd, dtype=torch.float64)
+        qfull[c:] = q[r0:r0 + n].double()
+        o = plain.attention_fast(qfull, ks[r].double(), vs[r].double(), group, window)
+        want[r0:r0 + n] = o[c:]
+        r0 += n
+    return out.double().cpu(), want
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(4, 2, 16, 8), (3, 1, 32, 16), (5, 5, 48, 16), (12, 2, 128, 16),
+                                            (7, 1, 80, 4), (2, 1, 256, 32), (6, 3, 64, 64)])
+def test_attention_float32(ops, nh, nkv, hd, page):
+    got, want = _attention_case(ops, nh, nkv, hd, page, torch.float32, None, seed=nh * 100 + hd)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < 1e-5 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(4, 2, 16, 8, 10), (12, 2, 128, 16, 64), (5, 5, 48, 16, 1),
+                                                   (3, 1, 32, 16, 100)])
+def test_attention_window(ops, nh, nkv, hd, page, window):
+    got, want = _attention_case(ops, nh, nkv, hd, page, torch.float32, window, seed=7)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < 1e-5 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(12, 2, 128, 16), (3, 1, 32, 16), (5, 5, 48, 8)])
+def test_attention_bfloat16(ops, nh, nkv, hd, page):
+    got, want = _attention_case(ops, nh, nkv, hd, page, torch.bfloat16, None, seed=3)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
+
+
+def test_attention_refuses_sizes_it_does_not_take(ops):
+    with pytest.raises(ops.KernelError, match="head_dim"):
+        ops.attention_plan(2, 272)
+
+
+def test_sample_greedy_takes_the_first_maximum(ops):
+    V = 1000
+    logits = rnd(4, V, seed=11)
+    logits[0, 700] = 50.0; logits[0, 300] = 50.0
+    logits[1, 999] = 60.0
+    logits[2, 0] = 60.0
+    logits[3, :] = -1.0
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    ops.sample(logits, None, None, out)
+    assert out.tolist() == [300, 999, 0, 0]
+
+
+def test_sample_temperature_inverts_the_cumulative_distribution(ops):
+    V, n = 151, 64
+    logits = rnd(n, V, seed=12, scale=2.0)
+    temp = torch.full((n,), 0.8, device=DEV)
+    temp[5] = 0.0
+    u = torch.linspace(0.0, 0.999, n, device=DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temp, u, out)
+    got = out.tolist()
+    for r in range(n):
+        if r == 5:
+            assert got[r] == int(logits[r].argmax())
+            continue
+        cdf = plain.temperature_cdf(logits[r].cpu(), 0.8)
+        lo = 0.0 if got[r] == 0 else float(cdf[got[r] - 1])
+        hi = float(cdf[got[r]])
+        assert lo - 1e-5 <= float(u[r]) <= hi + 1e-5, (r, got[r], lo, float(u[r]), hi)
+    # the same numbers give the same tokens
+    out2 = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temp, u, out2)
+    assert out2.tolist() == got
+    # a large vocabulary that is no multiple of the block
+    V = 151937
+    big = rnd(2, V, seed=13)
+    t2 = torch.tensor([1.0, 1.0], device=DEV); u2 = torch.tensor([0.25, 0.9], device=DEV)
+    o2 = torch.empty(2, dtype=torch.int32, device=DEV)
+    ops.sample(big, t2, u2, o2)
+    for r in range(2):
+        cdf = plain.temperature_cdf(big[r].cpu(), 1.0)
+        i = int(o2[r])
+        assert (0.0 if i == 0 else float(cdf[i - 1])) - 1e-4 <= float(u2[r]) <= float(cdf[i]) + 1e-4
