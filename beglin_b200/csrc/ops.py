@@ -69,8 +69,24 @@ _ARG_ERRORS = {-1: "unsupported element type", -2: "unsupported shape", -3: "mis
                -4: "sizes that this kernel does not take"}
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of this library have been launched (or recorded into a graph) so far."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    """Account for kernels that a replayed CUDA graph launched."""
+    global _launches
+    _launches += n
+
+
 def _check(rc: int, name: str) -> None:
+    global _launches
     if rc == 0:
+        _launches += 1
         return
     if rc < 0:
         raise KernelError(f"{name}: refused: {_ARG_ERRORS.get(rc, rc)}")

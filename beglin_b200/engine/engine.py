@@ -51,7 +51,7 @@ def require_gpu(device) -> torch.device:
 class Engine:
     def __init__(self, spec, tensors, *, dtype="bfloat16", device="cuda:0", max_tokens: int = 8192,
                  page_size: int = 16, max_requests: int = 8, max_context: Optional[int] = None,
-                 kv_split: int = 256, gemm: str = "auto", config=None, origin: str = ""):
+                 kv_split: int = 256, gemm: str = "auto", use_graphs: bool = True, config=None, origin: str = ""):
         """`tensors` is anything with names()/shape(name)/tensor(name): a Checkpoint or a TensorDict.
         `max_tokens` sizes the page pool: it holds that many positions (rounded up to whole pages)."""
         self.device = require_gpu(device)
@@ -71,6 +71,8 @@ class Engine:
             self.cache.allocate(self.device, self.dtype)
         self.sampler = Sampler(self.device)
         self.vocab = spec.vocab
+        self.use_graphs = use_graphs
+        self._graphs = {}
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -158,6 +160,25 @@ class Engine:
     def release(self, rid: Hashable) -> None:
         self.cache.release(rid)
 
+    # ------------------------------------------------------------------ decoding as a CUDA graph
+    def decode_graph(self, n: int):
+        from .decode_graph import DecodeGraph
+        g = self._graphs.get(n)
+        if g is None:
+            with torch.cuda.device(self.device):
+                g = self._graphs[n] = DecodeGraph(self, n)
+        return g
+
+    def decode(self, rids: Sequence[Hashable], tokens: Optional[Sequence[int]] = None,
+               temperatures: Optional[Sequence[float]] = None, uniforms: Optional[Sequence[float]] = None,
+               read_back: bool = True):
+        """One decoding step for live requests, one token each, run as a replayed CUDA graph:
+        `tokens` (host ids; None feeds what the last step sampled, kept on the device) in, the
+        sampled tokens out (greedy unless temperatures and uniform numbers are given)."""
+        self.cache.reserve([(r, self.cache.length(r) + 1) for r in rids])
+        with torch.cuda.device(self.device):
+            return self.decode_graph(len(rids)).step(rids, tokens, temperatures, uniforms, read_back)
+
     # ------------------------------------------------------------------ generation
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Union[int, Sequence[int]] = 32,
                  temperature: float = 0.0, seed: int = 0, stop_ids: Optional[Sequence[int]] = None,
@@ -190,13 +211,18 @@ class Engine:
                 plan = sched.plan()
                 if plan is None:
                     break
-                logits = self.run(plan.entries, sched._plan_lengths)
                 wanted = sched.wanted(plan)
+                temps = [r.temperature for r in wanted]
+                us = [uniform(r.seed, r.rid[1], len(r.output)) if r.temperature > 0 else 0.0 for r in wanted]
                 tokens: List[int] = []
-                if wanted:
-                    temps = [r.temperature for r in wanted]
-                    us = [uniform(r.seed, r.rid[1], len(r.output)) if r.temperature > 0 else 0.0 for r in wanted]
-                    tokens = self.sampler.sample(logits, temps, us)
+                if self.use_graphs and not plan.prefill:
+                    with torch.cuda.device(self.device):
+                        tokens = self.decode_graph(len(wanted)).step(
+                            [r.rid for r in wanted], [r.output[-1] for r in wanted], temps, us)
+                else:
+                    logits = self.run(plan.entries, sched._plan_lengths)
+                    if wanted:
+                        tokens = self.sampler.sample(logits, temps, us)
                 sched.update(plan, tokens)
             ops.raise_on_status(self.ctx.status)
         finally:

@@ -1,0 +1,251 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen2.5-1.5B layer sizes, random weights, bf16.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers N]
+    python bench.py --impl reference ...      # prints the reference arm's `unavailable` line
+
+A step is one decoding step of `batch` requests, each holding close to `context` positions in the
+paged cache.  It prints ONE JSON line: `value` is decoded tokens a second on the device (the step
+replayed as a CUDA graph, sampled tokens fed back on the device); `e2e` is the same through the
+Python entry point `Engine.decode`, host token ids in from pinned memory and sampled ids read back
+every step; `prefill` is one 2,048-token prompt in one step; `roofline` sets the bytes a decoding
+step has to read (every weight once and the cache of the live requests) against the measured copy
+bandwidth; `points` holds decoding at batch 1 and 64.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Qwen2.5-1.5B layer sizes: the third configuration of the baseline record.
+CONFIG_1P5B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 28, "hidden_size": 1536, "num_attention_heads": 12, "num_key_value_heads": 2,
+    "intermediate_size": 8960, "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True, "use_sliding_window": False, "hidden_act": "silu",
+    "max_position_embeddings": 32768,
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        out = {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+        if "bf16_tflops_sustained" in p:
+            out["bf16_tflops_sustained"] = float(p["bf16_tflops_sustained"])
+        return out
+    except (OSError, KeyError, ValueError):
+        return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.samples, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower() == "active" for s in self.samples)]
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def kv_bytes_per_token(cfg, layers):
+    hd = cfg["hidden_size"] // cfg["num_attention_heads"]
+    return layers * 2 * cfg["num_key_value_heads"] * hd * 2
+
+
+def prefill_flops(cfg, layers, T):
+    d, im, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    hd = d // cfg["num_attention_heads"]
+    qd, kvd = cfg["num_attention_heads"] * hd, cfg["num_key_value_heads"] * hd
+    linear = 2.0 * T * layers * (d * (qd + 2 * kvd) + qd * d + 3 * d * im)
+    attn = layers * 4.0 * qd * (T * (T + 1) / 2.0)
+    head = 2.0 * d * V                     # the last row only
+    return linear + attn + head
+
+
+def fill_cache(eng, rids, length, seed, chunk=2048):
+    """Prefill every request to `length` positions with seeded uniform token ids, through the step
+    function, a few requests at a time."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    per_step = max(1, 8192 // min(length, chunk))
+    for lo in range(0, len(rids), per_step):
+        group = rids[lo:lo + per_step]
+        ids = {r: torch.randint(0, eng.vocab, (length,), generator=g).tolist() for r in group}
+        for p in range(0, length, chunk):
+            eng.step([(r, ids[r][p:p + chunk], []) for r in group], check=False)
+    torch.cuda.synchronize()
+
+
+def time_decode(eng, batch, context, steps, warmup, seed, e2e):
+    """(ms per step on the device, launches of this package's kernels in the timed region).  With
+    `e2e` every step takes its tokens from the host and reads the sampled ones back."""
+    import torch
+    from beglin_b200.csrc import ops
+    rids = [("bench", batch, i) for i in range(batch)]
+    start_len = context - (warmup + steps) - 1
+    fill_cache(eng, rids, start_len, seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    toks = torch.randint(0, eng.vocab, (batch,), generator=g).tolist()
+    if e2e:
+        for _ in range(warmup):
+            toks = eng.decode(rids, toks, read_back=True)
+    else:
+        eng.decode(rids, toks, read_back=False)          # host tokens once; then fed back on the device
+        for _ in range(warmup - 1):
+            eng.decode(rids, None, read_back=False)
+    torch.cuda.synchronize()
+    before = ops.launch_count()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    if e2e:
+        for _ in range(steps):
+            toks = eng.decode(rids, toks, read_back=True)
+    else:
+        for _ in range(steps):
+            eng.decode(rids, None, read_back=False)
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / steps
+    launches = ops.launch_count() - before
+    ops.raise_on_status(eng.ctx.status)
+    for r in rids:
+        eng.release(r)
+    return ms, launches
+
+
+def time_prefill(eng, T, reps, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    best = float("inf")
+    for i in range(reps + 2):
+        ids = torch.randint(0, eng.vocab, (T,), generator=g).tolist()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        eng.step([("prefill", ids, [T - 1])], end=["prefill"], check=False)
+        t1.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            best = min(best, t0.elapsed_time(t1))
+    return best
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=CONFIG_1P5B["num_hidden_layers"])
+    ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64 and the prefill")
+    ap.add_argument("--gemm", default="auto")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a C program for Apple CPUs (Accelerate, NEON, SME2) with no Python "
+                          "package: pip reports \"Neither 'setup.py' nor 'pyproject.toml' found\", and "
+                          "qwen_infer.c does not compile on x86 Linux"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(3, args.warmup)
+
+    import torch
+    from beglin_b200 import Engine
+    pk = peaks()
+    cfg = dict(CONFIG_1P5B, num_hidden_layers=args.layers)
+    max_batch = args.batch if args.no_points else max(args.batch, 64)
+    page = 16
+    eng = Engine.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=max_batch * args.context,
+                        page_size=page, max_requests=max_batch, max_context=args.context, gemm=args.gemm)
+    weight_bytes = eng.model.weight_bytes()
+    kvb = kv_bytes_per_token(cfg, args.layers)
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches = time_decode(eng, args.batch, args.context, args.steps, args.warmup, seed=1, e2e=False)
+    clock_rec = clocks.stop()
+    ms_e2e, _ = time_decode(eng, args.batch, args.context, args.steps, args.warmup, seed=1, e2e=True)
+
+    value = args.batch * 1000.0 / ms
+    ctx_mid = args.context - 1 - args.steps / 2.0
+    step_bytes = weight_bytes + args.batch * ctx_mid * kvb
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    out = {
+        "metric": "decode tok/s @ batch 8; Qwen2.5-1.5B bf16", "value": round(value, 1), "unit": "tok/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (seeded uniform token ids, random weights)",
+        "config": {"model": "Qwen2.5-1.5B sizes", "layers": args.layers, "layers_of_config": CONFIG_1P5B["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
+                   "vocab": cfg["vocab_size"], "tied_head": True, "global_batch": args.batch, "seq_len": args.context,
+                   "page_size": page, "parallelism": "single GPU", "weights": "random, seeded",
+                   "l2": "inputs larger than L2 (weights and cache read once per step)",
+                   "peaks": pk["source"]},
+        "e2e": {"value": round(args.batch * 1000.0 / ms_e2e, 1), "unit": "tok/s",
+                "h2d_bytes_per_step": int(args.batch * 4 * 3 + args.batch * eng.cache.max_pages * 4),
+                "d2h_bytes_per_step": int(args.batch * 4)},
+        "gpu_launches": int(launches),
+        "clocks": clock_rec,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+    if not args.no_points:
+        points = {}
+        for b in (1, 64):
+            m, _ = time_decode(eng, b, args.context, min(args.steps, 32), args.warmup, seed=2, e2e=False)
+            points[f"decode_b{b}"] = round(b * 1000.0 / m, 1)
+        out["points"] = points
+        T = 2048
+        pms = time_prefill(eng, T, reps=3, seed=3)
+        flops = prefill_flops(cfg, args.layers, T)
+        out["prefill"] = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
+                          "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
