@@ -1,0 +1,371 @@
+// Tensor-core attention over the paged cache for bfloat16 queries and caches (head sizes 64, 128).
+//
+// Same contract as attention.cu: a CTA takes (query block, kv head, split of keys) and writes, for
+// every (row, head) that sees a key of the split, an unnormalised output with its running maximum
+// and sum; attention_merge joins the splits.  Scores, softmax and the output accumulators are float;
+// the two products of a 16-key block run as mma.sync m16n8k16 on bfloat16 operands with float
+// accumulation.  Keys and values are brought from the pages into shared memory with 16-byte
+// cp.async copies, three stages of 64 keys deep, in a layout that XORs the 16-byte column with the
+// key's low bits so that ldmatrix reads without bank conflicts.
+//
+// Two arrangements of the four warps:
+//   rows:  the query block has up to 64 rows (tokens x heads of the group); warp w owns rows
+//          16w..16w+15 and walks all keys of a stage (prompt portions).
+//   keys:  the query block is ONE token (<= 16 heads in the group); warp w owns keys 16w..16w+15 of
+//          every stage, and the four partial results are joined in shared memory (decoding, where
+//          the cache is streamed once and the tensor work is idle most of the time).
+#include "common.cuh"
+
+namespace bg {
+
+constexpr int AM_THREADS = 128;
+constexpr int AM_STAGE_KEYS = 64;
+constexpr int AM_STAGES = 3;
+constexpr float AM_LOG2E = 1.4426950408889634f;
+constexpr float AM_LN2 = 0.6931471805599453f;
+
+struct AttnMmaParams {
+    const __nv_bfloat16* q;
+    int q_stride;
+    const __nv_bfloat16* kv_pool;
+    int num_pages, page_size;
+    const int* block_table;
+    int max_pages;
+    const int* positions;
+    const int* qblk;
+    float* part_o;
+    float* part_ml;
+    int max_splits;
+    int nh, nkv, group;
+    int window, split;
+    float scale_log2;       // scale * log2(e)
+    unsigned* status;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, int src_bytes) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gmem_src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+    unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Byte offset of (row, 16-byte column c) in a tile whose rows are HD bf16 wide.
+template <int HD> __device__ __forceinline__ int swz(int row, int c) { return row * (HD * 2) + ((c ^ (row & 7)) << 4); }
+
+template <int HD, bool BY_KEYS>
+__global__ void __launch_bounds__(AM_THREADS)
+attention_mma_kernel(AttnMmaParams p) {
+    constexpr int CH = HD / 8;                 // 16-byte columns per row
+    constexpr int KSTEPS = HD / 16;            // k-steps of q.k
+    constexpr int NT_O = HD / 8;               // 8-wide column tiles of the output
+    constexpr int STAGE_BYTES = AM_STAGE_KEYS * HD * 2;
+    extern __shared__ __align__(128) unsigned char sm[];
+    unsigned char* q_s = sm;                                   // [64 rows][HD]
+    unsigned char* k_s = q_s + 64 * HD * 2;                    // [stages][64][HD]
+    unsigned char* v_s = k_s + AM_STAGES * STAGE_BYTES;        // [stages][64][HD]
+
+    const int qb = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+    const int req = p.qblk[qb * 3 + 0], row0 = p.qblk[qb * 3 + 1], nq = p.qblk[qb * 3 + 2];
+    if (nq <= 0) return;
+    const int group = p.group;
+    const int pos_first = p.positions[row0];
+    const int pos_last = p.positions[row0 + nq - 1];
+    const int lo_first = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int k_begin = max(sp * p.split, lo_first);
+    const int k_end = min((sp + 1) * p.split, pos_last + 1);
+    if (k_begin >= k_end) return;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_rows = nq * group;             // <= 64 (rows) or <= 16 (keys)
+
+    // ---- queries of the block into shared memory (rows beyond n_rows are zero)
+    for (int idx = tid; idx < 64 * CH; idx += AM_THREADS) {
+        int r = idx / CH, c = idx - r * CH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < n_rows) {
+            int qi = r / group, g = r - qi * group;
+            v = *reinterpret_cast<const uint4*>(p.q + (size_t)(row0 + qi) * p.q_stride + (size_t)(kvh * group + g) * HD + c * 8);
+        }
+        *reinterpret_cast<uint4*>(q_s + swz<HD>(r, c)) = v;
+    }
+
+    // ---- stage loader: thread t copies half a key row of K and of V
+    const int first_stage_key = (k_begin / AM_STAGE_KEYS) * AM_STAGE_KEYS;
+    const int n_stage = (k_end - first_stage_key + AM_STAGE_KEYS - 1) / AM_STAGE_KEYS;
+    const size_t page_elems = (size_t)2 * p.nkv * p.page_size * HD;
+    const size_t v_off = (size_t)p.nkv * p.page_size * HD;
+    auto load_stage = [&](int s) {
+        if (s < n_stage) {
+            const int buf = s % AM_STAGES;
+            const int j = tid >> 1, half = tid & 1;
+            const int key = first_stage_key + s * AM_STAGE_KEYS + j;
+            const __nv_bfloat16* src = p.kv_pool;
+            int bytes = 0;
+            if (key >= k_begin && key < k_end) {
+                int page = p.block_table[(size_t)req * p.max_pages + key / p.page_size];
+                if (page < 0 || page >= p.num_pages) {
+                    if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE);
+                } else {
+                    src = p.kv_pool + (size_t)page * page_elems + ((size_t)kvh * p.page_size + key % p.page_size) * HD;
+                    bytes = 16;
+                }
+            }
+            unsigned char* kd = k_s + buf * STAGE_BYTES;
+            unsigned char* vd = v_s + buf * STAGE_BYTES;
+#pragma unroll
+            for (int cc = 0; cc < CH / 2; ++cc) {
+                int c = half * (CH / 2) + cc;
+                cp_async16(kd + swz<HD>(j, c), src + (bytes ? c * 8 : 0), bytes);
+                cp_async16(vd + swz<HD>(j, c), src + (bytes ? v_off + c * 8 : 0), bytes);
+            }
+        }
+        cp_async_commit();
+    };
+    load_stage(0);
+    load_stage(1);
+    __syncthreads();                           // q_s is complete
+
+    // ---- this warp's query fragments and row bookkeeping
+    const int row_base = BY_KEYS ? 0 : warp * 16;
+    unsigned qf[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+        int r = row_base + (lane & 15);
+        int c = ks * 2 + (lane >> 4);
+        ldmatrix_x4(qf[ks], q_s + swz<HD>(r, c));
+    }
+    int pos_r[2], lo_r[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        int r = row_base + (lane >> 2) + h * 8;
+        if (r < n_rows) {
+            pos_r[h] = pos_first + r / group;
+            lo_r[h] = p.window > 0 ? max(0, pos_r[h] - p.window + 1) : 0;
+        } else {
+            pos_r[h] = -1; lo_r[h] = 0;
+        }
+    }
+    float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
+    float o[NT_O][4];
+#pragma unroll
+    for (int t = 0; t < NT_O; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f; }
+
+    constexpr int KB_PER_WARP = BY_KEYS ? 1 : 4;        // 16-key blocks of a stage that this warp walks
+    for (int s = 0; s < n_stage; ++s) {
+        load_stage(s + 2);
+        cp_async_wait<2>();
+        __syncthreads();
+        const int buf = s % AM_STAGES;
+        const unsigned char* kt = k_s + buf * STAGE_BYTES;
+        const unsigned char* vt = v_s + buf * STAGE_BYTES;
+        const int stage_key0 = first_stage_key + s * AM_STAGE_KEYS;
+#pragma unroll
+        for (int kbi = 0; kbi < KB_PER_WARP; ++kbi) {
+            const int kb = BY_KEYS ? warp : kbi;
+            const int key0 = stage_key0 + kb * 16;
+            if (key0 >= k_end || key0 + 16 <= k_begin) continue;           // warp-uniform
+            // scores of 16 rows x 16 keys
+            float sc[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f; }
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                unsigned kf[4];
+                int r = kb * 16 + (lane & 7) + ((lane >> 4) << 3);
+                int c = ks * 2 + ((lane >> 3) & 1);
+                ldmatrix_x4(kf, kt + swz<HD>(r, c));
+                mma_bf16(sc[0], qf[ks], kf[0], kf[1]);
+                mma_bf16(sc[1], qf[ks], kf[2], kf[3]);
+            }
+            // mask, running maximum
+            float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+                    int h = e >> 1;
+                    bool ok = key <= pos_r[h] && key >= lo_r[h] && key >= k_begin && key < k_end;
+                    float v = ok ? sc[j][e] * p.scale_log2 : -INFINITY;
+                    sc[j][e] = v;
+                    tmax[h] = fmaxf(tmax[h], v);
+                }
+            float corr[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 1));
+                tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
+                float m_new = fmaxf(m_r[h], tmax[h]);
+                corr[h] = (m_r[h] == -INFINITY) ? 0.0f : exp2f(m_r[h] - m_new);
+                m_r[h] = m_new;
+            }
+            float psum[2] = {0.0f, 0.0f};
+            unsigned pf[4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                float e0 = (sc[j][0] == -INFINITY) ? 0.0f : exp2f(sc[j][0] - m_r[0]);
+                float e1 = (sc[j][1] == -INFINITY) ? 0.0f : exp2f(sc[j][1] - m_r[0]);
+                float e2 = (sc[j][2] == -INFINITY) ? 0.0f : exp2f(sc[j][2] - m_r[1]);
+                float e3 = (sc[j][3] == -INFINITY) ? 0.0f : exp2f(sc[j][3] - m_r[1]);
+                psum[0] += e0 + e1;
+                psum[1] += e2 + e3;
+                pf[j * 2 + 0] = pack_bf16(e0, e1);
+                pf[j * 2 + 1] = pack_bf16(e2, e3);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 1);
+                psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 2);
+                l_r[h] = l_r[h] * corr[h] + psum[h];
+            }
+#pragma unroll
+            for (int t = 0; t < NT_O; ++t) {
+                o[t][0] *= corr[0]; o[t][1] *= corr[0]; o[t][2] *= corr[1]; o[t][3] *= corr[1];
+            }
+            // o += p . v   (16 keys, all HD columns, two 8-wide column tiles per ldmatrix)
+#pragma unroll
+            for (int t2 = 0; t2 < NT_O / 2; ++t2) {
+                unsigned vf[4];
+                int r = kb * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                int c = t2 * 2 + (lane >> 4);
+                ldmatrix_x4_trans(vf, vt + swz<HD>(r, c));
+                mma_bf16(o[t2 * 2 + 0], pf, vf[0], vf[1]);
+                mma_bf16(o[t2 * 2 + 1], pf, vf[2], vf[3]);
+            }
+        }
+        __syncthreads();                       // the stage's buffer may be refilled
+    }
+    cp_async_wait<0>();
+
+    // ---- write the partial results
+    if (!BY_KEYS) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            int r = row_base + (lane >> 2) + h * 8;
+            if (r >= n_rows) continue;
+            if (pos_r[h] < sp * p.split || lo_r[h] >= (sp + 1) * p.split) continue;
+            int qi = r / group, g = r - qi * group;
+            size_t prow = ((size_t)(row0 + qi) * p.nh + (size_t)kvh * group + g) * p.max_splits + sp;
+            float* po = p.part_o + prow * HD;
+#pragma unroll
+            for (int t = 0; t < NT_O; ++t) {
+                float2 v = make_float2(o[t][h * 2 + 0], o[t][h * 2 + 1]);
+                *reinterpret_cast<float2*>(po + t * 8 + (lane & 3) * 2) = v;
+            }
+            if ((lane & 3) == 0) { p.part_ml[prow * 2 + 0] = m_r[h] * AM_LN2; p.part_ml[prow * 2 + 1] = l_r[h]; }
+        }
+    } else {
+        // join the four warps' results: o_w, m_w, l_w -> shared memory (over the stage buffers)
+        float* o_sh = reinterpret_cast<float*>(k_s);               // [4][16][HD]
+        float* ml_sh = o_sh + 4 * 16 * HD;                         // [4][16][2]
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            int r = (lane >> 2) + h * 8;
+            float* dst = o_sh + ((size_t)warp * 16 + r) * HD;
+#pragma unroll
+            for (int t = 0; t < NT_O; ++t) {
+                dst[t * 8 + (lane & 3) * 2 + 0] = o[t][h * 2 + 0];
+                dst[t * 8 + (lane & 3) * 2 + 1] = o[t][h * 2 + 1];
+            }
+            if ((lane & 3) == 0) { ml_sh[(warp * 16 + r) * 2 + 0] = m_r[h]; ml_sh[(warp * 16 + r) * 2 + 1] = l_r[h]; }
+        }
+        __syncthreads();
+        const int pos = pos_first;
+        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        if (!(pos < sp * p.split || lo >= (sp + 1) * p.split)) {
+            for (int idx = tid; idx < n_rows * HD; idx += AM_THREADS) {
+                int r = idx / HD, d = idx - r * HD;
+                float m = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) m = fmaxf(m, ml_sh[(w * 16 + r) * 2]);
+                float acc = 0.0f, l = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    float mw = ml_sh[(w * 16 + r) * 2];
+                    float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
+                    acc = fmaf(o_sh[((size_t)w * 16 + r) * HD + d], f, acc);
+                    l = fmaf(ml_sh[(w * 16 + r) * 2 + 1], f, l);
+                }
+                size_t prow = ((size_t)row0 * p.nh + (size_t)kvh * group + r) * p.max_splits + sp;
+                p.part_o[prow * HD + d] = acc;
+                if (d == 0) { p.part_ml[prow * 2 + 0] = m * AM_LN2; p.part_ml[prow * 2 + 1] = l; }
+            }
+        }
+    }
+}
+
+template <int HD>
+static size_t am_smem_bytes() { return (size_t)64 * HD * 2 + (size_t)2 * AM_STAGES * AM_STAGE_KEYS * HD * 2; }
+
+template <int HD, bool BY_KEYS>
+static int am_launch(const AttnMmaParams& p, int n_qblk, int n_splits, cudaStream_t stream) {
+    auto kern = attention_mma_kernel<HD, BY_KEYS>;
+    size_t smem = am_smem_bytes<HD>();
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid(n_qblk, p.nkv, n_splits);
+    kern<<<grid, AM_THREADS, smem, stream>>>(p);
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+}  // namespace bg
+
+using namespace bg;
+
+// Whether the tensor-core kernel takes these sizes, and how many rows (tokens) a query block may
+// hold: by_keys != 0 asks for the decoding arrangement (one token per block).
+extern "C" int bg_attention_mma_plan(int group, int hd, int by_keys, int* bq_out) {
+    if (hd != 64 && hd != 128) return BG_ERR_UNSUPPORTED;
+    if (by_keys) {
+        if (group > 16) return BG_ERR_UNSUPPORTED;
+        *bq_out = 1;
+    } else {
+        if (group > 64) return BG_ERR_UNSUPPORTED;
+        *bq_out = 64 / group;
+    }
+    return BG_OK;
+}
+
+extern "C" int bg_attention_mma_partial(const void* q, int q_stride, const void* kv_pool, int num_pages, int page_size,
+                                        const int* block_table, int max_pages, const int* positions, const int* qblk,
+                                        int n_qblk, float* part_o, float* part_ml, int max_splits, int n_splits_launch,
+                                        int nh, int nkv, int hd, int window, int split, int by_keys, float scale,
+                                        unsigned* status, cudaStream_t stream) {
+    if (n_qblk <= 0 || n_splits_launch <= 0) return BG_OK;
+    if (nh % nkv != 0 || split % AM_STAGE_KEYS != 0) return BG_ERR_SHAPE;
+    if (n_splits_launch > max_splits || n_splits_launch > 65535 || nkv > 65535) return BG_ERR_SHAPE;
+    if ((q_stride % 8) != 0 || ((uintptr_t)q % 16) != 0 || ((uintptr_t)kv_pool % 16) != 0) return BG_ERR_ALIGN;
+    AttnMmaParams p;
+    p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.kv_pool = (const __nv_bfloat16*)kv_pool;
+    p.num_pages = num_pages; p.page_size = page_size; p.block_table = block_table; p.max_pages = max_pages;
+    p.positions = positions; p.qblk = qblk; p.part_o = part_o; p.part_ml = part_ml; p.max_splits = max_splits;
+    p.nh = nh; p.nkv = nkv; p.group = nh / nkv; p.window = window; p.split = split;
+    p.scale_log2 = scale * AM_LOG2E; p.status = status;
+    if (by_keys ? p.group > 16 : p.group > 64) return BG_ERR_UNSUPPORTED;
+    if (hd == 128) return by_keys ? am_launch<128, true>(p, n_qblk, n_splits_launch, stream)
+                                  : am_launch<128, false>(p, n_qblk, n_splits_launch, stream);
+    if (hd == 64) return by_keys ? am_launch<64, true>(p, n_qblk, n_splits_launch, stream)
+                                 : am_launch<64, false>(p, n_qblk, n_splits_launch, stream);
+    return BG_ERR_UNSUPPORTED;
+}

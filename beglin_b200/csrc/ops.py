@@ -33,6 +33,10 @@ _SIGNATURES = {
                              _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     "bg_attention_merge": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                            _c_int, _c_int, _c_int, _c_void_p],
+    "bg_attention_mma_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int)],
+    "bg_attention_mma_partial": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                 _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                 _c_int, _c_float, _c_void_p, _c_void_p],
     "bg_gemm_f32_nt": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_void_p],
     "bg_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
@@ -226,21 +230,36 @@ def rope_kv_append(qkv: torch.Tensor, n_rows: int, nh: int, nkv: int, hd: int, r
            "rope_kv_append")
 
 
-def attention_plan(group: int, hd: int) -> Tuple[int, int]:
-    """(rows per query block, keys per tile) that fit one CTA's shared memory for these sizes."""
+def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, decode_only: bool = False,
+                   prefer: str = "auto") -> Tuple[str, int, int]:
+    """(kernel, rows per query block, keys per tile) for these sizes.  Kernels: "mma_keys" (tensor
+    cores, one token per block, for steps of single tokens), "mma_rows" (tensor cores, up to 64 rows
+    per block) and "generic" (CUDA cores, every size up to head_dim 256, float or bfloat16)."""
+    L = lib()
+    if prefer not in ("auto", "generic", "mma"):
+        raise KernelError(f"unknown attention kernel choice '{prefer}'")
+    if dtype == torch.bfloat16 and prefer != "generic":
+        bq = _c_int(0)
+        if L.bg_attention_mma_plan(group, hd, 1 if decode_only else 0, ctypes.byref(bq)) == 0:
+            return ("mma_keys" if decode_only else "mma_rows"), bq.value, 64
+        if prefer == "mma":
+            raise KernelError(f"the tensor-core attention kernel does not take head_dim {hd} with {group} query "
+                              "heads per kv head (head_dim 64 or 128; at most 64 heads per kv head)")
     bq, tile = _c_int(0), _c_int(0)
-    rc = lib().bg_attention_plan(group, hd, ctypes.byref(bq), ctypes.byref(tile))
+    rc = L.bg_attention_plan(group, hd, ctypes.byref(bq), ctypes.byref(tile))
     if rc != 0:
         raise KernelError(f"attention: head_dim {hd} with {group} query heads per kv head is not supported "
                           "(head_dim must be at most 256)")
-    return bq.value, tile.value
+    return "generic", bq.value, tile.value
 
 
 def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table: torch.Tensor,
               positions: torch.Tensor, qblk: torch.Tensor, n_qblk: int, part_o: torch.Tensor, part_ml: torch.Tensor,
               max_splits: int, n_splits: int, n_rows: int, nh: int, nkv: int, hd: int, window: int, split: int,
-              tile: int, bq: int, scale: float, out: torch.Tensor, status: Optional[torch.Tensor]) -> None:
-    """Paged grouped-query attention of a step's rows; out is [T, nh*hd]."""
+              tile: int, bq: int, scale: float, out: torch.Tensor, status: Optional[torch.Tensor],
+              kernel: str = "generic") -> None:
+    """Paged grouped-query attention of a step's rows; out is [T, nh*hd].  `kernel`, `bq` and `tile`
+    come from `attention_plan`; `qblk` must be cut for that `bq`."""
     _cuda(q, kv_pool, block_table, positions, qblk, part_o, part_ml, out)
     _i32(positions, "positions"); _i32(block_table, "block_table"); _i32(qblk, "qblk")
     num_pages, two, nkv_, page_size, hd_ = kv_pool.shape
@@ -253,10 +272,21 @@ def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table
     if out.stride(1) != 1 or out.shape[1] < nh * hd or out.shape[0] < n_rows:
         raise KernelError("attention: out must be [T, nh*hd] with unit inner stride")
     L = lib()
-    _check(L.bg_attention_partial(_p(q), _dt(q), q_stride, _p(kv_pool), _dt(kv_pool), num_pages, page_size,
-                                  _p(block_table), block_table.shape[1], _p(positions), _p(qblk), n_qblk,
-                                  _p(part_o), _p(part_ml), max_splits, n_splits, nh, nkv, hd, window, split, tile, bq,
-                                  float(scale), _p(status), _stream()), "attention_partial")
+    if kernel == "generic":
+        _check(L.bg_attention_partial(_p(q), _dt(q), q_stride, _p(kv_pool), _dt(kv_pool), num_pages, page_size,
+                                      _p(block_table), block_table.shape[1], _p(positions), _p(qblk), n_qblk,
+                                      _p(part_o), _p(part_ml), max_splits, n_splits, nh, nkv, hd, window, split, tile,
+                                      bq, float(scale), _p(status), _stream()), "attention_partial")
+    elif kernel in ("mma_rows", "mma_keys"):
+        if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16:
+            raise KernelError("attention: the tensor-core kernel takes bfloat16 queries and caches")
+        _check(L.bg_attention_mma_partial(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
+                                          block_table.shape[1], _p(positions), _p(qblk), n_qblk, _p(part_o),
+                                          _p(part_ml), max_splits, n_splits, nh, nkv, hd, window, split,
+                                          1 if kernel == "mma_keys" else 0, float(scale), _p(status), _stream()),
+               "attention_mma_partial")
+    else:
+        raise KernelError(f"unknown attention kernel '{kernel}'")
     _check(L.bg_attention_merge(_p(part_o), _p(part_ml), _p(positions), _p(out), _dt(out), out.stride(0), n_rows, nh,
                                 hd, max_splits, split, window, _stream()), "attention_merge")
 

@@ -44,6 +44,7 @@ class StepBatch:
         self.starts = list(starts)
         self.lens = [len(e.tokens) for e in self.entries]
         self.max_position = max(pos) if pos else 0
+        self.decode_only = all(n == 1 for n in self.lens)      # every request brings a single token
         self.n_logit_rows = len(rows)
         self.token_ids = self._to_device(np.asarray(ids, dtype=np.int32))
         self.positions = self._to_device(np.asarray(pos, dtype=np.int32))

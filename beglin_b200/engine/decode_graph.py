@@ -32,6 +32,7 @@ class _StaticBatch:
         self.starts = [0] * n
         self.entries = []
         self.n_logit_rows = n
+        self.decode_only = True
         self.max_position = cache.max_context - 1
         i32 = dict(dtype=torch.int32, device=device)
         self.token_ids = torch.zeros(n, **i32)
@@ -48,7 +49,22 @@ class _StaticBatch:
         return self._qblk, self.n_rows
 
 
+class _Staging:
+    """One set of pinned host buffers for a step's uploads, with an event that says when the device
+    has taken them."""
+
+    def __init__(self, n: int, cache):
+        self.meta = torch.zeros((2, n), dtype=torch.int32).pin_memory()          # positions, slots
+        self.tokens = torch.zeros(n, dtype=torch.int32).pin_memory()
+        self.floats = torch.zeros((2, n), dtype=torch.float32).pin_memory()      # temperatures, uniforms
+        self.tables = {gi: torch.zeros((n, cache.max_pages), dtype=torch.int32).pin_memory()
+                       for gi in range(len(cache.kv_groups))}
+        self.event: Optional[torch.cuda.Event] = None
+
+
 class DecodeGraph:
+    RING = 4          # the host may prepare this many steps ahead of the device
+
     def __init__(self, engine, n: int):
         self.engine, self.n = engine, n
         dev = engine.device
@@ -58,37 +74,34 @@ class DecodeGraph:
         self.uniform = torch.zeros(n, dtype=torch.float32, device=dev)
         self.out_tokens = torch.zeros(n, dtype=torch.int32, device=dev)
         self.logits: Optional[torch.Tensor] = None
-        # pinned staging: [positions | slots | tokens] and one block table per group
-        self.h_meta = torch.zeros((3, n), dtype=torch.int32).pin_memory()
-        self.h_float = torch.zeros((2, n), dtype=torch.float32).pin_memory()
-        self.h_tables = {gi: torch.zeros((n, cache.max_pages), dtype=torch.int32).pin_memory()
-                         for gi in range(len(cache.kv_groups))}
+        self.ring = [_Staging(n, cache) for _ in range(self.RING)]
+        self.turn = 0
         self.h_out = torch.zeros(n, dtype=torch.int32).pin_memory()
-        self.d_meta = torch.zeros((3, n), dtype=torch.int32, device=dev)
-        self.d_float = torch.zeros((2, n), dtype=torch.float32, device=dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches = 0
-        self._table_version: Dict[int, object] = {}
+        self.h2d_bytes = 0                     # bytes uploaded by the last step
+        self._rids: Optional[tuple] = None     # what the device buffers describe
+        self._positions: Optional[List[int]] = None
+        self._tables: Dict[int, np.ndarray] = {}
+        self._sampling = False
 
     def _body(self) -> None:
         b = self.batch
-        b.positions.copy_(self.d_meta[0])
-        b.slots.copy_(self.d_meta[1])
         b.scratch.clear()
-        self.temperature.copy_(self.d_float[0])
-        self.uniform.copy_(self.d_float[1])
         logits = self.engine.model.forward(b, self.engine.cache)
         ops.sample(logits, self.temperature, self.uniform, self.out_tokens)
         b.token_ids.copy_(self.out_tokens)
+        b.positions.add_(1)                    # the next step of the same requests needs no upload
         self.logits = logits
 
     def _capture(self) -> None:
         side = torch.cuda.Stream(device=self.engine.device)
         side.wait_stream(torch.cuda.current_stream())
-        saved = self.batch.token_ids.clone()
+        saved_tokens, saved_pos = self.batch.token_ids.clone(), self.batch.positions.clone()
         with torch.cuda.stream(side):
             self._body()                       # warm-up outside the capture (library handles, allocations)
-            self.batch.token_ids.copy_(saved)
+            self.batch.token_ids.copy_(saved_tokens)
+            self.batch.positions.copy_(saved_pos)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         before = ops.launch_count()
@@ -102,28 +115,57 @@ class DecodeGraph:
              uniforms: Optional[Sequence[float]] = None, read_back: bool = True):
         """One decoding step for `rids` (all live, pages reserved by the caller for one more position
         each).  `tokens` None means: feed what the previous replay sampled (kept on the device).
-        Returns the sampled tokens as a list (read_back) or the device tensor."""
-        eng, cache, n = self.engine, self.engine.cache, self.n
+        Returns the sampled tokens as a list (read_back) or the device tensor.  Only what changed since
+        the last step is uploaded: positions advance on the device, block tables change when a request
+        gets a new page."""
+        cache, n, b = self.engine.cache, self.n, self.batch
         assert len(rids) == n
-        self.h_meta[0] = torch.as_tensor([cache.length(r) for r in rids], dtype=torch.int32)
-        self.h_meta[1] = torch.from_numpy(cache.slot_ids(rids))
+        st = self.ring[self.turn]
+        self.turn = (self.turn + 1) % self.RING
+        if st.event is not None:
+            st.event.synchronize()             # the device has read this set's last contents
+        sent = 0
+        positions = [cache.length(r) for r in rids]
+        key = tuple(rids)
+        if key != self._rids or positions != self._positions:
+            st.meta[0] = torch.as_tensor(positions, dtype=torch.int32)
+            st.meta[1] = torch.from_numpy(cache.slot_ids(rids))
+            b.positions.copy_(st.meta[0], non_blocking=True)
+            b.slots.copy_(st.meta[1], non_blocking=True)
+            sent += 8 * n
+            self._rids = key
         if tokens is not None:
-            self.h_meta[2] = torch.as_tensor(list(tokens), dtype=torch.int32)
-        self.d_meta.copy_(self.h_meta, non_blocking=True)
-        if tokens is not None:
-            self.batch.token_ids.copy_(self.d_meta[2])
-        if temperatures is not None:
-            self.h_float[0] = torch.as_tensor(list(temperatures), dtype=torch.float32)
-            self.h_float[1] = torch.as_tensor(list(uniforms), dtype=torch.float32)
-            self.d_float.copy_(self.h_float, non_blocking=True)
-        for gi, h in self.h_tables.items():
-            h.copy_(torch.from_numpy(cache.block_table(gi, rids)))
-            self.batch.block_tables[gi].copy_(h, non_blocking=True)
+            st.tokens.copy_(torch.as_tensor(list(tokens), dtype=torch.int32))
+            b.token_ids.copy_(st.tokens, non_blocking=True)
+            sent += 4 * n
+        if temperatures is not None and any(t > 0.0 for t in temperatures):
+            st.floats[0] = torch.as_tensor(list(temperatures), dtype=torch.float32)
+            st.floats[1] = torch.as_tensor(list(uniforms), dtype=torch.float32)
+            self.temperature.copy_(st.floats[0], non_blocking=True)
+            self.uniform.copy_(st.floats[1], non_blocking=True)
+            sent += 8 * n
+            self._sampling = True
+        elif self._sampling:
+            self.temperature.zero_()
+            self._sampling = False
+        for gi, h in st.tables.items():
+            table = cache.block_table(gi, rids)
+            last = self._tables.get(gi)
+            if last is None or not np.array_equal(last, table):
+                h.copy_(torch.from_numpy(table))
+                b.block_tables[gi].copy_(h, non_blocking=True)
+                self._tables[gi] = table
+                sent += table.size * 4
+        if sent:
+            st.event = torch.cuda.Event()
+            st.event.record()
+        self.h2d_bytes = sent
         if self.graph is None:
             self._capture()
         self.graph.replay()
         ops.count_launches(self.launches)
-        cache.commit([(r, cache.length(r) + 1) for r in rids])
+        cache.commit([(r, p + 1) for r, p in zip(rids, positions)])
+        self._positions = [p + 1 for p in positions]
         if read_back:
             self.h_out.copy_(self.out_tokens, non_blocking=True)
             torch.cuda.current_stream().synchronize()

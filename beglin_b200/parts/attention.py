@@ -64,7 +64,8 @@ class GQAAttention:
         self.position = shared_position(spec.position, ctx)
         scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(float(self.hd))
         self.scale = float(np.float32(scale))
-        self.bq, self.tile = ops.attention_plan(self.nh // self.nkv, self.hd)
+        self.plans = {d: ops.attention_plan(self.nh // self.nkv, self.hd, ctx.cache_dtype, d, ctx.attention)
+                      for d in (False, True)}
         self.window = int(spec.window) if spec.window else 0
 
     def forward(self, h: torch.Tensor, batch, cache: PagedKVView) -> torch.Tensor:
@@ -75,11 +76,12 @@ class GQAAttention:
                            cache.pool if self.spec.own_kv else None, cache.page_size, self.ctx.status)
         split = self.ctx.kv_split
         n_splits = batch.max_position // split + 1
-        qblk, n_qblk = batch.query_blocks(self.bq)
+        kernel, bq, tile = self.plans[bool(getattr(batch, "decode_only", False))]
+        qblk, n_qblk = batch.query_blocks(bq)
         part_o = torch.empty((T * self.nh * n_splits, self.hd), dtype=torch.float32, device=h.device)
         part_ml = torch.empty((T * self.nh * n_splits, 2), dtype=torch.float32, device=h.device)
         out = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=h.device)
         ops.attention(qkv, qkv.stride(0), cache.pool, cache.block_table, batch.positions, qblk, n_qblk, part_o,
-                      part_ml, n_splits, n_splits, T, self.nh, self.nkv, self.hd, self.window, split, self.tile,
-                      self.bq, self.scale, out, self.ctx.status)
+                      part_ml, n_splits, n_splits, T, self.nh, self.nkv, self.hd, self.window, split, tile,
+                      bq, self.scale, out, self.ctx.status, kernel)
         return self.o_proj(out)

@@ -134,9 +134,11 @@ def time_decode(eng, batch, context, steps, warmup, seed, e2e):
     before = ops.launch_count()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
+    h2d = 0
     if e2e:
         for _ in range(steps):
             toks = eng.decode(rids, toks, read_back=True)
+            h2d += eng.decode_graph(batch).h2d_bytes
     else:
         for _ in range(steps):
             eng.decode(rids, None, read_back=False)
@@ -147,7 +149,7 @@ def time_decode(eng, batch, context, steps, warmup, seed, e2e):
     ops.raise_on_status(eng.ctx.status)
     for r in rids:
         eng.release(r)
-    return ms, launches
+    return ms, launches, h2d / steps
 
 
 def time_prefill(eng, T, reps, seed):
@@ -204,9 +206,9 @@ def main():
 
     clocks = ClockSampler()
     clocks.start()
-    ms, launches = time_decode(eng, args.batch, args.context, args.steps, args.warmup, seed=1, e2e=False)
+    ms, launches, _ = time_decode(eng, args.batch, args.context, args.steps, args.warmup, seed=1, e2e=False)
     clock_rec = clocks.stop()
-    ms_e2e, _ = time_decode(eng, args.batch, args.context, args.steps, args.warmup, seed=1, e2e=True)
+    ms_e2e, _, h2d = time_decode(eng, args.batch, args.context, args.steps, args.warmup, seed=1, e2e=True)
 
     value = args.batch * 1000.0 / ms
     ctx_mid = args.context - 1 - args.steps / 2.0
@@ -225,7 +227,7 @@ def main():
                    "l2": "inputs larger than L2 (weights and cache read once per step)",
                    "peaks": pk["source"]},
         "e2e": {"value": round(args.batch * 1000.0 / ms_e2e, 1), "unit": "tok/s",
-                "h2d_bytes_per_step": int(args.batch * 4 * 3 + args.batch * eng.cache.max_pages * 4),
+                "h2d_bytes_per_step": round(h2d, 1),
                 "d2h_bytes_per_step": int(args.batch * 4)},
         "gpu_launches": int(launches),
         "clocks": clock_rec,
@@ -235,7 +237,7 @@ def main():
     if not args.no_points:
         points = {}
         for b in (1, 64):
-            m, _ = time_decode(eng, b, args.context, min(args.steps, 32), args.warmup, seed=2, e2e=False)
+            m, _, _ = time_decode(eng, b, args.context, min(args.steps, 32), args.warmup, seed=2, e2e=False)
             points[f"decode_b{b}"] = round(b * 1000.0 / m, 1)
         out["points"] = points
         T = 2048

@@ -38,7 +38,16 @@ TINY_C = {
     "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                      "original_max_position_embeddings": 64},
 }
-TINY = {"A": (TINY_A, dict(std=0.02, bias_std=0.02), 8),
+# Head size 64 with three query heads per kv head: in bfloat16 this one runs the tensor-core attention.
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 192, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 176, "vocab_size": 200, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 1024,
+    "use_sliding_window": True, "sliding_window": 100, "max_window_layers": 1,
+}
+TINY = {"D": (TINY_D, dict(std=0.05, bias_std=0.05), 16),
+        "A": (TINY_A, dict(std=0.02, bias_std=0.02), 8),
         "B": (TINY_B, dict(std=0.02, bias_std=0.05), 16),
         "C": (TINY_C, dict(std=0.05, bias_std=0.05), 16)}     # name -> (config, init, page size)
 

@@ -165,19 +165,21 @@ def test_rope_table_and_kv_append(ops, interleaved, dtype):
         ops.raise_on_status(status)
 
 
-def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64):
+def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64, prefer="generic", decode_only=False):
     """Three requests in one step: a long prompt portion on top of earlier context, a decoded token
     far into a long context, and a fresh short prompt.  Pages are handed out in shuffled order and
     everything not held is poison."""
     torch.manual_seed(seed)
     group = nh // nkv
     ctx = [(37, 21), (150, 1), (0, 5)]               # (positions already in the cache, new rows)
+    if decode_only:
+        ctx = [(37, 1), (150, 1), (0, 1), (63, 1), (64, 1), (127, 1), (200, 1)]
     total = [c + n for c, n in ctx]
     n_pages_each = [-(-t // page) for t in total]
     n_pages = sum(n_pages_each) + 5
     perm = torch.randperm(n_pages).tolist()
     max_pages = max(n_pages_each) + 2
-    bt = torch.full((3, max_pages), -1, dtype=torch.int32)
+    bt = torch.full((len(ctx), max_pages), -1, dtype=torch.int32)
     pool = torch.full((n_pages, 2, nkv, page, hd), float("nan"), dtype=dtype)
     ks, vs, qs = [], [], []
     it = iter(perm)
@@ -195,12 +197,13 @@ def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64):
     rows = sum(n for _, n in ctx)
     q = (torch.randn(rows, nh, hd) * 0.7).to(dtype)
     # make one far key stand out for the decoded token: its score dominates unless it is missed
-    far = 3
-    q[21, :, :] = 0; q[21, :, 0] = 8.0
+    far, far_row = 3, (1 if decode_only else 21)
+    q[far_row, :, :] = 0; q[far_row, :, 0] = 8.0
     ks[1][far, :, 0] = 8.0
     pool[int(bt[1, far // page]), 0, :, far % page, 0] = 8.0
     positions, row_req, qblk = [], [], []
-    bq, tile = ops.attention_plan(group, hd)
+    kernel, bq, tile = ops.attention_plan(group, hd, dtype, decode_only, prefer)
+    assert kernel == {"generic": "generic", "mma": "mma_keys" if decode_only else "mma_rows"}[prefer]
     r0 = 0
     for r, (c, n) in enumerate(ctx):
         positions += list(range(c, c + n)); row_req += [r] * n
@@ -217,7 +220,7 @@ def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64):
     qd = q.reshape(rows, nh * hd).to(DEV).contiguous()
     scale = 1.0 / math.sqrt(hd)
     ops.attention(qd, qd.stride(0), pool.to(DEV), bt.to(DEV), positions_t, qblk_t, len(qblk), part_o, part_ml,
-                  n_splits, n_splits, rows, nh, nkv, hd, window or 0, split, tile, bq, scale, out, status)
+                  n_splits, n_splits, rows, nh, nkv, hd, window or 0, split, tile, bq, scale, out, status, kernel)
     ops.raise_on_status(status)
     # reference: every request's rows against its whole key/value sequence
     want = torch.empty(rows, nh * hd, dtype=torch.float64)
@@ -255,9 +258,25 @@ def test_attention_bfloat16(ops, nh, nkv, hd, page):
     assert (got - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(12, 2, 128, 16, None), (4, 4, 64, 8, None), (14, 2, 64, 32, 40),
+                                                   (16, 1, 128, 16, None), (12, 2, 128, 16, 100), (3, 1, 128, 4, None)])
+@pytest.mark.parametrize("decode_only", [False, True])
+def test_attention_tensor_core_kernel(ops, nh, nkv, hd, page, window, decode_only):
+    got, want = _attention_case(ops, nh, nkv, hd, page, torch.bfloat16, window, seed=5, prefer="mma",
+                                decode_only=decode_only)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
+
+
 def test_attention_refuses_sizes_it_does_not_take(ops):
     with pytest.raises(ops.KernelError, match="head_dim"):
         ops.attention_plan(2, 272)
+    with pytest.raises(ops.KernelError, match="tensor-core"):
+        ops.attention_plan(2, 48, torch.bfloat16, False, "mma")
+    assert ops.attention_plan(2, 48, torch.bfloat16)[0] == "generic"
+    assert ops.attention_plan(6, 128, torch.bfloat16, True)[0] == "mma_keys"
+    assert ops.attention_plan(32, 128, torch.bfloat16, True)[0] == "generic"      # more than 16 heads per kv head
+    assert ops.attention_plan(6, 128, torch.float32)[0] == "generic"
 
 
 def test_sample_greedy_takes_the_first_maximum(ops):

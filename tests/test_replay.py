@@ -17,7 +17,8 @@ from helpers import TINY, TOL_BF16, TOL_F32, make_model, plain_logits, rel_err, 
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [70, 45, 100, 33, 120, 64], "B": [130, 33, 250, 97, 64, 180], "C": [300, 41, 150, 90, 270, 65]}
+LENGTHS = {"A": [70, 45, 100, 33, 120, 64], "B": [130, 33, 250, 97, 64, 180], "C": [300, 41, 150, 90, 270, 65],
+           "D": [300, 41, 150, 90, 270, 65]}
 
 
 def requests_for(name):
@@ -48,7 +49,7 @@ def check_against_plain(got, folder, reqs, tol):
     return worst
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_four_ways_of_cutting(model_root, name, dtype):
     stored = torch.float32 if dtype == "float32" else torch.bfloat16
@@ -60,7 +61,7 @@ def test_four_ways_of_cutting(model_root, name, dtype):
     results = {}
     for way, steps, max_tokens in (("whole", rl.whole(reqs), 320), ("tail", rl.last_one_by_one(reqs), 320),
                                    ("portions", rl.portions(reqs), 320), ("mixed", mixed_steps, peak)):
-        eng = engine_for(folder, dtype, max_tokens, page, kv_split=64 if name != "C" else 256)
+        eng = engine_for(folder, dtype, max_tokens, page, kv_split=64 if name in "AB" else 256)
         got = rl.run_in_process(eng, steps)
         eng.cache.check()
         assert eng.cache.free_pages() == eng.cache.num_pages and not eng.cache.live()
