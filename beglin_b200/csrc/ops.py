@@ -39,6 +39,8 @@ _SIGNATURES = {
                                  _c_int, _c_float, _c_void_p, _c_void_p],
     "bg_gemm_f32_nt": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_void_p],
+    "bg_gemm_bf16_tn": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
+                        _c_int, _c_int, _c_void_p, _c_void_p],
     "bg_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
 }
 
@@ -306,6 +308,34 @@ def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
         raise KernelError("gemm_f32_nt: bias must have one value per output feature")
     _check(lib().bg_gemm_f32_nt(_p(a), a.stride(0), _p(w), w.stride(0), _p(bias), _p(out), out.stride(0), M, N, K,
                                 1 if accumulate else 0, _stream()), "gemm_f32_nt")
+
+
+def gemm_bf16_tn(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                 splits: int = 1, status: Optional[torch.Tensor] = None) -> None:
+    """out = x[T, K] @ w[N, K]^T (+ bias) on the tcgen05 tensor cores, bfloat16 in, float accumulation.
+    `out` is [T, N] (float32 or bfloat16) for splits == 1, or float32 [splits, T, N] partial sums over
+    ranges of K, which the consumer adds up in index order (the bias is in partial 0)."""
+    _cuda(x, w, bias, out, status)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_bf16_tn takes bfloat16 operands")
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError(f"gemm_bf16_tn: shapes x{tuple(x.shape)} w{tuple(w.shape)} do not fit")
+    if K % 8 or x.stride(0) % 8 or w.stride(0) % 8:
+        raise KernelError("gemm_bf16_tn: the inner size and the row strides must be multiples of 8 (TMA wants "
+                          "16-byte row strides)")
+    want = (T, N) if splits == 1 else (splits, T, N)
+    if tuple(out.shape) != want or not out.is_contiguous():
+        raise KernelError(f"gemm_bf16_tn: out is {tuple(out.shape)}, expected contiguous {want}")
+    if splits > 1 and out.dtype != torch.float32:
+        raise KernelError("gemm_bf16_tn: partial sums are float32")
+    if splits > (K + 63) // 64:
+        raise KernelError("gemm_bf16_tn: more splits than 64-wide blocks of K")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N or not bias.is_contiguous()):
+        raise KernelError("gemm_bf16_tn: bias must be float32 with one value per output feature")
+    _check(lib().bg_gemm_bf16_tn(_p(w), N, K, w.stride(0), _p(x), T, x.stride(0), _p(bias), _p(out), _dt(out), N,
+                                 splits, _p(status), _stream()), "gemm_bf16_tn")
 
 
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],

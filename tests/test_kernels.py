@@ -322,3 +322,33 @@ def test_sample_temperature_inverts_the_cumulative_distribution(ops):
         cdf = plain.temperature_cdf(big[r].cpu(), 1.0)
         i = int(o2[r])
         assert (0.0 if i == 0 else float(cdf[i - 1])) - 1e-4 <= float(u2[r]) <= float(cdf[i]) + 1e-4
+
+
+@pytest.mark.parametrize("T,N,K,splits", [(1, 128, 64, 1), (8, 256, 1536, 1), (8, 2048, 1536, 8), (5, 200, 136, 2),
+                                          (16, 1536, 8960, 14), (17, 384, 192, 1), (64, 300, 520, 3),
+                                          (100, 256, 256, 1), (300, 520, 328, 1), (2048, 1536, 1536, 1)])
+def test_gemm_tcgen05(ops, T, N, K, splits):
+    """The tensor-core product against float64, at sizes with ragged edges in all three dimensions."""
+    x = rnd(T, K, dtype=torch.bfloat16, seed=21)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=22, scale=0.1)
+    b = rnd(N, seed=23)
+    want = x.double() @ w.double().t() + b.double()
+    status = ops.new_status(DEV)
+    if splits == 1:
+        for dt, tol in ((torch.float32, 2e-5), (torch.bfloat16, 8e-3)):
+            out = torch.full((T, N), float("nan"), dtype=dt, device=DEV)
+            ops.gemm_bf16_tn(x, w, b, out, 1, status)
+            ops.raise_on_status(status)
+            assert (out.double() - want).abs().max() <= tol * want.abs().max(), dt
+    else:
+        out = torch.full((splits, T, N), float("nan"), device=DEV)
+        ops.gemm_bf16_tn(x, w, b, out, splits, status)
+        ops.raise_on_status(status)
+        assert (out.double().sum(0) - want).abs().max() <= 2e-5 * want.abs().max()
+    # a row's result does not depend on the rows around it
+    if T > 1 and splits == 1:
+        one = torch.empty((1, N), device=DEV)
+        full = torch.empty((T, N), device=DEV)
+        ops.gemm_bf16_tn(x, w, b, full, 1, status)
+        ops.gemm_bf16_tn(x[T // 2:T // 2 + 1], w, b, one, 1, status)
+        assert torch.equal(one[0], full[T // 2])
