@@ -188,7 +188,9 @@ attention_partial_kernel(AttnParams p) {
 }
 
 // out[t, h, :] = sum_s o_s * exp(m_s - m) / sum_s l_s * exp(m_s - m), over the splits the row sees,
-// in split order.  One warp per (row, head).
+// in split order.  One warp per (row, head): the lanes first take one split each to find the maximum
+// and the weights (so these loads are in flight together), then every lane sums its output features
+// over the splits.
 template <typename TO>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
@@ -202,20 +204,33 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
     const int s_lo = lo / split, s_hi = pos / split;
     const size_t prow = (size_t)w * max_splits;
     float m = -INFINITY;
-    for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, part_ml[(prow + s) * 2]);
-    float l = 0.0f;
+    for (int s = s_lo + lane; s <= s_hi; s += 32) m = fmaxf(m, part_ml[(prow + s) * 2]);
+    m = warp_max(m);
     float acc[ATT_MAX_DPL];
 #pragma unroll
     for (int i = 0; i < ATT_MAX_DPL; ++i) acc[i] = 0.0f;
-    for (int s = s_lo; s <= s_hi; ++s) {
-        const float ms = part_ml[(prow + s) * 2];
-        const float f = (ms == -INFINITY) ? 0.0f : expf(ms - m);
-        l = fmaf(part_ml[(prow + s) * 2 + 1], f, l);
-        const float* po = part_o + (prow + s) * hd;
+    float l = 0.0f;
+    for (int s0 = s_lo; s0 <= s_hi; s0 += 32) {
+        // this lane's split of the group of 32: its weight and its share of the sum
+        const int mine = s0 + lane;
+        float f_mine = 0.0f, l_mine = 0.0f;
+        if (mine <= s_hi) {
+            const float ms = part_ml[(prow + mine) * 2];
+            f_mine = (ms == -INFINITY) ? 0.0f : expf(ms - m);
+            l_mine = part_ml[(prow + mine) * 2 + 1];
+        }
+        const int n = min(32, s_hi - s0 + 1);
+#pragma unroll 4
+        for (int j = 0; j < n; ++j) {
+            const float f = __shfl_sync(0xffffffffu, f_mine, j);
+            const float lj = __shfl_sync(0xffffffffu, l_mine, j);
+            l = fmaf(lj, f, l);
+            const float* po = part_o + (prow + s0 + j) * hd;
 #pragma unroll
-        for (int i = 0; i < ATT_MAX_DPL; ++i) {
-            int d = i * 32 + lane;
-            if (d < hd) acc[i] = fmaf(po[d], f, acc[i]);
+            for (int i = 0; i < ATT_MAX_DPL; ++i) {
+                int d = i * 32 + lane;
+                if (d < hd) acc[i] = fmaf(po[d], f, acc[i]);
+            }
         }
     }
     const float inv = 1.0f / l;

@@ -2,6 +2,8 @@
 // SwiGLU, the rotary table of a step, and the rotation of q and k fused with the append of k and v
 // to the paged cache.  Statistics, angles and the residual are float; inputs and outputs may be
 // float or bfloat16.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace bg {
@@ -26,11 +28,12 @@ __global__ void embed_gather_kernel(const TT* __restrict__ table, const int* __r
 
 // ---------------------------------------------------------------------------------------------
 // For output row r (source row s = rows ? rows[r] : r):
-//   v = x[s] (+ delta[s]);  if update: x[s] = v;  out[r] = v * rsqrt(mean(v^2) + eps) * w
+//   v = x[s] + sum_p delta[p][s];  if update: x[s] = v;  out[r] = v * rsqrt(mean(v^2) + eps) * w
 // (qwen_infer.c:711-714; the add is the residual sum of :1552 and :1577 moved in front of the norm
-// that follows it).  One block per row; the row is held in shared memory between the two passes.
+// that follows it).  delta may be the partial sums of a split-K product, [parts][T][d], added in
+// index order.  One block per row; the row is held in shared memory between the two passes.
 template <typename TD, typename TW, typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int parts, size_t part_stride,
                                    const TW* __restrict__ w, float eps, TO* __restrict__ out,
                                    const int* __restrict__ rows, int d, int update) {
     extern __shared__ float row_buf[];
@@ -41,7 +44,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     float ss = 0.0f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = xr[i];
-        if (delta) v += to_float(delta[(size_t)s * d + i]);
+        if (delta) {
+            const TD* dp = delta + (size_t)s * d + i;
+            for (int p = 0; p < parts; ++p) v += to_float(dp[p * part_stride]);
+        }
         row_buf[i] = v;
         if (update) xr[i] = v;
         ss += v * v;
@@ -53,6 +59,51 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
         o[i] = from_float<TO>(row_buf[i] * inv * to_float(w[i]));
 }
 
+// The same for a width that is a multiple of 4 with float addends: 16-byte loads and stores, so a
+// row of a few thousand features is one round trip per thread.
+template <typename TW, typename TO>
+__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ x, const float* __restrict__ delta, int parts,
+                                        size_t part_stride, const TW* __restrict__ w, float eps, TO* __restrict__ out,
+                                        const int* __restrict__ rows, int d, int update) {
+    extern __shared__ float row_buf[];
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)s * d);
+    float4* rb = reinterpret_cast<float4*>(row_buf);
+    const int d4 = d >> 2;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        float4 v = xr[i];
+        if (delta) {
+            const float4* dp = reinterpret_cast<const float4*>(delta + (size_t)s * d) + i;
+            const size_t ps4 = part_stride >> 2;
+#pragma unroll 4
+            for (int p = 0; p < parts; ++p) {
+                float4 a = dp[p * ps4];
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            }
+        }
+        rb[i] = v;
+        if (update) xr[i] = v;
+        ss += v.x * v.x;
+        ss += v.y * v.y;
+        ss += v.z * v.z;
+        ss += v.w * v.w;
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    TO* o = out + (size_t)r * d;
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        float4 v = rb[i];
+        float w0 = to_float(w[4 * i]), w1 = to_float(w[4 * i + 1]), w2 = to_float(w[4 * i + 2]), w3 = to_float(w[4 * i + 3]);
+        o[4 * i + 0] = from_float<TO>(v.x * inv * w0);
+        o[4 * i + 1] = from_float<TO>(v.y * inv * w1);
+        o[4 * i + 2] = from_float<TO>(v.z * inv * w2);
+        o[4 * i + 3] = from_float<TO>(v.w * inv * w3);
+    }
+}
+
 // x[t] += delta[t] without a norm (the last residual add when no norm follows).
 template <typename TD>
 __global__ void add_residual_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n) {
@@ -61,17 +112,24 @@ __global__ void add_residual_kernel(float* __restrict__ x, const TD* __restrict_
 }
 
 // ---------------------------------------------------------------------------------------------
-// out[t, i] = silu(gu[t, i]) * gu[t, im + i]   with silu(g) = g / (1 + exp(-g))  (qwen_infer.c:727-733)
-template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int rows, int im) {
+// out[t, i] = silu(g) * u with g = sum_p gu[p][t, i], u = sum_p gu[p][t, im + i] and
+// silu(g) = g / (1 + exp(-g))  (qwen_infer.c:727-733).  gu may be the partial sums of a split-K
+// product, [parts][rows][2 im].
+template <typename TI, typename TO>
+__global__ void swiglu_kernel(const TI* __restrict__ gu, int parts, size_t part_stride, TO* __restrict__ out,
+                              int rows, int im) {
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t total = (size_t)rows * im;
     if (idx >= total) return;
     size_t t = idx / im;
     int i = (int)(idx - t * im);
-    float g = to_float(gu[t * 2 * (size_t)im + i]);
-    float u = to_float(gu[t * 2 * (size_t)im + im + i]);
-    out[idx] = from_float<T>((g / (1.0f + expf(-g))) * u);
+    const TI* gp = gu + t * 2 * (size_t)im + i;
+    float g = 0.0f, u = 0.0f;
+    for (int p = 0; p < parts; ++p) {
+        g += to_float(gp[p * part_stride]);
+        u += to_float(gp[p * part_stride + im]);
+    }
+    out[idx] = from_float<TO>((g / (1.0f + expf(-g))) * u);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -89,33 +147,48 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
 }
 
 // ---------------------------------------------------------------------------------------------
-// For token t of request row_req[t] at position positions[t]:
-//   rotate every q head in place, and (when kv_pool is given) rotate every k head and store it
-//   together with v into the page block_table[req][pos / page_size] at slot pos % page_size.
-// Pairs are (i, i + half) for split-half and (2i, 2i + 1) for interleaved pairing
-// (qwen_infer.c:782-790); features from rot on are copied.  qkv rows are [q | k | v].
-// The pool of one layer is [num_pages][2][nkv][page_size][hd].
-template <typename TA, typename TC>
-__global__ void rope_kv_append_kernel(TA* __restrict__ qkv, int row_stride, const float2* __restrict__ cos_sin,
+// For token t of request row_req[t] at position positions[t], with the row [q | k | v] =
+// sum_p src[p][t]:  rotate every q head into q_out, and (when kv_pool is given) rotate every k head
+// and store it together with v into the page block_table[req][pos / page_size] at slot
+// pos % page_size.  Pairs are (i, i + half) for split-half and (2i, 2i + 1) for interleaved pairing
+// (qwen_infer.c:782-790); features from rot on are copied.  src may be the partial sums of a
+// split-K product.  The pool of one layer is [num_pages][2][nkv][page_size][hd].
+template <typename TS>
+__device__ __forceinline__ float summed(const TS* p, int parts, size_t part_stride) {
+    float v = 0.0f;
+    for (int i = 0; i < parts; ++i) v += to_float(p[i * part_stride]);
+    return v;
+}
+
+template <typename TS>
+__device__ __forceinline__ float rotated(const TS* head, int parts, size_t part_stride, int i, int rot, int half,
+                                         int interleaved, const float2* cs) {
+    float me = summed(head + i, parts, part_stride);
+    if (i >= rot) return me;
+    int pi, partner;
+    bool first;
+    if (interleaved) { pi = i >> 1; first = (i & 1) == 0; partner = first ? i + 1 : i - 1; }
+    else { first = i < half; pi = first ? i : i - half; partner = first ? i + half : i - half; }
+    float other = summed(head + partner, parts, part_stride);
+    float2 f = cs[pi];
+    return first ? (me * f.x - other * f.y) : (me * f.x + other * f.y);
+}
+
+template <typename TS, typename TQ, typename TC>
+__global__ void rope_kv_append_kernel(const TS* __restrict__ src, int src_stride, int parts, size_t part_stride,
+                                      TQ* __restrict__ q_out, int q_stride, const float2* __restrict__ cos_sin,
                                       const int* __restrict__ positions, const int* __restrict__ row_req,
                                       const int* __restrict__ block_table, int max_pages,
                                       TC* __restrict__ kv_pool, int num_pages, int page_size,
                                       int nh, int nkv, int hd, int rot, int interleaved, unsigned* status) {
     const int t = blockIdx.x;
     const int half = rot >> 1;
-    TA* row = qkv + (size_t)t * row_stride;
+    const TS* row = src + (size_t)t * src_stride;
     const float2* cs = cos_sin ? cos_sin + (size_t)t * half : nullptr;
-    // q heads, in place
-    if (half > 0) {
-        for (int idx = threadIdx.x; idx < nh * half; idx += blockDim.x) {
-            int h = idx / half, i = idx - h * half;
-            int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
-            TA* v = row + (size_t)h * hd;
-            float a = to_float(v[ia]), b = to_float(v[ib]);
-            float2 f = cs[i];
-            v[ia] = from_float<TA>(a * f.x - b * f.y);
-            v[ib] = from_float<TA>(b * f.x + a * f.y);
-        }
+    TQ* qo = q_out + (size_t)t * q_stride;
+    for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
+        int h = idx / hd, i = idx - h * hd;
+        qo[idx] = from_float<TQ>(rotated(row + (size_t)h * hd, parts, part_stride, i, rot, half, interleaved, cs));
     }
     if (!kv_pool) return;
     const int pos = positions[t];
@@ -126,27 +199,15 @@ __global__ void rope_kv_append_kernel(TA* __restrict__ qkv, int row_stride, cons
         return;
     }
     const int slot = pos % page_size;
-    const TA* k = row + (size_t)nh * hd;
-    const TA* vv = k + (size_t)nkv * hd;
+    const TS* k = row + (size_t)nh * hd;
+    const TS* vv = k + (size_t)nkv * hd;
     TC* kdst = kv_pool + ((size_t)page * 2 + 0) * nkv * page_size * hd;
     TC* vdst = kv_pool + ((size_t)page * 2 + 1) * nkv * page_size * hd;
     for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
         int h = idx / hd, i = idx - h * hd;
         size_t dst = ((size_t)h * page_size + slot) * hd + i;
-        vdst[dst] = from_float<TC>(to_float(vv[idx]));
-        float val;
-        if (i < rot) {
-            int pi, partner;
-            bool first;
-            if (interleaved) { pi = i >> 1; first = (i & 1) == 0; partner = first ? i + 1 : i - 1; }
-            else { first = i < half; pi = first ? i : i - half; partner = first ? i + half : i - half; }
-            float me = to_float(k[(size_t)h * hd + i]), other = to_float(k[(size_t)h * hd + partner]);
-            float2 f = cs[pi];
-            val = first ? (me * f.x - other * f.y) : (me * f.x + other * f.y);
-        } else {
-            val = to_float(k[idx]);
-        }
-        kdst[dst] = from_float<TC>(val);
+        vdst[dst] = from_float<TC>(summed(vv + idx, parts, part_stride));
+        kdst[dst] = from_float<TC>(rotated(k + (size_t)h * hd, parts, part_stride, i, rot, half, interleaved, cs));
     }
 }
 
@@ -163,34 +224,49 @@ extern "C" int bg_embed_gather(const void* table, int table_dtype, const int* id
     return BG_OK;
 }
 
-template <typename TD, typename TW>
-static int add_rmsnorm_out(float* x, const void* delta, const void* w, float eps, void* out, int out_dtype,
-                           const int* rows, int n_rows, int d, int update, cudaStream_t stream) {
+template <typename TD, typename TW, typename TO>
+static int add_rmsnorm_launch(float* x, const void* delta, int parts, size_t part_stride, const void* w, float eps,
+                              void* out, const int* rows, int n_rows, int d, int update, cudaStream_t stream) {
     size_t smem = (size_t)d * sizeof(float);
     if (smem > 200 * 1024) return BG_ERR_SHAPE;
-    if (out_dtype == BG_DTYPE_F32) {
-        auto kern = add_rmsnorm_kernel<TD, TW, float>;
+    const bool vec = std::is_same<TD, float>::value && (d % 4 == 0) && (part_stride % 4 == 0) &&
+                     ((uintptr_t)x % 16 == 0) && ((uintptr_t)delta % 16 == 0);
+    if (vec) {
+        auto kern = add_rmsnorm_vec4_kernel<TW, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<n_rows, 256, smem, stream>>>(x, (const TD*)delta, (const TW*)w, eps, (float*)out, rows, d, update);
-    } else if (out_dtype == BG_DTYPE_BF16) {
-        auto kern = add_rmsnorm_kernel<TD, TW, __nv_bfloat16>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<n_rows, 256, smem, stream>>>(x, (const TD*)delta, (const TW*)w, eps, (__nv_bfloat16*)out, rows, d, update);
+        int threads = d / 4 >= 512 ? 512 : (d / 4 >= 256 ? 256 : 128);
+        kern<<<n_rows, threads, smem, stream>>>(x, (const float*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out,
+                                                rows, d, update);
     } else {
-        return BG_ERR_DTYPE;
+        auto kern = add_rmsnorm_kernel<TD, TW, TO>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kern<<<n_rows, 256, smem, stream>>>(x, (const TD*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out, rows,
+                                            d, update);
     }
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
 
-// delta may be null (then delta_dtype is ignored); rows may be null (then row r reads source row r).
-extern "C" int bg_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w, int w_dtype,
-                              float eps, void* out, int out_dtype, const int* rows, int n_rows, int d,
-                              int update, cudaStream_t stream) {
+template <typename TD, typename TW>
+static int add_rmsnorm_out(float* x, const void* delta, int parts, size_t part_stride, const void* w, float eps, void* out,
+                           int out_dtype, const int* rows, int n_rows, int d, int update, cudaStream_t stream) {
+    if (out_dtype == BG_DTYPE_F32)
+        return add_rmsnorm_launch<TD, TW, float>(x, delta, parts, part_stride, w, eps, out, rows, n_rows, d, update, stream);
+    if (out_dtype == BG_DTYPE_BF16)
+        return add_rmsnorm_launch<TD, TW, __nv_bfloat16>(x, delta, parts, part_stride, w, eps, out, rows, n_rows, d, update, stream);
+    return BG_ERR_DTYPE;
+}
+
+// delta may be null (then delta_dtype is ignored) or [parts][T][d] with part_stride elements between
+// parts; rows may be null (then row r reads source row r).
+extern "C" int bg_add_rmsnorm(float* x, const void* delta, int delta_dtype, int parts, long long part_stride,
+                              const void* w, int w_dtype, float eps, void* out, int out_dtype, const int* rows,
+                              int n_rows, int d, int update, cudaStream_t stream) {
     if (n_rows <= 0) return BG_OK;
-    if (!delta) delta_dtype = BG_DTYPE_F32;
+    if (!delta) { delta_dtype = BG_DTYPE_F32; parts = 0; }
     BG_DISPATCH_DTYPE(delta_dtype, TD, BG_DISPATCH_DTYPE(w_dtype, TW,
-        return (add_rmsnorm_out<TD, TW>(x, delta, w, eps, out, out_dtype, rows, n_rows, d, update, stream))));
+        return (add_rmsnorm_out<TD, TW>(x, delta, parts, (size_t)part_stride, w, eps, out, out_dtype, rows, n_rows, d,
+                                        update, stream))));
     return BG_OK;
 }
 
@@ -202,12 +278,22 @@ extern "C" int bg_add_residual(float* x, const void* delta, int delta_dtype, lon
     return BG_OK;
 }
 
-extern "C" int bg_swiglu(const void* gu, void* out, int dtype, int rows, int im, cudaStream_t stream) {
-    if (rows <= 0) return BG_OK;
+template <typename TI>
+static int swiglu_in(const void* gu, int parts, size_t part_stride, void* out, int out_dtype, int rows, int im,
+                     cudaStream_t stream) {
     size_t total = (size_t)rows * im;
     unsigned blocks = (unsigned)((total + 255) / 256);
-    BG_DISPATCH_DTYPE(dtype, T, swiglu_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gu, (T*)out, rows, im));
+    BG_DISPATCH_DTYPE(out_dtype, TO, swiglu_kernel<TI, TO><<<blocks, 256, 0, stream>>>(
+        (const TI*)gu, parts, part_stride, (TO*)out, rows, im));
     BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_swiglu(const void* gu, int in_dtype, int parts, long long part_stride, void* out, int out_dtype,
+                         int rows, int im, cudaStream_t stream) {
+    if (rows <= 0) return BG_OK;
+    if (parts < 1) return BG_ERR_SHAPE;
+    BG_DISPATCH_DTYPE(in_dtype, TI, return (swiglu_in<TI>(gu, parts, (size_t)part_stride, out, out_dtype, rows, im, stream)));
     return BG_OK;
 }
 
@@ -220,28 +306,42 @@ extern "C" int bg_rope_table(const int* positions, const float* inv_freq, float*
     return BG_OK;
 }
 
-template <typename TA>
-static int rope_kv_cache(void* qkv, int row_stride, const float* cos_sin, const int* positions, const int* row_req,
-                         const int* block_table, int max_pages, void* kv_pool, int cache_dtype, int num_pages,
-                         int page_size, int T, int nh, int nkv, int hd, int rot, int interleaved, unsigned* status,
-                         cudaStream_t stream) {
-    BG_DISPATCH_DTYPE(cache_dtype, TC, rope_kv_append_kernel<TA, TC><<<T, 256, 0, stream>>>(
-        (TA*)qkv, row_stride, (const float2*)cos_sin, positions, row_req, block_table, max_pages,
-        (TC*)kv_pool, num_pages, page_size, nh, nkv, hd, rot, interleaved, status));
+template <typename TS, typename TQ>
+static int rope_kv_cache(const void* src, int src_stride, int parts, size_t part_stride, void* q_out, int q_stride,
+                         const float* cos_sin, const int* positions, const int* row_req, const int* block_table,
+                         int max_pages, void* kv_pool, int cache_dtype, int num_pages, int page_size, int T, int nh,
+                         int nkv, int hd, int rot, int interleaved, unsigned* status, cudaStream_t stream) {
+    BG_DISPATCH_DTYPE(cache_dtype, TC, rope_kv_append_kernel<TS, TQ, TC><<<T, 256, 0, stream>>>(
+        (const TS*)src, src_stride, parts, part_stride, (TQ*)q_out, q_stride, (const float2*)cos_sin, positions, row_req,
+        block_table, max_pages, (TC*)kv_pool, num_pages, page_size, nh, nkv, hd, rot, interleaved, status));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
 
-// kv_pool may be null: then only q is rotated (a mixer that reads another stage's cache).
-extern "C" int bg_rope_kv_append(void* qkv, int act_dtype, int row_stride, const float* cos_sin, const int* positions,
+template <typename TS>
+static int rope_kv_q(const void* src, int src_stride, int parts, size_t part_stride, void* q_out, int q_dtype, int q_stride,
+                     const float* cos_sin, const int* positions, const int* row_req, const int* block_table,
+                     int max_pages, void* kv_pool, int cache_dtype, int num_pages, int page_size, int T, int nh, int nkv,
+                     int hd, int rot, int interleaved, unsigned* status, cudaStream_t stream) {
+    BG_DISPATCH_DTYPE(q_dtype, TQ, return (rope_kv_cache<TS, TQ>(src, src_stride, parts, part_stride, q_out, q_stride,
+        cos_sin, positions, row_req, block_table, max_pages, kv_pool, cache_dtype, num_pages, page_size, T, nh, nkv, hd,
+        rot, interleaved, status, stream)));
+    return BG_OK;
+}
+
+// src rows are [q | k | v] (or only q when kv_pool is null: a mixer that reads another stage's
+// cache).  q_out must not alias src.
+extern "C" int bg_rope_kv_append(const void* src, int src_dtype, int src_stride, int parts, long long part_stride,
+                                 void* q_out, int q_dtype, int q_stride, const float* cos_sin, const int* positions,
                                  const int* row_req, const int* block_table, int max_pages, void* kv_pool,
                                  int cache_dtype, int num_pages, int page_size, int T, int nh, int nkv, int hd,
                                  int rot, int interleaved, unsigned* status, cudaStream_t stream) {
     if (T <= 0) return BG_OK;
-    if (rot < 0 || rot > hd || (rot & 1)) return BG_ERR_SHAPE;
+    if (rot < 0 || rot > hd || (rot & 1) || parts < 1) return BG_ERR_SHAPE;
     if (rot > 0 && !cos_sin) return BG_ERR_SHAPE;
     if (!kv_pool) cache_dtype = BG_DTYPE_F32;
-    BG_DISPATCH_DTYPE(act_dtype, TA, return (rope_kv_cache<TA>(qkv, row_stride, cos_sin, positions, row_req, block_table,
-        max_pages, kv_pool, cache_dtype, num_pages, page_size, T, nh, nkv, hd, rot, interleaved, status, stream)));
+    BG_DISPATCH_DTYPE(src_dtype, TS, return (rope_kv_q<TS>(src, src_stride, parts, (size_t)part_stride, q_out, q_dtype,
+        q_stride, cos_sin, positions, row_req, block_table, max_pages, kv_pool, cache_dtype, num_pages, page_size, T, nh,
+        nkv, hd, rot, interleaved, status, stream)));
     return BG_OK;
 }

@@ -321,9 +321,11 @@ extern "C" int bg_gemm_bf16_tn(const void* W, int n_out, int K, int ldw, const v
     int rc = make_map(&mx, X, T, K, ldx, bn);
     if (rc != BG_OK) return rc;
     switch (bn) {
-        case 16: return tc_launch<16, 8>(mw, mx, p, splits, stream);
-        case 32: return tc_launch<32, 8>(mw, mx, p, splits, stream);
-        case 64: return tc_launch<64, 8>(mw, mx, p, splits, stream);
+        // few tokens: the product is bound by the weight stream; four stages let three CTAs share an SM, so
+        // one CTA's start and epilogue overlap the others' loads
+        case 16: return tc_launch<16, 4>(mw, mx, p, splits, stream);
+        case 32: return tc_launch<32, 4>(mw, mx, p, splits, stream);
+        case 64: return tc_launch<64, 4>(mw, mx, p, splits, stream);
         case 128: return tc_launch<128, 6>(mw, mx, p, splits, stream);
         default: return tc_launch<256, 4>(mw, mx, p, splits, stream);
     }

@@ -20,13 +20,14 @@ _c_int, _c_float, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void
 
 _SIGNATURES = {
     "bg_embed_gather": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
-    "bg_add_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_void_p,
-                       _c_int, _c_int, _c_int, _c_void_p],
+    "bg_add_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_float, _c_void_p, _c_int,
+                       _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "bg_add_residual": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
-    "bg_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_swiglu": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "bg_rope_table": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
-    "bg_rope_kv_append": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
-                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "bg_rope_kv_append": [_c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
+                          _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                          _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "bg_attention_plan": [_c_int, _c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
     "bg_attention_partial": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int,
                              _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
@@ -41,7 +42,7 @@ _SIGNATURES = {
                        _c_int, _c_void_p],
     "bg_gemm_bf16_tn": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                         _c_int, _c_int, _c_void_p, _c_void_p],
-    "bg_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "bg_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
 }
 
 _lib = None
@@ -157,9 +158,20 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stat
            "embed_gather")
 
 
+def _parts(t: torch.Tensor, what: str):
+    """(number of partial sums, elements between them) of a product's result: [T, N], or
+    [parts, T, N] float32 from a split-K product."""
+    if t.dim() == 2:
+        return 1, 0
+    if t.dim() == 3 and t.is_contiguous():
+        return t.shape[0], t.shape[1] * t.shape[2]
+    raise KernelError(f"{what} must be [T, N] or contiguous [parts, T, N]")
+
+
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
                 rows: Optional[torch.Tensor] = None, update: bool = True) -> None:
-    """v = x[s] (+ delta[s]); x[s] = v when update; out[r] = rmsnorm(v) * weight, s = rows[r] or r."""
+    """v = x[s] (+ delta[s], or the sum over p of delta[p][s]); x[s] = v when update;
+    out[r] = rmsnorm(v) * weight, s = rows[r] or r."""
     _cuda(x, delta, weight, out, rows)
     d = x.shape[1]
     n = rows.numel() if rows is not None else x.shape[0]
@@ -167,13 +179,16 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
         raise KernelError("add_rmsnorm: x must be contiguous float32; out and weight contiguous")
     if tuple(out.shape) != (n, d) or weight.numel() != d:
         raise KernelError(f"add_rmsnorm: out is {tuple(out.shape)}, expected {(n, d)}; weight has {weight.numel()} of {d}")
-    if delta is not None and (tuple(delta.shape) != tuple(x.shape) or not delta.is_contiguous()):
-        raise KernelError("add_rmsnorm: delta must be contiguous and shaped like x")
+    parts, stride = 0, 0
+    if delta is not None:
+        parts, stride = _parts(delta, "add_rmsnorm: delta")
+        if tuple(delta.shape[-2:]) != tuple(x.shape) or not delta.is_contiguous():
+            raise KernelError("add_rmsnorm: delta must be contiguous and shaped like x")
     if rows is not None:
         _i32(rows, "rows")
-    _check(lib().bg_add_rmsnorm(_p(x), _p(delta), _dt(delta) if delta is not None else F32, _p(weight), _dt(weight),
-                                float(eps), _p(out), _dt(out), _p(rows), n, d, 1 if update else 0, _stream()),
-           "add_rmsnorm")
+    _check(lib().bg_add_rmsnorm(_p(x), _p(delta), _dt(delta) if delta is not None else F32, parts, stride, _p(weight),
+                                _dt(weight), float(eps), _p(out), _dt(out), _p(rows), n, d, 1 if update else 0,
+                                _stream()), "add_rmsnorm")
 
 
 def add_residual(x: torch.Tensor, delta: torch.Tensor) -> None:
@@ -184,15 +199,16 @@ def add_residual(x: torch.Tensor, delta: torch.Tensor) -> None:
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, im + i]."""
+    """out[t, i] = silu(g[t, i]) * g[t, im + i], g = gate_up or the sum of its partial sums."""
     _cuda(gate_up, out)
-    rows, two_im = gate_up.shape
+    parts, stride = _parts(gate_up, "swiglu: gate_up")
+    rows, two_im = gate_up.shape[-2:]
     im = two_im // 2
-    if two_im != 2 * im or tuple(out.shape) != (rows, im) or out.dtype != gate_up.dtype:
-        raise KernelError("swiglu: gate_up must be [rows, 2*im] and out [rows, im] of the same type")
+    if two_im != 2 * im or tuple(out.shape) != (rows, im):
+        raise KernelError("swiglu: gate_up must be [rows, 2*im] and out [rows, im]")
     if not gate_up.is_contiguous() or not out.is_contiguous():
         raise KernelError("swiglu: tensors must be contiguous")
-    _check(lib().bg_swiglu(_p(gate_up), _p(out), _dt(out), rows, im, _stream()), "swiglu")
+    _check(lib().bg_swiglu(_p(gate_up), _dt(gate_up), parts, stride, _p(out), _dt(out), rows, im, _stream()), "swiglu")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
@@ -206,18 +222,22 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tenso
     _check(lib().bg_rope_table(_p(positions), _p(inv_freq), _p(out), T, half, _stream()), "rope_table")
 
 
-def rope_kv_append(qkv: torch.Tensor, n_rows: int, nh: int, nkv: int, hd: int, rot: int, interleaved: bool,
-                   cos_sin: Optional[torch.Tensor], positions: torch.Tensor, row_req: torch.Tensor,
+def rope_kv_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh: int, nkv: int, hd: int, rot: int,
+                   interleaved: bool, cos_sin: Optional[torch.Tensor], positions: torch.Tensor, row_req: torch.Tensor,
                    block_table: torch.Tensor, kv_pool: Optional[torch.Tensor], page_size: int,
                    status: Optional[torch.Tensor]) -> None:
-    """Rotate q (and k) of rows [q | k | v] in place and store k, v into kv_pool
-    [num_pages, 2, nkv, page_size, hd] through the block table [B, max_pages]."""
-    _cuda(qkv, cos_sin, positions, row_req, block_table, kv_pool)
+    """Rows [q | k | v] of `src` ([T, W], or partial sums [parts, T, W]): rotate q into q_out [T, nh*hd],
+    rotate k and store k and v into kv_pool [num_pages, 2, nkv, page_size, hd] through the block table
+    [B, max_pages].  With kv_pool None the rows hold q only."""
+    _cuda(src, q_out, cos_sin, positions, row_req, block_table, kv_pool)
     _i32(positions, "positions"); _i32(row_req, "row_req"); _i32(block_table, "block_table")
-    width = qkv.shape[1]
+    parts, stride = _parts(src, "rope_kv_append: src")
+    width = src.shape[-1]
     need = nh * hd + (2 * nkv * hd if kv_pool is not None else 0)
-    if qkv.stride(1) != 1 or width < need:
+    if src.stride(-1) != 1 or width < need:
         raise KernelError(f"rope_kv_append: rows of {width} features cannot hold q, k, v ({need})")
+    if q_out.data_ptr() == src.data_ptr() or q_out.stride(1) != 1 or q_out.shape[1] < nh * hd or q_out.shape[0] < n_rows:
+        raise KernelError("rope_kv_append: q_out must be a separate [T, nh*hd] tensor")
     num_pages = 0
     if kv_pool is not None:
         if tuple(kv_pool.shape[1:]) != (2, nkv, page_size, hd) or not kv_pool.is_contiguous():
@@ -225,11 +245,11 @@ def rope_kv_append(qkv: torch.Tensor, n_rows: int, nh: int, nkv: int, hd: int, r
         num_pages = kv_pool.shape[0]
     if rot > 0 and (cos_sin is None or cos_sin.shape[0] < n_rows or cos_sin.shape[1] != rot // 2 or cos_sin.dtype != torch.float32):
         raise KernelError("rope_kv_append: cos_sin must be float32 [T, rot/2, 2]")
-    _check(lib().bg_rope_kv_append(_p(qkv), _dt(qkv), qkv.stride(0), _p(cos_sin), _p(positions), _p(row_req),
-                                   _p(block_table), block_table.shape[1], _p(kv_pool),
-                                   _dt(kv_pool) if kv_pool is not None else F32, num_pages, page_size, n_rows,
-                                   nh, nkv, hd, rot, 1 if interleaved else 0, _p(status), _stream()),
-           "rope_kv_append")
+    _check(lib().bg_rope_kv_append(_p(src), _dt(src), src.stride(-2), parts, stride, _p(q_out), _dt(q_out),
+                                   q_out.stride(0), _p(cos_sin), _p(positions), _p(row_req), _p(block_table),
+                                   block_table.shape[1], _p(kv_pool), _dt(kv_pool) if kv_pool is not None else F32,
+                                   num_pages, page_size, n_rows, nh, nkv, hd, rot, 1 if interleaved else 0,
+                                   _p(status), _stream()), "rope_kv_append")
 
 
 def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, decode_only: bool = False,
@@ -350,4 +370,7 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: O
     for t in (temperature, uniform):
         if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
             raise KernelError("sample: temperature and uniform must be float32 [n]")
-    _check(lib().bg_sample(_p(logits), n, V, _p(temperature), _p(uniform), _p(out), _stream()), "sample")
+    scratch = torch.empty(n * 64 * 3, dtype=torch.float32, device=logits.device)
+    _check(lib().bg_sample(_p(logits), n, V, _p(temperature), _p(uniform), _p(out), _p(scratch), _stream()), "sample")
+    global _launches
+    _launches += 1            # two kernels

@@ -28,7 +28,7 @@ class SwiGLU:
         self.down = Linear(tensors["down_proj.weight"], None, ctx)
 
     def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
-        gu = self.gate_up(h)
-        act = torch.empty((h.shape[0], self.spec.intermediate), dtype=gu.dtype, device=h.device)
+        gu = self.gate_up.partial(h)
+        act = torch.empty((h.shape[0], self.spec.intermediate), dtype=self.ctx.compute_dtype, device=h.device)
         ops.swiglu(gu, act)
-        return self.down(act)
+        return self.down.partial(act)

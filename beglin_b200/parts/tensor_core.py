@@ -1,20 +1,67 @@
-"""Choice of the tcgen05 tensor-core product for a weight matrix.  `plan` returns a callable
-(x, bias, out_dtype) -> y for shapes the kernel takes, or None, in which case the caller uses the
-vendor library's product."""
+"""Choice between the tcgen05 tensor-core product of this package and the vendor library's product
+for a bfloat16 weight matrix, and the split of K for steps of few tokens.
+
+With few tokens a product is bound by streaming the weight matrix once, and a matrix with few
+128-row tiles would leave most SMs idle; K is then cut into ranges, each CTA writes a float partial
+sum, and the kernel that consumes the result adds the partial sums in index order.  How many ranges
+depends only on the matrix's shape and the number of tokens in the step.
+"""
 from __future__ import annotations
 
-from typing import Callable, Optional
+from typing import Optional
 
 import torch
 
+from ..csrc import ops
 from .context import BuildContext
 
+SM_COUNT = 148
+FEW_TOKENS = 64            # up to this many rows a product is treated as weight-streaming
 
-def plan(weight: torch.Tensor, ctx: BuildContext) -> Optional[Callable]:
-    from ..csrc import ops
-    maker = getattr(ops, "tcgen05_linear", None)
-    if maker is None:
-        if ctx.gemm == "tcgen05":
-            raise RuntimeError("the tcgen05 product was asked for but the kernel library does not have it")
+
+class TensorCoreProduct:
+    def __init__(self, weight: torch.Tensor, ctx: BuildContext):
+        self.weight, self.ctx = weight, ctx
+        self.n_out, self.k = weight.shape
+        self.tiles = -(-self.n_out // 128)
+        self.k_blocks = -(-self.k // 64)
+
+    @staticmethod
+    def takes(weight: torch.Tensor) -> bool:
+        return weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0 and weight.stride(0) % 8 == 0
+
+    def wins(self, T: int) -> bool:
+        """Whether this kernel is the faster one for a step of T rows (measured on B200 at the
+        Qwen2.5-1.5B shapes): it is where cutting K fills the machine, that is for few tokens and a
+        matrix of fewer 128-row tiles than half the SMs."""
+        return T <= FEW_TOKENS and self.tiles <= SM_COUNT // 2
+
+    def splits(self, T: int) -> int:
+        if T > FEW_TOKENS:
+            return 1
+        want = max(1, -(-SM_COUNT // self.tiles))                 # enough CTAs for every SM
+        want = min(want, max(1, self.k_blocks // 2))              # at least two k-blocks per range
+        want = min(want, max(1, self.k // (8 * T)))               # partial sums stay a fraction of the weight bytes
+        per = -(-self.k_blocks // want)
+        return -(-self.k_blocks // per)                           # no empty range
+
+    def __call__(self, x: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype, partial: bool) -> torch.Tensor:
+        T = x.shape[0]
+        s = self.splits(T) if partial else 1
+        if s > 1:
+            out = torch.empty((s, T, self.n_out), dtype=torch.float32, device=x.device)
+        else:
+            out = torch.empty((T, self.n_out), dtype=out_dtype, device=x.device)
+        ops.gemm_bf16_tn(x, self.weight, bias, out, s, self.ctx.status)
+        return out
+
+
+def plan(weight: torch.Tensor, ctx: BuildContext) -> Optional[TensorCoreProduct]:
+    if ctx.gemm == "library":
         return None
-    return maker(weight, required=(ctx.gemm == "tcgen05"))
+    if not TensorCoreProduct.takes(weight):
+        if ctx.gemm == "tcgen05":
+            raise ValueError(f"the tcgen05 product was asked for, but it does not take a {tuple(weight.shape)} "
+                             f"{weight.dtype} matrix (bfloat16, inner size a multiple of 8)")
+        return None
+    return TensorCoreProduct(weight, ctx)

@@ -65,6 +65,13 @@ def test_add_rmsnorm(ops, d, out_dtype):
     ops.add_rmsnorm(x2, delta, w, eps, out2, rows=rows, update=False)
     assert torch.equal(x2, x)
     assert torch.equal(out2, out[rows.long()])
+    # the addend as partial sums of a split-K product: added in index order, same result
+    x4 = x.clone()
+    parts = torch.stack([0.5 * delta.float(), 0.25 * delta.float(), 0.25 * delta.float()]).contiguous()
+    out4 = torch.empty((T, d), dtype=out_dtype, device=DEV)
+    ops.add_rmsnorm(x4, parts, w, eps, out4)
+    assert (x4.double() - want_x).abs().max() < 1e-6
+    assert (out4.double() - want).abs().max() < tol * want.abs().max()
     out3 = torch.empty((T, d), dtype=out_dtype, device=DEV)
     ops.add_rmsnorm(x2, None, w, eps, out3)
     want3 = plain.rmsnorm(x.double(), w.double(), eps)
@@ -79,6 +86,10 @@ def test_swiglu(ops, dtype):
     want = plain.swiglu(gu[:, :203].double(), gu[:, 203:].double())
     tol = 1e-6 if dtype == torch.float32 else 1e-2
     assert (out.double() - want).abs().max() <= tol * want.abs().max()
+    parts = torch.stack([0.5 * gu.float(), 0.5 * gu.float()]).contiguous()
+    out2 = torch.empty((5, 203), dtype=dtype, device=DEV)
+    ops.swiglu(parts, out2)
+    assert (out2.double() - want).abs().max() <= tol * want.abs().max()
 
 
 def test_gemm_f32_is_true_float_and_row_invariant(ops):
@@ -127,7 +138,13 @@ def test_rope_table_and_kv_append(ops, interleaved, dtype):
     bt[0, :2] = torch.tensor([4, 7]); bt[1, :1] = torch.tensor([2]); bt[2, :6] = torch.tensor([9, 0, 1, 3, 5, 6])
     pool = torch.full((n_pages, 2, nkv, page, hd), float("nan"), dtype=dtype, device=DEV)
     status = ops.new_status(DEV)
-    ops.rope_kv_append(qkv, T, nh, nkv, hd, rot, interleaved, table, positions, row_req, bt, pool, page, status)
+    # the rows arrive as three partial sums of a split-K product (float) or as one tensor
+    if dtype == torch.float32:
+        parts = torch.stack([0.25 * qkv, 0.5 * qkv, 0.25 * qkv]).contiguous()
+    else:
+        parts = qkv
+    q_out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    ops.rope_kv_append(parts, q_out, T, nh, nkv, hd, rot, interleaved, table, positions, row_req, bt, pool, page, status)
     ops.raise_on_status(status)
 
     def rotate(v, t):        # v [heads, hd] float64
@@ -150,17 +167,17 @@ def test_rope_table_and_kv_append(ops, interleaved, dtype):
         q = rotate(o[:nh * hd].reshape(nh, hd), t)
         k = rotate(o[nh * hd:(nh + nkv) * hd].reshape(nkv, hd), t)
         v = o[(nh + nkv) * hd:].reshape(nkv, hd)
-        assert (qkv[t, :nh * hd].double().cpu().reshape(nh, hd) - q).abs().max() < tol * 4
+        assert (q_out[t].double().cpu().reshape(nh, hd) - q).abs().max() < tol * 4
         p = int(positions[t]); pg = int(bt[int(row_req[t]), p // page]); sl = p % page
         assert (pool[pg, 0, :, sl].double().cpu() - k).abs().max() < tol * 4
         assert (pool[pg, 1, :, sl].double().cpu() - v).abs().max() < tol * 4
         written.add((pg, sl))
-        assert torch.equal(qkv[t, nh * hd:], orig[t, nh * hd:])        # k and v rows themselves are not touched
+        assert torch.equal(qkv[t], orig[t])                             # the source rows are not touched
     finite = torch.isfinite(pool[:, 0, 0, :, 0].float()).cpu()
     assert {(int(a), int(b)) for a, b in finite.nonzero()} == written   # nothing else was written
     # a page outside the pool is recorded, not written
     bt[1, 0] = 99
-    ops.rope_kv_append(orig.clone(), T, nh, nkv, hd, rot, interleaved, table, positions, row_req, bt, pool, page, status)
+    ops.rope_kv_append(orig.clone(), q_out, T, nh, nkv, hd, rot, interleaved, table, positions, row_req, bt, pool, page, status)
     with pytest.raises(ops.KernelError, match="page"):
         ops.raise_on_status(status)
 
