@@ -220,16 +220,27 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
             l_mine = part_ml[(prow + mine) * 2 + 1];
         }
         const int n = min(32, s_hi - s0 + 1);
-#pragma unroll 4
-        for (int j = 0; j < n; ++j) {
-            const float f = __shfl_sync(0xffffffffu, f_mine, j);
-            const float lj = __shfl_sync(0xffffffffu, l_mine, j);
-            l = fmaf(lj, f, l);
-            const float* po = part_o + (prow + s0 + j) * hd;
+        for (int j0 = 0; j0 < n; j0 += 4) {
+            // the loads of four splits go out together, then they are added in split order
+            float v[4][ATT_MAX_DPL];
 #pragma unroll
-            for (int i = 0; i < ATT_MAX_DPL; ++i) {
-                int d = i * 32 + lane;
-                if (d < hd) acc[i] = fmaf(po[d], f, acc[i]);
+            for (int jj = 0; jj < 4; ++jj) {
+                const float* po = part_o + (prow + s0 + j0 + jj) * hd;
+#pragma unroll
+                for (int i = 0; i < ATT_MAX_DPL; ++i) {
+                    int d = i * 32 + lane;
+                    v[jj][i] = (j0 + jj < n && d < hd) ? po[d] : 0.0f;
+                }
+            }
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const float f = __shfl_sync(0xffffffffu, f_mine, (j0 + jj) & 31);
+                const float lj = __shfl_sync(0xffffffffu, l_mine, (j0 + jj) & 31);
+                if (j0 + jj < n) {
+                    l = fmaf(lj, f, l);
+#pragma unroll
+                    for (int i = 0; i < ATT_MAX_DPL; ++i) acc[i] = fmaf(v[jj][i], f, acc[i]);
+                }
             }
         }
     }

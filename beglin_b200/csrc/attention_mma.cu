@@ -40,6 +40,8 @@ struct AttnMmaParams {
     int window, split;
     float scale_log2;       // scale * log2(e)
     unsigned* status;
+    __nv_bfloat16* out;     // rows arrangement only: when set, a CTA walks ALL keys of its block and writes
+    int out_stride;         // the finished rows here (no partial results, no merge)
 };
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, int src_bytes) {
@@ -91,8 +93,9 @@ attention_mma_kernel(AttnMmaParams p) {
     const int pos_first = p.positions[row0];
     const int pos_last = p.positions[row0 + nq - 1];
     const int lo_first = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
-    const int k_begin = max(sp * p.split, lo_first);
-    const int k_end = min((sp + 1) * p.split, pos_last + 1);
+    const bool direct = !BY_KEYS && p.out != nullptr;
+    const int k_begin = direct ? lo_first : max(sp * p.split, lo_first);
+    const int k_end = direct ? pos_last + 1 : min((sp + 1) * p.split, pos_last + 1);
     if (k_begin >= k_end) return;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -165,6 +168,11 @@ attention_mma_kernel(AttnMmaParams p) {
             pos_r[h] = -1; lo_r[h] = 0;
         }
     }
+    // the span of keys that the rows of this warp can see at all
+    const int warp_row_hi = min(n_rows - 1, row_base + 15);
+    const int warp_pos_hi = row_base < n_rows ? pos_first + warp_row_hi / group : -1;
+    const int warp_pos_lo = pos_first + min(row_base, n_rows - 1) / group;
+    const int warp_lo = p.window > 0 ? max(0, warp_pos_lo - p.window + 1) : 0;
     float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
     float o[NT_O][4];
 #pragma unroll
@@ -184,6 +192,7 @@ attention_mma_kernel(AttnMmaParams p) {
             const int kb = BY_KEYS ? warp : kbi;
             const int key0 = stage_key0 + kb * 16;
             if (key0 >= k_end || key0 + 16 <= k_begin) continue;           // warp-uniform
+            if (key0 > warp_pos_hi || key0 + 16 <= warp_lo) continue;      // no row of this warp sees these keys
             // scores of 16 rows x 16 keys
             float sc[2][4];
 #pragma unroll
@@ -258,7 +267,19 @@ attention_mma_kernel(AttnMmaParams p) {
     cp_async_wait<0>();
 
     // ---- write the partial results
-    if (!BY_KEYS) {
+    if (direct) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            int r = row_base + (lane >> 2) + h * 8;
+            if (r >= n_rows) continue;
+            int qi = r / group, g = r - qi * group;
+            const float inv = 1.0f / l_r[h];
+            __nv_bfloat16* po = p.out + (size_t)(row0 + qi) * p.out_stride + (size_t)(kvh * group + g) * HD;
+#pragma unroll
+            for (int t = 0; t < NT_O; ++t)
+                *reinterpret_cast<unsigned*>(po + t * 8 + (lane & 3) * 2) = pack_bf16(o[t][h * 2 + 0] * inv, o[t][h * 2 + 1] * inv);
+        }
+    } else if (!BY_KEYS) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             int r = row_base + (lane >> 2) + h * 8;
@@ -351,8 +372,9 @@ extern "C" int bg_attention_mma_partial(const void* q, int q_stride, const void*
                                         const int* block_table, int max_pages, const int* positions, const int* qblk,
                                         int n_qblk, float* part_o, float* part_ml, int max_splits, int n_splits_launch,
                                         int nh, int nkv, int hd, int window, int split, int by_keys, float scale,
-                                        unsigned* status, cudaStream_t stream) {
+                                        void* direct_out, int out_stride, unsigned* status, cudaStream_t stream) {
     if (n_qblk <= 0 || n_splits_launch <= 0) return BG_OK;
+    if (direct_out && (by_keys || n_splits_launch != 1 || (out_stride % 2) != 0)) return BG_ERR_SHAPE;
     if (nh % nkv != 0 || split % AM_STAGE_KEYS != 0) return BG_ERR_SHAPE;
     if (n_splits_launch > max_splits || n_splits_launch > 65535 || nkv > 65535) return BG_ERR_SHAPE;
     if ((q_stride % 8) != 0 || ((uintptr_t)q % 16) != 0 || ((uintptr_t)kv_pool % 16) != 0) return BG_ERR_ALIGN;
@@ -362,6 +384,7 @@ extern "C" int bg_attention_mma_partial(const void* q, int q_stride, const void*
     p.positions = positions; p.qblk = qblk; p.part_o = part_o; p.part_ml = part_ml; p.max_splits = max_splits;
     p.nh = nh; p.nkv = nkv; p.group = nh / nkv; p.window = window; p.split = split;
     p.scale_log2 = scale * AM_LOG2E; p.status = status;
+    p.out = (__nv_bfloat16*)direct_out; p.out_stride = out_stride;
     if (by_keys ? p.group > 16 : p.group > 64) return BG_ERR_UNSUPPORTED;
     if (hd == 128) return by_keys ? am_launch<128, true>(p, n_qblk, n_splits_launch, stream)
                                   : am_launch<128, false>(p, n_qblk, n_splits_launch, stream);

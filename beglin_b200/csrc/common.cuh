@@ -71,6 +71,56 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return t;
 }
 
+// Eight consecutive values as floats, from 16-byte aligned memory, and back.
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// Sum of `parts` float4 values that lie `stride4` float4 apart, added in index order.  The loads of
+// eight parts are issued together, so the sum costs one or two round trips, not one per part.
+__device__ __forceinline__ float4 sum_parts4(const float4* p, int parts, size_t stride4) {
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int p0 = 0; p0 < parts; p0 += 8) {
+        float4 a[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = (p0 + j < parts) ? p[(size_t)(p0 + j) * stride4] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { acc.x += a[j].x; acc.y += a[j].y; acc.z += a[j].z; acc.w += a[j].w; }
+    }
+    return acc;
+}
+// The same for single values of any element type.
+template <typename T>
+__device__ __forceinline__ float sum_parts(const T* p, int parts, size_t stride) {
+    float acc = 0.0f;
+    for (int p0 = 0; p0 < parts; p0 += 8) {
+        float a[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = (p0 + j < parts) ? to_float(p[(size_t)(p0 + j) * stride]) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc += a[j];
+    }
+    return acc;
+}
+
 }  // namespace bg
 
 // Dispatch on a runtime dtype code to a template argument.

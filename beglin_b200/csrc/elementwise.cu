@@ -44,10 +44,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     float ss = 0.0f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = xr[i];
-        if (delta) {
-            const TD* dp = delta + (size_t)s * d + i;
-            for (int p = 0; p < parts; ++p) v += to_float(dp[p * part_stride]);
-        }
+        if (delta) v += sum_parts(delta + (size_t)s * d + i, parts, part_stride);
         row_buf[i] = v;
         if (update) xr[i] = v;
         ss += v * v;
@@ -59,48 +56,52 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
         o[i] = from_float<TO>(row_buf[i] * inv * to_float(w[i]));
 }
 
-// The same for a width that is a multiple of 4 with float addends: 16-byte loads and stores, so a
-// row of a few thousand features is one round trip per thread.
-template <typename TW, typename TO>
-__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ x, const float* __restrict__ delta, int parts,
+// The same for a width that is a multiple of 8 and 16-byte aligned rows: every thread moves eight
+// features with 16-byte loads and stores, so a row of a few thousand features is one round trip.
+template <typename TD, typename TW, typename TO>
+__global__ void add_rmsnorm_vec8_kernel(float* __restrict__ x, const TD* __restrict__ delta, int parts,
                                         size_t part_stride, const TW* __restrict__ w, float eps, TO* __restrict__ out,
                                         const int* __restrict__ rows, int d, int update) {
     extern __shared__ float row_buf[];
     __shared__ float red[32];
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
-    float4* xr = reinterpret_cast<float4*>(x + (size_t)s * d);
-    float4* rb = reinterpret_cast<float4*>(row_buf);
-    const int d4 = d >> 2;
+    float* xr = x + (size_t)s * d;
+    const int d8 = d >> 3;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
-        float4 v = xr[i];
+    for (int c = threadIdx.x; c < d8; c += blockDim.x) {
+        float v[8];
+        load8(xr + 8 * c, v);
         if (delta) {
-            const float4* dp = reinterpret_cast<const float4*>(delta + (size_t)s * d) + i;
-            const size_t ps4 = part_stride >> 2;
-#pragma unroll 4
-            for (int p = 0; p < parts; ++p) {
-                float4 a = dp[p * ps4];
-                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            const TD* dp = delta + (size_t)s * d + 8 * c;
+            if (std::is_same<TD, float>::value) {
+                const float4* d4 = reinterpret_cast<const float4*>(dp);
+                float4 a = sum_parts4(d4, parts, part_stride >> 2), b = sum_parts4(d4 + 1, parts, part_stride >> 2);
+                v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+            } else {
+                for (int p = 0; p < parts; ++p) {
+                    float a[8];
+                    load8(dp + (size_t)p * part_stride, a);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] += a[i];
+                }
             }
         }
-        rb[i] = v;
-        if (update) xr[i] = v;
-        ss += v.x * v.x;
-        ss += v.y * v.y;
-        ss += v.z * v.z;
-        ss += v.w * v.w;
+        store8(row_buf + 8 * c, v);
+        if (update) store8(xr + 8 * c, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
     }
     ss = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)d + eps);
     TO* o = out + (size_t)r * d;
-    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
-        float4 v = rb[i];
-        float w0 = to_float(w[4 * i]), w1 = to_float(w[4 * i + 1]), w2 = to_float(w[4 * i + 2]), w3 = to_float(w[4 * i + 3]);
-        o[4 * i + 0] = from_float<TO>(v.x * inv * w0);
-        o[4 * i + 1] = from_float<TO>(v.y * inv * w1);
-        o[4 * i + 2] = from_float<TO>(v.z * inv * w2);
-        o[4 * i + 3] = from_float<TO>(v.w * inv * w3);
+    for (int c = threadIdx.x; c < d8; c += blockDim.x) {
+        float v[8], g[8];
+        load8(row_buf + 8 * c, v);
+        load8(w + 8 * c, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = v[i] * inv * g[i];
+        store8(o + 8 * c, v);
     }
 }
 
@@ -124,12 +125,25 @@ __global__ void swiglu_kernel(const TI* __restrict__ gu, int parts, size_t part_
     size_t t = idx / im;
     int i = (int)(idx - t * im);
     const TI* gp = gu + t * 2 * (size_t)im + i;
-    float g = 0.0f, u = 0.0f;
-    for (int p = 0; p < parts; ++p) {
-        g += to_float(gp[p * part_stride]);
-        u += to_float(gp[p * part_stride + im]);
-    }
+    float g = sum_parts(gp, parts, part_stride);
+    float u = sum_parts(gp + im, parts, part_stride);
     out[idx] = from_float<TO>((g / (1.0f + expf(-g))) * u);
+}
+
+// One tensor (no partial sums), im a multiple of 8: eight features per thread, 16-byte accesses.
+template <typename TI, typename TO>
+__global__ void swiglu_vec8_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int rows, int im) {
+    const int im8 = im >> 3;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * im8) return;
+    size_t t = idx / im8;
+    int c = (int)(idx - t * im8);
+    float g[8], u[8];
+    load8(gu + t * 2 * (size_t)im + 8 * c, g);
+    load8(gu + t * 2 * (size_t)im + im + 8 * c, u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] = (g[i] / (1.0f + expf(-g[i]))) * u[i];
+    store8(out + t * (size_t)im + 8 * c, g);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -153,27 +167,6 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
 // pos % page_size.  Pairs are (i, i + half) for split-half and (2i, 2i + 1) for interleaved pairing
 // (qwen_infer.c:782-790); features from rot on are copied.  src may be the partial sums of a
 // split-K product.  The pool of one layer is [num_pages][2][nkv][page_size][hd].
-template <typename TS>
-__device__ __forceinline__ float summed(const TS* p, int parts, size_t part_stride) {
-    float v = 0.0f;
-    for (int i = 0; i < parts; ++i) v += to_float(p[i * part_stride]);
-    return v;
-}
-
-template <typename TS>
-__device__ __forceinline__ float rotated(const TS* head, int parts, size_t part_stride, int i, int rot, int half,
-                                         int interleaved, const float2* cs) {
-    float me = summed(head + i, parts, part_stride);
-    if (i >= rot) return me;
-    int pi, partner;
-    bool first;
-    if (interleaved) { pi = i >> 1; first = (i & 1) == 0; partner = first ? i + 1 : i - 1; }
-    else { first = i < half; pi = first ? i : i - half; partner = first ? i + half : i - half; }
-    float other = summed(head + partner, parts, part_stride);
-    float2 f = cs[pi];
-    return first ? (me * f.x - other * f.y) : (me * f.x + other * f.y);
-}
-
 template <typename TS, typename TQ, typename TC>
 __global__ void rope_kv_append_kernel(const TS* __restrict__ src, int src_stride, int parts, size_t part_stride,
                                       TQ* __restrict__ q_out, int q_stride, const float2* __restrict__ cos_sin,
@@ -181,33 +174,58 @@ __global__ void rope_kv_append_kernel(const TS* __restrict__ src, int src_stride
                                       const int* __restrict__ block_table, int max_pages,
                                       TC* __restrict__ kv_pool, int num_pages, int page_size,
                                       int nh, int nkv, int hd, int rot, int interleaved, unsigned* status) {
+    extern __shared__ float row_s[];                 // the token's summed row [q | k | v]
     const int t = blockIdx.x;
     const int half = rot >> 1;
+    const int width = (nh + (kv_pool ? 2 * nkv : 0)) * hd;
     const TS* row = src + (size_t)t * src_stride;
+    // the page of this token (independent of the row's values: in flight together with them)
+    int page = 0, slot = 0;
+    if (kv_pool) {
+        const int pos = positions[t];
+        page = block_table[(size_t)row_req[t] * max_pages + pos / page_size];
+        slot = pos % page_size;
+    }
+    if (std::is_same<TS, float>::value && (width % 4 == 0) && (src_stride % 4 == 0) && (part_stride % 4 == 0) &&
+        ((uintptr_t)src % 16 == 0)) {
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        for (int i = threadIdx.x; i < width / 4; i += blockDim.x)
+            reinterpret_cast<float4*>(row_s)[i] = sum_parts4(r4 + i, parts, part_stride >> 2);
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) row_s[i] = sum_parts(row + i, parts, part_stride);
+    }
+    __syncthreads();
     const float2* cs = cos_sin ? cos_sin + (size_t)t * half : nullptr;
+    auto rotated = [&](const float* head, int i) -> float {
+        float me = head[i];
+        if (i >= rot) return me;
+        int pi, partner;
+        bool first;
+        if (interleaved) { pi = i >> 1; first = (i & 1) == 0; partner = first ? i + 1 : i - 1; }
+        else { first = i < half; pi = first ? i : i - half; partner = first ? i + half : i - half; }
+        float other = head[partner];
+        float2 f = cs[pi];
+        return first ? (me * f.x - other * f.y) : (me * f.x + other * f.y);
+    };
     TQ* qo = q_out + (size_t)t * q_stride;
     for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
         int h = idx / hd, i = idx - h * hd;
-        qo[idx] = from_float<TQ>(rotated(row + (size_t)h * hd, parts, part_stride, i, rot, half, interleaved, cs));
+        qo[idx] = from_float<TQ>(rotated(row_s + h * hd, i));
     }
     if (!kv_pool) return;
-    const int pos = positions[t];
-    const int req = row_req[t];
-    const int page = block_table[(size_t)req * max_pages + pos / page_size];
     if (page < 0 || page >= num_pages) {
         if (threadIdx.x == 0 && status) atomicOr(status, BG_STATUS_BAD_PAGE);
         return;
     }
-    const int slot = pos % page_size;
-    const TS* k = row + (size_t)nh * hd;
-    const TS* vv = k + (size_t)nkv * hd;
+    const float* k = row_s + nh * hd;
+    const float* vv = k + nkv * hd;
     TC* kdst = kv_pool + ((size_t)page * 2 + 0) * nkv * page_size * hd;
     TC* vdst = kv_pool + ((size_t)page * 2 + 1) * nkv * page_size * hd;
     for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
         int h = idx / hd, i = idx - h * hd;
         size_t dst = ((size_t)h * page_size + slot) * hd + i;
-        vdst[dst] = from_float<TC>(summed(vv + idx, parts, part_stride));
-        kdst[dst] = from_float<TC>(rotated(k + (size_t)h * hd, parts, part_stride, i, rot, half, interleaved, cs));
+        vdst[dst] = from_float<TC>(vv[idx]);
+        kdst[dst] = from_float<TC>(rotated(k + h * hd, i));
     }
 }
 
@@ -229,13 +247,13 @@ static int add_rmsnorm_launch(float* x, const void* delta, int parts, size_t par
                               void* out, const int* rows, int n_rows, int d, int update, cudaStream_t stream) {
     size_t smem = (size_t)d * sizeof(float);
     if (smem > 200 * 1024) return BG_ERR_SHAPE;
-    const bool vec = std::is_same<TD, float>::value && (d % 4 == 0) && (part_stride % 4 == 0) &&
-                     ((uintptr_t)x % 16 == 0) && ((uintptr_t)delta % 16 == 0);
+    const bool vec = (d % 8 == 0) && (part_stride % 8 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)delta % 16 == 0) &&
+                     ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
     if (vec) {
-        auto kern = add_rmsnorm_vec4_kernel<TW, TO>;
+        auto kern = add_rmsnorm_vec8_kernel<TD, TW, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        int threads = d / 4 >= 512 ? 512 : (d / 4 >= 256 ? 256 : 128);
-        kern<<<n_rows, threads, smem, stream>>>(x, (const float*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out,
+        int threads = d / 8 >= 512 ? 512 : (d / 8 >= 256 ? 256 : (d / 8 >= 128 ? 128 : 64));
+        kern<<<n_rows, threads, smem, stream>>>(x, (const TD*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out,
                                                 rows, d, update);
     } else {
         auto kern = add_rmsnorm_kernel<TD, TW, TO>;
@@ -281,10 +299,18 @@ extern "C" int bg_add_residual(float* x, const void* delta, int delta_dtype, lon
 template <typename TI>
 static int swiglu_in(const void* gu, int parts, size_t part_stride, void* out, int out_dtype, int rows, int im,
                      cudaStream_t stream) {
-    size_t total = (size_t)rows * im;
-    unsigned blocks = (unsigned)((total + 255) / 256);
-    BG_DISPATCH_DTYPE(out_dtype, TO, swiglu_kernel<TI, TO><<<blocks, 256, 0, stream>>>(
-        (const TI*)gu, parts, part_stride, (TO*)out, rows, im));
+    const bool vec = parts == 1 && (im % 8 == 0) && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    if (vec) {
+        size_t total = (size_t)rows * (im / 8);
+        unsigned blocks = (unsigned)((total + 255) / 256);
+        BG_DISPATCH_DTYPE(out_dtype, TO, swiglu_vec8_kernel<TI, TO><<<blocks, 256, 0, stream>>>(
+            (const TI*)gu, (TO*)out, rows, im));
+    } else {
+        size_t total = (size_t)rows * im;
+        unsigned blocks = (unsigned)((total + 255) / 256);
+        BG_DISPATCH_DTYPE(out_dtype, TO, swiglu_kernel<TI, TO><<<blocks, 256, 0, stream>>>(
+            (const TI*)gu, parts, part_stride, (TO*)out, rows, im));
+    }
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
@@ -311,7 +337,9 @@ static int rope_kv_cache(const void* src, int src_stride, int parts, size_t part
                          const float* cos_sin, const int* positions, const int* row_req, const int* block_table,
                          int max_pages, void* kv_pool, int cache_dtype, int num_pages, int page_size, int T, int nh,
                          int nkv, int hd, int rot, int interleaved, unsigned* status, cudaStream_t stream) {
-    BG_DISPATCH_DTYPE(cache_dtype, TC, rope_kv_append_kernel<TS, TQ, TC><<<T, 256, 0, stream>>>(
+    const size_t smem = (size_t)(nh + 2 * nkv) * hd * sizeof(float);
+    if (smem > 48 * 1024) return BG_ERR_SHAPE;
+    BG_DISPATCH_DTYPE(cache_dtype, TC, rope_kv_append_kernel<TS, TQ, TC><<<T, 256, smem, stream>>>(
         (const TS*)src, src_stride, parts, part_stride, (TQ*)q_out, q_stride, (const float2*)cos_sin, positions, row_req,
         block_table, max_pages, (TC*)kv_pool, num_pages, page_size, nh, nkv, hd, rot, interleaved, status));
     BG_LAUNCH_CHECK();

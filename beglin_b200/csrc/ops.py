@@ -37,7 +37,7 @@ _SIGNATURES = {
     "bg_attention_mma_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int)],
     "bg_attention_mma_partial": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                  _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                 _c_int, _c_float, _c_void_p, _c_void_p],
+                                 _c_int, _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p],
     "bg_gemm_f32_nt": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_void_p],
     "bg_gemm_bf16_tn": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
@@ -276,41 +276,50 @@ def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, deco
 
 
 def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table: torch.Tensor,
-              positions: torch.Tensor, qblk: torch.Tensor, n_qblk: int, part_o: torch.Tensor, part_ml: torch.Tensor,
-              max_splits: int, n_splits: int, n_rows: int, nh: int, nkv: int, hd: int, window: int, split: int,
-              tile: int, bq: int, scale: float, out: torch.Tensor, status: Optional[torch.Tensor],
-              kernel: str = "generic") -> None:
+              positions: torch.Tensor, qblk: torch.Tensor, n_qblk: int, max_position: int, n_rows: int, nh: int,
+              nkv: int, hd: int, window: int, split: int, tile: int, bq: int, scale: float, out: torch.Tensor,
+              status: Optional[torch.Tensor], kernel: str = "generic") -> None:
     """Paged grouped-query attention of a step's rows; out is [T, nh*hd].  `kernel`, `bq` and `tile`
-    come from `attention_plan`; `qblk` must be cut for that `bq`."""
-    _cuda(q, kv_pool, block_table, positions, qblk, part_o, part_ml, out)
+    come from `attention_plan`; `qblk` must be cut for that `bq`; `max_position` is the largest
+    position among the rows (or a bound on it).
+
+    "generic" and "mma_keys" cut the keys into splits of `split` positions, write partial results and
+    merge them; "mma_rows" lets one CTA walk all keys of its query block and writes `out` directly."""
+    _cuda(q, kv_pool, block_table, positions, qblk, out)
     _i32(positions, "positions"); _i32(block_table, "block_table"); _i32(qblk, "qblk")
     num_pages, two, nkv_, page_size, hd_ = kv_pool.shape
     if (two, nkv_, hd_) != (2, nkv, hd) or not kv_pool.is_contiguous():
         raise KernelError(f"attention: kv_pool is {tuple(kv_pool.shape)}, expected [pages, 2, {nkv}, page, {hd}]")
-    if part_o.dtype != torch.float32 or part_ml.dtype != torch.float32:
-        raise KernelError("attention: partial buffers must be float32")
-    if part_o.numel() < n_rows * nh * max_splits * hd or part_ml.numel() < n_rows * nh * max_splits * 2:
-        raise KernelError("attention: partial buffers are too small for this step")
     if out.stride(1) != 1 or out.shape[1] < nh * hd or out.shape[0] < n_rows:
         raise KernelError("attention: out must be [T, nh*hd] with unit inner stride")
     L = lib()
+    if kernel == "mma_rows":
+        if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+            raise KernelError("attention: the tensor-core kernel takes bfloat16 queries, caches and outputs")
+        _check(L.bg_attention_mma_partial(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
+                                          block_table.shape[1], _p(positions), _p(qblk), n_qblk, None, None, 1, 1,
+                                          nh, nkv, hd, window, split, 0, float(scale), _p(out), out.stride(0),
+                                          _p(status), _stream()), "attention_mma")
+        return
+    n_splits = max_position // split + 1
+    part_o = torch.empty((n_rows * nh * n_splits, hd), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((n_rows * nh * n_splits, 2), dtype=torch.float32, device=q.device)
     if kernel == "generic":
         _check(L.bg_attention_partial(_p(q), _dt(q), q_stride, _p(kv_pool), _dt(kv_pool), num_pages, page_size,
                                       _p(block_table), block_table.shape[1], _p(positions), _p(qblk), n_qblk,
-                                      _p(part_o), _p(part_ml), max_splits, n_splits, nh, nkv, hd, window, split, tile,
+                                      _p(part_o), _p(part_ml), n_splits, n_splits, nh, nkv, hd, window, split, tile,
                                       bq, float(scale), _p(status), _stream()), "attention_partial")
-    elif kernel in ("mma_rows", "mma_keys"):
+    elif kernel == "mma_keys":
         if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16:
             raise KernelError("attention: the tensor-core kernel takes bfloat16 queries and caches")
         _check(L.bg_attention_mma_partial(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
                                           block_table.shape[1], _p(positions), _p(qblk), n_qblk, _p(part_o),
-                                          _p(part_ml), max_splits, n_splits, nh, nkv, hd, window, split,
-                                          1 if kernel == "mma_keys" else 0, float(scale), _p(status), _stream()),
-               "attention_mma_partial")
+                                          _p(part_ml), n_splits, n_splits, nh, nkv, hd, window, split, 1,
+                                          float(scale), None, 0, _p(status), _stream()), "attention_mma_partial")
     else:
         raise KernelError(f"unknown attention kernel '{kernel}'")
     _check(L.bg_attention_merge(_p(part_o), _p(part_ml), _p(positions), _p(out), _dt(out), out.stride(0), n_rows, nh,
-                                hd, max_splits, split, window, _stream()), "attention_merge")
+                                hd, n_splits, split, window, _stream()), "attention_merge")
 
 
 def gemm_f32_nt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,

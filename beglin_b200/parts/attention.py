@@ -75,14 +75,10 @@ class GQAAttention:
         ops.rope_kv_append(qkv, q, T, self.nh, self.nkv, self.hd, self.position.rotary_dim, self.position.interleaved,
                            self.position.table(batch), batch.positions, batch.row_req, cache.block_table,
                            cache.pool if self.spec.own_kv else None, cache.page_size, self.ctx.status)
-        split = self.ctx.kv_split
-        n_splits = batch.max_position // split + 1
         kernel, bq, tile = self.plans[bool(getattr(batch, "decode_only", False))]
         qblk, n_qblk = batch.query_blocks(bq)
-        part_o = torch.empty((T * self.nh * n_splits, self.hd), dtype=torch.float32, device=h.device)
-        part_ml = torch.empty((T * self.nh * n_splits, 2), dtype=torch.float32, device=h.device)
         out = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=h.device)
-        ops.attention(q, q.stride(0), cache.pool, cache.block_table, batch.positions, qblk, n_qblk, part_o,
-                      part_ml, n_splits, n_splits, T, self.nh, self.nkv, self.hd, self.window, split, tile,
-                      bq, self.scale, out, self.ctx.status, kernel)
+        ops.attention(q, q.stride(0), cache.pool, cache.block_table, batch.positions, qblk, n_qblk,
+                      batch.max_position, T, self.nh, self.nkv, self.hd, self.window, self.ctx.kv_split, tile, bq,
+                      self.scale, out, self.ctx.status, kernel)
         return self.o_proj.partial(out)

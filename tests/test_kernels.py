@@ -229,15 +229,12 @@ def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64, prefe
         r0 += n
     positions_t = torch.tensor(positions, dtype=torch.int32, device=DEV)
     qblk_t = torch.tensor(qblk, dtype=torch.int32, device=DEV)
-    n_splits = max(positions) // split + 1
-    part_o = torch.full((rows * nh * n_splits, hd), float("nan"), device=DEV)
-    part_ml = torch.full((rows * nh * n_splits, 2), float("nan"), device=DEV)
     out = torch.full((rows, nh * hd), float("nan"), dtype=dtype, device=DEV)
     status = ops.new_status(DEV)
     qd = q.reshape(rows, nh * hd).to(DEV).contiguous()
     scale = 1.0 / math.sqrt(hd)
-    ops.attention(qd, qd.stride(0), pool.to(DEV), bt.to(DEV), positions_t, qblk_t, len(qblk), part_o, part_ml,
-                  n_splits, n_splits, rows, nh, nkv, hd, window or 0, split, tile, bq, scale, out, status, kernel)
+    ops.attention(qd, qd.stride(0), pool.to(DEV), bt.to(DEV), positions_t, qblk_t, len(qblk), max(positions), rows,
+                  nh, nkv, hd, window or 0, split, tile, bq, scale, out, status, kernel)
     ops.raise_on_status(status)
     # reference: every request's rows against its whole key/value sequence
     want = torch.empty(rows, nh * hd, dtype=torch.float64)
