@@ -56,6 +56,8 @@ attention_partial_kernel(AttnParams p) {
     float* l_s = m_s + n_rows_max;                       // [n_rows_max]
     long long* base_s = (long long*)(l_s + n_rows_max);   // [tile] element offsets (the float count before it is even)
 
+    pdl_launch();
+    pdl_wait();
     const int qb = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
     const int req = p.qblk[qb * 3 + 0], row0 = p.qblk[qb * 3 + 1], nq = p.qblk[qb * 3 + 2];
     if (nq <= 0) return;
@@ -195,6 +197,8 @@ template <typename TO>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
                                        int T, int nh, int hd, int max_splits, int split, int window) {
+    pdl_launch();
+    pdl_wait();
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (w >= T * nh) return;
@@ -297,7 +301,7 @@ extern "C" int bg_attention_partial(const void* q, int q_dtype, int q_stride, co
         auto kern = attention_partial_kernel<TQ, TC>;                                                      \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return (int)e;                                                               \
-        kern<<<grid, ATT_THREADS, smem, stream>>>(p);                                                      \
+        launch(kern, grid, dim3(ATT_THREADS), smem, stream, p);                                                      \
     } while (0)
     if (q_dtype == BG_DTYPE_F32 && cache_dtype == BG_DTYPE_F32) BG_ATT_LAUNCH(float, float);
     else if (q_dtype == BG_DTYPE_BF16 && cache_dtype == BG_DTYPE_BF16) BG_ATT_LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -315,7 +319,7 @@ extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, con
     if (T <= 0) return BG_OK;
     long long warps = (long long)T * nh;
     unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
-    BG_DISPATCH_DTYPE(out_dtype, TO, attention_merge_kernel<TO><<<blocks, 256, 0, stream>>>(
+    BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_kernel<TO>, dim3(blocks), dim3(256), 0, stream,
         part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
     BG_LAUNCH_CHECK();
     return BG_OK;

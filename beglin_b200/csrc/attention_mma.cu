@@ -21,6 +21,7 @@ namespace bg {
 constexpr int AM_THREADS = 128;
 constexpr int AM_STAGE_KEYS = 64;
 constexpr int AM_STAGES = 3;
+constexpr int AM_TABLE = 128;              // block-table entries held in shared memory at a time
 constexpr float AM_LOG2E = 1.4426950408889634f;
 constexpr float AM_LN2 = 0.6931471805599453f;
 
@@ -44,9 +45,9 @@ struct AttnMmaParams {
     int out_stride;         // the finished rows here (no partial results, no merge)
 };
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, int src_bytes) {
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
     unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gmem_src), "r"(src_bytes) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
@@ -86,6 +87,8 @@ attention_mma_kernel(AttnMmaParams p) {
     unsigned char* k_s = q_s + 64 * HD * 2;                    // [stages][64][HD]
     unsigned char* v_s = k_s + AM_STAGES * STAGE_BYTES;        // [stages][64][HD]
 
+    pdl_launch();
+    pdl_wait();
     const int qb = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
     const int req = p.qblk[qb * 3 + 0], row0 = p.qblk[qb * 3 + 1], nq = p.qblk[qb * 3 + 2];
     if (nq <= 0) return;
@@ -112,41 +115,64 @@ attention_mma_kernel(AttnMmaParams p) {
         *reinterpret_cast<uint4*>(q_s + swz<HD>(r, c)) = v;
     }
 
-    // ---- stage loader: thread t copies half a key row of K and of V
+    __syncthreads();                           // q_s is complete
+
+    // ---- stage loader: thread t copies half a key row of K and of V.  The block-table entries of 128
+    // pages at a time are kept in shared memory, so a stage's copies start without a table load of
+    // their own (a stage of 64 keys never straddles two such groups).
+    __shared__ int table_s[AM_TABLE];
+    int table_group = -1;
     const int first_stage_key = (k_begin / AM_STAGE_KEYS) * AM_STAGE_KEYS;
     const int n_stage = (k_end - first_stage_key + AM_STAGE_KEYS - 1) / AM_STAGE_KEYS;
+    const int last_page = (k_end - 1) / p.page_size;
     const size_t page_elems = (size_t)2 * p.nkv * p.page_size * HD;
     const size_t v_off = (size_t)p.nkv * p.page_size * HD;
     auto load_stage = [&](int s) {
         if (s < n_stage) {
+            const int stage_key0 = first_stage_key + s * AM_STAGE_KEYS;
+            const int group_of_stage = (stage_key0 / p.page_size) / AM_TABLE;
+            if (group_of_stage != table_group) {                 // uniform over the CTA
+                __syncthreads();
+                table_group = group_of_stage;
+                const int base = table_group * AM_TABLE;
+                for (int i = tid; i < AM_TABLE; i += AM_THREADS)
+                    table_s[i] = (base + i <= last_page) ? p.block_table[(size_t)req * p.max_pages + base + i] : -1;
+                __syncthreads();
+            }
             const int buf = s % AM_STAGES;
             const int j = tid >> 1, half = tid & 1;
-            const int key = first_stage_key + s * AM_STAGE_KEYS + j;
-            const __nv_bfloat16* src = p.kv_pool;
-            int bytes = 0;
+            const int key = stage_key0 + j;
+            const __nv_bfloat16* src = nullptr;
             if (key >= k_begin && key < k_end) {
-                int page = p.block_table[(size_t)req * p.max_pages + key / p.page_size];
+                const int page = table_s[key / p.page_size - table_group * AM_TABLE];
                 if (page < 0 || page >= p.num_pages) {
                     if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE);
                 } else {
                     src = p.kv_pool + (size_t)page * page_elems + ((size_t)kvh * p.page_size + key % p.page_size) * HD;
-                    bytes = 16;
                 }
             }
             unsigned char* kd = k_s + buf * STAGE_BYTES;
             unsigned char* vd = v_s + buf * STAGE_BYTES;
+            if (src) {
 #pragma unroll
-            for (int cc = 0; cc < CH / 2; ++cc) {
-                int c = half * (CH / 2) + cc;
-                cp_async16(kd + swz<HD>(j, c), src + (bytes ? c * 8 : 0), bytes);
-                cp_async16(vd + swz<HD>(j, c), src + (bytes ? v_off + c * 8 : 0), bytes);
+                for (int cc = 0; cc < CH / 2; ++cc) {
+                    int c = half * (CH / 2) + cc;
+                    cp_async16(kd + swz<HD>(j, c), src + c * 8);
+                    cp_async16(vd + swz<HD>(j, c), src + v_off + c * 8);
+                }
+            } else {                                             // a key outside the range: zeros
+#pragma unroll
+                for (int cc = 0; cc < CH / 2; ++cc) {
+                    int c = half * (CH / 2) + cc;
+                    *reinterpret_cast<uint4*>(kd + swz<HD>(j, c)) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(vd + swz<HD>(j, c)) = make_uint4(0, 0, 0, 0);
+                }
             }
         }
         cp_async_commit();
     };
     load_stage(0);
     load_stage(1);
-    __syncthreads();                           // q_s is complete
 
     // ---- this warp's query fragments and row bookkeeping
     const int row_base = BY_KEYS ? 0 : warp * 16;
@@ -345,7 +371,7 @@ static int am_launch(const AttnMmaParams& p, int n_qblk, int n_splits, cudaStrea
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(n_qblk, p.nkv, n_splits);
-    kern<<<grid, AM_THREADS, smem, stream>>>(p);
+    launch(kern, grid, dim3(AM_THREADS), smem, stream, p);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

@@ -6,6 +6,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define BG_DTYPE_F32 0
 #define BG_DTYPE_BF16 1
@@ -27,6 +28,36 @@
     do { cudaError_t e_ = cudaGetLastError(); if (e_ != cudaSuccess) return (int)e_; } while (0)
 
 namespace bg {
+
+// Programmatic dependent launch: a kernel launched with the attribute below may begin (be scheduled,
+// set up shared memory, fetch what no earlier kernel of the step writes, such as weights) while its
+// predecessor in the stream is still running.  It must call pdl_wait() before it reads anything an
+// earlier kernel wrote and before it writes global memory; pdl_wait returns once the predecessor has
+// completed and its writes are visible.  Every kernel of this library calls pdl_launch() first (its
+// successor may be scheduled as soon as all of this grid's blocks run) and pdl_wait() before it
+// touches the step's data, so completion carries along the chain.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+#ifdef __CUDACC__
+// 1: launch with the programmatic-serialization attribute (default); 0: plain launches.
+inline int& pdl_enabled() {
+    static int on = [] { const char* e = getenv("BEGLIN_B200_PDL"); return (e && e[0] == '0') ? 0 : 1; }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+#endif
 
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }

@@ -14,6 +14,8 @@ namespace bg {
 template <typename TT>
 __global__ void embed_gather_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int d, int vocab, unsigned* status) {
+    pdl_launch();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * d;
@@ -38,6 +40,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
                                    const int* __restrict__ rows, int d, int update) {
     extern __shared__ float row_buf[];
     __shared__ float red[32];
+    pdl_launch();
+    pdl_wait();
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float* xr = x + (size_t)s * d;
@@ -64,6 +68,8 @@ __global__ void add_rmsnorm_vec8_kernel(float* __restrict__ x, const TD* __restr
                                         const int* __restrict__ rows, int d, int update) {
     extern __shared__ float row_buf[];
     __shared__ float red[32];
+    pdl_launch();
+    pdl_wait();
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float* xr = x + (size_t)s * d;
@@ -108,6 +114,8 @@ __global__ void add_rmsnorm_vec8_kernel(float* __restrict__ x, const TD* __restr
 // x[t] += delta[t] without a norm (the last residual add when no norm follows).
 template <typename TD>
 __global__ void add_residual_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n) {
+    pdl_launch();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] += to_float(delta[i]);
 }
@@ -119,6 +127,8 @@ __global__ void add_residual_kernel(float* __restrict__ x, const TD* __restrict_
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, int parts, size_t part_stride, TO* __restrict__ out,
                               int rows, int im) {
+    pdl_launch();
+    pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t total = (size_t)rows * im;
     if (idx >= total) return;
@@ -133,6 +143,8 @@ __global__ void swiglu_kernel(const TI* __restrict__ gu, int parts, size_t part_
 // One tensor (no partial sums), im a multiple of 8: eight features per thread, 16-byte accesses.
 template <typename TI, typename TO>
 __global__ void swiglu_vec8_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int rows, int im) {
+    pdl_launch();
+    pdl_wait();
     const int im8 = im >> 3;
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)rows * im8) return;
@@ -151,6 +163,8 @@ __global__ void swiglu_vec8_kernel(const TI* __restrict__ gu, TO* __restrict__ o
 // to float, as qwen_infer.c:791-794 computes it once per token for all layers and heads.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   float2* __restrict__ cos_sin, int T, int half) {
+    pdl_launch();
+    pdl_wait();
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= T * half) return;
     int t = idx / half, i = idx - t * half;
@@ -175,6 +189,8 @@ __global__ void rope_kv_append_kernel(const TS* __restrict__ src, int src_stride
                                       TC* __restrict__ kv_pool, int num_pages, int page_size,
                                       int nh, int nkv, int hd, int rot, int interleaved, unsigned* status) {
     extern __shared__ float row_s[];                 // the token's summed row [q | k | v]
+    pdl_launch();
+    pdl_wait();
     const int t = blockIdx.x;
     const int half = rot >> 1;
     const int width = (nh + (kv_pool ? 2 * nkv : 0)) * hd;
@@ -236,7 +252,7 @@ using namespace bg;
 extern "C" int bg_embed_gather(const void* table, int table_dtype, const int* ids, float* out, int T,
                                int d, int vocab, unsigned* status, cudaStream_t stream) {
     if (T <= 0) return BG_OK;
-    BG_DISPATCH_DTYPE(table_dtype, TT, embed_gather_kernel<TT><<<T, 256, 0, stream>>>(
+    BG_DISPATCH_DTYPE(table_dtype, TT, launch(embed_gather_kernel<TT>, dim3(T), dim3(256), 0, stream,
         (const TT*)table, ids, out, d, vocab, status));
     BG_LAUNCH_CHECK();
     return BG_OK;
@@ -253,12 +269,12 @@ static int add_rmsnorm_launch(float* x, const void* delta, int parts, size_t par
         auto kern = add_rmsnorm_vec8_kernel<TD, TW, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         int threads = d / 8 >= 512 ? 512 : (d / 8 >= 256 ? 256 : (d / 8 >= 128 ? 128 : 64));
-        kern<<<n_rows, threads, smem, stream>>>(x, (const TD*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out,
+        launch(kern, dim3(n_rows), dim3(threads), smem, stream, x, (const TD*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out,
                                                 rows, d, update);
     } else {
         auto kern = add_rmsnorm_kernel<TD, TW, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<n_rows, 256, smem, stream>>>(x, (const TD*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out, rows,
+        launch(kern, dim3(n_rows), dim3(256), smem, stream, x, (const TD*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out, rows,
                                             d, update);
     }
     BG_LAUNCH_CHECK();
@@ -291,7 +307,7 @@ extern "C" int bg_add_rmsnorm(float* x, const void* delta, int delta_dtype, int 
 extern "C" int bg_add_residual(float* x, const void* delta, int delta_dtype, long long n, cudaStream_t stream) {
     if (n <= 0) return BG_OK;
     unsigned blocks = (unsigned)((n + 255) / 256);
-    BG_DISPATCH_DTYPE(delta_dtype, TD, add_residual_kernel<TD><<<blocks, 256, 0, stream>>>(x, (const TD*)delta, (size_t)n));
+    BG_DISPATCH_DTYPE(delta_dtype, TD, launch(add_residual_kernel<TD>, dim3(blocks), dim3(256), 0, stream, x, (const TD*)delta, (size_t)n));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
@@ -303,12 +319,12 @@ static int swiglu_in(const void* gu, int parts, size_t part_stride, void* out, i
     if (vec) {
         size_t total = (size_t)rows * (im / 8);
         unsigned blocks = (unsigned)((total + 255) / 256);
-        BG_DISPATCH_DTYPE(out_dtype, TO, swiglu_vec8_kernel<TI, TO><<<blocks, 256, 0, stream>>>(
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_vec8_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream,
             (const TI*)gu, (TO*)out, rows, im));
     } else {
         size_t total = (size_t)rows * im;
         unsigned blocks = (unsigned)((total + 255) / 256);
-        BG_DISPATCH_DTYPE(out_dtype, TO, swiglu_kernel<TI, TO><<<blocks, 256, 0, stream>>>(
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream,
             (const TI*)gu, parts, part_stride, (TO*)out, rows, im));
     }
     BG_LAUNCH_CHECK();
@@ -327,7 +343,7 @@ extern "C" int bg_rope_table(const int* positions, const float* inv_freq, float*
                              cudaStream_t stream) {
     if (T <= 0 || half <= 0) return BG_OK;
     int total = T * half;
-    rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(positions, inv_freq, (float2*)cos_sin, T, half);
+    launch(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, positions, inv_freq, (float2*)cos_sin, T, half);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
@@ -339,7 +355,7 @@ static int rope_kv_cache(const void* src, int src_stride, int parts, size_t part
                          int nkv, int hd, int rot, int interleaved, unsigned* status, cudaStream_t stream) {
     const size_t smem = (size_t)(nh + 2 * nkv) * hd * sizeof(float);
     if (smem > 48 * 1024) return BG_ERR_SHAPE;
-    BG_DISPATCH_DTYPE(cache_dtype, TC, rope_kv_append_kernel<TS, TQ, TC><<<T, 256, smem, stream>>>(
+    BG_DISPATCH_DTYPE(cache_dtype, TC, launch(rope_kv_append_kernel<TS, TQ, TC>, dim3(T), dim3(256), smem, stream,
         (const TS*)src, src_stride, parts, part_stride, (TQ*)q_out, q_stride, (const float2*)cos_sin, positions, row_req,
         block_table, max_pages, (TC*)kv_pool, num_pages, page_size, nh, nkv, hd, rot, interleaved, status));
     BG_LAUNCH_CHECK();

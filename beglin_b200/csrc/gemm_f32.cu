@@ -15,6 +15,8 @@ __global__ void __launch_bounds__(GF_THREADS)
 gemm_f32_nt_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw,
                    const float* __restrict__ bias, float* __restrict__ C, int ldc,
                    int M, int N, int K, int accumulate) {
+    pdl_launch();
+    pdl_wait();
     __shared__ float As[GF_BK][GF_BM + 4];
     __shared__ float Ws[GF_BK][GF_BN + 4];
     const int tid = threadIdx.x;
@@ -75,7 +77,7 @@ extern "C" int bg_gemm_f32_nt(const float* A, int lda, const float* W, int ldw, 
     if (K <= 0) return BG_ERR_SHAPE;
     dim3 grid((N + bg::GF_BN - 1) / bg::GF_BN, (M + bg::GF_BM - 1) / bg::GF_BM);
     if (grid.y > 65535) return BG_ERR_SHAPE;
-    bg::gemm_f32_nt_kernel<<<grid, bg::GF_THREADS, 0, stream>>>(A, lda, W, ldw, bias, C, ldc, M, N, K, accumulate);
+    bg::launch(bg::gemm_f32_nt_kernel, grid, dim3(bg::GF_THREADS), 0, stream, A, lda, W, ldw, bias, C, ldc, M, N, K, accumulate);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

@@ -128,6 +128,7 @@ gemm_bf16_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
     const int kb0 = split * p.kb_per_split;
     const int n_kb = min(p.kb_per_split, n_kb_total - kb0);
 
+    pdl_launch();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&acc_bar, 1);
@@ -147,11 +148,19 @@ gemm_bf16_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
     if (warp == 0) {
         // ---------------- TMA producer
         if (lane == 0 && n_kb > 0) {
-            for (int i = 0; i < n_kb; ++i) {
+            // The weights do not depend on any earlier kernel of the step: the first stages' weight tiles
+            // are requested at once, while the kernel that produces the activations may still be running.
+            const int ahead = n_kb < STAGES ? n_kb : STAGES;
+            for (int i = 0; i < ahead; ++i) {
+                mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+                tma_load_2d(tiles + (size_t)i * STAGE_BYTES, &map_w, (kb0 + i) * TC_BK, tile_m * TC_BM, &full_bar[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; ++i)
+                tma_load_2d(tiles + (size_t)i * STAGE_BYTES + A_BYTES, &map_x, (kb0 + i) * TC_BK, tile_n * BN, &full_bar[i]);
+            for (int i = ahead; i < n_kb; ++i) {
                 const int s = i % STAGES;
-                if (i >= STAGES) {
-                    if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) { atomicExch(&failed, 1); break; }
-                }
+                if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) { atomicExch(&failed, 1); break; }
                 unsigned char* a = tiles + (size_t)s * STAGE_BYTES;
                 unsigned char* b = a + A_BYTES;
                 mbar_expect_tx(&full_bar[s], STAGE_BYTES);
@@ -185,6 +194,7 @@ gemm_bf16_tn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __g
         const int quarter = warp & 3;
         const int m = tile_m * TC_BM + quarter * 32 + lane;
         bool ok = true;
+        pdl_wait();
         if (n_kb > 0) {
             ok = mbar_wait(&acc_bar, 0);
             if (!ok) atomicExch(&failed, 1);
@@ -271,7 +281,7 @@ static int tc_launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
         set = true;
     }
     dim3 grid((p.n_out + TC_BM - 1) / TC_BM, (p.T + BN - 1) / BN, splits);
-    kern<<<grid, TC_THREADS, smem, stream>>>(mw, mx, p);
+    launch(kern, grid, dim3(TC_THREADS), smem, stream, mw, mx, p);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

@@ -60,6 +60,8 @@ sample_stage1_kernel(const float* __restrict__ logits, int V, const float* __res
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ float red[32];
+    pdl_launch();
+    pdl_wait();
     const int r = blockIdx.x, c = blockIdx.y;
     const int per = (V + SAMPLE_CHUNKS - 1) / SAMPLE_CHUNKS;
     const int b = c * per, e = min(V, b + per);
@@ -96,6 +98,8 @@ sample_stage2_kernel(const float* __restrict__ logits, int V, const float* __res
     __shared__ float s_part[STAGE_THREADS];
     __shared__ float s_gmax, s_target, s_before;
     __shared__ int s_chunk, s_pick;
+    pdl_launch();
+    pdl_wait();
     const int r = blockIdx.x;
     const float T = temperature ? temperature[r] : 0.0f;
     if (threadIdx.x == 0) {
@@ -184,9 +188,9 @@ extern "C" int bg_sample(const float* logits, int n, int V, const float* tempera
     int* c_arg = (int*)(c_max + (size_t)n * bg::SAMPLE_CHUNKS);
     float* c_sum = (float*)(c_arg + (size_t)n * bg::SAMPLE_CHUNKS);
     dim3 grid(n, bg::SAMPLE_CHUNKS);
-    bg::sample_stage1_kernel<<<grid, bg::STAGE_THREADS, 0, stream>>>(logits, V, temperature, c_max, c_arg, c_sum);
+    bg::launch(bg::sample_stage1_kernel, grid, dim3(bg::STAGE_THREADS), 0, stream, logits, V, temperature, c_max, c_arg, c_sum);
     BG_LAUNCH_CHECK();
-    bg::sample_stage2_kernel<<<n, bg::STAGE_THREADS, 0, stream>>>(logits, V, temperature, uniform, c_max, c_arg, c_sum, out);
+    bg::launch(bg::sample_stage2_kernel, dim3(n), dim3(bg::STAGE_THREADS), 0, stream, logits, V, temperature, uniform, c_max, c_arg, c_sum, out);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
