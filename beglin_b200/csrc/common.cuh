@@ -126,15 +126,15 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
 }
 
 // Sum of `parts` float4 values that lie `stride4` float4 apart, added in index order.  The loads of
-// eight parts are issued together, so the sum costs one or two round trips, not one per part.
+// sixteen parts are issued together, so the sum costs one round trip for the split counts in use.
 __device__ __forceinline__ float4 sum_parts4(const float4* p, int parts, size_t stride4) {
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int p0 = 0; p0 < parts; p0 += 8) {
-        float4 a[8];
+    for (int p0 = 0; p0 < parts; p0 += 16) {
+        float4 a[16];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) a[j] = (p0 + j < parts) ? p[(size_t)(p0 + j) * stride4] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int j = 0; j < 16; ++j) a[j] = (p0 + j < parts) ? p[(size_t)(p0 + j) * stride4] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { acc.x += a[j].x; acc.y += a[j].y; acc.z += a[j].z; acc.w += a[j].w; }
+        for (int j = 0; j < 16; ++j) { acc.x += a[j].x; acc.y += a[j].y; acc.z += a[j].z; acc.w += a[j].w; }
     }
     return acc;
 }

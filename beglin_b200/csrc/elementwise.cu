@@ -111,6 +111,42 @@ __global__ void add_rmsnorm_vec8_kernel(float* __restrict__ x, const TD* __restr
     }
 }
 
+// For float partial sums and few rows: one float4 per thread, so the loads of all parts of a row are
+// in flight at once across the block (the kernel is a chain of dependent round trips otherwise).
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(512) add_rmsnorm_parts_kernel(float* __restrict__ x, const float* __restrict__ delta, int parts,
+                                         size_t part_stride, const TW* __restrict__ w, float eps, TO* __restrict__ out,
+                                         const int* __restrict__ rows, int d, int update) {
+    extern __shared__ float row_buf[];
+    __shared__ float red[32];
+    pdl_launch();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)s * d);
+    float4* rb = reinterpret_cast<float4*>(row_buf);
+    const int d4 = d >> 2;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        float4 a = sum_parts4(reinterpret_cast<const float4*>(delta + (size_t)s * d) + i, parts, part_stride >> 2);
+        float4 v = xr[i];
+        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+        rb[i] = v;
+        if (update) xr[i] = v;
+        ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    TO* o = out + (size_t)r * d;
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        float4 v = rb[i];
+        o[4 * i + 0] = from_float<TO>(v.x * inv * to_float(w[4 * i + 0]));
+        o[4 * i + 1] = from_float<TO>(v.y * inv * to_float(w[4 * i + 1]));
+        o[4 * i + 2] = from_float<TO>(v.z * inv * to_float(w[4 * i + 2]));
+        o[4 * i + 3] = from_float<TO>(v.w * inv * to_float(w[4 * i + 3]));
+    }
+}
+
 // x[t] += delta[t] without a norm (the last residual add when no norm follows).
 template <typename TD>
 __global__ void add_residual_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n) {
@@ -265,7 +301,13 @@ static int add_rmsnorm_launch(float* x, const void* delta, int parts, size_t par
     if (smem > 200 * 1024) return BG_ERR_SHAPE;
     const bool vec = (d % 8 == 0) && (part_stride % 8 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)delta % 16 == 0) &&
                      ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
-    if (vec) {
+    if (vec && std::is_same<TD, float>::value && parts > 1) {
+        auto kern = add_rmsnorm_parts_kernel<TW, TO>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        int threads = d / 4 >= 512 ? 512 : (d / 4 >= 256 ? 384 : 128);
+        launch(kern, dim3(n_rows), dim3(threads), smem, stream, x, (const float*)delta, parts, part_stride, (const TW*)w, eps,
+               (TO*)out, rows, d, update);
+    } else if (vec) {
         auto kern = add_rmsnorm_vec8_kernel<TD, TW, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         int threads = d / 8 >= 512 ? 512 : (d / 8 >= 256 ? 256 : (d / 8 >= 128 ? 128 : 64));

@@ -32,9 +32,10 @@ class TensorCoreProduct:
 
     def wins(self, T: int) -> bool:
         """Whether this kernel is the faster one for a step of T rows (measured on B200 at the
-        Qwen2.5-1.5B shapes): it is where cutting K fills the machine, that is for few tokens and a
-        matrix of fewer 128-row tiles than half the SMs."""
-        return T <= FEW_TOKENS and self.tiles <= SM_COUNT // 2
+        Qwen2.5-1.5B shapes): it is for few tokens, where the product is a stream of weights, K is
+        cut so that every SM has work, and under programmatic dependent launch the weight tiles are
+        requested while the previous kernel still runs, which the library's kernel cannot do."""
+        return T <= FEW_TOKENS
 
     def splits(self, T: int) -> int:
         if T > FEW_TOKENS:
