@@ -20,7 +20,9 @@ namespace bg {
 
 constexpr int AM_THREADS = 128;
 constexpr int AM_STAGE_KEYS = 64;
-constexpr int AM_STAGES = 3;
+// Stages of 64 keys in flight per CTA: 3 for prompt portions and for decoding grids that fit the machine
+// at once (the latency of one CTA is what counts); 2 for larger decoding grids (less shared memory,
+// three CTAs per SM, and the throughput of the stream is what counts).
 constexpr int AM_TABLE = 128;              // block-table entries held in shared memory at a time
 constexpr float AM_LOG2E = 1.4426950408889634f;
 constexpr float AM_LN2 = 0.6931471805599453f;
@@ -30,6 +32,7 @@ struct AttnMmaParams {
     int q_stride;
     const __nv_bfloat16* kv_pool;
     int num_pages, page_size;
+    int page_shift;         // log2(page_size) when it is a power of two, else -1
     const int* block_table;
     int max_pages;
     const int* positions;
@@ -67,6 +70,12 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the hardware's approximation (relative error about 2^-22; -inf gives 0).
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -75,22 +84,25 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // Byte offset of (row, 16-byte column c) in a tile whose rows are HD bf16 wide.
 template <int HD> __device__ __forceinline__ int swz(int row, int c) { return row * (HD * 2) + ((c ^ (row & 7)) << 4); }
 
-template <int HD, bool BY_KEYS>
+template <int HD, bool BY_KEYS, int AM_STAGES>
 __global__ void __launch_bounds__(AM_THREADS)
 attention_mma_kernel(AttnMmaParams p) {
     constexpr int CH = HD / 8;                 // 16-byte columns per row
     constexpr int KSTEPS = HD / 16;            // k-steps of q.k
     constexpr int NT_O = HD / 8;               // 8-wide column tiles of the output
     constexpr int STAGE_BYTES = AM_STAGE_KEYS * HD * 2;
+    constexpr int Q_ROWS = BY_KEYS ? 16 : 64;
     extern __shared__ __align__(128) unsigned char sm[];
-    unsigned char* q_s = sm;                                   // [64 rows][HD]
-    unsigned char* k_s = q_s + 64 * HD * 2;                    // [stages][64][HD]
+    unsigned char* q_s = sm;                                   // [Q_ROWS][HD]
+    unsigned char* k_s = q_s + Q_ROWS * HD * 2;                // [stages][64][HD]
     unsigned char* v_s = k_s + AM_STAGES * STAGE_BYTES;        // [stages][64][HD]
 
     pdl_launch();
     pdl_wait();
     const int qb = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
-    const int req = p.qblk[qb * 3 + 0], row0 = p.qblk[qb * 3 + 1], nq = p.qblk[qb * 3 + 2];
+    // without a list of query blocks, block i is row i of request i (a step of single tokens)
+    const int req = p.qblk ? p.qblk[qb * 3 + 0] : qb, row0 = p.qblk ? p.qblk[qb * 3 + 1] : qb;
+    const int nq = p.qblk ? p.qblk[qb * 3 + 2] : 1;
     if (nq <= 0) return;
     const int group = p.group;
     const int pos_first = p.positions[row0];
@@ -105,26 +117,29 @@ attention_mma_kernel(AttnMmaParams p) {
     const int n_rows = nq * group;             // <= 64 (rows) or <= 16 (keys)
 
     // ---- queries of the block into shared memory (rows beyond n_rows are zero)
-    for (int idx = tid; idx < 64 * CH; idx += AM_THREADS) {
+    for (int idx = tid; idx < Q_ROWS * CH; idx += AM_THREADS) {
         int r = idx / CH, c = idx - r * CH;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (r < n_rows) {
-            int qi = r / group, g = r - qi * group;
+            int qi = BY_KEYS ? 0 : r / group, g = r - qi * group;
             v = *reinterpret_cast<const uint4*>(p.q + (size_t)(row0 + qi) * p.q_stride + (size_t)(kvh * group + g) * HD + c * 8);
         }
         *reinterpret_cast<uint4*>(q_s + swz<HD>(r, c)) = v;
     }
 
-    __syncthreads();                           // q_s is complete
-
     // ---- stage loader: thread t copies half a key row of K and of V.  The block-table entries of 128
     // pages at a time are kept in shared memory, so a stage's copies start without a table load of
     // their own (a stage of 64 keys never straddles two such groups).
     __shared__ int table_s[AM_TABLE];
-    int table_group = -1;
     const int first_stage_key = (k_begin / AM_STAGE_KEYS) * AM_STAGE_KEYS;
     const int n_stage = (k_end - first_stage_key + AM_STAGE_KEYS - 1) / AM_STAGE_KEYS;
     const int last_page = (k_end - 1) / p.page_size;
+    int table_group = (first_stage_key / p.page_size) / AM_TABLE;     // the first group goes out with the queries
+    for (int i = tid; i < AM_TABLE; i += AM_THREADS) {
+        const int pi = table_group * AM_TABLE + i;
+        table_s[i] = pi <= last_page ? p.block_table[(size_t)req * p.max_pages + pi] : -1;
+    }
+    __syncthreads();                           // q_s and table_s are complete
     const size_t page_elems = (size_t)2 * p.nkv * p.page_size * HD;
     const size_t v_off = (size_t)p.nkv * p.page_size * HD;
     auto load_stage = [&](int s) {
@@ -140,30 +155,30 @@ attention_mma_kernel(AttnMmaParams p) {
                 __syncthreads();
             }
             const int buf = s % AM_STAGES;
-            const int j = tid >> 1, half = tid & 1;
-            const int key = stage_key0 + j;
-            const __nv_bfloat16* src = nullptr;
-            if (key >= k_begin && key < k_end) {
-                const int page = table_s[key / p.page_size - table_group * AM_TABLE];
-                if (page < 0 || page >= p.num_pages) {
-                    if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE);
-                } else {
-                    src = p.kv_pool + (size_t)page * page_elems + ((size_t)kvh * p.page_size + key % p.page_size) * HD;
-                }
-            }
             unsigned char* kd = k_s + buf * STAGE_BYTES;
             unsigned char* vd = v_s + buf * STAGE_BYTES;
-            if (src) {
+            // thread t copies 16-byte piece t % CH of rows t / CH, t / CH + ROWS_PER_PASS, ...: the lanes of
+            // a warp read whole rows, so every 32-byte sector is asked for once
+            constexpr int ROWS_PER_PASS = AM_THREADS / CH;
+            const int c = tid % CH;
 #pragma unroll
-                for (int cc = 0; cc < CH / 2; ++cc) {
-                    int c = half * (CH / 2) + cc;
-                    cp_async16(kd + swz<HD>(j, c), src + c * 8);
-                    cp_async16(vd + swz<HD>(j, c), src + v_off + c * 8);
+            for (int j = tid / CH; j < AM_STAGE_KEYS; j += ROWS_PER_PASS) {
+                const int key = stage_key0 + j;
+                const __nv_bfloat16* src = nullptr;
+                if (key >= k_begin && key < k_end) {
+                    const int pi = p.page_shift >= 0 ? key >> p.page_shift : key / p.page_size;
+                    const int slot = p.page_shift >= 0 ? key & (p.page_size - 1) : key - pi * p.page_size;
+                    const int page = table_s[pi - table_group * AM_TABLE];
+                    if (page < 0 || page >= p.num_pages) {
+                        if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE);
+                    } else {
+                        src = p.kv_pool + (size_t)page * page_elems + ((size_t)kvh * p.page_size + slot) * HD + c * 8;
+                    }
                 }
-            } else {                                             // a key outside the range: zeros
-#pragma unroll
-                for (int cc = 0; cc < CH / 2; ++cc) {
-                    int c = half * (CH / 2) + cc;
+                if (src) {
+                    cp_async16(kd + swz<HD>(j, c), src);
+                    cp_async16(vd + swz<HD>(j, c), src + v_off);
+                } else {                                         // a key outside the range: zeros
                     *reinterpret_cast<uint4*>(kd + swz<HD>(j, c)) = make_uint4(0, 0, 0, 0);
                     *reinterpret_cast<uint4*>(vd + swz<HD>(j, c)) = make_uint4(0, 0, 0, 0);
                 }
@@ -171,8 +186,8 @@ attention_mma_kernel(AttnMmaParams p) {
         }
         cp_async_commit();
     };
-    load_stage(0);
-    load_stage(1);
+#pragma unroll
+    for (int s = 0; s < AM_STAGES - 1; ++s) load_stage(s);
 
     // ---- this warp's query fragments and row bookkeeping
     const int row_base = BY_KEYS ? 0 : warp * 16;
@@ -194,78 +209,102 @@ attention_mma_kernel(AttnMmaParams p) {
             pos_r[h] = -1; lo_r[h] = 0;
         }
     }
-    // the span of keys that the rows of this warp can see at all
+    // the span of keys that the rows of this warp can see at all, and the span that ALL its rows see
     const int warp_row_hi = min(n_rows - 1, row_base + 15);
     const int warp_pos_hi = row_base < n_rows ? pos_first + warp_row_hi / group : -1;
     const int warp_pos_lo = pos_first + min(row_base, n_rows - 1) / group;
     const int warp_lo = p.window > 0 ? max(0, warp_pos_lo - p.window + 1) : 0;
+    const int warp_lo_hi = p.window > 0 ? max(0, warp_pos_hi - p.window + 1) : 0;
+    // byte offsets inside a 16-key block that do not change from block to block: the XOR of the swizzle
+    // depends on the row's low three bits, which for a given lane are the same in every block
+    int koff[KSTEPS], voff[NT_O / 2];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+        koff[ks] = swz<HD>((lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1));
+#pragma unroll
+    for (int t2 = 0; t2 < NT_O / 2; ++t2)
+        voff[t2] = swz<HD>((lane & 7) + (((lane >> 3) & 1) << 3), t2 * 2 + (lane >> 4));
+
     float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
     float o[NT_O][4];
 #pragma unroll
     for (int t = 0; t < NT_O; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f; }
 
-    constexpr int KB_PER_WARP = BY_KEYS ? 1 : 4;        // 16-key blocks of a stage that this warp walks
+    constexpr int KB = BY_KEYS ? 1 : 4;                 // 16-key blocks of a stage that this warp walks
+    constexpr int BLOCK_BYTES = 16 * HD * 2;
     for (int s = 0; s < n_stage; ++s) {
-        load_stage(s + 2);
-        cp_async_wait<2>();
+        load_stage(s + AM_STAGES - 1);
+        cp_async_wait<AM_STAGES - 1>();
         __syncthreads();
         const int buf = s % AM_STAGES;
         const unsigned char* kt = k_s + buf * STAGE_BYTES;
         const unsigned char* vt = v_s + buf * STAGE_BYTES;
         const int stage_key0 = first_stage_key + s * AM_STAGE_KEYS;
+        // this warp's keys of the stage: [w_key0, w_key0 + 16 * KB)
+        const int w_key0 = stage_key0 + (BY_KEYS ? warp * 16 : 0);
+        const int vis_lo = max(max(w_key0, k_begin), warp_lo);                   // keys some row of the warp sees
+        const int vis_hi = min(min(w_key0 + 16 * KB, k_end), warp_pos_hi + 1);
+        if (vis_lo < vis_hi) {                                                   // warp-uniform
+            // ---- scores of 16 rows x 16*KB keys
+            // (k-step outermost, so the 2*KB accumulators form independent chains of dependent MMAs)
+            float sc[2 * KB][4];
 #pragma unroll
-        for (int kbi = 0; kbi < KB_PER_WARP; ++kbi) {
-            const int kb = BY_KEYS ? warp : kbi;
-            const int key0 = stage_key0 + kb * 16;
-            if (key0 >= k_end || key0 + 16 <= k_begin) continue;           // warp-uniform
-            if (key0 > warp_pos_hi || key0 + 16 <= warp_lo) continue;      // no row of this warp sees these keys
-            // scores of 16 rows x 16 keys
-            float sc[2][4];
-#pragma unroll
-            for (int j = 0; j < 2; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f; }
+            for (int j = 0; j < 2 * KB; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f; }
+            const unsigned char* kwarp = kt + (BY_KEYS ? warp * BLOCK_BYTES : 0);
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks) {
-                unsigned kf[4];
-                int r = kb * 16 + (lane & 7) + ((lane >> 4) << 3);
-                int c = ks * 2 + ((lane >> 3) & 1);
-                ldmatrix_x4(kf, kt + swz<HD>(r, c));
-                mma_bf16(sc[0], qf[ks], kf[0], kf[1]);
-                mma_bf16(sc[1], qf[ks], kf[2], kf[3]);
-            }
-            // mask, running maximum
-            float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
-                    int h = e >> 1;
-                    bool ok = key <= pos_r[h] && key >= lo_r[h] && key >= k_begin && key < k_end;
-                    float v = ok ? sc[j][e] * p.scale_log2 : -INFINITY;
-                    sc[j][e] = v;
-                    tmax[h] = fmaxf(tmax[h], v);
+                for (int kbi = 0; kbi < KB; ++kbi) {
+                    unsigned kf[4];
+                    ldmatrix_x4(kf, kwarp + kbi * BLOCK_BYTES + koff[ks]);
+                    mma_bf16(sc[2 * kbi], qf[ks], kf[0], kf[1]);
+                    mma_bf16(sc[2 * kbi + 1], qf[ks], kf[2], kf[3]);
                 }
-            float corr[2];
+            }
+            // ---- scale; mask only where a row of the warp does not see a key of the warp's span
+            const bool all_seen = w_key0 >= k_begin && w_key0 + 16 * KB <= k_end && w_key0 >= warp_lo_hi &&
+                                  w_key0 + 16 * KB - 1 <= warp_pos_lo && row_base + 15 < n_rows;
+            float tmax[2] = {-INFINITY, -INFINITY};
+            if (all_seen) {
+#pragma unroll
+                for (int j = 0; j < 2 * KB; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        sc[j][e] *= p.scale_log2;
+                        tmax[e >> 1] = fmaxf(tmax[e >> 1], sc[j][e]);
+                    }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 2 * KB; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = w_key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+                        const int h = e >> 1;
+                        const bool ok = key <= pos_r[h] && key >= lo_r[h] && key >= k_begin && key < k_end;
+                        const float v = ok ? sc[j][e] * p.scale_log2 : -INFINITY;
+                        sc[j][e] = v;
+                        tmax[h] = fmaxf(tmax[h], v);
+                    }
+            }
+            float corr[2], m_use[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 1));
                 tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
-                float m_new = fmaxf(m_r[h], tmax[h]);
-                corr[h] = (m_r[h] == -INFINITY) ? 0.0f : exp2f(m_r[h] - m_new);
+                const float m_new = fmaxf(m_r[h], tmax[h]);
+                m_use[h] = (m_new == -INFINITY) ? 0.0f : m_new;                  // a row that has seen nothing yet
+                corr[h] = ex2(m_r[h] - m_use[h]);                               // ex2(-inf) = 0
                 m_r[h] = m_new;
             }
             float psum[2] = {0.0f, 0.0f};
-            unsigned pf[4];
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                float e0 = (sc[j][0] == -INFINITY) ? 0.0f : exp2f(sc[j][0] - m_r[0]);
-                float e1 = (sc[j][1] == -INFINITY) ? 0.0f : exp2f(sc[j][1] - m_r[0]);
-                float e2 = (sc[j][2] == -INFINITY) ? 0.0f : exp2f(sc[j][2] - m_r[1]);
-                float e3 = (sc[j][3] == -INFINITY) ? 0.0f : exp2f(sc[j][3] - m_r[1]);
-                psum[0] += e0 + e1;
-                psum[1] += e2 + e3;
-                pf[j * 2 + 0] = pack_bf16(e0, e1);
-                pf[j * 2 + 1] = pack_bf16(e2, e3);
+            for (int j = 0; j < 2 * KB; ++j) {
+                sc[j][0] = ex2(sc[j][0] - m_use[0]);
+                sc[j][1] = ex2(sc[j][1] - m_use[0]);
+                sc[j][2] = ex2(sc[j][2] - m_use[1]);
+                sc[j][3] = ex2(sc[j][3] - m_use[1]);
+                psum[0] += sc[j][0] + sc[j][1];
+                psum[1] += sc[j][2] + sc[j][3];
             }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -277,15 +316,22 @@ attention_mma_kernel(AttnMmaParams p) {
             for (int t = 0; t < NT_O; ++t) {
                 o[t][0] *= corr[0]; o[t][1] *= corr[0]; o[t][2] *= corr[1]; o[t][3] *= corr[1];
             }
-            // o += p . v   (16 keys, all HD columns, two 8-wide column tiles per ldmatrix)
+            // ---- o += p . v, block by block (16 keys, all HD columns, two 8-wide column tiles per ldmatrix)
 #pragma unroll
-            for (int t2 = 0; t2 < NT_O / 2; ++t2) {
-                unsigned vf[4];
-                int r = kb * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-                int c = t2 * 2 + (lane >> 4);
-                ldmatrix_x4_trans(vf, vt + swz<HD>(r, c));
-                mma_bf16(o[t2 * 2 + 0], pf, vf[0], vf[1]);
-                mma_bf16(o[t2 * 2 + 1], pf, vf[2], vf[3]);
+            for (int kbi = 0; kbi < KB; ++kbi) {
+                unsigned pf[4];
+                pf[0] = pack_bf16(sc[2 * kbi][0], sc[2 * kbi][1]);
+                pf[1] = pack_bf16(sc[2 * kbi][2], sc[2 * kbi][3]);
+                pf[2] = pack_bf16(sc[2 * kbi + 1][0], sc[2 * kbi + 1][1]);
+                pf[3] = pack_bf16(sc[2 * kbi + 1][2], sc[2 * kbi + 1][3]);
+                const unsigned char* vblock = vt + (BY_KEYS ? warp : kbi) * BLOCK_BYTES;
+#pragma unroll
+                for (int t2 = 0; t2 < NT_O / 2; ++t2) {
+                    unsigned vf[4];
+                    ldmatrix_x4_trans(vf, vblock + voff[t2]);
+                    mma_bf16(o[t2 * 2 + 0], pf, vf[0], vf[1]);
+                    mma_bf16(o[t2 * 2 + 1], pf, vf[2], vf[3]);
+                }
             }
         }
         __syncthreads();                       // the stage's buffer may be refilled
@@ -361,19 +407,28 @@ attention_mma_kernel(AttnMmaParams p) {
     }
 }
 
-template <int HD>
-static size_t am_smem_bytes() { return (size_t)64 * HD * 2 + (size_t)2 * AM_STAGES * AM_STAGE_KEYS * HD * 2; }
+template <int HD, bool BY_KEYS, int STAGES>
+static size_t am_smem_bytes() {
+    return (size_t)(BY_KEYS ? 16 : 64) * HD * 2 + (size_t)2 * STAGES * AM_STAGE_KEYS * HD * 2;
+}
 
-template <int HD, bool BY_KEYS>
-static int am_launch(const AttnMmaParams& p, int n_qblk, int n_splits, cudaStream_t stream) {
-    auto kern = attention_mma_kernel<HD, BY_KEYS>;
-    size_t smem = am_smem_bytes<HD>();
+template <int HD, bool BY_KEYS, int STAGES>
+static int am_launch_stages(const AttnMmaParams& p, int n_qblk, int n_splits, cudaStream_t stream) {
+    auto kern = attention_mma_kernel<HD, BY_KEYS, STAGES>;
+    size_t smem = am_smem_bytes<HD, BY_KEYS, STAGES>();
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(n_qblk, p.nkv, n_splits);
-    launch(kern, grid, dim3(AM_THREADS), smem, stream, p);
-    BG_LAUNCH_CHECK();
+    e = launch(kern, grid, dim3(AM_THREADS), smem, stream, p);
+    if (e != cudaSuccess) return (int)e;
     return BG_OK;
+}
+
+template <int HD, bool BY_KEYS>
+static int am_launch(const AttnMmaParams& p, int n_qblk, int n_splits, cudaStream_t stream) {
+    if (BY_KEYS && (long long)n_qblk * p.nkv * n_splits > 2 * 148)
+        return am_launch_stages<HD, BY_KEYS, 2>(p, n_qblk, n_splits, stream);
+    return am_launch_stages<HD, BY_KEYS, 3>(p, n_qblk, n_splits, stream);
 }
 
 }  // namespace bg
@@ -406,7 +461,9 @@ extern "C" int bg_attention_mma_partial(const void* q, int q_stride, const void*
     if ((q_stride % 8) != 0 || ((uintptr_t)q % 16) != 0 || ((uintptr_t)kv_pool % 16) != 0) return BG_ERR_ALIGN;
     AttnMmaParams p;
     p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.kv_pool = (const __nv_bfloat16*)kv_pool;
-    p.num_pages = num_pages; p.page_size = page_size; p.block_table = block_table; p.max_pages = max_pages;
+    p.num_pages = num_pages; p.page_size = page_size; p.block_table = block_table;
+    p.page_shift = -1;
+    for (int sh = 0; sh < 30; ++sh) if ((1 << sh) == page_size) p.page_shift = sh; p.max_pages = max_pages;
     p.positions = positions; p.qblk = qblk; p.part_o = part_o; p.part_ml = part_ml; p.max_splits = max_splits;
     p.nh = nh; p.nkv = nkv; p.group = nh / nkv; p.window = window; p.split = split;
     p.scale_log2 = scale * AM_LOG2E; p.status = status;

@@ -286,7 +286,11 @@ def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table
     "generic" and "mma_keys" cut the keys into splits of `split` positions, write partial results and
     merge them; "mma_rows" lets one CTA walk all keys of its query block and writes `out` directly."""
     _cuda(q, kv_pool, block_table, positions, qblk, out)
-    _i32(positions, "positions"); _i32(block_table, "block_table"); _i32(qblk, "qblk")
+    _i32(positions, "positions"); _i32(block_table, "block_table")
+    if qblk is not None:
+        _i32(qblk, "qblk")
+    elif kernel != "mma_keys" or n_qblk != n_rows:
+        raise KernelError("attention: only the decoding kernel runs without a list of query blocks (block i = row i)")
     num_pages, two, nkv_, page_size, hd_ = kv_pool.shape
     if (two, nkv_, hd_) != (2, nkv, hd) or not kv_pool.is_contiguous():
         raise KernelError(f"attention: kv_pool is {tuple(kv_pool.shape)}, expected [pages, 2, {nkv}, page, {hd}]")
@@ -313,7 +317,8 @@ def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table
         if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16:
             raise KernelError("attention: the tensor-core kernel takes bfloat16 queries and caches")
         _check(L.bg_attention_mma_partial(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
-                                          block_table.shape[1], _p(positions), _p(qblk), n_qblk, _p(part_o),
+                                          block_table.shape[1], _p(positions), _p(qblk) if qblk is not None else None,
+                                          n_qblk, _p(part_o),
                                           _p(part_ml), n_splits, n_splits, nh, nkv, hd, window, split, 1,
                                           float(scale), None, 0, _p(status), _stream()), "attention_mma_partial")
     else:

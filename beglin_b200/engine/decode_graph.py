@@ -33,6 +33,7 @@ class _StaticBatch:
         self.entries = []
         self.n_logit_rows = n
         self.decode_only = True
+        self.implicit_blocks = True
         self.max_position = cache.max_context - 1
         i32 = dict(dtype=torch.int32, device=device)
         self.token_ids = torch.zeros(n, **i32)
@@ -45,8 +46,10 @@ class _StaticBatch:
         self._qblk = torch.stack([torch.arange(n), torch.arange(n), torch.ones(n, dtype=torch.long)], dim=1) \
             .to(torch.int32).to(device).contiguous()
 
-    def query_blocks(self, bq: int) -> Tuple[torch.Tensor, int]:
-        return self._qblk, self.n_rows
+    def query_blocks(self, bq: int) -> Tuple[Optional[torch.Tensor], int]:
+        """Block i is row i of request i.  The decoding kernel knows that without a list (bq == 1 and
+        every request brings one row), which spares it a dependent load; other kernels get the list."""
+        return (None if bq == 1 and self.implicit_blocks else self._qblk), self.n_rows
 
 
 class _Staging:

@@ -77,6 +77,9 @@ class GQAAttention:
                            cache.pool if self.spec.own_kv else None, cache.page_size, self.ctx.status)
         kernel, bq, tile = self.plans[bool(getattr(batch, "decode_only", False))]
         qblk, n_qblk = batch.query_blocks(bq)
+        if qblk is None and kernel != "mma_keys":
+            batch.implicit_blocks = False              # this kernel wants the list
+            qblk, n_qblk = batch.query_blocks(bq)
         out = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=h.device)
         ops.attention(q, q.stride(0), cache.pool, cache.block_table, batch.positions, qblk, n_qblk,
                       batch.max_position, T, self.nh, self.nkv, self.hd, self.window, self.ctx.kv_split, tile, bq,
