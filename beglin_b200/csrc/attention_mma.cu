@@ -251,14 +251,35 @@ attention_mma_kernel(AttnMmaParams p) {
 #pragma unroll
             for (int j = 0; j < 2 * KB; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f; }
             const unsigned char* kwarp = kt + (BY_KEYS ? warp * BLOCK_BYTES : 0);
+            if (BY_KEYS) {
+                // one block of 16 keys per warp: the k-steps go round-robin into four accumulator pairs, so
+                // eight short chains of dependent MMAs run side by side instead of two long ones
+                float part[4][2][4];
 #pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks) {
+                for (int a = 0; a < 4; ++a)
 #pragma unroll
-                for (int kbi = 0; kbi < KB; ++kbi) {
+                    for (int j = 0; j < 2; ++j) { part[a][j][0] = part[a][j][1] = part[a][j][2] = part[a][j][3] = 0.0f; }
+#pragma unroll
+                for (int ks = 0; ks < KSTEPS; ++ks) {
                     unsigned kf[4];
-                    ldmatrix_x4(kf, kwarp + kbi * BLOCK_BYTES + koff[ks]);
-                    mma_bf16(sc[2 * kbi], qf[ks], kf[0], kf[1]);
-                    mma_bf16(sc[2 * kbi + 1], qf[ks], kf[2], kf[3]);
+                    ldmatrix_x4(kf, kwarp + koff[ks]);
+                    mma_bf16(part[ks & 3][0], qf[ks], kf[0], kf[1]);
+                    mma_bf16(part[ks & 3][1], qf[ks], kf[2], kf[3]);
+                }
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sc[j][e] = (part[0][j][e] + part[1][j][e]) + (part[2][j][e] + part[3][j][e]);
+            } else {
+#pragma unroll
+                for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+                    for (int kbi = 0; kbi < KB; ++kbi) {
+                        unsigned kf[4];
+                        ldmatrix_x4(kf, kwarp + kbi * BLOCK_BYTES + koff[ks]);
+                        mma_bf16(sc[2 * kbi], qf[ks], kf[0], kf[1]);
+                        mma_bf16(sc[2 * kbi + 1], qf[ks], kf[2], kf[3]);
+                    }
                 }
             }
             // ---- scale; mask only where a row of the warp does not see a key of the warp's span

@@ -275,6 +275,20 @@ def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, deco
     return "generic", bq.value, tile.value
 
 
+def decode_split(n_streams: int, context: int) -> int:
+    """Keys per CTA for the decoding kernel.  Each (request, kv head) is a stream of `context` keys;
+    it is cut so that the grid has about three CTAs per SM: many short ranges when few requests decode
+    (latency of one CTA is what counts), few long ones when many do (a CTA's start-up and the merging
+    of its result are spread over more keys).  A multiple of 64 between 128 and 2048; it depends on
+    the shapes of the step only."""
+    want = max(1, (3 * 148) // max(1, n_streams))
+    split = -(-context // want)
+    split = int(min(2048, max(128, -(-split // 64) * 64)))
+    if split < 256 and n_streams * -(-context // 256) >= 148:
+        split = 256                       # ranges of 256 already fill the machine
+    return split
+
+
 def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table: torch.Tensor,
               positions: torch.Tensor, qblk: torch.Tensor, n_qblk: int, max_position: int, n_rows: int, nh: int,
               nkv: int, hd: int, window: int, split: int, tile: int, bq: int, scale: float, out: torch.Tensor,
@@ -305,6 +319,8 @@ def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table
                                           nh, nkv, hd, window, split, 0, float(scale), _p(out), out.stride(0),
                                           _p(status), _stream()), "attention_mma")
         return
+    if kernel == "mma_keys":
+        split = decode_split(n_qblk * nkv, max_position + 1)
     n_splits = max_position // split + 1
     part_o = torch.empty((n_rows * nh * n_splits, hd), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((n_rows * nh * n_splits, 2), dtype=torch.float32, device=q.device)
