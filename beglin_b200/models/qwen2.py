@@ -105,13 +105,12 @@ class Qwen2Config:
 
         tie = f.boolean("tie_word_embeddings")
         if names is not None:
+            # with a tensor list, presence decides, as in the reference, which never reads the key: the head
+            # is lm_head.weight when that tensor exists, else the embedding table (qwen_infer.c:318-319)
             has_head = "lm_head.weight" in names
-            if tie is None:
-                tie = not has_head           # the reference infers tying from the tensor (:318-319)
-            elif tie and has_head:
-                pass                         # a tied folder may still carry a copy; the table is used
-            elif not tie and not has_head:
+            if tie is False and not has_head:
                 raise ConfigError(f"{f.origin}: tie_word_embeddings=false but the tensor list has no lm_head.weight")
+            tie = not has_head
         elif tie is None:
             tie = False
 

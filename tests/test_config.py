@@ -97,6 +97,9 @@ def test_bias_and_tying_follow_the_tensor_list():
     assert cfg.qkv_bias is True and cfg.tie_word_embeddings is False
     with pytest.raises(ConfigError, match="lm_head"):
         load_config(dict(TINY_A, tie_word_embeddings=False), tensor_names=names)
+    # a folder that says "tied" but carries a head of its own: the tensor wins, as in the reference
+    _, cfg = load_config(dict(TINY_A, tie_word_embeddings=True), tensor_names=names + ["lm_head.weight"])
+    assert cfg.tie_word_embeddings is False
 
 
 def test_json_roundtrip_of_typed_config():

@@ -65,7 +65,8 @@ def test_four_ways_of_cutting(model_root, name, dtype):
         got = rl.run_in_process(eng, steps)
         eng.cache.check()
         assert eng.cache.free_pages() == eng.cache.num_pages and not eng.cache.live()
-        check_against_plain(got, folder, reqs, tol)
+        worst = check_against_plain(got, folder, reqs, tol)
+        print(f"{name} {dtype} {way}: worst relative error {worst:.3g} (limit {tol:g})")
         results[way] = got
         del eng
     if dtype == "float32":
