@@ -118,7 +118,14 @@ def _cuda(*tensors) -> None:
             raise KernelError("beglin_b200 kernels run on a CUDA device only; got a tensor on " + str(t.device))
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The raw handle of torch's current stream on the current device (a cheap call; the public
+    torch.cuda.current_stream() costs several microseconds, which counts at hundreds of launches a step)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -386,6 +393,15 @@ def gemm_bf16_tn(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
         raise KernelError("gemm_bf16_tn: bias must be float32 with one value per output feature")
     _check(lib().bg_gemm_bf16_tn(_p(w), N, K, w.stride(0), _p(x), T, x.stride(0), _p(bias), _p(out), _dt(out), N,
                                  splits, _p(status), _stream()), "gemm_bf16_tn")
+
+
+def gemm_bf16_tn_unchecked(x: torch.Tensor, w_ptr: int, n_out: int, k: int, ldw: int, bias_ptr, out: torch.Tensor,
+                           splits: int, status_ptr) -> None:
+    """gemm_bf16_tn for a caller that has checked the weight once (Linear): x must be contiguous
+    bfloat16 [T, k] and out contiguous [T, n_out] or float32 [splits, T, n_out]."""
+    _check(_lib.bg_gemm_bf16_tn(w_ptr, n_out, k, ldw, x.data_ptr(), x.shape[0], x.stride(0), bias_ptr, out.data_ptr(),
+                                F32 if out.dtype == torch.float32 else BF16, n_out, splits, status_ptr, _stream()),
+           "gemm_bf16_tn")
 
 
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],

@@ -25,6 +25,10 @@ class TensorCoreProduct:
         self.n_out, self.k = weight.shape
         self.tiles = -(-self.n_out // 128)
         self.k_blocks = -(-self.k // 64)
+        ops.lib()
+        self._w_ptr, self._ldw = weight.data_ptr(), weight.stride(0)
+        self._status_ptr = None if ctx.status is None else ctx.status.data_ptr()
+        self._splits = {}
 
     @staticmethod
     def takes(weight: torch.Tensor) -> bool:
@@ -38,6 +42,12 @@ class TensorCoreProduct:
         return T <= FEW_TOKENS
 
     def splits(self, T: int) -> int:
+        s = self._splits.get(T)
+        if s is None:
+            s = self._splits[T] = self._choose_splits(T)
+        return s
+
+    def _choose_splits(self, T: int) -> int:
         if T > FEW_TOKENS:
             return 1
         want = max(1, -(-SM_COUNT // self.tiles))                 # enough CTAs for every SM
@@ -53,7 +63,10 @@ class TensorCoreProduct:
             out = torch.empty((s, T, self.n_out), dtype=torch.float32, device=x.device)
         else:
             out = torch.empty((T, self.n_out), dtype=out_dtype, device=x.device)
-        ops.gemm_bf16_tn(x, self.weight, bias, out, s, self.ctx.status)
+        if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.shape[1] != self.k or x.stride(0) % 8:
+            raise ops.KernelError(f"the tcgen05 product takes contiguous bfloat16 rows of {self.k} features")
+        ops.gemm_bf16_tn_unchecked(x, self._w_ptr, self.n_out, self.k, self._ldw, None if bias is None else bias.data_ptr(),
+                                   out, s, self._status_ptr)
         return out
 
 
