@@ -336,7 +336,14 @@ extern "C" int bg_gemm_bf16_tn(const void* W, int n_out, int K, int ldw, const v
         case 16: return tc_launch<16, 4>(mw, mx, p, splits, stream);
         case 32: return tc_launch<32, 4>(mw, mx, p, splits, stream);
         case 64: return tc_launch<64, 4>(mw, mx, p, splits, stream);
-        case 128: return tc_launch<128, 6>(mw, mx, p, splits, stream);
-        default: return tc_launch<256, 4>(mw, mx, p, splits, stream);
+        case 128: return tc_launch<128, 3>(mw, mx, p, splits, stream);
+        default: {
+            // many tokens: the product is bound by the tensor cores.  With more CTAs than SMs, two stages keep
+            // a CTA under half of an SM's shared memory, so two CTAs share the SM and one's epilogue overlaps
+            // the other's MMAs; a grid that does not fill the machine gets the deeper pipeline instead.
+            const long long ctas = (long long)((n_out + TC_BM - 1) / TC_BM) * ((T + 255) / 256) * splits;
+            if (ctas > 148) return tc_launch<256, 2>(mw, mx, p, splits, stream);
+            return tc_launch<256, 4>(mw, mx, p, splits, stream);
+        }
     }
 }
