@@ -281,6 +281,66 @@ __global__ void rope_kv_append_kernel(const TS* __restrict__ src, int src_stride
     }
 }
 
+// The common bfloat16 case (one tensor, split-half pairs over the whole head, head_dim a multiple of
+// 16, bfloat16 cache): every thread rotates eight features of the first half of a head together with
+// their eight partners, with 16-byte loads and stores and no staging in shared memory.
+__global__ void __launch_bounds__(128)
+rope_kv_append_bf16_kernel(const __nv_bfloat16* __restrict__ src, int src_stride, __nv_bfloat16* __restrict__ q_out,
+                           int q_stride, const float2* __restrict__ cos_sin, const int* __restrict__ positions,
+                           const int* __restrict__ row_req, const int* __restrict__ block_table, int max_pages,
+                           __nv_bfloat16* __restrict__ kv_pool, int num_pages, int page_size, int nh, int nkv, int hd,
+                           unsigned* status) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int half = hd >> 1, chunks = half >> 3;              // 8-feature chunks per half head
+    const __nv_bfloat16* row = src + (size_t)t * src_stride;
+    const float2* cs = cos_sin + (size_t)t * half;
+    int page = -1, slot = 0;
+    if (kv_pool) {
+        const int pos = positions[t];
+        page = block_table[(size_t)row_req[t] * max_pages + pos / page_size];
+        slot = pos % page_size;
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0 && status) atomicOr(status, BG_STATUS_BAD_PAGE);
+            page = -1;
+        }
+    }
+    const int n_heads = nh + (kv_pool ? nkv : 0);
+    for (int item = threadIdx.x; item < n_heads * chunks; item += blockDim.x) {
+        const int h = item / chunks, c = item - h * chunks;
+        float a[8], b[8];
+        load8(row + (size_t)h * hd + 8 * c, a);
+        load8(row + (size_t)h * hd + half + 8 * c, b);
+        float ra[8], rb[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 f = cs[8 * c + i];
+            ra[i] = a[i] * f.x - b[i] * f.y;
+            rb[i] = b[i] * f.x + a[i] * f.y;
+        }
+        __nv_bfloat16* dst;
+        if (h < nh) {
+            dst = q_out + (size_t)t * q_stride + (size_t)h * hd;
+        } else {
+            if (page < 0) continue;
+            dst = kv_pool + ((size_t)page * 2 + 0) * nkv * page_size * hd + ((size_t)(h - nh) * page_size + slot) * hd;
+        }
+        store8(dst + 8 * c, ra);
+        store8(dst + half + 8 * c, rb);
+    }
+    if (kv_pool && page >= 0) {                                  // v: a plain copy
+        const __nv_bfloat16* v = row + (size_t)(nh + nkv) * hd;
+        __nv_bfloat16* vdst = kv_pool + ((size_t)page * 2 + 1) * nkv * page_size * hd;
+        const int vc = hd >> 3;
+        for (int item = threadIdx.x; item < nkv * vc; item += blockDim.x) {
+            const int h = item / vc, c = item - h * vc;
+            *reinterpret_cast<uint4*>(vdst + ((size_t)h * page_size + slot) * hd + 8 * c) =
+                *reinterpret_cast<const uint4*>(v + (size_t)h * hd + 8 * c);
+        }
+    }
+}
+
 }  // namespace bg
 
 using namespace bg;
@@ -425,6 +485,15 @@ extern "C" int bg_rope_kv_append(const void* src, int src_dtype, int src_stride,
     if (T <= 0) return BG_OK;
     if (rot < 0 || rot > hd || (rot & 1) || parts < 1) return BG_ERR_SHAPE;
     if (rot > 0 && !cos_sin) return BG_ERR_SHAPE;
+    if (src_dtype == BG_DTYPE_BF16 && q_dtype == BG_DTYPE_BF16 && (!kv_pool || cache_dtype == BG_DTYPE_BF16) && parts == 1 &&
+        !interleaved && rot == hd && hd % 16 == 0 && src_stride % 8 == 0 && q_stride % 8 == 0 &&
+        (uintptr_t)src % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)kv_pool % 16 == 0) {
+        launch(rope_kv_append_bf16_kernel, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)src, src_stride,
+               (__nv_bfloat16*)q_out, q_stride, (const float2*)cos_sin, positions, row_req, block_table, max_pages,
+               (__nv_bfloat16*)kv_pool, num_pages, page_size, nh, nkv, hd, status);
+        BG_LAUNCH_CHECK();
+        return BG_OK;
+    }
     if (!kv_pool) cache_dtype = BG_DTYPE_F32;
     BG_DISPATCH_DTYPE(src_dtype, TS, return (rope_kv_q<TS>(src, src_stride, parts, (size_t)part_stride, q_out, q_dtype,
         q_stride, cos_sin, positions, row_req, block_table, max_pages, kv_pool, cache_dtype, num_pages, page_size, T, nh,

@@ -118,8 +118,9 @@ def test_gemm_f32_is_true_float_and_row_invariant(ops):
 
 @pytest.mark.parametrize("interleaved", [False, True])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_rope_table_and_kv_append(ops, interleaved, dtype):
-    nh, nkv, hd, rot, page, T = 3, 2, 48, 32, 8, 6
+@pytest.mark.parametrize("hd,rot", [(48, 32), (64, 64), (128, 128)])      # partial rotary; whole heads (16-byte path)
+def test_rope_table_and_kv_append(ops, interleaved, dtype, hd, rot):
+    nh, nkv, page, T = 3, 2, 8, 6
     theta = 50000.0
     positions = torch.tensor([9, 10, 11, 0, 40, 7], dtype=torch.int32, device=DEV)
     row_req = torch.tensor([0, 0, 0, 1, 2, 1], dtype=torch.int32, device=DEV)
