@@ -217,6 +217,13 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
 // pos % page_size.  Pairs are (i, i + half) for split-half and (2i, 2i + 1) for interleaved pairing
 // (qwen_infer.c:782-790); features from rot on are copied.  src may be the partial sums of a
 // split-K product.  The pool of one layer is [num_pages][2][nkv][page_size][hd].
+// One rotated feature: me*cos - other*sin for the first of a pair, me*cos + other*sin for the second,
+// with the rounding steps spelled out so that every kernel below gives the same bits.
+__device__ __forceinline__ float rope_rotate(float me, float other, float2 f, bool first) {
+    const float cross = __fmul_rn(other, f.y);
+    return __fmaf_rn(me, f.x, first ? -cross : cross);
+}
+
 template <typename TS, typename TQ, typename TC>
 __global__ void rope_kv_append_kernel(const TS* __restrict__ src, int src_stride, int parts, size_t part_stride,
                                       TQ* __restrict__ q_out, int q_stride, const float2* __restrict__ cos_sin,
@@ -256,8 +263,7 @@ __global__ void rope_kv_append_kernel(const TS* __restrict__ src, int src_stride
         if (interleaved) { pi = i >> 1; first = (i & 1) == 0; partner = first ? i + 1 : i - 1; }
         else { first = i < half; pi = first ? i : i - half; partner = first ? i + half : i - half; }
         float other = head[partner];
-        float2 f = cs[pi];
-        return first ? (me * f.x - other * f.y) : (me * f.x + other * f.y);
+        return rope_rotate(me, other, cs[pi], first);
     };
     TQ* qo = q_out + (size_t)t * q_stride;
     for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
@@ -316,8 +322,8 @@ rope_kv_append_bf16_kernel(const __nv_bfloat16* __restrict__ src, int src_stride
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float2 f = cs[8 * c + i];
-            ra[i] = a[i] * f.x - b[i] * f.y;
-            rb[i] = b[i] * f.x + a[i] * f.y;
+            ra[i] = rope_rotate(a[i], b[i], f, true);
+            rb[i] = rope_rotate(b[i], a[i], f, false);
         }
         __nv_bfloat16* dst;
         if (h < nh) {
@@ -339,6 +345,51 @@ rope_kv_append_bf16_kernel(const __nv_bfloat16* __restrict__ src, int src_stride
                 *reinterpret_cast<const uint4*>(v + (size_t)h * hd + 8 * c);
         }
     }
+}
+
+// For steps of few tokens: one block per (token, head) and one thread per feature, which sums its own
+// value and its partner's from the partial sums directly.  Nothing is staged and nothing is waited for
+// but the loads themselves, which are all in flight together.
+template <typename TS, typename TQ, typename TC>
+__global__ void rope_kv_append_heads_kernel(const TS* __restrict__ src, int src_stride, int parts, size_t part_stride,
+                                            TQ* __restrict__ q_out, int q_stride, const float2* __restrict__ cos_sin,
+                                            const int* __restrict__ positions, const int* __restrict__ row_req,
+                                            const int* __restrict__ block_table, int max_pages,
+                                            TC* __restrict__ kv_pool, int num_pages, int page_size,
+                                            int nh, int nkv, int hd, int rot, int interleaved, unsigned* status) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y, i = threadIdx.x;
+    if (i >= hd) return;
+    const int half = rot >> 1;
+    const bool is_v = h >= nh + nkv;
+    const TS* head = src + (size_t)t * src_stride + (size_t)h * hd;
+    int page = 0, slot = 0;
+    if (h >= nh) {
+        const int pos = positions[t];
+        page = block_table[(size_t)row_req[t] * max_pages + pos / page_size];
+        slot = pos % page_size;
+    }
+    float val = sum_parts(head + i, parts, part_stride);
+    if (!is_v && i < rot) {
+        int pi, partner;
+        bool first;
+        if (interleaved) { pi = i >> 1; first = (i & 1) == 0; partner = first ? i + 1 : i - 1; }
+        else { first = i < half; pi = first ? i : i - half; partner = first ? i + half : i - half; }
+        const float other = sum_parts(head + partner, parts, part_stride);
+        val = rope_rotate(val, other, cos_sin[(size_t)t * half + pi], first);
+    }
+    if (h < nh) {
+        q_out[(size_t)t * q_stride + (size_t)h * hd + i] = from_float<TQ>(val);
+        return;
+    }
+    if (page < 0 || page >= num_pages) {
+        if (i == 0 && status) atomicOr(status, BG_STATUS_BAD_PAGE);
+        return;
+    }
+    const int kvh = is_v ? h - nh - nkv : h - nh;
+    TC* dst = kv_pool + ((size_t)page * 2 + (is_v ? 1 : 0)) * nkv * page_size * hd + ((size_t)kvh * page_size + slot) * hd;
+    dst[i] = from_float<TC>(val);
 }
 
 }  // namespace bg
@@ -455,6 +506,14 @@ static int rope_kv_cache(const void* src, int src_stride, int parts, size_t part
                          const float* cos_sin, const int* positions, const int* row_req, const int* block_table,
                          int max_pages, void* kv_pool, int cache_dtype, int num_pages, int page_size, int T, int nh,
                          int nkv, int hd, int rot, int interleaved, unsigned* status, cudaStream_t stream) {
+    if (T <= 64 && hd <= 1024) {
+        dim3 grid(T, nh + (kv_pool ? 2 * nkv : 0));
+        BG_DISPATCH_DTYPE(cache_dtype, TC, launch(rope_kv_append_heads_kernel<TS, TQ, TC>, grid, dim3((hd + 31) / 32 * 32), 0,
+            stream, (const TS*)src, src_stride, parts, part_stride, (TQ*)q_out, q_stride, (const float2*)cos_sin, positions,
+            row_req, block_table, max_pages, (TC*)kv_pool, num_pages, page_size, nh, nkv, hd, rot, interleaved, status));
+        BG_LAUNCH_CHECK();
+        return BG_OK;
+    }
     const size_t smem = (size_t)(nh + 2 * nkv) * hd * sizeof(float);
     if (smem > 48 * 1024) return BG_ERR_SHAPE;
     BG_DISPATCH_DTYPE(cache_dtype, TC, launch(rope_kv_append_kernel<TS, TQ, TC>, dim3(T), dim3(256), smem, stream,
