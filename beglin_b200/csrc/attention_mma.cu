@@ -105,18 +105,14 @@ attention_mma_kernel(AttnMmaParams p) {
     const int nq = p.qblk ? p.qblk[qb * 3 + 2] : 1;
     if (nq <= 0) return;
     const int group = p.group;
-    const int pos_first = p.positions[row0];
-    const int pos_last = p.positions[row0 + nq - 1];
-    const int lo_first = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
-    const bool direct = !BY_KEYS && p.out != nullptr;
-    const int k_begin = direct ? lo_first : max(sp * p.split, lo_first);
-    const int k_end = direct ? pos_last + 1 : min((sp + 1) * p.split, pos_last + 1);
-    if (k_begin >= k_end) return;
-
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n_rows = nq * group;             // <= 64 (rows) or <= 16 (keys)
 
-    // ---- queries of the block into shared memory (rows beyond n_rows are zero)
+    // ---- everything that does not depend on the positions goes out first, so that the positions, the
+    // queries and the block table arrive in one round trip: the queries of the block into shared memory
+    // (rows beyond n_rows are zero) ...
+    const int pos_first = p.positions[row0];
+    const int pos_last = p.positions[row0 + nq - 1];
     for (int idx = tid; idx < Q_ROWS * CH; idx += AM_THREADS) {
         int r = idx / CH, c = idx - r * CH;
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -126,19 +122,29 @@ attention_mma_kernel(AttnMmaParams p) {
         }
         *reinterpret_cast<uint4*>(q_s + swz<HD>(r, c)) = v;
     }
-
-    // ---- stage loader: thread t copies half a key row of K and of V.  The block-table entries of 128
-    // pages at a time are kept in shared memory, so a stage's copies start without a table load of
-    // their own (a stage of 64 keys never straddles two such groups).
+    // ... and the block-table entries of 128 pages at a time, kept in shared memory so that a stage's
+    // copies start without a table load of their own (a stage of 64 keys never straddles two such groups).
+    // The group fetched here is the one the first keys of this CTA's range lie in when there is no window.
     __shared__ int table_s[AM_TABLE];
+    const bool direct = !BY_KEYS && p.out != nullptr;
+    const int pre_key = direct ? 0 : sp * p.split;
+    const int pre_group = (p.page_shift >= 0 ? pre_key >> p.page_shift : pre_key / p.page_size) / AM_TABLE;
+    for (int i = tid; i < AM_TABLE; i += AM_THREADS) {
+        const int pi = pre_group * AM_TABLE + i;
+        table_s[i] = pi < p.max_pages ? p.block_table[(size_t)req * p.max_pages + pi] : -1;
+    }
+
+    const int lo_first = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int k_begin = direct ? lo_first : max(sp * p.split, lo_first);
+    const int k_end = direct ? pos_last + 1 : min((sp + 1) * p.split, pos_last + 1);
+    if (k_begin >= k_end) return;
+
+    // ---- stage loader: thread t copies 16-byte pieces of key rows of K and of V
     const int first_stage_key = (k_begin / AM_STAGE_KEYS) * AM_STAGE_KEYS;
     const int n_stage = (k_end - first_stage_key + AM_STAGE_KEYS - 1) / AM_STAGE_KEYS;
     const int last_page = (k_end - 1) / p.page_size;
-    int table_group = (first_stage_key / p.page_size) / AM_TABLE;     // the first group goes out with the queries
-    for (int i = tid; i < AM_TABLE; i += AM_THREADS) {
-        const int pi = table_group * AM_TABLE + i;
-        table_s[i] = pi <= last_page ? p.block_table[(size_t)req * p.max_pages + pi] : -1;
-    }
+    int table_group = (first_stage_key / p.page_size) / AM_TABLE;
+    if (table_group != pre_group) table_group = -1;               // a window moved the range: fetched by the loader
     __syncthreads();                           // q_s and table_s are complete
     const size_t page_elems = (size_t)2 * p.nkv * p.page_size * HD;
     const size_t v_off = (size_t)p.nkv * p.page_size * HD;
