@@ -120,18 +120,26 @@ __global__ void __launch_bounds__(512) add_rmsnorm_parts_kernel(float* __restric
     extern __shared__ float row_buf[];
     __shared__ float red[32];
     pdl_launch();
+    // the norm's weight is written by no kernel of the step: the first chunk's values are fetched while
+    // the kernel that produces the addends may still be running
+    const int d4 = d >> 2;
+    float w0[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if ((int)threadIdx.x < d4) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w0[j] = to_float(w[4 * threadIdx.x + j]);
+    }
     pdl_wait();
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float4* xr = reinterpret_cast<float4*>(x + (size_t)s * d);
     float4* rb = reinterpret_cast<float4*>(row_buf);
-    const int d4 = d >> 2;
     float ss = 0.0f;
+    float4 mine = make_float4(0.0f, 0.0f, 0.0f, 0.0f);          // this thread's first chunk stays in registers
     for (int i = threadIdx.x; i < d4; i += blockDim.x) {
         float4 a = sum_parts4(reinterpret_cast<const float4*>(delta + (size_t)s * d) + i, parts, part_stride >> 2);
         float4 v = xr[i];
         v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
-        rb[i] = v;
+        if (i == (int)threadIdx.x) mine = v; else rb[i] = v;
         if (update) xr[i] = v;
         ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
     }
@@ -139,11 +147,14 @@ __global__ void __launch_bounds__(512) add_rmsnorm_parts_kernel(float* __restric
     const float inv = 1.0f / sqrtf(ss / (float)d + eps);
     TO* o = out + (size_t)r * d;
     for (int i = threadIdx.x; i < d4; i += blockDim.x) {
-        float4 v = rb[i];
-        o[4 * i + 0] = from_float<TO>(v.x * inv * to_float(w[4 * i + 0]));
-        o[4 * i + 1] = from_float<TO>(v.y * inv * to_float(w[4 * i + 1]));
-        o[4 * i + 2] = from_float<TO>(v.z * inv * to_float(w[4 * i + 2]));
-        o[4 * i + 3] = from_float<TO>(v.w * inv * to_float(w[4 * i + 3]));
+        const bool first = i == (int)threadIdx.x;
+        float4 v = first ? mine : rb[i];
+        const float g0 = first ? w0[0] : to_float(w[4 * i + 0]), g1 = first ? w0[1] : to_float(w[4 * i + 1]);
+        const float g2 = first ? w0[2] : to_float(w[4 * i + 2]), g3 = first ? w0[3] : to_float(w[4 * i + 3]);
+        o[4 * i + 0] = from_float<TO>(v.x * inv * g0);
+        o[4 * i + 1] = from_float<TO>(v.y * inv * g1);
+        o[4 * i + 2] = from_float<TO>(v.z * inv * g2);
+        o[4 * i + 3] = from_float<TO>(v.w * inv * g3);
     }
 }
 
