@@ -89,7 +89,7 @@ def attention_decode(a) -> None:
 def attention_prefill(a) -> None:
     T, nh, nkv, hd, page = a.tokens, a.heads, a.kv_heads, a.head_dim, a.page
     pool, bt = _filled_cache(1, T, nkv, hd, page)
-    kernel, bq, tile = ops.attention_plan(nh // nkv, hd, torch.bfloat16, False)
+    kernel, bq, tile = ops.attention_plan(nh // nkv, hd, torch.bfloat16, False, a.kernel)
     q = torch.randn(T, nh * hd, device=DEV).to(torch.bfloat16)
     positions = torch.arange(T, dtype=torch.int32, device=DEV)
     blocks = [(0, b, min(bq, T - b)) for b in range(0, T, bq)]
@@ -125,6 +125,7 @@ def main() -> None:
     d.set_defaults(fn=attention_decode)
     p = sub.add_parser("attention-prefill")
     p.add_argument("--tokens", type=int, default=2048); p.set_defaults(fn=attention_prefill)
+    p.add_argument("--kernel", default="auto", choices=["auto", "mma", "tcgen05", "generic"])
     for s in (d, p):
         s.add_argument("--heads", type=int, default=12); s.add_argument("--kv-heads", type=int, default=2)
         s.add_argument("--head-dim", type=int, default=128); s.add_argument("--page", type=int, default=16)

@@ -38,6 +38,9 @@ _SIGNATURES = {
     "bg_attention_mma_partial": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                  _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                  _c_int, _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p],
+    "bg_attention_tc_plan": [_c_int, _c_int, ctypes.POINTER(_c_int)],
+    "bg_attention_tc": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
+                        _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     "bg_gemm_f32_nt": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_void_p],
     "bg_gemm_bf16_tn": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
@@ -259,14 +262,25 @@ def rope_kv_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh: int,
                                    _p(status), _stream()), "rope_kv_append")
 
 
+# choices of `prefer` under which prompt portions run the tcgen05 kernel
+TC_ROWS_FOR = ("tcgen05",)
+
+
 def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, decode_only: bool = False,
                    prefer: str = "auto") -> Tuple[str, int, int]:
     """(kernel, rows per query block, keys per tile) for these sizes.  Kernels: "mma_keys" (tensor
     cores, one token per block, for steps of single tokens), "mma_rows" (tensor cores, up to 64 rows
     per block) and "generic" (CUDA cores, every size up to head_dim 256, float or bfloat16)."""
     L = lib()
-    if prefer not in ("auto", "generic", "mma"):
+    if prefer not in ("auto", "generic", "mma", "tcgen05"):
         raise KernelError(f"unknown attention kernel choice '{prefer}'")
+    if dtype == torch.bfloat16 and not decode_only and prefer in TC_ROWS_FOR:
+        bq = _c_int(0)
+        if L.bg_attention_tc_plan(group, hd, ctypes.byref(bq)) == 0:
+            return "tc_rows", bq.value, 64
+        if prefer == "tcgen05":
+            raise KernelError(f"the tcgen05 attention kernel does not take head_dim {hd} with {group} query heads "
+                              "per kv head (head_dim 64 or 128; at most 128 heads per kv head)")
     if dtype == torch.bfloat16 and prefer != "generic":
         bq = _c_int(0)
         if L.bg_attention_mma_plan(group, hd, 1 if decode_only else 0, ctypes.byref(bq)) == 0:
@@ -312,12 +326,21 @@ def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table
         _i32(qblk, "qblk")
     elif kernel != "mma_keys" or n_qblk != n_rows:
         raise KernelError("attention: only the decoding kernel runs without a list of query blocks (block i = row i)")
+    if kernel == "tc_rows" and status is None:
+        raise KernelError("attention: the tcgen05 kernel wants a status word (its waits are bounded)")
     num_pages, two, nkv_, page_size, hd_ = kv_pool.shape
     if (two, nkv_, hd_) != (2, nkv, hd) or not kv_pool.is_contiguous():
         raise KernelError(f"attention: kv_pool is {tuple(kv_pool.shape)}, expected [pages, 2, {nkv}, page, {hd}]")
     if out.stride(1) != 1 or out.shape[1] < nh * hd or out.shape[0] < n_rows:
         raise KernelError("attention: out must be [T, nh*hd] with unit inner stride")
     L = lib()
+    if kernel == "tc_rows":
+        if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+            raise KernelError("attention: the tcgen05 kernel takes bfloat16 queries, caches and outputs")
+        _check(L.bg_attention_tc(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
+                                 block_table.shape[1], _p(positions), _p(qblk), n_qblk, _p(out), out.stride(0), nh, nkv,
+                                 hd, window, float(scale), _p(status), _stream()), "attention_tcgen05")
+        return
     if kernel == "mma_rows":
         if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
             raise KernelError("attention: the tensor-core kernel takes bfloat16 queries, caches and outputs")

@@ -183,7 +183,8 @@ def test_rope_table_and_kv_append(ops, interleaved, dtype, hd, rot):
         ops.raise_on_status(status)
 
 
-def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64, prefer="generic", decode_only=False):
+def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64, prefer="generic", decode_only=False,
+                    long=False):
     """Three requests in one step: a long prompt portion on top of earlier context, a decoded token
     far into a long context, and a fresh short prompt.  Pages are handed out in shuffled order and
     everything not held is poison."""
@@ -192,6 +193,8 @@ def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64, prefe
     ctx = [(37, 21), (150, 1), (0, 5)]               # (positions already in the cache, new rows)
     if decode_only:
         ctx = [(37, 1), (150, 1), (0, 1), (63, 1), (64, 1), (127, 1), (200, 1)]
+    if long:                                         # many key tiles: every pipeline stage is reused several times
+        ctx = [(517, 90), (1000, 1), (0, 333)] if not decode_only else [(517, 1), (1000, 1), (0, 1), (2100, 1)]
     total = [c + n for c, n in ctx]
     n_pages_each = [-(-t // page) for t in total]
     n_pages = sum(n_pages_each) + 5
@@ -215,13 +218,13 @@ def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64, prefe
     rows = sum(n for _, n in ctx)
     q = (torch.randn(rows, nh, hd) * 0.7).to(dtype)
     # make one far key stand out for the decoded token: its score dominates unless it is missed
-    far, far_row = 3, (1 if decode_only else 21)
+    far, far_row = 3, (1 if decode_only else ctx[0][1])
     q[far_row, :, :] = 0; q[far_row, :, 0] = 8.0
     ks[1][far, :, 0] = 8.0
     pool[int(bt[1, far // page]), 0, :, far % page, 0] = 8.0
     positions, row_req, qblk = [], [], []
     kernel, bq, tile = ops.attention_plan(group, hd, dtype, decode_only, prefer)
-    assert kernel == {"generic": "generic", "mma": "mma_keys" if decode_only else "mma_rows"}[prefer]
+    assert kernel == {"generic": "generic", "mma": "mma_keys" if decode_only else "mma_rows", "tcgen05": "tc_rows"}[prefer]
     r0 = 0
     for r, (c, n) in enumerate(ctx):
         positions += list(range(c, c + n)); row_req += [r] * n
@@ -279,6 +282,23 @@ def test_attention_bfloat16(ops, nh, nkv, hd, page):
 def test_attention_tensor_core_kernel(ops, nh, nkv, hd, page, window, decode_only):
     got, want = _attention_case(ops, nh, nkv, hd, page, torch.bfloat16, window, seed=5, prefer="mma",
                                 decode_only=decode_only)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(12, 2, 128, 16, None), (4, 4, 64, 8, None), (14, 2, 64, 32, 40),
+                                                   (16, 1, 128, 16, None), (12, 2, 128, 16, 100), (3, 1, 128, 4, None)])
+def test_attention_tcgen05_kernel(ops, nh, nkv, hd, page, window):
+    got, want = _attention_case(ops, nh, nkv, hd, page, torch.bfloat16, window, seed=5, prefer="tcgen05")
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("prefer,decode_only", [("tcgen05", False), ("mma", False), ("mma", True), ("generic", False)])
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(12, 2, 128, 16, None), (6, 2, 64, 16, 300)])
+def test_attention_long_contexts(ops, prefer, decode_only, nh, nkv, hd, page, window):
+    got, want = _attention_case(ops, nh, nkv, hd, page, torch.bfloat16, window, seed=9, split=256, prefer=prefer,
+                                decode_only=decode_only, long=True)
     assert torch.isfinite(got).all()
     assert (got - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
 
