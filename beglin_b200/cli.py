@@ -61,7 +61,7 @@ def main(argv: List[str]) -> int:
 
     maxseq = _env_int("QWEN_SAFETENSORS_MAXSEQ", 2048)
     dtype = os.environ.get("QWEN_DTYPE", "bf16")
-    page = _env_int("QWEN_PAGE_SIZE", 16)
+    page = _env_int("QWEN_PAGE_SIZE", 64)
     batch = max(1, _env_int("QWEN_BATCH", 8))
     seed_random = os.environ.get("QWEN_RANDOM")
     if seed_random and not os.path.exists(os.path.join(base, "model.safetensors")) \

@@ -9,11 +9,22 @@
 //   O += P V       tcgen05.mma, P K-major, the value tile as it lies in the cache (N-major), O in
 //                  tensor memory (head_dim columns); when a row's maximum grows, its O is rescaled
 //                  by tcgen05.ld / tcgen05.st before the product is issued.
-// Keys and values come from the pages through cp.async: three loader warps, one per stage, each
-// signs its stage as soon as its own copies have landed; one thread issues the MMAs.  Every wait on an mbarrier is bounded in time and records BG_STATUS_TIMEOUT.
+// Keys and values come from the pages by TMA (cp.async.bulk.tensor over the page pool seen as a 2-D
+// tensor [rows, head_dim], boxes of one page x 64 features, 128-byte swizzle), each through a ring of
+// three stages of its own: the keys' stage is free as soon as the scores are done, the values' only
+// after the second product.  Issuing an asynchronous operation (a copy, an MMA, a commit) costs the
+// issuing thread on the order of a hundred cycles, so the roles are spread over warps: warp 0 issues
+// S = Q K^T, warp 6 issues O += P V, warp 5 copies keys, warp 7 copies values, warps 1-4 are the
+// softmax.  A tile of values at the ragged end of the keys is completed by its loader (rows that the
+// block must not see are zeroed, so that 0 * garbage cannot be NaN) before it is released.
+// Every wait on an mbarrier is bounded in time and records BG_STATUS_TIMEOUT.
 //
 // The result is the finished row, out[t, h, :] = O / l, as in attention_mma.cu's rows arrangement.
 #include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #include "common.cuh"
 
@@ -22,8 +33,7 @@ namespace bg {
 constexpr int AT_BM = 128;                 // rows per CTA
 constexpr int AT_BK = 64;                  // keys per tile
 constexpr int AT_STAGES = 3;
-constexpr int AT_THREADS = 256;            // warp 0: MMA; warps 1-4: softmax; warps 5-7: loaders, one per stage
-constexpr int AT_LOADERS = 32;             // threads that sign a stage's "full" barrier
+constexpr int AT_THREADS = 256;            // warps 0 and 6: MMA issue; warps 1-4: softmax; warps 5 and 7: loaders
 constexpr unsigned long long AT_WAIT_NS = 1000000000ull;
 constexpr float AT_LOG2E = 1.4426950408889634f;
 
@@ -55,10 +65,12 @@ __device__ __forceinline__ bool at_mbar_wait(unsigned long long* bar, unsigned p
     unsigned long long t0 = 0;
     for (unsigned it = 0;; ++it) {
         unsigned done;
+        // the hint lets the hardware park the thread (up to 2 us) instead of polling: polls of many waiting
+        // threads would crowd the shared-memory pipeline that the copies of other warps need
         asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
                      : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
-        if ((it & 255u) == 255u) {
+        if ((it & 15u) == 15u) {
             unsigned long long now;
             asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
             if (t0 == 0) t0 = now;
@@ -66,7 +78,19 @@ __device__ __forceinline__ bool at_mbar_wait(unsigned long long* bar, unsigned p
         }
     }
 }
+__device__ __forceinline__ void at_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(at_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void at_tma_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                 ::"r"(at_smem(dst)), "l"(map), "r"(x), "r"(y), "r"(at_smem(bar)) : "memory");
+}
 __device__ __forceinline__ void at_fence_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ bool at_elect() {
+    unsigned one;
+    asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(one));
+    return one != 0;
+}
 __device__ __forceinline__ void at_tc_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void at_tc_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void at_commit(unsigned long long* bar) {
@@ -136,7 +160,7 @@ __host__ __device__ constexpr unsigned at_idesc(int m, int n, int b_nmajor) {
 
 template <int HD>
 __global__ void __launch_bounds__(AT_THREADS)
-attention_tcgen05_kernel(AttnTcParams p) {
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParams p) {
     constexpr int CB = HD / 64;                          // 64-feature column blocks of a row
     constexpr int Q_BYTES = CB * AT_BM * 128;
     constexpr int KV_BLOCK = AT_BK * 128;                // one column block of a key or value tile
@@ -150,7 +174,7 @@ attention_tcgen05_kernel(AttnTcParams p) {
     unsigned char* k_s = q_s + Q_BYTES;
     unsigned char* v_s = k_s + AT_STAGES * KV_BYTES;
     unsigned char* p_s = v_s + AT_STAGES * KV_BYTES;     // two buffers
-    __shared__ __align__(8) unsigned long long kv_full[AT_STAGES], kv_empty[AT_STAGES];
+    __shared__ __align__(8) unsigned long long k_full[AT_STAGES], k_empty[AT_STAGES], v_full[AT_STAGES], v_empty[AT_STAGES], kv_landed[AT_STAGES];
     __shared__ __align__(8) unsigned long long s_full[2], s_empty[2], p_full[2], p_empty[2], o_ready;
     __shared__ unsigned tmem_sh;
     __shared__ int failed;
@@ -159,7 +183,10 @@ attention_tcgen05_kernel(AttnTcParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int qb = blockIdx.x, kvh = blockIdx.y;
     if (tid == 0) {
-        for (int s = 0; s < AT_STAGES; ++s) { at_mbar_init(&kv_full[s], AT_LOADERS); at_mbar_init(&kv_empty[s], 1); }
+        for (int s = 0; s < AT_STAGES; ++s) {
+            at_mbar_init(&k_full[s], 1); at_mbar_init(&k_empty[s], 1); at_mbar_init(&v_full[s], 1); at_mbar_init(&v_empty[s], 1);
+            at_mbar_init(&kv_landed[s], 1);
+        }
         for (int b = 0; b < 2; ++b) {
             at_mbar_init(&s_full[b], 1); at_mbar_init(&s_empty[b], 128);
             at_mbar_init(&p_full[b], 128); at_mbar_init(&p_empty[b], 1);
@@ -200,48 +227,61 @@ attention_tcgen05_kernel(AttnTcParams p) {
     at_tc_after();
     const unsigned tmem = tmem_sh;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr unsigned idesc_qk = at_idesc(AT_BM, AT_BK, 0);
-            constexpr unsigned idesc_pv = at_idesc(AT_BM, HD, 1);
-            const unsigned q_addr = at_smem(q_s);
-            bool ok = true;
-            auto issue_qk = [&](int i) {
+    if (warp == 0 || warp == 6) {
+        // ------------------------------------------------------------------ MMA issuers: warp 0 the scores, warp 6 the values
+        // The whole warp runs the loop and one elected lane issues: addresses and descriptors then stay in
+        // uniform registers, which keeps the issue of one small MMA to a few cycles.
+        constexpr unsigned idesc_qk = at_idesc(AT_BM, AT_BK, 0);
+        constexpr unsigned idesc_pv = at_idesc(AT_BM, HD, 1);
+        const unsigned q_addr = at_smem(q_s);
+        bool ok = true;
+        auto wait_all = [&](unsigned long long* bar, unsigned parity) {
+            return __all_sync(0xffffffffu, at_mbar_wait(bar, parity)) != 0;
+        };
+        if (warp == 0) {
+            // scores: S[b] = Q K(i)^T as soon as the keys have landed and the buffer has been read
+            for (int i = 0; i < n_tiles && ok; ++i) {
                 const int st = i % AT_STAGES, b = i & 1;
-                ok = ok && at_mbar_wait(&kv_full[st], (i / AT_STAGES) & 1);
-                if (ok && i >= 2) ok = at_mbar_wait(&s_empty[b], ((i >> 1) - 1) & 1);
-                if (!ok) return;
+                ok = wait_all(&k_full[st], (i / AT_STAGES) & 1);
+                if (ok && i >= 2) ok = wait_all(&s_empty[b], ((i >> 1) - 1) & 1);
+                if (!ok) break;
                 at_tc_after();
                 const unsigned k_addr = at_smem(k_s + st * KV_BYTES);
+                if (at_elect()) {
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    const unsigned off = (ks >> 2) * 0 + (ks & 3) * 32;
-                    at_mma(tmem + (unsigned)b * 64, at_desc_kmajor(q_addr + (ks >> 2) * (AT_BM * 128) + off),
-                           at_desc_kmajor(k_addr + (ks >> 2) * KV_BLOCK + off), idesc_qk, ks > 0 ? 1u : 0u);
+                    for (int ks = 0; ks < HD / 16; ++ks) {
+                        const unsigned off = (ks & 3) * 32;
+                        at_mma(tmem + (unsigned)b * 64, at_desc_kmajor(q_addr + (ks >> 2) * (AT_BM * 128) + off),
+                               at_desc_kmajor(k_addr + (ks >> 2) * KV_BLOCK + off), idesc_qk, ks > 0 ? 1u : 0u);
+                    }
+                    at_commit(&s_full[b]);
+                    at_commit(&k_empty[st]);
                 }
-                at_commit(&s_full[b]);
-            };
-            if (n_tiles > 0) issue_qk(0);
+                __syncwarp();
+            }
+        } else {
+            // values: O += P(i) V(i) once the softmax warps have written P(i)
             for (int i = 0; i < n_tiles && ok; ++i) {
-                if (i + 1 < n_tiles) issue_qk(i + 1);
-                if (!ok) break;
                 const int st = i % AT_STAGES, b = i & 1;
-                ok = at_mbar_wait(&p_full[b], (i >> 1) & 1);
+                ok = wait_all(&v_full[st], (i / AT_STAGES) & 1) && wait_all(&p_full[b], (i >> 1) & 1);
                 if (!ok) break;
                 at_tc_after();
                 const unsigned p_addr = at_smem(p_s + b * P_BYTES);
                 const unsigned v_addr = at_smem(v_s + st * KV_BYTES);
+                if (at_elect()) {
 #pragma unroll
-                for (int ks = 0; ks < AT_BK / 16; ++ks)
-                    at_mma(tmem + O_COL, at_desc_kmajor(p_addr + ks * 32), at_desc_nmajor(v_addr + ks * 2048, KV_BLOCK, 1024),
-                           idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
-                at_commit(&kv_empty[st]);
-                at_commit(&p_empty[b]);
+                    for (int ks = 0; ks < AT_BK / 16; ++ks)
+                        at_mma(tmem + O_COL, at_desc_kmajor(p_addr + ks * 32), at_desc_nmajor(v_addr + ks * 2048, KV_BLOCK, 1024),
+                               idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
+                    at_commit(&v_empty[st]);
+                    at_commit(&p_empty[b]);
+                }
+                __syncwarp();
             }
-            if (ok) at_commit(&o_ready);
-            else atomicExch(&failed, 1);
+            if (ok) { if (at_elect()) at_commit(&o_ready); }
+            __syncwarp();
         }
+        if (!ok && lane == 0) atomicExch(&failed, 1);
     } else if (warp <= 4) {
         // ------------------------------------------------------------------ softmax: one thread per row
         const int quarter = warp & 3;                    // the tensor-memory lanes this warp may touch
@@ -250,6 +290,8 @@ attention_tcgen05_kernel(AttnTcParams p) {
         const bool real = r < n_rows;
         const int pos = real ? pos_first + r / group : -1;
         const int lo = (real && p.window > 0) ? max(0, pos - p.window + 1) : 0;
+        const int warp_pos_min = __reduce_min_sync(0xffffffffu, real ? pos : 0x7fffffff);
+        const int warp_lo_max = __reduce_max_sync(0xffffffffu, lo);
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
         for (int i = 0; i < n_tiles && ok; ++i) {
@@ -270,35 +312,46 @@ attention_tcgen05_kernel(AttnTcParams p) {
             }
             at_tc_before();
             at_mbar_arrive(&s_empty[b]);                 // the scores are in registers
-            float tmax = -INFINITY;
+            // only a tile that some row of the warp sees in part is masked element by element
+            float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (key0 + AT_BK - 1 > warp_pos_min || key0 < warp_lo_max) {
 #pragma unroll
-            for (int j = 0; j < 64; ++j) {
-                const int key = key0 + j;
-                const bool seen = key <= pos && key >= lo;
-                s[j] = seen ? s[j] * p.scale_log2 : -INFINITY;
-                tmax = fmaxf(tmax, s[j]);
+                for (int j = 0; j < 64; ++j) {
+                    const int key = key0 + j;
+                    s[j] = (key <= pos && key >= lo) ? s[j] : -INFINITY;
+                    tm[j & 3] = fmaxf(tm[j & 3], s[j]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 64; ++j) tm[j & 3] = fmaxf(tm[j & 3], s[j]);
             }
-            const float m_new = fmaxf(m, tmax);
+            const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3])) * p.scale_log2;   // the scale is positive
+            // The reference maximum m moves only when some row of the warp outgrows it by more than 8 (a factor
+            // of 256, harmless in float and bfloat16): then the rows' O and l are rescaled; otherwise the
+            // exponentials keep the old reference and nothing that was accumulated needs touching.
+            const bool grow = __any_sync(0xffffffffu, tmax > m + 8.0f) || (i == 0);
+            const float m_new = grow ? fmaxf(m, tmax) : m;
             const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
-            const float corr = at_ex2(m - m_use);
-            float sum = 0.0f;
+            const float corr = grow ? at_ex2(m - m_use) : 1.0f;
+            float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             if (i >= 2) { ok = at_mbar_wait(&p_empty[b], ((i >> 1) - 1) & 1); if (!ok) break; }
             unsigned char* prow = p_s + b * P_BYTES + r * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 float e[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) { e[j] = at_ex2(s[c * 8 + j] - m_use); sum += e[j]; }
+                for (int j = 0; j < 8; ++j) { e[j] = at_ex2(fmaf(s[c * 8 + j], p.scale_log2, -m_use)); sums[j & 3] += e[j]; }
                 uint4 pk;
                 __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(e[2 * j], e[2 * j + 1]);
                 *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = pk;
             }
+            const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
             l = l * corr + sum;
             m = m_new;
             // rows whose maximum grew: O *= corr, once the previous product has landed
-            if (i > 0 && __any_sync(0xffffffffu, corr < 1.0f)) {
+            if (i > 0 && grow) {
                 ok = at_mbar_wait(&p_empty[(i - 1) & 1], ((i - 1) >> 1) & 1);
                 if (!ok) break;
                 at_tc_after();
@@ -342,48 +395,81 @@ attention_tcgen05_kernel(AttnTcParams p) {
             }
         }
     } else {
-        // ------------------------------------------------------------------ loaders: warp 5 + s owns stage s
-        const int st = warp - 5;
-        const size_t page_elems = (size_t)2 * p.nkv * p.page_size * HD;
-        const size_t v_off = (size_t)p.nkv * p.page_size * HD;
-        constexpr int PIECES = HD / 8;                   // 16-byte pieces per key row
-        unsigned char* kd = k_s + st * KV_BYTES;
-        unsigned char* vd = v_s + st * KV_BYTES;
-        const int c = lane % PIECES, cb = c >> 3, cc = c & 7;
+        // ------------------------------------------------------------------ loaders: TMA, a tile of 64 keys at a time;
+        // warp 5 brings the keys, warp 7 the values, each through a ring of stages of its own
+        const int which = warp == 7;
+        unsigned char* ring = which ? v_s : k_s;
+        unsigned long long* full = which ? v_full : k_full;
+        unsigned long long* empty = which ? v_empty : k_empty;
+        const int ps = p.page_size;
+        const int n_pg = AT_BK / ps;                     // pages per tile (page_size divides 64)
         bool ok = true;
-        for (int i = st; i < n_tiles; i += AT_STAGES) {
+        unsigned landed_phase = 0;                       // bit s: parity of stage s's "landed" barrier
+        auto fetch_pages = [&](int i, int (&pg)[2]) {
+            const int key0 = (tile0 + i) * AT_BK;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int k = h * 32 + lane;
+                const int pi = key0 / ps + k;
+                pg[h] = -1;
+                if (i < n_tiles && k < n_pg && pi < p.max_pages && key0 + k * ps < k_end && key0 + (k + 1) * ps > k_begin)
+                    pg[h] = p.block_table[(size_t)req * p.max_pages + pi];
+            }
+        };
+        int pg_next[2];
+        fetch_pages(0, pg_next);
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const int st = i % AT_STAGES;
             if (i >= AT_STAGES) {
-                ok = at_mbar_wait(&kv_empty[st], ((i / AT_STAGES) - 1) & 1);
+                ok = at_mbar_wait(&empty[st], ((i / AT_STAGES) - 1) & 1);
                 if (!ok) break;
             }
             const int key0 = (tile0 + i) * AT_BK;
-            // lane copies piece lane % PIECES of keys lane / PIECES, + 32 / PIECES, ...: whole rows per warp access
-            for (int j = lane / PIECES; j < AT_BK; j += 32 / PIECES) {
-                const int key = key0 + j;
-                const unsigned off = cb * KV_BLOCK + j * 128 + ((cc ^ (j & 7)) << 4);
-                const __nv_bfloat16* src = nullptr;
-                if (key >= k_begin && key < k_end) {
-                    const int pi = p.page_shift >= 0 ? key >> p.page_shift : key / p.page_size;
-                    const int slot = p.page_shift >= 0 ? key & (p.page_size - 1) : key - pi * p.page_size;
-                    const int page = p.block_table[(size_t)req * p.max_pages + pi];
-                    if (page < 0 || page >= p.num_pages) {
-                        if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE);
-                    } else {
-                        src = p.kv_pool + (size_t)page * page_elems + ((size_t)kvh * p.page_size + slot) * HD + c * 8;
-                    }
-                }
-                if (src) {
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(at_smem(kd + off)), "l"(src) : "memory");
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(at_smem(vd + off)), "l"(src + v_off) : "memory");
-                } else {
-                    *reinterpret_cast<uint4*>(kd + off) = make_uint4(0, 0, 0, 0);
-                    *reinterpret_cast<uint4*>(vd + off) = make_uint4(0, 0, 0, 0);
+            unsigned char* dst = ring + st * KV_BYTES;
+            // page numbers of the tile (fetched one tile ahead): lanes 0..n_pg-1 hold one each, in two rounds
+            int pg[2] = {pg_next[0], pg_next[1]};
+            fetch_pages(i + 1, pg_next);
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                if (pg[h] >= p.num_pages) { if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE); pg[h] = -1; }
+            const unsigned have0 = __ballot_sync(0xffffffffu, pg[0] >= 0), have1 = __ballot_sync(0xffffffffu, pg[1] >= 0);
+            const int n_have = __popc(have0) + __popc(have1);
+            // Key rows that no query may see need no care (their scores are masked, whatever they are); value rows
+            // do: 0 * garbage can be NaN.  So a ragged tile of values lands on a barrier of its own, the rows
+            // outside the range or in pages that are not held are zeroed, and only then is the tile released.
+            const bool direct = !which || (n_have == n_pg && key0 >= k_begin && key0 + AT_BK <= k_end);
+            unsigned long long* bar = direct ? &full[st] : &kv_landed[st];
+            if (lane == 0) {
+                if (n_have > 0) at_expect_tx(bar, (unsigned)n_have * ps * HD * 2);
+                else if (direct) at_mbar_arrive(bar);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (pg[h] >= 0) {
+                    const int row = ((pg[h] * 2 + which) * p.nkv + kvh) * ps;
+#pragma unroll
+                    for (int cb = 0; cb < CB; ++cb)
+                        at_tma_2d(dst + cb * KV_BLOCK + (h * 32 + lane) * ps * 128, &map_kv, cb * 64, row, bar);
                 }
             }
-            asm volatile("cp.async.commit_group;\n" ::: "memory");
-            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-            at_fence_async();                            // the tile is read through the async proxy
-            at_mbar_arrive(&kv_full[st]);
+            if (!direct) {
+                if (n_have > 0) {
+                    ok = at_mbar_wait(&kv_landed[st], (landed_phase >> st) & 1);
+                    landed_phase ^= 1u << st;
+                    if (!ok) break;
+                }
+                for (int idx = lane; idx < AT_BK * (HD / 8); idx += 32) {
+                    const int j = idx / (HD / 8), c = idx - j * (HD / 8);
+                    const int key = key0 + j, k = j / ps;
+                    const int held = k < 32 ? ((have0 >> k) & 1) : ((have1 >> (k - 32)) & 1);
+                    if (!held || key < k_begin || key >= k_end)
+                        *reinterpret_cast<uint4*>(dst + (c >> 3) * KV_BLOCK + j * 128 + (((c & 7) ^ (j & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+                }
+                at_fence_async();
+                __syncwarp();
+                if (lane == 0) at_mbar_arrive(&full[st]);
+            }
         }
         if (!ok) atomicExch(&failed, 1);
     }
@@ -396,13 +482,39 @@ attention_tcgen05_kernel(AttnTcParams p) {
     if (tid == 0 && failed && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
 }
 
+typedef CUresult (*AtEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The page pool of one layer, [num_pages][2][nkv][page_size][hd], as a 2-D tensor of rows of hd features;
+// a box is one page of one kv head, 64 features wide.
+static int at_pool_map(CUtensorMap* map, const void* pool, long long rows, int hd, int page_size) {
+    static AtEncodeFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return (AtEncodeFn)f;
+    }();
+    if (!fn) return BG_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? BG_OK : BG_ERR_SHAPE;
+}
+
 template <int HD>
-static int at_launch(const AttnTcParams& p, int n_qblk, cudaStream_t stream) {
+static int at_launch(const CUtensorMap& map, const AttnTcParams& p, int n_qblk, cudaStream_t stream) {
     auto kern = attention_tcgen05_kernel<HD>;
     const size_t smem = (size_t)(HD / 64) * AT_BM * 128 + (size_t)2 * AT_STAGES * (HD / 64) * AT_BK * 128 + 2 * AT_BM * 128 + 1024;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    e = launch(kern, dim3(n_qblk, p.nkv), dim3(AT_THREADS), smem, stream, p);
+    e = launch(kern, dim3(n_qblk, p.nkv), dim3(AT_THREADS), smem, stream, map, p);
     if (e != cudaSuccess) return (int)e;
     return BG_OK;
 }
@@ -412,8 +524,9 @@ static int at_launch(const AttnTcParams& p, int n_qblk, cudaStream_t stream) {
 using namespace bg;
 
 // Rows (tokens) per query block for these sizes, or BG_ERR_UNSUPPORTED.
-extern "C" int bg_attention_tc_plan(int group, int hd, int* bq_out) {
+extern "C" int bg_attention_tc_plan(int group, int hd, int page_size, int* bq_out) {
     if ((hd != 64 && hd != 128) || group < 1 || group > 128) return BG_ERR_UNSUPPORTED;
+    if (page_size < 1 || page_size > 64 || 64 % page_size != 0) return BG_ERR_UNSUPPORTED;
     *bq_out = 128 / group;
     return BG_OK;
 }
@@ -423,7 +536,8 @@ extern "C" int bg_attention_tc(const void* q, int q_stride, const void* kv_pool,
                                void* out, int out_stride, int nh, int nkv, int hd, int window, float scale,
                                unsigned* status, cudaStream_t stream) {
     if (n_qblk <= 0) return BG_OK;
-    if (nh % nkv != 0 || (hd != 64 && hd != 128) || nh / nkv > 128) return BG_ERR_UNSUPPORTED;
+    if (nh % nkv != 0 || (hd != 64 && hd != 128) || nh / nkv > 128 || !(scale > 0.0f)) return BG_ERR_UNSUPPORTED;
+    if (page_size < 1 || page_size > 64 || 64 % page_size != 0) return BG_ERR_UNSUPPORTED;
     if ((q_stride % 8) || (out_stride % 8) || ((uintptr_t)q % 16) || ((uintptr_t)kv_pool % 16) || ((uintptr_t)out % 16)) return BG_ERR_ALIGN;
     if (nkv > 65535) return BG_ERR_SHAPE;
     AttnTcParams p;
@@ -433,5 +547,21 @@ extern "C" int bg_attention_tc(const void* q, int q_stride, const void* kv_pool,
     p.block_table = block_table; p.max_pages = max_pages; p.positions = positions; p.qblk = qblk;
     p.out = (__nv_bfloat16*)out; p.out_stride = out_stride; p.nh = nh; p.nkv = nkv; p.group = nh / nkv;
     p.window = window; p.scale_log2 = scale * AT_LOG2E; p.status = status;
-    return hd == 128 ? at_launch<128>(p, n_qblk, stream) : at_launch<64>(p, n_qblk, stream);
+    // the pool's map is made once per (pointer, shape)
+    static std::mutex mu;
+    static std::map<std::tuple<const void*, int, int, int, int>, CUtensorMap> maps;
+    CUtensorMap map;
+    {
+        std::lock_guard<std::mutex> g(mu);
+        auto key = std::make_tuple(kv_pool, num_pages, nkv, page_size, hd);
+        auto it = maps.find(key);
+        if (it == maps.end()) {
+            int rc = at_pool_map(&map, kv_pool, (long long)num_pages * 2 * nkv * page_size, hd, page_size);
+            if (rc != BG_OK) return rc;
+            maps.emplace(key, map);
+        } else {
+            map = it->second;
+        }
+    }
+    return hd == 128 ? at_launch<128>(map, p, n_qblk, stream) : at_launch<64>(map, p, n_qblk, stream);
 }

@@ -43,11 +43,12 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
     unsigned long long t0 = 0;
     for (unsigned it = 0;; ++it) {
         unsigned done;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        // the hint lets the hardware park the thread (up to 2 us) instead of polling: polls of many waiting
+        // threads would crowd the shared-memory pipeline that the copies of other warps need
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(done) : "r"(addr), "r"(parity), "r"(2000u) : "memory");
         if (done) return true;
-        if ((it & 255u) == 255u) {
+        if ((it & 15u) == 15u) {
             unsigned long long now;
             asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
             if (t0 == 0) t0 = now;

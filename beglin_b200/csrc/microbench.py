@@ -71,7 +71,7 @@ def attention_decode(a) -> None:
     one = B * ctx * 2 * nkv * hd * 2
     copies = max(1, min(16, int(400e6 // one)))                  # rotate caches so that they come from HBM
     caches = [_filled_cache(B, ctx, nkv, hd, page) for _ in range(copies)]
-    kernel, bq, tile = ops.attention_plan(nh // nkv, hd, torch.bfloat16, True)
+    kernel, bq, tile = ops.attention_plan(nh // nkv, hd, torch.bfloat16, True, page_size=page)
     q = torch.randn(B, nh * hd, device=DEV).to(torch.bfloat16)
     positions = torch.full((B,), ctx - 1, dtype=torch.int32, device=DEV)
     qblk = torch.stack([torch.arange(B), torch.arange(B), torch.ones(B, dtype=torch.long)], 1).to(torch.int32).to(DEV)
@@ -89,7 +89,7 @@ def attention_decode(a) -> None:
 def attention_prefill(a) -> None:
     T, nh, nkv, hd, page = a.tokens, a.heads, a.kv_heads, a.head_dim, a.page
     pool, bt = _filled_cache(1, T, nkv, hd, page)
-    kernel, bq, tile = ops.attention_plan(nh // nkv, hd, torch.bfloat16, False, a.kernel)
+    kernel, bq, tile = ops.attention_plan(nh // nkv, hd, torch.bfloat16, False, a.kernel, page)
     q = torch.randn(T, nh * hd, device=DEV).to(torch.bfloat16)
     positions = torch.arange(T, dtype=torch.int32, device=DEV)
     blocks = [(0, b, min(bq, T - b)) for b in range(0, T, bq)]

@@ -38,7 +38,7 @@ _SIGNATURES = {
     "bg_attention_mma_partial": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                  _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                  _c_int, _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p],
-    "bg_attention_tc_plan": [_c_int, _c_int, ctypes.POINTER(_c_int)],
+    "bg_attention_tc_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int)],
     "bg_attention_tc": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
                         _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     "bg_gemm_f32_nt": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
@@ -262,12 +262,13 @@ def rope_kv_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh: int,
                                    _p(status), _stream()), "rope_kv_append")
 
 
+
 # choices of `prefer` under which prompt portions run the tcgen05 kernel
-TC_ROWS_FOR = ("tcgen05",)
+TC_ROWS_FOR = ("auto", "tcgen05")
 
 
 def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, decode_only: bool = False,
-                   prefer: str = "auto") -> Tuple[str, int, int]:
+                   prefer: str = "auto", page_size: int = 16) -> Tuple[str, int, int]:
     """(kernel, rows per query block, keys per tile) for these sizes.  Kernels: "mma_keys" (tensor
     cores, one token per block, for steps of single tokens), "mma_rows" (tensor cores, up to 64 rows
     per block) and "generic" (CUDA cores, every size up to head_dim 256, float or bfloat16)."""
@@ -276,11 +277,12 @@ def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, deco
         raise KernelError(f"unknown attention kernel choice '{prefer}'")
     if dtype == torch.bfloat16 and not decode_only and prefer in TC_ROWS_FOR:
         bq = _c_int(0)
-        if L.bg_attention_tc_plan(group, hd, ctypes.byref(bq)) == 0:
+        if L.bg_attention_tc_plan(group, hd, page_size, ctypes.byref(bq)) == 0:
             return "tc_rows", bq.value, 64
         if prefer == "tcgen05":
             raise KernelError(f"the tcgen05 attention kernel does not take head_dim {hd} with {group} query heads "
-                              "per kv head (head_dim 64 or 128; at most 128 heads per kv head)")
+                              f"per kv head and pages of {page_size} (head_dim 64 or 128; at most 128 heads per kv head; "
+                              "a page size that divides 64)")
     if dtype == torch.bfloat16 and prefer != "generic":
         bq = _c_int(0)
         if L.bg_attention_mma_plan(group, hd, 1 if decode_only else 0, ctypes.byref(bq)) == 0:

@@ -50,7 +50,7 @@ def require_gpu(device) -> torch.device:
 
 class Engine:
     def __init__(self, spec, tensors, *, dtype="bfloat16", device="cuda:0", max_tokens: int = 8192,
-                 page_size: int = 16, max_requests: int = 8, max_context: Optional[int] = None,
+                 page_size: int = 64, max_requests: int = 8, max_context: Optional[int] = None,
                  kv_split: int = 256, gemm: str = "auto", attention: str = "auto", use_graphs: bool = True,
                  config=None, origin: str = ""):
         """`tensors` is anything with names()/shape(name)/tensor(name): a Checkpoint or a TensorDict.

@@ -64,8 +64,8 @@ class GQAAttention:
         self.position = shared_position(spec.position, ctx)
         scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(float(self.hd))
         self.scale = float(np.float32(scale))
-        self.plans = {d: ops.attention_plan(self.nh // self.nkv, self.hd, ctx.cache_dtype, d, ctx.attention)
-                      for d in (False, True)}
+        self.plans = {d: ops.attention_plan(self.nh // self.nkv, self.hd, ctx.cache_dtype, d, ctx.attention,
+                                            ctx.page_size) for d in (False, True)}
         self.window = int(spec.window) if spec.window else 0
 
     def forward(self, h: torch.Tensor, batch, cache: PagedKVView) -> torch.Tensor:

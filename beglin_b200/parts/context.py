@@ -13,7 +13,7 @@ class BuildContext:
     device: torch.device
     compute_dtype: torch.dtype              # torch.float32 (true 32-bit path) or torch.bfloat16
     cache_dtype: Optional[torch.dtype] = None
-    page_size: int = 16
+    page_size: int = 64
     kv_split: int = 256                     # keys per attention split; fixed, so results do not depend on load
     gemm: str = "auto"                      # "auto", "library" or "tcgen05" for the bfloat16 products
     attention: str = "auto"                 # "auto", "generic" (CUDA cores) or "mma" (tensor cores) kernel

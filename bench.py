@@ -198,7 +198,7 @@ def main():
     pk = peaks()
     cfg = dict(CONFIG_1P5B, num_hidden_layers=args.layers)
     max_batch = args.batch if args.no_points else max(args.batch, 64)
-    page = 16
+    page = 64
     eng = Engine.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=max_batch * args.context,
                         page_size=page, max_requests=max_batch, max_context=args.context, gemm=args.gemm)
     weight_bytes = eng.model.weight_bytes()

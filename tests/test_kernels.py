@@ -223,7 +223,7 @@ def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64, prefe
     ks[1][far, :, 0] = 8.0
     pool[int(bt[1, far // page]), 0, :, far % page, 0] = 8.0
     positions, row_req, qblk = [], [], []
-    kernel, bq, tile = ops.attention_plan(group, hd, dtype, decode_only, prefer)
+    kernel, bq, tile = ops.attention_plan(group, hd, dtype, decode_only, prefer, page)
     assert kernel == {"generic": "generic", "mma": "mma_keys" if decode_only else "mma_rows", "tcgen05": "tc_rows"}[prefer]
     r0 = 0
     for r, (c, n) in enumerate(ctx):
@@ -287,7 +287,8 @@ def test_attention_tensor_core_kernel(ops, nh, nkv, hd, page, window, decode_onl
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page,window", [(12, 2, 128, 16, None), (4, 4, 64, 8, None), (14, 2, 64, 32, 40),
-                                                   (16, 1, 128, 16, None), (12, 2, 128, 16, 100), (3, 1, 128, 4, None)])
+                                                   (16, 1, 128, 16, None), (12, 2, 128, 16, 100), (3, 1, 128, 4, None),
+                                                   (6, 3, 128, 64, None), (8, 2, 64, 1, 50)])
 def test_attention_tcgen05_kernel(ops, nh, nkv, hd, page, window):
     got, want = _attention_case(ops, nh, nkv, hd, page, torch.bfloat16, window, seed=5, prefer="tcgen05")
     assert torch.isfinite(got).all()
