@@ -196,7 +196,7 @@ attention_partial_kernel(AttnParams p) {
 template <typename TO>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
-                                       int T, int nh, int hd, int max_splits, int split, int window) {
+                                       int T, int nh, int hd, int max_splits, int split_arg, int window) {
     pdl_launch();
     pdl_wait();
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -204,6 +204,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
     if (w >= T * nh) return;
     const int t = w / nh, h = w - t * nh;
     const int pos = positions[t];
+    const int split = keys_per_split(split_arg, pos + 1, max_splits);
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int s_lo = lo / split, s_hi = pos / split;
     const size_t prow = (size_t)w * max_splits;

@@ -4,25 +4,31 @@
 // every (row, head) that sees a key of the split, an unnormalised output with its running maximum
 // and sum; attention_merge joins the splits.  Scores, softmax and the output accumulators are float;
 // the two products of a 16-key block run as mma.sync m16n8k16 on bfloat16 operands with float
-// accumulation.  Keys and values are brought from the pages into shared memory with 16-byte
-// cp.async copies, three stages of 64 keys deep, in a layout that XORs the 16-byte column with the
-// key's low bits so that ldmatrix reads without bank conflicts.
+// accumulation.  Keys and values are brought from the pages into shared memory three stages of 64
+// keys deep.  When the page size divides 64 a fifth warp does nothing but ask for them by TMA (one box
+// per page, kv head and 64 features: one instruction moves kilobytes, where a warp's 16-byte copies
+// in flight are too few to keep up with HBM, and the address arithmetic of a stage, a long chain for
+// one thread, stays off the four computing warps' path); stages are handed over through mbarriers.
+// Else the four warps copy with 16-byte cp.async themselves.  The layout is the one the TMA's 128-byte
+// swizzle gives: per 64 features a block of rows of 128 bytes, the 16-byte column XORed with the
+// key's low bits, so that ldmatrix reads without bank conflicts.
 //
 // Two arrangements of the four warps:
 //   rows:  the query block has up to 64 rows (tokens x heads of the group); warp w owns rows
 //          16w..16w+15 and walks all keys of a stage (prompt portions).
-//   keys:  the query block is ONE token (<= 16 heads in the group); warp w owns keys 16w..16w+15 of
-//          every stage, and the four partial results are joined in shared memory (decoding, where
-//          the cache is streamed once and the tensor work is idle most of the time).
-#include "common.cuh"
+//   keys:  the query block is ONE token (<= 16 heads in the group); warp w owns every fourth stage of
+//          64 keys (stage s lands in buffer s % 4, which is warp s % 4's), walks it alone, and the four
+//          partial results are joined in shared memory at the end (decoding: a stage is a long chain of
+//          dependent steps for one warp, so four of them run side by side, each with 64 keys' worth of
+//          independent MMAs, and no barrier of the CTA stands between two stages).
+#include "page_tma.cuh"
 
 namespace bg {
 
-constexpr int AM_THREADS = 128;
+constexpr int AM_THREADS = 128;             // the computing warps
+constexpr int AM_ALL = AM_THREADS + 32;     // and the warp that asks for the copies
 constexpr int AM_STAGE_KEYS = 64;
-// Stages of 64 keys in flight per CTA: 3 for prompt portions and for decoding grids that fit the machine
-// at once (the latency of one CTA is what counts); 2 for larger decoding grids (less shared memory,
-// three CTAs per SM, and the throughput of the stream is what counts).
+// Stages of 64 keys in flight per CTA: 3 for prompt portions, 4 (a buffer per warp) for decoding.
 constexpr int AM_TABLE = 128;              // block-table entries held in shared memory at a time
 constexpr float AM_LOG2E = 1.4426950408889634f;
 constexpr float AM_LN2 = 0.6931471805599453f;
@@ -46,6 +52,8 @@ struct AttnMmaParams {
     unsigned* status;
     __nv_bfloat16* out;     // rows arrangement only: when set, a CTA walks ALL keys of its block and writes
     int out_stride;         // the finished rows here (no partial results, no merge)
+    int use_tma;            // pages are copied as TMA boxes (the page size divides 64)
+    int whole_pages;        // a page is a stage (64 positions): keys and values of a stage come in ONE box
 };
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
@@ -83,19 +91,27 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 // Byte offset of (row, 16-byte column c) in a tile whose rows are HD bf16 wide.
 template <int HD> __device__ __forceinline__ int swz(int row, int c) { return row * (HD * 2) + ((c ^ (row & 7)) << 4); }
+// key and value tiles: a block of 64 rows x 128 bytes per 64 features
+__device__ __forceinline__ int swz_kv(int row, int c) {
+    return (c >> 3) * (AM_STAGE_KEYS * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+}
 
 template <int HD, bool BY_KEYS, int AM_STAGES>
-__global__ void __launch_bounds__(AM_THREADS)
-attention_mma_kernel(AttnMmaParams p) {
+__global__ void __launch_bounds__(AM_ALL)
+attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_constant__ CUtensorMap map_page, AttnMmaParams p) {
     constexpr int CH = HD / 8;                 // 16-byte columns per row
     constexpr int KSTEPS = HD / 16;            // k-steps of q.k
     constexpr int NT_O = HD / 8;               // 8-wide column tiles of the output
     constexpr int STAGE_BYTES = AM_STAGE_KEYS * HD * 2;
     constexpr int Q_ROWS = BY_KEYS ? 16 : 64;
-    extern __shared__ __align__(128) unsigned char sm[];
-    unsigned char* q_s = sm;                                   // [Q_ROWS][HD]
-    unsigned char* k_s = q_s + Q_ROWS * HD * 2;                // [stages][64][HD]
-    unsigned char* v_s = k_s + AM_STAGES * STAGE_BYTES;        // [stages][64][HD]
+    extern __shared__ unsigned char sm_raw[];
+    unsigned char* sm = (unsigned char*)(((uintptr_t)sm_raw + 1023) & ~(uintptr_t)1023);   // the swizzle wants 1024
+    unsigned char* k_s = sm;                                   // stage b: keys at b * 2 * STAGE_BYTES, [HD / 64][64][128 bytes],
+    unsigned char* v_s = k_s + STAGE_BYTES;                    // and its values right behind them, the same
+    unsigned char* q_s = k_s + 2 * AM_STAGES * STAGE_BYTES;    // [Q_ROWS][HD]
+    constexpr int BUF_BYTES = 2 * STAGE_BYTES;
+    __shared__ __align__(8) unsigned long long full_bar[AM_STAGES], empty_bar[AM_STAGES];
+    __shared__ int gave_up;
 
     pdl_launch();
     pdl_wait();
@@ -113,7 +129,7 @@ attention_mma_kernel(AttnMmaParams p) {
     // (rows beyond n_rows are zero) ...
     const int pos_first = p.positions[row0];
     const int pos_last = p.positions[row0 + nq - 1];
-    for (int idx = tid; idx < Q_ROWS * CH; idx += AM_THREADS) {
+    for (int idx = tid; idx < Q_ROWS * CH; idx += AM_ALL) {
         int r = idx / CH, c = idx - r * CH;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (r < n_rows) {
@@ -126,17 +142,23 @@ attention_mma_kernel(AttnMmaParams p) {
     // copies start without a table load of their own (a stage of 64 keys never straddles two such groups).
     // The group fetched here is the one the first keys of this CTA's range lie in when there is no window.
     __shared__ int table_s[AM_TABLE];
+    if (tid == 0) {
+        for (int s = 0; s < AM_STAGES; ++s) { pt_mbar_init(&full_bar[s], 1); pt_mbar_init(&empty_bar[s], BY_KEYS ? 1 : AM_THREADS / 32); }
+        gave_up = 0;
+        pt_mbar_init_fence();
+    }
     const bool direct = !BY_KEYS && p.out != nullptr;
-    const int pre_key = direct ? 0 : sp * p.split;
+    const int split = keys_per_split(p.split, pos_last + 1, (int)gridDim.z);
+    const int pre_key = direct ? 0 : sp * split;
     const int pre_group = (p.page_shift >= 0 ? pre_key >> p.page_shift : pre_key / p.page_size) / AM_TABLE;
-    for (int i = tid; i < AM_TABLE; i += AM_THREADS) {
+    for (int i = tid; i < AM_TABLE; i += AM_ALL) {
         const int pi = pre_group * AM_TABLE + i;
         table_s[i] = pi < p.max_pages ? p.block_table[(size_t)req * p.max_pages + pi] : -1;
     }
 
     const int lo_first = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
-    const int k_begin = direct ? lo_first : max(sp * p.split, lo_first);
-    const int k_end = direct ? pos_last + 1 : min((sp + 1) * p.split, pos_last + 1);
+    const int k_begin = direct ? lo_first : max(sp * split, lo_first);
+    const int k_end = direct ? pos_last + 1 : min((sp + 1) * split, pos_last + 1);
     if (k_begin >= k_end) return;
 
     // ---- stage loader: thread t copies 16-byte pieces of key rows of K and of V
@@ -146,23 +168,80 @@ attention_mma_kernel(AttnMmaParams p) {
     int table_group = (first_stage_key / p.page_size) / AM_TABLE;
     if (table_group != pre_group) table_group = -1;               // a window moved the range: fetched by the loader
     __syncthreads();                           // q_s and table_s are complete
+    auto compute_sync = [] { asm volatile("bar.sync 1, %0;\n" ::"n"(AM_THREADS) : "memory"); };   // the four computing warps
+    if (warp == AM_THREADS / 32) {
+        // ---- the copying warp.  A page of a stage is 2 * HD / 64 boxes (keys and values, 64 features each);
+        // box o of the stage is lane o's, so that one instruction of the warp asks for up to 32 boxes (what
+        // costs is the instruction, not the box).  Pages that lie wholly outside the range of keys are left
+        // out; rows outside it are zeroed by the computing warps once the stage has landed.
+        if (!p.use_tma) return;
+        constexpr int PER_PAGE = 2 * (HD / 64);
+        const int ps = p.page_size, shift = p.page_shift;
+        const int n_box = (AM_STAGE_KEYS >> shift) * PER_PAGE;
+        const int* table = p.block_table + (size_t)req * p.max_pages;
+        auto page_of = [&](int s, int o) {               // the page that box o of stage s comes from, or -1
+            const int key_lo = first_stage_key + s * AM_STAGE_KEYS + (o / PER_PAGE) * ps;
+            if (s >= n_stage || o >= n_box || key_lo >= k_end || key_lo + ps <= k_begin || (key_lo >> shift) >= p.max_pages) return -1;
+            return table[key_lo >> shift];
+        };
+        int next_page = page_of(0, p.whole_pages ? lane * PER_PAGE : lane);
+        for (int s = 0; s < n_stage; ++s) {
+            const int buf = s % AM_STAGES;
+            int page = next_page;
+            next_page = page_of(s + 1, p.whole_pages ? lane * PER_PAGE : lane);   // fetched while this stage's copies go out
+            if (s >= AM_STAGES && !pt_mbar_wait(&empty_bar[buf], ((s / AM_STAGES) - 1) & 1, &gave_up)) {
+                if (p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
+                return;
+            }
+            unsigned char* kd = k_s + buf * BUF_BYTES;
+            if (p.whole_pages) {                         // lane 0 holds the stage's page
+                if (lane == 0) {
+                    if (page >= p.num_pages) { if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE); page = -1; }
+                    if (page >= 0) {
+                        pt_expect_tx(&full_bar[buf], BUF_BYTES);
+                        pt_tma_page(kd, &map_page, page * 2 * p.nkv + kvh, &full_bar[buf]);
+                    } else {
+                        pt_mbar_arrive(&full_bar[buf]);
+                    }
+                }
+                continue;
+            }
+            for (int h = 0; h * 32 < n_box; ++h) {       // more than one round only for pages of fewer than 8 positions
+                const int o = h * 32 + lane;
+                if (h > 0) page = page_of(s, o);
+                if (page >= p.num_pages) { if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE); page = -1; }
+                const unsigned have = __ballot_sync(0xffffffffu, page >= 0);
+                if (lane == 0 && have) pt_expect_only(&full_bar[buf], (unsigned)__popc(have) * ps * 128);
+                __syncwarp();
+                if (page >= 0) {
+                    const int k = o / PER_PAGE, rem = o % PER_PAGE, which = rem / (HD / 64), cb = rem % (HD / 64);
+                    pt_tma_2d(kd + which * STAGE_BYTES + cb * (AM_STAGE_KEYS * 128) + k * ps * 128, &map_kv, cb * 64,
+                              ((page * 2 + which) * p.nkv + kvh) * ps, &full_bar[buf]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) pt_mbar_arrive(&full_bar[buf]);   // the one arrival the phase waits for, after every expect_tx
+        }
+        return;
+    }
     const size_t page_elems = (size_t)2 * p.nkv * p.page_size * HD;
     const size_t v_off = (size_t)p.nkv * p.page_size * HD;
     auto load_stage = [&](int s) {
+        if (p.use_tma) return;                                   // the copying warp's job
         if (s < n_stage) {
             const int stage_key0 = first_stage_key + s * AM_STAGE_KEYS;
             const int group_of_stage = (stage_key0 / p.page_size) / AM_TABLE;
-            if (group_of_stage != table_group) {                 // uniform over the CTA
-                __syncthreads();
+            if (group_of_stage != table_group) {                 // uniform over the computing warps
+                compute_sync();
                 table_group = group_of_stage;
                 const int base = table_group * AM_TABLE;
                 for (int i = tid; i < AM_TABLE; i += AM_THREADS)
                     table_s[i] = (base + i <= last_page) ? p.block_table[(size_t)req * p.max_pages + base + i] : -1;
-                __syncthreads();
+                compute_sync();
             }
             const int buf = s % AM_STAGES;
-            unsigned char* kd = k_s + buf * STAGE_BYTES;
-            unsigned char* vd = v_s + buf * STAGE_BYTES;
+            unsigned char* kd = k_s + buf * BUF_BYTES;
+            unsigned char* vd = v_s + buf * BUF_BYTES;
             // thread t copies 16-byte piece t % CH of rows t / CH, t / CH + ROWS_PER_PASS, ...: the lanes of
             // a warp read whole rows, so every 32-byte sector is asked for once
             constexpr int ROWS_PER_PASS = AM_THREADS / CH;
@@ -182,18 +261,20 @@ attention_mma_kernel(AttnMmaParams p) {
                     }
                 }
                 if (src) {
-                    cp_async16(kd + swz<HD>(j, c), src);
-                    cp_async16(vd + swz<HD>(j, c), src + v_off);
+                    cp_async16(kd + swz_kv(j, c), src);
+                    cp_async16(vd + swz_kv(j, c), src + v_off);
                 } else {                                         // a key outside the range: zeros
-                    *reinterpret_cast<uint4*>(kd + swz<HD>(j, c)) = make_uint4(0, 0, 0, 0);
-                    *reinterpret_cast<uint4*>(vd + swz<HD>(j, c)) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(kd + swz_kv(j, c)) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(vd + swz_kv(j, c)) = make_uint4(0, 0, 0, 0);
                 }
             }
         }
         cp_async_commit();
     };
+    if (!BY_KEYS) {
 #pragma unroll
-    for (int s = 0; s < AM_STAGES - 1; ++s) load_stage(s);
+        for (int s = 0; s < AM_STAGES - 1; ++s) load_stage(s);
+    }
 
     // ---- this warp's query fragments and row bookkeeping
     const int row_base = BY_KEYS ? 0 : warp * 16;
@@ -226,28 +307,74 @@ attention_mma_kernel(AttnMmaParams p) {
     int koff[KSTEPS], voff[NT_O / 2];
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ++ks)
-        koff[ks] = swz<HD>((lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1));
+        koff[ks] = swz_kv((lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1));
 #pragma unroll
     for (int t2 = 0; t2 < NT_O / 2; ++t2)
-        voff[t2] = swz<HD>((lane & 7) + (((lane >> 3) & 1) << 3), t2 * 2 + (lane >> 4));
+        voff[t2] = swz_kv((lane & 7) + (((lane >> 3) & 1) << 3), t2 * 2 + (lane >> 4));
 
     float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
     float o[NT_O][4];
 #pragma unroll
     for (int t = 0; t < NT_O; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f; }
 
-    constexpr int KB = BY_KEYS ? 1 : 4;                 // 16-key blocks of a stage that this warp walks
-    constexpr int BLOCK_BYTES = 16 * HD * 2;
-    for (int s = 0; s < n_stage; ++s) {
-        load_stage(s + AM_STAGES - 1);
-        cp_async_wait<AM_STAGES - 1>();
-        __syncthreads();
+    constexpr int KB = 4;                               // 16-key blocks of a stage
+    constexpr int BLOCK_BYTES = 16 * 128;               // 16 keys further down, in every block of 64 features
+    for (int s = BY_KEYS ? warp : 0; s < n_stage; s += (BY_KEYS ? AM_THREADS / 32 : 1)) {
+        if (!BY_KEYS) load_stage(s + AM_STAGES - 1);
         const int buf = s % AM_STAGES;
-        const unsigned char* kt = k_s + buf * STAGE_BYTES;
-        const unsigned char* vt = v_s + buf * STAGE_BYTES;
+        unsigned char* kt = k_s + buf * BUF_BYTES;
+        unsigned char* vt = v_s + buf * BUF_BYTES;
         const int stage_key0 = first_stage_key + s * AM_STAGE_KEYS;
+        // who reads this stage: the warp alone (keys arrangement) or the four warps together
+        const int t0 = BY_KEYS ? lane : tid, nt = BY_KEYS ? 32 : AM_THREADS;
+        if (p.use_tma) {
+            // A wait that runs out records it and goes on (with whatever the buffer holds; the host raises on
+            // the status): every thread then still reaches the barriers below.
+            if (!pt_mbar_wait(&full_bar[buf], (s / AM_STAGES) & 1, &gave_up) && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
+            if (stage_key0 < k_begin || stage_key0 + AM_STAGE_KEYS > k_end) {      // uniform over the readers
+                // whole pages were copied: rows outside the range of keys become zeros (a value row that no
+                // query sees must not hold garbage, since 0 * NaN is NaN)
+                for (int idx = t0; idx < AM_STAGE_KEYS * CH; idx += nt) {
+                    const int j = idx / CH, c = idx - j * CH;
+                    if (stage_key0 + j < k_begin || stage_key0 + j >= k_end) {
+                        *reinterpret_cast<uint4*>(kt + swz_kv(j, c)) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(vt + swz_kv(j, c)) = make_uint4(0, 0, 0, 0);
+                    }
+                }
+                pt_fence_async();
+                if (BY_KEYS) __syncwarp(); else compute_sync();
+            }
+        } else if (BY_KEYS) {
+            // pages of a size that does not divide 64: the warp copies its stage itself, 16 bytes at a time
+            for (int idx = lane; idx < AM_STAGE_KEYS * CH; idx += 32) {
+                const int j = idx / CH, c = idx - j * CH, key = stage_key0 + j;
+                const __nv_bfloat16* src = nullptr;
+                if (key >= k_begin && key < k_end) {
+                    const int pi = key / p.page_size, slot = key - pi * p.page_size;
+                    const int page = pi < p.max_pages ? p.block_table[(size_t)req * p.max_pages + pi] : -1;
+                    if (page < 0 || page >= p.num_pages) {
+                        if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE);
+                    } else {
+                        src = p.kv_pool + (size_t)page * page_elems + ((size_t)kvh * p.page_size + slot) * HD + c * 8;
+                    }
+                }
+                if (src) {
+                    cp_async16(kt + swz_kv(j, c), src);
+                    cp_async16(vt + swz_kv(j, c), src + v_off);
+                } else {
+                    *reinterpret_cast<uint4*>(kt + swz_kv(j, c)) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(vt + swz_kv(j, c)) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncwarp();
+        } else {
+            cp_async_wait<AM_STAGES - 1>();
+            compute_sync();
+        }
         // this warp's keys of the stage: [w_key0, w_key0 + 16 * KB)
-        const int w_key0 = stage_key0 + (BY_KEYS ? warp * 16 : 0);
+        const int w_key0 = stage_key0;
         const int vis_lo = max(max(w_key0, k_begin), warp_lo);                   // keys some row of the warp sees
         const int vis_hi = min(min(w_key0 + 16 * KB, k_end), warp_pos_hi + 1);
         if (vis_lo < vis_hi) {                                                   // warp-uniform
@@ -256,36 +383,15 @@ attention_mma_kernel(AttnMmaParams p) {
             float sc[2 * KB][4];
 #pragma unroll
             for (int j = 0; j < 2 * KB; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f; }
-            const unsigned char* kwarp = kt + (BY_KEYS ? warp * BLOCK_BYTES : 0);
-            if (BY_KEYS) {
-                // one block of 16 keys per warp: the k-steps go round-robin into four accumulator pairs, so
-                // eight short chains of dependent MMAs run side by side instead of two long ones
-                float part[4][2][4];
+            const unsigned char* kwarp = kt;
 #pragma unroll
-                for (int a = 0; a < 4; ++a)
+            for (int ks = 0; ks < KSTEPS; ++ks) {
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) { part[a][j][0] = part[a][j][1] = part[a][j][2] = part[a][j][3] = 0.0f; }
-#pragma unroll
-                for (int ks = 0; ks < KSTEPS; ++ks) {
+                for (int kbi = 0; kbi < KB; ++kbi) {
                     unsigned kf[4];
-                    ldmatrix_x4(kf, kwarp + koff[ks]);
-                    mma_bf16(part[ks & 3][0], qf[ks], kf[0], kf[1]);
-                    mma_bf16(part[ks & 3][1], qf[ks], kf[2], kf[3]);
-                }
-#pragma unroll
-                for (int j = 0; j < 2; ++j)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) sc[j][e] = (part[0][j][e] + part[1][j][e]) + (part[2][j][e] + part[3][j][e]);
-            } else {
-#pragma unroll
-                for (int ks = 0; ks < KSTEPS; ++ks) {
-#pragma unroll
-                    for (int kbi = 0; kbi < KB; ++kbi) {
-                        unsigned kf[4];
-                        ldmatrix_x4(kf, kwarp + kbi * BLOCK_BYTES + koff[ks]);
-                        mma_bf16(sc[2 * kbi], qf[ks], kf[0], kf[1]);
-                        mma_bf16(sc[2 * kbi + 1], qf[ks], kf[2], kf[3]);
-                    }
+                    ldmatrix_x4(kf, kwarp + kbi * BLOCK_BYTES + koff[ks]);
+                    mma_bf16(sc[2 * kbi], qf[ks], kf[0], kf[1]);
+                    mma_bf16(sc[2 * kbi + 1], qf[ks], kf[2], kf[3]);
                 }
             }
             // ---- scale; mask only where a row of the warp does not see a key of the warp's span
@@ -351,7 +457,7 @@ attention_mma_kernel(AttnMmaParams p) {
                 pf[1] = pack_bf16(sc[2 * kbi][2], sc[2 * kbi][3]);
                 pf[2] = pack_bf16(sc[2 * kbi + 1][0], sc[2 * kbi + 1][1]);
                 pf[3] = pack_bf16(sc[2 * kbi + 1][2], sc[2 * kbi + 1][3]);
-                const unsigned char* vblock = vt + (BY_KEYS ? warp : kbi) * BLOCK_BYTES;
+                const unsigned char* vblock = vt + kbi * BLOCK_BYTES;
 #pragma unroll
                 for (int t2 = 0; t2 < NT_O / 2; ++t2) {
                     unsigned vf[4];
@@ -361,9 +467,15 @@ attention_mma_kernel(AttnMmaParams p) {
                 }
             }
         }
-        __syncthreads();                       // the stage's buffer may be refilled
+        // the stage's buffer may be refilled
+        if (p.use_tma) {
+            __syncwarp();
+            if (lane == 0) pt_mbar_arrive(&empty_bar[buf]);
+        } else if (!BY_KEYS) {
+            compute_sync();
+        }
     }
-    cp_async_wait<0>();
+    if (!p.use_tma && !BY_KEYS) cp_async_wait<0>();
 
     // ---- write the partial results
     if (direct) {
@@ -383,7 +495,7 @@ attention_mma_kernel(AttnMmaParams p) {
         for (int h = 0; h < 2; ++h) {
             int r = row_base + (lane >> 2) + h * 8;
             if (r >= n_rows) continue;
-            if (pos_r[h] < sp * p.split || lo_r[h] >= (sp + 1) * p.split) continue;
+            if (pos_r[h] < sp * split || lo_r[h] >= (sp + 1) * split) continue;
             int qi = r / group, g = r - qi * group;
             size_t prow = ((size_t)(row0 + qi) * p.nh + (size_t)kvh * group + g) * p.max_splits + sp;
             float* po = p.part_o + prow * HD;
@@ -395,7 +507,9 @@ attention_mma_kernel(AttnMmaParams p) {
             if ((lane & 3) == 0) { p.part_ml[prow * 2 + 0] = m_r[h] * AM_LN2; p.part_ml[prow * 2 + 1] = l_r[h]; }
         }
     } else {
-        // join the four warps' results: o_w, m_w, l_w -> shared memory (over the stage buffers)
+        // join the four warps' results: o_w, m_w, l_w -> shared memory (over the stage buffers, once every
+        // warp has read its last keys and values from them)
+        compute_sync();
         float* o_sh = reinterpret_cast<float*>(k_s);               // [4][16][HD]
         float* ml_sh = o_sh + 4 * 16 * HD;                         // [4][16][2]
 #pragma unroll
@@ -409,10 +523,10 @@ attention_mma_kernel(AttnMmaParams p) {
             }
             if ((lane & 3) == 0) { ml_sh[(warp * 16 + r) * 2 + 0] = m_r[h]; ml_sh[(warp * 16 + r) * 2 + 1] = l_r[h]; }
         }
-        __syncthreads();
+        compute_sync();
         const int pos = pos_first;
         const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-        if (!(pos < sp * p.split || lo >= (sp + 1) * p.split)) {
+        if (!(pos < sp * split || lo >= (sp + 1) * split)) {
             for (int idx = tid; idx < n_rows * HD; idx += AM_THREADS) {
                 int r = idx / HD, d = idx - r * HD;
                 float m = -INFINITY;
@@ -436,26 +550,25 @@ attention_mma_kernel(AttnMmaParams p) {
 
 template <int HD, bool BY_KEYS, int STAGES>
 static size_t am_smem_bytes() {
-    return (size_t)(BY_KEYS ? 16 : 64) * HD * 2 + (size_t)2 * STAGES * AM_STAGE_KEYS * HD * 2;
+    return (size_t)(BY_KEYS ? 16 : 64) * HD * 2 + (size_t)2 * STAGES * AM_STAGE_KEYS * HD * 2 + 1024;
 }
 
 template <int HD, bool BY_KEYS, int STAGES>
-static int am_launch_stages(const AttnMmaParams& p, int n_qblk, int n_splits, cudaStream_t stream) {
+static int am_launch_stages(const CUtensorMap& map, const CUtensorMap& map5, const AttnMmaParams& p, int n_qblk, int n_splits, cudaStream_t stream) {
     auto kern = attention_mma_kernel<HD, BY_KEYS, STAGES>;
     size_t smem = am_smem_bytes<HD, BY_KEYS, STAGES>();
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(n_qblk, p.nkv, n_splits);
-    e = launch(kern, grid, dim3(AM_THREADS), smem, stream, p);
+    e = launch(kern, grid, dim3(AM_ALL), smem, stream, map, map5, p);
     if (e != cudaSuccess) return (int)e;
     return BG_OK;
 }
 
 template <int HD, bool BY_KEYS>
-static int am_launch(const AttnMmaParams& p, int n_qblk, int n_splits, cudaStream_t stream) {
-    if (BY_KEYS && (long long)n_qblk * p.nkv * n_splits > 2 * 148)
-        return am_launch_stages<HD, BY_KEYS, 2>(p, n_qblk, n_splits, stream);
-    return am_launch_stages<HD, BY_KEYS, 3>(p, n_qblk, n_splits, stream);
+static int am_launch(const CUtensorMap& map, const CUtensorMap& map5, const AttnMmaParams& p, int n_qblk, int n_splits, cudaStream_t stream) {
+    if (BY_KEYS) return am_launch_stages<HD, BY_KEYS, AM_THREADS / 32>(map, map5, p, n_qblk, n_splits, stream);   // a buffer per warp
+    return am_launch_stages<HD, BY_KEYS, 3>(map, map5, p, n_qblk, n_splits, stream);
 }
 
 }  // namespace bg
@@ -483,7 +596,7 @@ extern "C" int bg_attention_mma_partial(const void* q, int q_stride, const void*
                                         void* direct_out, int out_stride, unsigned* status, cudaStream_t stream) {
     if (n_qblk <= 0 || n_splits_launch <= 0) return BG_OK;
     if (direct_out && (by_keys || n_splits_launch != 1 || (out_stride % 2) != 0)) return BG_ERR_SHAPE;
-    if (nh % nkv != 0 || split % AM_STAGE_KEYS != 0) return BG_ERR_SHAPE;
+    if (nh % nkv != 0 || split % AM_STAGE_KEYS != 0 || (split <= 0 && !by_keys)) return BG_ERR_SHAPE;
     if (n_splits_launch > max_splits || n_splits_launch > 65535 || nkv > 65535) return BG_ERR_SHAPE;
     if ((q_stride % 8) != 0 || ((uintptr_t)q % 16) != 0 || ((uintptr_t)kv_pool % 16) != 0) return BG_ERR_ALIGN;
     AttnMmaParams p;
@@ -496,9 +609,16 @@ extern "C" int bg_attention_mma_partial(const void* q, int q_stride, const void*
     p.scale_log2 = scale * AM_LOG2E; p.status = status;
     p.out = (__nv_bfloat16*)direct_out; p.out_stride = out_stride;
     if (by_keys ? p.group > 16 : p.group > 64) return BG_ERR_UNSUPPORTED;
-    if (hd == 128) return by_keys ? am_launch<128, true>(p, n_qblk, n_splits_launch, stream)
-                                  : am_launch<128, false>(p, n_qblk, n_splits_launch, stream);
-    if (hd == 64) return by_keys ? am_launch<64, true>(p, n_qblk, n_splits_launch, stream)
-                                 : am_launch<64, false>(p, n_qblk, n_splits_launch, stream);
+    if (hd != 64 && hd != 128) return BG_ERR_UNSUPPORTED;
+    CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    CUtensorMap map5;
+    memset(&map5, 0, sizeof(map5));
+    p.use_tma = pt_page_size_ok(page_size) && p.page_shift >= 0 && pt_pool_map(&map, kv_pool, num_pages, nkv, page_size, hd) == BG_OK;
+    p.whole_pages = p.use_tma && page_size == AM_STAGE_KEYS && pt_page_map(&map5, kv_pool, num_pages, nkv, page_size, hd) == BG_OK;
+    if (hd == 128) return by_keys ? am_launch<128, true>(map, map5, p, n_qblk, n_splits_launch, stream)
+                                  : am_launch<128, false>(map, map5, p, n_qblk, n_splits_launch, stream);
+    if (hd == 64) return by_keys ? am_launch<64, true>(map, map5, p, n_qblk, n_splits_launch, stream)
+                                 : am_launch<64, false>(map, map5, p, n_qblk, n_splits_launch, stream);
     return BG_ERR_UNSUPPORTED;
 }

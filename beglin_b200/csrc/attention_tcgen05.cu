@@ -20,13 +20,7 @@
 // Every wait on an mbarrier is bounded in time and records BG_STATUS_TIMEOUT.
 //
 // The result is the finished row, out[t, h, :] = O / l, as in attention_mma.cu's rows arrangement.
-#include <cuda.h>
-
-#include <map>
-#include <mutex>
-#include <tuple>
-
-#include "common.cuh"
+#include "page_tma.cuh"
 
 namespace bg {
 
@@ -482,32 +476,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
     if (tid == 0 && failed && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
 }
 
-typedef CUresult (*AtEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// The page pool of one layer, [num_pages][2][nkv][page_size][hd], as a 2-D tensor of rows of hd features;
-// a box is one page of one kv head, 64 features wide.
-static int at_pool_map(CUtensorMap* map, const void* pool, long long rows, int hd, int page_size) {
-    static AtEncodeFn fn = [] {
-        void* f = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            f = nullptr;
-        return (AtEncodeFn)f;
-    }();
-    if (!fn) return BG_ERR_UNSUPPORTED;
-    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)page_size};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? BG_OK : BG_ERR_SHAPE;
-}
-
 template <int HD>
 static int at_launch(const CUtensorMap& map, const AttnTcParams& p, int n_qblk, cudaStream_t stream) {
     auto kern = attention_tcgen05_kernel<HD>;
@@ -547,21 +515,8 @@ extern "C" int bg_attention_tc(const void* q, int q_stride, const void* kv_pool,
     p.block_table = block_table; p.max_pages = max_pages; p.positions = positions; p.qblk = qblk;
     p.out = (__nv_bfloat16*)out; p.out_stride = out_stride; p.nh = nh; p.nkv = nkv; p.group = nh / nkv;
     p.window = window; p.scale_log2 = scale * AT_LOG2E; p.status = status;
-    // the pool's map is made once per (pointer, shape)
-    static std::mutex mu;
-    static std::map<std::tuple<const void*, int, int, int, int>, CUtensorMap> maps;
     CUtensorMap map;
-    {
-        std::lock_guard<std::mutex> g(mu);
-        auto key = std::make_tuple(kv_pool, num_pages, nkv, page_size, hd);
-        auto it = maps.find(key);
-        if (it == maps.end()) {
-            int rc = at_pool_map(&map, kv_pool, (long long)num_pages * 2 * nkv * page_size, hd, page_size);
-            if (rc != BG_OK) return rc;
-            maps.emplace(key, map);
-        } else {
-            map = it->second;
-        }
-    }
+    int rc = pt_pool_map(&map, kv_pool, num_pages, nkv, page_size, hd);
+    if (rc != BG_OK) return rc;
     return hd == 128 ? at_launch<128>(map, p, n_qblk, stream) : at_launch<64>(map, p, n_qblk, stream);
 }

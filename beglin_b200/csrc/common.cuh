@@ -59,6 +59,17 @@ inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t 
 }
 #endif
 
+// Keys per split of a request's keys.  A positive `split` is taken as it is (the same boundaries for every
+// request: results then do not depend on a request's length).  split <= 0 spreads the request's own
+// n_keys evenly over the n_splits CTAs that the grid has for it, in multiples of 256 (decoding inside a
+// captured graph, whose grid is fixed while the requests grow).
+__host__ __device__ __forceinline__ int keys_per_split(int split, int n_keys, int n_splits) {
+    if (split > 0) return split;
+    const int s = (n_keys + n_splits - 1) / n_splits;
+    const int r = (s + 255) / 256 * 256;
+    return r < 256 ? 256 : r;
+}
+
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -298,18 +298,14 @@ def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, deco
     return "generic", bq.value, tile.value
 
 
-def decode_split(n_streams: int, context: int) -> int:
-    """Keys per CTA for the decoding kernel.  Each (request, kv head) is a stream of `context` keys;
-    it is cut so that the grid has about three CTAs per SM: many short ranges when few requests decode
-    (latency of one CTA is what counts), few long ones when many do (a CTA's start-up and the merging
-    of its result are spread over more keys).  A multiple of 64 between 128 and 2048; it depends on
-    the shapes of the step only."""
-    want = max(1, (3 * 148) // max(1, n_streams))
-    split = -(-context // want)
-    split = int(min(2048, max(128, -(-split // 64) * 64)))
-    if split < 256 and n_streams * -(-context // 256) >= 148:
-        split = 256                       # ranges of 256 already fill the machine
-    return split
+def decode_splits(n_streams: int, context: int) -> int:
+    """How many CTAs share the keys of one (request, kv head) stream in the decoding kernel.  A CTA has
+    a shared-memory buffer per warp and is alone on its SM, so the streams are cut to make one wave
+    of CTAs (148 SMs): more CTAs wait for a second wave, fewer leave SMs idle while the others walk
+    longer ranges.  No more than one CTA per 256 keys of `context` (a stage of 64 for each of the four
+    warps).  Each request's keys are spread evenly over its CTAs by the kernel itself, by the
+    request's own length, so the count depends on the shapes of the step only."""
+    return max(1, min(148 // max(1, n_streams), -(-context // 256)))
 
 
 def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table: torch.Tensor,
@@ -320,8 +316,10 @@ def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table
     come from `attention_plan`; `qblk` must be cut for that `bq`; `max_position` is the largest
     position among the rows (or a bound on it).
 
-    "generic" and "mma_keys" cut the keys into splits of `split` positions, write partial results and
-    merge them; "mma_rows" lets one CTA walk all keys of its query block and writes `out` directly."""
+    "generic" cuts the keys into splits of `split` positions (the same boundaries for every request),
+    writes partial results and merges them; "mma_keys" (decoding) spreads every request's own keys over
+    `decode_splits` CTAs and merges likewise; "mma_rows" and "tc_rows" let one CTA walk all keys of its
+    query block and write `out` directly."""
     _cuda(q, kv_pool, block_table, positions, qblk, out)
     _i32(positions, "positions"); _i32(block_table, "block_table")
     if qblk is not None:
@@ -352,8 +350,9 @@ def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table
                                           _p(status), _stream()), "attention_mma")
         return
     if kernel == "mma_keys":
-        split = decode_split(n_qblk * nkv, max_position + 1)
-    n_splits = max_position // split + 1
+        split, n_splits = 0, decode_splits(n_qblk * nkv, max_position + 1)
+    else:
+        n_splits = max_position // split + 1
     part_o = torch.empty((n_rows * nh * n_splits, hd), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((n_rows * nh * n_splits, 2), dtype=torch.float32, device=q.device)
     if kernel == "generic":
