@@ -135,6 +135,7 @@ __global__ void __launch_bounds__(512) add_rmsnorm_parts_kernel(float* __restric
     float4* rb = reinterpret_cast<float4*>(row_buf);
     float ss = 0.0f;
     float4 mine = make_float4(0.0f, 0.0f, 0.0f, 0.0f);          // this thread's first chunk stays in registers
+#pragma unroll 1
     for (int i = threadIdx.x; i < d4; i += blockDim.x) {
         float4 a = sum_parts4(reinterpret_cast<const float4*>(delta + (size_t)s * d) + i, parts, part_stride >> 2);
         float4 v = xr[i];
@@ -146,6 +147,7 @@ __global__ void __launch_bounds__(512) add_rmsnorm_parts_kernel(float* __restric
     ss = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)d + eps);
     TO* o = out + (size_t)r * d;
+#pragma unroll 1
     for (int i = threadIdx.x; i < d4; i += blockDim.x) {
         const bool first = i == (int)threadIdx.x;
         float4 v = first ? mine : rb[i];

@@ -1,0 +1,359 @@
+// The product of a step of few tokens (up to 64) with what stands before and behind it fused in, on
+// the fifth-generation tensor cores:
+//
+//   acc[t, n] = sum_k X[t, k] * W[n, k]        W: [n_out, K] bfloat16 by TMA, 128 output features per CTA
+//
+//   X         either bfloat16 activations by TMA, or made here from the float residual stream:
+//             X[t, k] = bf16(x[t, k] * rstd[t] * g[k]) with rstd[t] = 1 / sqrt(ssq[t] / K + eps), where
+//             ssq[t] is the sum (in index order) of partial sums of squares that the kernel which wrote
+//             x left behind.  That is RMSNorm (qwen_infer.c:689-704) without a kernel of its own: the
+//             four warps that later run the epilogue make the operand tiles, stage by stage.
+//   split-K   blockIdx.z takes a range of 64-wide k-blocks; the CTAs of one output tile form a thread
+//             block cluster (1, 1, splits), leave their accumulators in shared memory and add them up
+//             over distributed shared memory in rank order: rank r owns 128 / splits rows of the tile.
+//             No partial sums go to global memory, and the order of the sum is fixed by the shapes.
+//   epilogue  plain:    out[t, n] = acc (+ bias[n]), float or bfloat16;
+//             residual: x[t, n] += acc (+ bias[n]) in the float residual stream, and the sums of squares
+//                       of the new x over the CTA's rows go to ssq_out[part][t] (for the next norm);
+//             swiglu:   W's rows are interleaved, 64 of the gate then the 64 of up that belong to them:
+//                       h[t, 64 * tile + i] = silu(acc[i]) * acc[64 + i] as bfloat16
+//                       (qwen_infer.c:727-733), so gate_up never reaches global memory.
+//
+// Every wait on an mbarrier is bounded and records BG_STATUS_TIMEOUT; a CTA that gave up still goes
+// through the cluster's barriers, so its peers do not wait for it.
+#include "tc_common.cuh"
+
+namespace bg {
+
+constexpr int GF_STAGES = 4;
+constexpr int GF_PLAIN = 0, GF_RESIDUAL = 1, GF_SWIGLU = 2;
+
+struct FusedParams {
+    // the operand made from the residual stream (xf == null: X comes by TMA)
+    const float* xf;
+    int ldxf;
+    const float* ssq_in;            // [n_ssq_in][ssq_in_stride]
+    int n_ssq_in, ssq_in_stride;
+    const __nv_bfloat16* norm_w;    // [K]
+    float eps;
+    // the epilogue
+    const float* bias;              // [n_out] or null
+    int mode;
+    void* out;                      // plain: [T][ldo]; residual: the float stream [T][ldo]; swiglu: bfloat16 [T][ldo]
+    int out_dtype, ldo;
+    float* ssq_out;                 // residual: [tiles * splits][ssq_out_stride]
+    int ssq_out_stride;
+    int n_out, T, K, kb_per_split, splits;
+    unsigned* status;
+};
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// a float at the same shared-memory offset in the CTA of the given rank of the cluster
+__device__ __forceinline__ float ld_peer(unsigned local_addr, unsigned rank) {
+    unsigned a;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(a) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }   // warps 2..5
+
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, FusedParams p) {
+    constexpr int STAGES = GF_STAGES;
+    constexpr unsigned A_BYTES = TC_BM * TC_BK * 2;
+    constexpr unsigned B_BYTES = BN * TC_BK * 2;
+    constexpr unsigned STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr unsigned TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr int CHUNKS = BN * 8 / 128;                 // 16-byte pieces of an operand tile per epilogue thread
+    extern __shared__ unsigned char gf_smem_raw[];
+    unsigned char* tiles = (unsigned char*)(((uintptr_t)gf_smem_raw + 1023) & ~(uintptr_t)1023);
+    float* red = reinterpret_cast<float*>(tiles);                         // [BN][128], over the stages once they are done
+    float* sq = red + BN * TC_BM;                                          // [BN][rows of this rank]
+    __shared__ __align__(8) unsigned long long full_bar[STAGES];
+    __shared__ __align__(8) unsigned long long empty_bar[STAGES];
+    __shared__ __align__(8) unsigned long long acc_bar;
+    __shared__ unsigned tmem_base_sh;
+    __shared__ int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_m = blockIdx.x, tile_n = blockIdx.y, split = blockIdx.z;    // split == rank in the cluster
+    const int n_kb_total = (p.K + TC_BK - 1) / TC_BK;
+    const int kb0 = split * p.kb_per_split;
+    const int n_kb = min(p.kb_per_split, n_kb_total - kb0);
+    const bool make_x = p.xf != nullptr;
+
+    pdl_launch();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], make_x ? 5 : 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&acc_bar, 1);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(&tmem_base_sh)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = tmem_base_sh;
+
+    if (warp == 0) {
+        // ---------------- TMA producer: the weights (requested before the kernel ahead has finished) and,
+        // when they come by TMA, the activations
+        if (lane == 0 && n_kb > 0) {
+            const unsigned stage_tx = make_x ? A_BYTES : STAGE_BYTES;
+            const int ahead = n_kb < STAGES ? n_kb : STAGES;
+            for (int i = 0; i < ahead; ++i) {
+                mbar_expect_tx(&full_bar[i], stage_tx);
+                tma_load_2d(tiles + (size_t)i * STAGE_BYTES, &map_w, (kb0 + i) * TC_BK, tile_m * TC_BM, &full_bar[i]);
+            }
+            pdl_wait();
+            if (!make_x)
+                for (int i = 0; i < ahead; ++i)
+                    tma_load_2d(tiles + (size_t)i * STAGE_BYTES + A_BYTES, &map_x, (kb0 + i) * TC_BK, tile_n * BN, &full_bar[i]);
+            for (int i = ahead; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) { atomicExch(&failed, 1); break; }
+                unsigned char* a = tiles + (size_t)s * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], stage_tx);
+                tma_load_2d(a, &map_w, (kb0 + i) * TC_BK, tile_m * TC_BM, &full_bar[s]);
+                if (!make_x) tma_load_2d(a + A_BYTES, &map_x, (kb0 + i) * TC_BK, tile_n * BN, &full_bar[s]);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer
+        if (lane == 0 && n_kb > 0) {
+            constexpr unsigned idesc = instr_desc_bf16(TC_BM, BN < 16 ? 16 : BN);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % STAGES;
+                ok = mbar_wait(&full_bar[s], (i / STAGES) & 1);
+                if (!ok) { atomicExch(&failed, 1); break; }
+                tc_fence_after();
+                const unsigned a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                const unsigned b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)
+                    tc_mma(tmem_base, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                           (i > 0 || k > 0) ? 1u : 0u);
+                tc_commit(&empty_bar[s]);
+            }
+            tc_commit(&acc_bar);
+        }
+    } else {
+        // ---------------- warps 2..5: first the operand tiles from the residual stream, then the epilogue
+        const int te = threadIdx.x - 64;                                   // 0..127
+        const int quarter = warp & 3;                                      // the tensor-memory lanes of this warp
+        bool ok = true;
+        pdl_wait();
+        if (make_x && n_kb > 0) {
+            // thread te makes pieces te, te + 128, ...: piece e is token e / 8 of the tile, features 8 (e % 8) ..+7
+            float rstd[CHUNKS];
+            const float* xrow[CHUNKS];
+#pragma unroll
+            for (int j = 0; j < CHUNKS; ++j) {
+                const int t = tile_n * BN + (te + j * 128) / 8;
+                float ssq = 0.0f;
+                if (t < p.T)
+                    for (int q = 0; q < p.n_ssq_in; ++q) ssq += p.ssq_in[(size_t)q * p.ssq_in_stride + t];
+                rstd[j] = t < p.T ? 1.0f / sqrtf(ssq / (float)p.K + p.eps) : 0.0f;
+                xrow[j] = p.xf + (size_t)(t < p.T ? t : 0) * p.ldxf;
+            }
+            const int c8 = te & 7;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % STAGES;
+                const int k = (kb0 + i) * TC_BK + c8 * 8;
+                // the values go out before the wait for the stage, so that they are here when it is free
+                float v[CHUNKS][8], g[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) g[q] = 0.0f;
+                if (k < p.K) load8(p.norm_w + k, g);                       // K is a multiple of 8
+#pragma unroll
+                for (int j = 0; j < CHUNKS; ++j) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) v[j][q] = 0.0f;
+                    if (k < p.K && rstd[j] != 0.0f) load8(xrow[j] + k, v[j]);
+                }
+                if (i >= STAGES) {
+                    ok = mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1);
+                    if (!ok) { atomicExch(&failed, 1); break; }
+                }
+                unsigned char* b = tiles + (size_t)s * STAGE_BYTES + A_BYTES;
+#pragma unroll
+                for (int j = 0; j < CHUNKS; ++j) {
+                    const int t = (te + j * 128) / 8;                      // row of the tile
+                    float o[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) o[q] = v[j][q] * rstd[j] * g[q];
+                    store8(reinterpret_cast<__nv_bfloat16*>(b + t * 128 + ((c8 ^ (t & 7)) << 4)), o);
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&full_bar[s])) : "memory");
+            }
+        }
+        if (ok && n_kb > 0) {
+            ok = mbar_wait(&acc_bar, 0);
+            if (!ok) atomicExch(&failed, 1);
+            tc_fence_after();
+        }
+        // the accumulator of this CTA's range of K: red[token][row of the tile]
+        const int m_local = quarter * 32 + lane;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+            unsigned r[16];
+            if (ok && n_kb > 0) {
+                tc_ld16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c, r);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) red[(c + j) * TC_BM + m_local] = __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (p.splits > 1) cluster_sync_all();                                  // every CTA's red is complete
+
+    if (warp >= 2) {
+        const int te = threadIdx.x - 64;
+        const int S = p.splits, rank = split;
+        const int rows_per = TC_BM / S, half = rows_per / 2;
+        const unsigned red_addr = smem_u32(red);
+        for (int e = te; e < rows_per * BN; e += 128) {
+            const int rl = e % rows_per, c = e / rows_per;
+            // swiglu: a rank owns rows of the gate and the rows of up that belong to them
+            const int row = p.mode == GF_SWIGLU ? (rl < half ? rank * half + rl : 64 + rank * half + (rl - half)) : rank * rows_per + rl;
+            float v = 0.0f;
+            if (S == 1) {
+                v = red[c * TC_BM + row];
+            } else {
+                for (int s = 0; s < S; ++s) v += ld_peer(red_addr + (unsigned)(c * TC_BM + row) * 4u, (unsigned)s);
+            }
+            const int n = tile_m * TC_BM + row, t = tile_n * BN + c;
+            const bool real = n < p.n_out && t < p.T;
+            if (p.bias && n < p.n_out) v += p.bias[n];
+            if (p.mode == GF_PLAIN) {
+                if (real) {
+                    if (p.out_dtype == BG_DTYPE_F32) ((float*)p.out)[(size_t)t * p.ldo + n] = v;
+                    else ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(v);
+                }
+            } else if (p.mode == GF_RESIDUAL) {
+                float x = 0.0f;
+                if (real) {
+                    float* px = (float*)p.out + (size_t)t * p.ldo + n;
+                    x = *px + v;
+                    *px = x;
+                }
+                sq[c * rows_per + rl] = x * x;
+            } else {
+                sq[c * rows_per + rl] = v;
+            }
+        }
+        epilogue_sync();
+        if (p.mode == GF_RESIDUAL) {
+            // the sum of squares of this rank's rows, token by token, in row order
+            if (te < BN) {
+                const int t = tile_n * BN + te;
+                float acc = 0.0f;
+                for (int i = 0; i < rows_per; ++i) acc += sq[te * rows_per + i];
+                if (t < p.T && p.ssq_out) p.ssq_out[(size_t)(tile_m * S + rank) * p.ssq_out_stride + t] = acc;
+            }
+        } else if (p.mode == GF_SWIGLU) {
+            for (int e = te; e < half * BN; e += 128) {
+                const int i = e % half, c = e / half;
+                const int t = tile_n * BN + c;
+                const float g = sq[c * rows_per + i], u = sq[c * rows_per + half + i];
+                if (t < p.T)
+                    ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + tile_m * 64 + rank * half + i] =
+                        __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+            }
+        }
+    }
+    if (p.splits > 1) cluster_sync_all();                                  // nobody leaves while a peer may read its red
+    else __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && failed && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
+}
+
+template <int BN>
+static int gf_launch(const CUtensorMap& mw, const CUtensorMap& mx, const FusedParams& p, cudaStream_t stream) {
+    auto kern = gemm_fused_kernel<BN>;
+    size_t smem = (size_t)GF_STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+    static bool set = false;
+    if (!set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        set = true;
+    }
+    dim3 grid((p.n_out + TC_BM - 1) / TC_BM, (p.T + BN - 1) / BN, p.splits);
+    cudaError_t e = launch_cluster(kern, grid, dim3(TC_THREADS), smem, stream, p.splits, mw, mx, p);
+    if (e != cudaSuccess) return (int)e;
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+}  // namespace bg
+
+using namespace bg;
+
+// See the head of the file.  X (bfloat16 [T, K], row stride ldx) or xf (float [T, K], row stride ldxf, with
+// ssq_in, norm_w and eps) is the left operand; splits is 1, 2, 4 or 8.
+extern "C" int bg_gemm_fused(const void* W, int n_out, int K, int ldw, const void* X, int ldx, const float* xf, int ldxf,
+                             const float* ssq_in, int n_ssq_in, int ssq_in_stride, const void* norm_w, float eps, int T,
+                             const float* bias, int mode, void* out, int out_dtype, int ldo, float* ssq_out,
+                             int ssq_out_stride, int splits, unsigned* status, cudaStream_t stream) {
+    if (T <= 0 || n_out <= 0) return BG_OK;
+    if (K <= 0 || T > 64) return BG_ERR_SHAPE;
+    if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return BG_ERR_SHAPE;
+    if ((ldw % 8) || (K % 8) || ((uintptr_t)W % 16)) return BG_ERR_ALIGN;
+    if ((X == nullptr) == (xf == nullptr)) return BG_ERR_SHAPE;
+    if (X && ((ldx % 8) || ((uintptr_t)X % 16))) return BG_ERR_ALIGN;
+    if (xf && ((ldxf % 4) || ((uintptr_t)xf % 16) || ((uintptr_t)norm_w % 16) || !ssq_in || !norm_w || n_ssq_in < 1)) return BG_ERR_ALIGN;
+    if (mode == GF_PLAIN) {
+        if (out_dtype != BG_DTYPE_F32 && out_dtype != BG_DTYPE_BF16) return BG_ERR_DTYPE;
+    } else if (mode == GF_RESIDUAL) {
+        if (out_dtype != BG_DTYPE_F32) return BG_ERR_DTYPE;
+    } else if (mode == GF_SWIGLU) {
+        if (out_dtype != BG_DTYPE_BF16) return BG_ERR_DTYPE;
+        if (n_out % TC_BM) return BG_ERR_SHAPE;
+    } else {
+        return BG_ERR_SHAPE;
+    }
+    const int n_kb = (K + TC_BK - 1) / TC_BK;
+    FusedParams p;
+    p.xf = xf; p.ldxf = ldxf; p.ssq_in = ssq_in; p.n_ssq_in = n_ssq_in; p.ssq_in_stride = ssq_in_stride;
+    p.norm_w = (const __nv_bfloat16*)norm_w; p.eps = eps;
+    p.bias = bias; p.mode = mode; p.out = out; p.out_dtype = out_dtype; p.ldo = ldo;
+    p.ssq_out = ssq_out; p.ssq_out_stride = ssq_out_stride;
+    p.n_out = n_out; p.T = T; p.K = K; p.splits = splits;
+    p.kb_per_split = (n_kb + splits - 1) / splits;
+    p.status = status;
+    if ((long long)(splits - 1) * p.kb_per_split >= n_kb) return BG_ERR_SHAPE;      // an empty range of K
+    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : 64;
+    CUtensorMap mw, mx;
+    int rc = weight_map(&mw, W, n_out, K, ldw);
+    if (rc != BG_OK) return rc;
+    if (X) {
+        rc = make_map(&mx, X, T, K, ldx, bn);
+        if (rc != BG_OK) return rc;
+    } else {
+        memset(&mx, 0, sizeof(mx));
+    }
+    switch (bn) {
+        case 16: return gf_launch<16>(mw, mx, p, stream);
+        case 32: return gf_launch<32>(mw, mx, p, stream);
+        default: return gf_launch<64>(mw, mx, p, stream);
+    }
+}

@@ -45,6 +45,9 @@ _SIGNATURES = {
                        _c_int, _c_void_p],
     "bg_gemm_bf16_tn": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                         _c_int, _c_int, _c_void_p, _c_void_p],
+    "bg_gemm_fused": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int,
+                      _c_void_p, _c_float, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
+                      _c_void_p, _c_void_p],
     "bg_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
 }
 
@@ -426,6 +429,60 @@ def gemm_bf16_tn_unchecked(x: torch.Tensor, w_ptr: int, n_out: int, k: int, ldw:
     _check(_lib.bg_gemm_bf16_tn(w_ptr, n_out, k, ldw, x.data_ptr(), x.shape[0], x.stride(0), bias_ptr, out.data_ptr(),
                                 F32 if out.dtype == torch.float32 else BF16, n_out, splits, status_ptr, _stream()),
            "gemm_bf16_tn")
+
+
+FUSED_PLAIN, FUSED_RESIDUAL, FUSED_SWIGLU = 0, 1, 2
+
+
+def gemm_fused(w: torch.Tensor, out: torch.Tensor, mode: int = FUSED_PLAIN, *, x: Optional[torch.Tensor] = None,
+               xf: Optional[torch.Tensor] = None, ssq_in: Optional[torch.Tensor] = None,
+               norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, bias: Optional[torch.Tensor] = None,
+               ssq_out: Optional[torch.Tensor] = None, splits: int = 1, status: Optional[torch.Tensor] = None) -> None:
+    """The product of up to 64 rows with w[N, K]^T on the tcgen05 tensor cores, with its neighbours fused in.
+
+    Left operand: `x` (bfloat16 [T, K]), or the float32 residual stream `xf` [T, K] normalised on the fly:
+    bf16(xf * rstd * norm_weight), rstd = 1 / sqrt(sum_p ssq_in[p] / K + eps), ssq_in float32 [parts, >= T].
+    K is cut into `splits` (1, 2, 4 or 8) ranges whose CTAs add up inside a thread block cluster.
+    mode FUSED_PLAIN: out[T, N] = product (+ bias), float32 or bfloat16.
+    mode FUSED_RESIDUAL: out (float32 [T, N], the residual stream) += product (+ bias); ssq_out
+      [ceil(N / 128) * splits, >= T] receives partial sums of squares of the new rows.
+    mode FUSED_SWIGLU: w's rows are interleaved (64 of gate, then their 64 of up); out bfloat16 [T, N / 2] =
+      silu(gate) * up."""
+    _cuda(w, out, x, xf, ssq_in, norm_weight, bias, ssq_out, status)
+    N, K = w.shape
+    if w.dtype != torch.bfloat16 or w.stride(1) != 1:
+        raise KernelError("gemm_fused takes a bfloat16 weight with contiguous rows")
+    if (x is None) == (xf is None):
+        raise KernelError("gemm_fused takes either x (bfloat16) or xf (float32 with ssq_in and norm_weight)")
+    src = x if x is not None else xf
+    T = src.shape[0]
+    if src.shape[1] != K or src.stride(1) != 1 or T > 64:
+        raise KernelError(f"gemm_fused: the left operand is {tuple(src.shape)}, expected up to 64 rows of {K}")
+    if x is not None and x.dtype != torch.bfloat16:
+        raise KernelError("gemm_fused: x must be bfloat16")
+    if xf is not None:
+        if xf.dtype != torch.float32 or ssq_in is None or norm_weight is None:
+            raise KernelError("gemm_fused: xf must be float32 and come with ssq_in and norm_weight")
+        if ssq_in.dtype != torch.float32 or ssq_in.dim() != 2 or ssq_in.shape[1] < T or ssq_in.stride(1) != 1:
+            raise KernelError("gemm_fused: ssq_in must be float32 [parts, >= T]")
+        if norm_weight.dtype != torch.bfloat16 or norm_weight.numel() != K or not norm_weight.is_contiguous():
+            raise KernelError("gemm_fused: norm_weight must be bfloat16 with one value per input feature")
+    n_cols = N // 2 if mode == FUSED_SWIGLU else N
+    if out.shape[0] != T or out.shape[1] != n_cols or out.stride(1) != 1:
+        raise KernelError(f"gemm_fused: out is {tuple(out.shape)}, expected {(T, n_cols)}")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N or not bias.is_contiguous()):
+        raise KernelError("gemm_fused: bias must be float32 with one value per output feature")
+    if mode == FUSED_RESIDUAL and ssq_out is not None:
+        parts = -(-N // 128) * splits
+        if ssq_out.dtype != torch.float32 or ssq_out.dim() != 2 or ssq_out.shape[0] < parts or ssq_out.shape[1] < T \
+                or ssq_out.stride(1) != 1:
+            raise KernelError(f"gemm_fused: ssq_out must be float32 [>= {parts}, >= {T}]")
+    _check(lib().bg_gemm_fused(_p(w), N, K, w.stride(0), _p(x), x.stride(0) if x is not None else 0, _p(xf),
+                               xf.stride(0) if xf is not None else 0, _p(ssq_in),
+                               ssq_in.shape[0] if ssq_in is not None else 0, ssq_in.stride(0) if ssq_in is not None else 0,
+                               _p(norm_weight), float(eps), T, _p(bias), mode, _p(out), _dt(out), out.stride(0),
+                               _p(ssq_out), ssq_out.stride(0) if ssq_out is not None else 0, splits, _p(status),
+                               _stream()), "gemm_fused")
 
 
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],

@@ -388,3 +388,81 @@ def test_gemm_tcgen05(ops, T, N, K, splits):
         ops.gemm_bf16_tn(x, w, b, full, 1, status)
         ops.gemm_bf16_tn(x[T // 2:T // 2 + 1], w, b, one, 1, status)
         assert torch.equal(one[0], full[T // 2])
+
+
+def _interleave_gate_up(gate, up):
+    """Rows in blocks of 64: gate[0:64], up[0:64], gate[64:128], up[64:128], ..."""
+    im = gate.shape[0]
+    return torch.stack([gate.reshape(im // 64, 64, -1), up.reshape(im // 64, 64, -1)], 1).reshape(2 * im, -1)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,N,K,splits", [(8, 256, 512, 1), (8, 384, 1536, 8), (5, 200, 264, 2), (16, 128, 1024, 4),
+                                          (33, 1536, 1536, 8), (64, 300, 640, 2), (17, 256, 192, 1)])
+def test_gemm_fused_plain_and_residual(ops, T, N, K, splits):
+    torch.manual_seed(T * 31 + N)
+    x = (torch.randn(T, K) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(N) * 0.1
+    want = x.double() @ w.double().t() + bias.double()
+    status = ops.new_status(DEV)
+    for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 1e-2)):
+        out = torch.full((T, N), float("nan"), dtype=dtype, device=DEV)
+        ops.gemm_fused(w.to(DEV), out, ops.FUSED_PLAIN, x=x.to(DEV), bias=bias.to(DEV), splits=splits, status=status)
+        ops.raise_on_status(status)
+        assert (out.double().cpu() - want).abs().max() < tol * max(1.0, float(want.abs().max()))
+    # residual: the stream is updated in place and the sums of squares of its new rows come back in parts
+    stream = torch.randn(T, N)
+    xs = stream.clone().to(DEV)
+    parts = -(-N // 128) * splits
+    ssq = torch.full((parts, 64), float("nan"), device=DEV)
+    ops.gemm_fused(w.to(DEV), xs, ops.FUSED_RESIDUAL, x=x.to(DEV), bias=bias.to(DEV), ssq_out=ssq, splits=splits, status=status)
+    ops.raise_on_status(status)
+    new = stream.double() + want
+    assert (xs.double().cpu() - new).abs().max() < 2e-5 * max(1.0, float(new.abs().max()))
+    got_ssq = ssq[:, :T].double().sum(0).cpu()
+    assert torch.allclose(got_ssq, (xs.double().cpu() ** 2).sum(1), rtol=1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,N,K,splits,parts", [(8, 256, 512, 1, 3), (8, 2048, 1536, 8, 96), (3, 136, 200, 2, 1),
+                                               (40, 256, 1536, 4, 12), (64, 128, 640, 1, 5)])
+def test_gemm_fused_norm_prologue(ops, T, N, K, splits, parts):
+    torch.manual_seed(N + K)
+    xf = torch.randn(T, K) * 2.0
+    g = (1.0 + 0.2 * torch.randn(K)).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    eps = 1e-5
+    # the sums of squares arrive cut into parts (here: by ranges of columns, as a producing kernel leaves them)
+    cols = torch.linspace(0, K, parts + 1).long()
+    ssq = torch.zeros(parts, 64)
+    for i in range(parts):
+        ssq[i, :T] = (xf[:, cols[i]:cols[i + 1]].double() ** 2).sum(1).float()
+    rstd = 1.0 / torch.sqrt((xf.double() ** 2).sum(1) / K + eps)
+    xn = (xf.double() * rstd[:, None] * g.double()).to(torch.bfloat16)
+    want = xn.double() @ w.double().t()
+    out = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
+    status = ops.new_status(DEV)
+    ops.gemm_fused(w.to(DEV), out, ops.FUSED_PLAIN, xf=xf.to(DEV), ssq_in=ssq.to(DEV), norm_weight=g.to(DEV), eps=eps,
+                   splits=splits, status=status)
+    ops.raise_on_status(status)
+    # the operand is rounded to bfloat16 once: a value on a rounding boundary may fall to the other side
+    assert (out.double().cpu() - want).abs().max() < 4e-3 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,im,K,splits", [(8, 128, 512, 1), (8, 896, 1536, 2), (20, 64, 264, 1), (50, 256, 1024, 8),
+                                           (3, 192, 640, 4)])
+def test_gemm_fused_swiglu(ops, T, im, K, splits):
+    torch.manual_seed(im + K)
+    x = (torch.randn(T, K) * 0.5).to(torch.bfloat16)
+    gate = (torch.randn(im, K) * 0.08).to(torch.bfloat16)
+    up = (torch.randn(im, K) * 0.08).to(torch.bfloat16)
+    gv, uv = x.double() @ gate.double().t(), x.double() @ up.double().t()
+    want = gv / (1.0 + torch.exp(-gv)) * uv
+    out = torch.full((T, im), float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = ops.new_status(DEV)
+    ops.gemm_fused(_interleave_gate_up(gate, up).contiguous().to(DEV), out, ops.FUSED_SWIGLU, x=x.to(DEV), splits=splits,
+                   status=status)
+    ops.raise_on_status(status)
+    assert (out.double().cpu() - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
