@@ -172,10 +172,12 @@ __global__ void add_residual_kernel(float* __restrict__ x, const TD* __restrict_
 // ---------------------------------------------------------------------------------------------
 // out[t, i] = silu(g) * u with g = sum_p gu[p][t, i], u = sum_p gu[p][t, im + i] and
 // silu(g) = g / (1 + exp(-g))  (qwen_infer.c:727-733).  gu may be the partial sums of a split-K
-// product, [parts][rows][2 im].
+// product, [parts][rows][2 im].  With block > 0 the columns of gu are interleaved in blocks of that
+// many features, gate then up, gate then up (the layout that lets one CTA of the fused product hold
+// both): gate i is column (i / block) * 2 block + i % block and its up lies `block` columns on.
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, int parts, size_t part_stride, TO* __restrict__ out,
-                              int rows, int im) {
+                              int rows, int im, int block) {
     pdl_launch();
     pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -183,15 +185,16 @@ __global__ void swiglu_kernel(const TI* __restrict__ gu, int parts, size_t part_
     if (idx >= total) return;
     size_t t = idx / im;
     int i = (int)(idx - t * im);
-    const TI* gp = gu + t * 2 * (size_t)im + i;
+    const int col = block > 0 ? (i / block) * 2 * block + i % block : i;
+    const TI* gp = gu + t * 2 * (size_t)im + col;
     float g = sum_parts(gp, parts, part_stride);
-    float u = sum_parts(gp + im, parts, part_stride);
+    float u = sum_parts(gp + (block > 0 ? block : im), parts, part_stride);
     out[idx] = from_float<TO>((g / (1.0f + expf(-g))) * u);
 }
 
 // One tensor (no partial sums), im a multiple of 8: eight features per thread, 16-byte accesses.
 template <typename TI, typename TO>
-__global__ void swiglu_vec8_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int rows, int im) {
+__global__ void swiglu_vec8_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int rows, int im, int block) {
     pdl_launch();
     pdl_wait();
     const int im8 = im >> 3;
@@ -199,9 +202,11 @@ __global__ void swiglu_vec8_kernel(const TI* __restrict__ gu, TO* __restrict__ o
     if (idx >= (size_t)rows * im8) return;
     size_t t = idx / im8;
     int c = (int)(idx - t * im8);
+    const int i = 8 * c;                                     // block is a multiple of 8 here
+    const int col = block > 0 ? (i / block) * 2 * block + i % block : i;
     float g[8], u[8];
-    load8(gu + t * 2 * (size_t)im + 8 * c, g);
-    load8(gu + t * 2 * (size_t)im + im + 8 * c, u);
+    load8(gu + t * 2 * (size_t)im + col, g);
+    load8(gu + t * 2 * (size_t)im + col + (block > 0 ? block : im), u);
 #pragma unroll
     for (int i = 0; i < 8; ++i) g[i] = (g[i] / (1.0f + expf(-g[i]))) * u[i];
     store8(out + t * (size_t)im + 8 * c, g);
@@ -479,29 +484,29 @@ extern "C" int bg_add_residual(float* x, const void* delta, int delta_dtype, lon
 }
 
 template <typename TI>
-static int swiglu_in(const void* gu, int parts, size_t part_stride, void* out, int out_dtype, int rows, int im,
+static int swiglu_in(const void* gu, int parts, size_t part_stride, void* out, int out_dtype, int rows, int im, int block,
                      cudaStream_t stream) {
-    const bool vec = parts == 1 && (im % 8 == 0) && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    const bool vec = parts == 1 && (im % 8 == 0) && (block % 8 == 0) && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0);
     if (vec) {
         size_t total = (size_t)rows * (im / 8);
         unsigned blocks = (unsigned)((total + 255) / 256);
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_vec8_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream,
-            (const TI*)gu, (TO*)out, rows, im));
+            (const TI*)gu, (TO*)out, rows, im, block));
     } else {
         size_t total = (size_t)rows * im;
         unsigned blocks = (unsigned)((total + 255) / 256);
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream,
-            (const TI*)gu, parts, part_stride, (TO*)out, rows, im));
+            (const TI*)gu, parts, part_stride, (TO*)out, rows, im, block));
     }
     BG_LAUNCH_CHECK();
     return BG_OK;
 }
 
 extern "C" int bg_swiglu(const void* gu, int in_dtype, int parts, long long part_stride, void* out, int out_dtype,
-                         int rows, int im, cudaStream_t stream) {
+                         int rows, int im, int block, cudaStream_t stream) {
     if (rows <= 0) return BG_OK;
-    if (parts < 1) return BG_ERR_SHAPE;
-    BG_DISPATCH_DTYPE(in_dtype, TI, return (swiglu_in<TI>(gu, parts, (size_t)part_stride, out, out_dtype, rows, im, stream)));
+    if (parts < 1 || block < 0 || (block > 0 && im % block != 0)) return BG_ERR_SHAPE;
+    BG_DISPATCH_DTYPE(in_dtype, TI, return (swiglu_in<TI>(gu, parts, (size_t)part_stride, out, out_dtype, rows, im, block, stream)));
     return BG_OK;
 }
 

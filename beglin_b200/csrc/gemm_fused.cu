@@ -9,9 +9,10 @@
 //             x left behind.  That is RMSNorm (qwen_infer.c:689-704) without a kernel of its own: the
 //             four warps that later run the epilogue make the operand tiles, stage by stage.
 //   split-K   blockIdx.z takes a range of 64-wide k-blocks; the CTAs of one output tile form a thread
-//             block cluster (1, 1, splits), leave their accumulators in shared memory and add them up
-//             over distributed shared memory in rank order: rank r owns 128 / splits rows of the tile.
-//             No partial sums go to global memory, and the order of the sum is fixed by the shapes.
+//             block cluster (1, 1, splits).  Rank r owns 128 / splits rows of the tile: every CTA stores
+//             those rows of its accumulator into rank r's shared memory (distributed shared memory), the
+//             cluster meets at ONE barrier, and rank r adds the parts up in rank order.  No partial sums
+//             go to global memory, and the order of the sum is fixed by the shapes.
 //   epilogue  plain:    out[t, n] = acc (+ bias[n]), float or bfloat16;
 //             residual: x[t, n] += acc (+ bias[n]) in the float residual stream, and the sums of squares
 //                       of the new x over the CTA's rows go to ssq_out[part][t] (for the next norm);
@@ -25,7 +26,6 @@
 
 namespace bg {
 
-constexpr int GF_STAGES = 4;
 constexpr int GF_PLAIN = 0, GF_RESIDUAL = 1, GF_SWIGLU = 2;
 
 struct FusedParams {
@@ -51,20 +51,20 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
-// a float at the same shared-memory offset in the CTA of the given rank of the cluster
-__device__ __forceinline__ float ld_peer(unsigned local_addr, unsigned rank) {
+// the address, in the cluster's shared window, of this CTA's shared-memory address in the CTA of the given rank
+__device__ __forceinline__ unsigned peer_addr(unsigned local_addr, unsigned rank) {
     unsigned a;
-    float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(a) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(a) : "memory");
-    return v;
+    return a;
+}
+__device__ __forceinline__ void st_cluster(unsigned addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
 }
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }   // warps 2..5
 
-template <int BN>
+template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, FusedParams p) {
-    constexpr int STAGES = GF_STAGES;
     constexpr unsigned A_BYTES = TC_BM * TC_BK * 2;
     constexpr unsigned B_BYTES = BN * TC_BK * 2;
     constexpr unsigned STAGE_BYTES = A_BYTES + B_BYTES;
@@ -72,8 +72,10 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     constexpr int CHUNKS = BN * 8 / 128;                 // 16-byte pieces of an operand tile per epilogue thread
     extern __shared__ unsigned char gf_smem_raw[];
     unsigned char* tiles = (unsigned char*)(((uintptr_t)gf_smem_raw + 1023) & ~(uintptr_t)1023);
-    float* red = reinterpret_cast<float*>(tiles);                         // [BN][128], over the stages once they are done
-    float* sq = red + BN * TC_BM;                                          // [BN][rows of this rank]
+    // what the ranks of the cluster send to this one: [rank][token][row of this rank's share]; it is written by
+    // peers while this CTA may still be in its main loop, so it has shared memory of its own
+    float* recv = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES);
+    float* sq = reinterpret_cast<float*>(tiles);                           // [BN][rows of this rank], over the stages once they are done
     __shared__ __align__(8) unsigned long long full_bar[STAGES];
     __shared__ __align__(8) unsigned long long empty_bar[STAGES];
     __shared__ __align__(8) unsigned long long acc_bar;
@@ -157,46 +159,73 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             // thread te makes pieces te, te + 128, ...: piece e is token e / 8 of the tile, features 8 (e % 8) ..+7
             float rstd[CHUNKS];
             const float* xrow[CHUNKS];
+            const int c8 = te & 7;
 #pragma unroll
             for (int j = 0; j < CHUNKS; ++j) {
+                // the eight threads of a token share the parts of its sum of squares: thread c8 adds parts c8,
+                // c8 + 8, ... (four loads on their way at a time), then the eight sums meet in a fixed order
                 const int t = tile_n * BN + (te + j * 128) / 8;
                 float ssq = 0.0f;
-                if (t < p.T)
-                    for (int q = 0; q < p.n_ssq_in; ++q) ssq += p.ssq_in[(size_t)q * p.ssq_in_stride + t];
+                if (t < p.T) {
+                    for (int q = c8; q < p.n_ssq_in; q += 32) {
+                        float a[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            a[u] = q + 8 * u < p.n_ssq_in ? p.ssq_in[(size_t)(q + 8 * u) * p.ssq_in_stride + t] : 0.0f;
+                        ssq += (a[0] + a[1]) + (a[2] + a[3]);
+                    }
+                }
+                ssq += __shfl_xor_sync(0xffffffffu, ssq, 1);
+                ssq += __shfl_xor_sync(0xffffffffu, ssq, 2);
+                ssq += __shfl_xor_sync(0xffffffffu, ssq, 4);
                 rstd[j] = t < p.T ? 1.0f / sqrtf(ssq / (float)p.K + p.eps) : 0.0f;
                 xrow[j] = p.xf + (size_t)(t < p.T ? t : 0) * p.ldxf;
             }
-            const int c8 = te & 7;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % STAGES;
+            // the values of DEPTH k-blocks are on their way at any time: a k-block costs one trip to L2, and
+            // one at a time would make the operand tiles slower than the weights arrive
+            constexpr int DEPTH = CHUNKS == 1 ? 4 : (CHUNKS == 2 ? 2 : 1);
+            float v[DEPTH][CHUNKS][8], g[DEPTH][8];
+            auto fetch = [&](int i, int slot) {
                 const int k = (kb0 + i) * TC_BK + c8 * 8;
-                // the values go out before the wait for the stage, so that they are here when it is free
-                float v[CHUNKS][8], g[8];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) g[q] = 0.0f;
-                if (k < p.K) load8(p.norm_w + k, g);                       // K is a multiple of 8
+                for (int q = 0; q < 8; ++q) g[slot][q] = 0.0f;
+                if (i < n_kb && k < p.K) load8(p.norm_w + k, g[slot]);     // K is a multiple of 8
 #pragma unroll
                 for (int j = 0; j < CHUNKS; ++j) {
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) v[j][q] = 0.0f;
-                    if (k < p.K && rstd[j] != 0.0f) load8(xrow[j] + k, v[j]);
+                    for (int q = 0; q < 8; ++q) v[slot][j][q] = 0.0f;
+                    if (i < n_kb && k < p.K && rstd[j] != 0.0f) load8(xrow[j] + k, v[slot][j]);
                 }
-                if (i >= STAGES) {
-                    ok = mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1);
-                    if (!ok) { atomicExch(&failed, 1); break; }
-                }
-                unsigned char* b = tiles + (size_t)s * STAGE_BYTES + A_BYTES;
+            };
 #pragma unroll
-                for (int j = 0; j < CHUNKS; ++j) {
-                    const int t = (te + j * 128) / 8;                      // row of the tile
-                    float o[8];
+            for (int d = 0; d < DEPTH; ++d) fetch(d, d);
+            for (int i0 = 0; i0 < n_kb && ok; i0 += DEPTH) {
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) o[q] = v[j][q] * rstd[j] * g[q];
-                    store8(reinterpret_cast<__nv_bfloat16*>(b + t * 128 + ((c8 ^ (t & 7)) << 4)), o);
+                for (int d = 0; d < DEPTH; ++d) {
+                    const int i = i0 + d;
+                    if (i < n_kb && ok) {
+                        const int s = i % STAGES;
+                        if (i >= STAGES) {
+                            ok = mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1);
+                            if (!ok) atomicExch(&failed, 1);
+                        }
+                        if (ok) {
+                            unsigned char* b = tiles + (size_t)s * STAGE_BYTES + A_BYTES;
+#pragma unroll
+                            for (int j = 0; j < CHUNKS; ++j) {
+                                const int t = (te + j * 128) / 8;          // row of the tile
+                                float o[8];
+#pragma unroll
+                                for (int q = 0; q < 8; ++q) o[q] = v[d][j][q] * rstd[j] * g[d][q];
+                                store8(reinterpret_cast<__nv_bfloat16*>(b + t * 128 + ((c8 ^ (t & 7)) << 4)), o);
+                            }
+                            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                            __syncwarp();
+                            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&full_bar[s])) : "memory");
+                        }
+                    }
+                    fetch(i + DEPTH, d);
                 }
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                __syncwarp();
-                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&full_bar[s])) : "memory");
             }
         }
         if (ok && n_kb > 0) {
@@ -204,10 +233,23 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             if (!ok) atomicExch(&failed, 1);
             tc_fence_after();
         }
-        // the accumulator of this CTA's range of K: red[token][row of the tile]
+        // Row m of this CTA's accumulator goes to the rank that owns it, into that rank's recv[my rank][token][row
+        // of its share].  (swiglu: a rank owns rows of the gate and the rows of up that belong to them.)
+        const int S = p.splits, rank = split;
+        const int rows_per = TC_BM / S, half = rows_per / 2;               // powers of two
         const int m_local = quarter * 32 + lane;
+        int owner, rl;
+        if (p.mode == GF_SWIGLU) {
+            const int m = m_local & 63;
+            owner = m / half; rl = (m_local >> 6) * half + (m & (half - 1));
+        } else {
+            owner = m_local / rows_per; rl = m_local & (rows_per - 1);
+        }
+        const int t_real = min(BN, p.T - tile_n * BN);                     // columns beyond it are padding
+        // where token 0 of this row goes: the owner's recv[rank][0][rl] (one token further is rows_per floats on)
+        const unsigned dst0 = peer_addr(smem_u32(recv) + (unsigned)(rank * BN * rows_per + rl) * 4u, (unsigned)owner);
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 16) {
+        for (int c = 0; c < BN && c < t_real; c += 16) {
             unsigned r[16];
             if (ok && n_kb > 0) {
                 tc_ld16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c, r);
@@ -216,70 +258,83 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 for (int j = 0; j < 16; ++j) r[j] = 0u;
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) red[(c + j) * TC_BM + m_local] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) {
+                if (c + j < t_real) st_cluster(dst0 + (unsigned)((c + j) * rows_per) * 4u, __uint_as_float(r[j]));
+            }
         }
         tc_fence_before();
     }
-    __syncthreads();
-    if (p.splits > 1) cluster_sync_all();                                  // every CTA's red is complete
+    if (p.splits > 1) cluster_sync_all();                                  // every rank has what the others sent it
+    else __syncthreads();
 
     if (warp >= 2) {
         const int te = threadIdx.x - 64;
         const int S = p.splits, rank = split;
         const int rows_per = TC_BM / S, half = rows_per / 2;
-        const unsigned red_addr = smem_u32(red);
-        for (int e = te; e < rows_per * BN; e += 128) {
-            const int rl = e % rows_per, c = e / rows_per;
-            // swiglu: a rank owns rows of the gate and the rows of up that belong to them
-            const int row = p.mode == GF_SWIGLU ? (rl < half ? rank * half + rl : 64 + rank * half + (rl - half)) : rank * rows_per + rl;
-            float v = 0.0f;
-            if (S == 1) {
-                v = red[c * TC_BM + row];
-            } else {
-                for (int s = 0; s < S; ++s) v += ld_peer(red_addr + (unsigned)(c * TC_BM + row) * 4u, (unsigned)s);
-            }
-            const int n = tile_m * TC_BM + row, t = tile_n * BN + c;
-            const bool real = n < p.n_out && t < p.T;
-            if (p.bias && n < p.n_out) v += p.bias[n];
-            if (p.mode == GF_PLAIN) {
-                if (real) {
-                    if (p.out_dtype == BG_DTYPE_F32) ((float*)p.out)[(size_t)t * p.ldo + n] = v;
-                    else ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(v);
+        const int t_real = min(BN, p.T - tile_n * BN);
+        // thread te: row te % rows_per of this rank's share, tokens te / rows_per, + S, + 2 S, ...
+        const int rl = te & (rows_per - 1);
+        const int row = p.mode == GF_SWIGLU ? (rl < half ? rank * half + rl : 64 + rank * half + (rl - half)) : rank * rows_per + rl;
+        const int n = tile_m * TC_BM + row;
+        const float bias = (p.bias && n < p.n_out) ? p.bias[n] : 0.0f;
+        const int c0 = te / rows_per;
+        const int part = BN * rows_per;                                    // floats between two ranks' parts
+        // the sum over the ranks, in rank order (the loads go out together; S is 1, 2, 4, 8 or 16)
+        auto total = [&](int c) {
+            const float* rp = recv + c * rows_per + rl;
+            float a[16];
+#pragma unroll
+            for (int s = 0; s < 16; ++s) a[s] = s < S ? rp[s * part] : 0.0f;
+            float v = a[0];
+#pragma unroll
+            for (int s = 1; s < 16; ++s) v += a[s];
+            return v + bias;
+        };
+        if (p.mode == GF_PLAIN) {
+            if (n < p.n_out) {
+                if (p.out_dtype == BG_DTYPE_F32) {
+                    float* po = (float*)p.out + (size_t)(tile_n * BN + c0) * p.ldo + n;
+#pragma unroll 4
+                    for (int c = c0; c < t_real; c += S, po += (size_t)S * p.ldo) *po = total(c);
+                } else {
+                    __nv_bfloat16* po = (__nv_bfloat16*)p.out + (size_t)(tile_n * BN + c0) * p.ldo + n;
+#pragma unroll 4
+                    for (int c = c0; c < t_real; c += S, po += (size_t)S * p.ldo) *po = __float2bfloat16_rn(total(c));
                 }
-            } else if (p.mode == GF_RESIDUAL) {
+            }
+        } else if (p.mode == GF_RESIDUAL) {
+            float* po = (float*)p.out + (size_t)(tile_n * BN + c0) * p.ldo + n;
+#pragma unroll 4
+            for (int c = c0; c < t_real; c += S, po += (size_t)S * p.ldo) {
                 float x = 0.0f;
-                if (real) {
-                    float* px = (float*)p.out + (size_t)t * p.ldo + n;
-                    x = *px + v;
-                    *px = x;
+                if (n < p.n_out) {
+                    x = *po + total(c);
+                    *po = x;
                 }
                 sq[c * rows_per + rl] = x * x;
-            } else {
-                sq[c * rows_per + rl] = v;
             }
+        } else {
+#pragma unroll 4
+            for (int c = c0; c < t_real; c += S) sq[c * rows_per + rl] = total(c);
         }
         epilogue_sync();
         if (p.mode == GF_RESIDUAL) {
             // the sum of squares of this rank's rows, token by token, in row order
-            if (te < BN) {
-                const int t = tile_n * BN + te;
+            if (te < t_real) {
                 float acc = 0.0f;
                 for (int i = 0; i < rows_per; ++i) acc += sq[te * rows_per + i];
-                if (t < p.T && p.ssq_out) p.ssq_out[(size_t)(tile_m * S + rank) * p.ssq_out_stride + t] = acc;
+                if (p.ssq_out) p.ssq_out[(size_t)(tile_m * S + rank) * p.ssq_out_stride + tile_n * BN + te] = acc;
             }
         } else if (p.mode == GF_SWIGLU) {
-            for (int e = te; e < half * BN; e += 128) {
-                const int i = e % half, c = e / half;
-                const int t = tile_n * BN + c;
+            const int i = te & (half - 1);
+            for (int c = te / half; c < t_real; c += 128 / half) {
                 const float g = sq[c * rows_per + i], u = sq[c * rows_per + half + i];
-                if (t < p.T)
-                    ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + tile_m * 64 + rank * half + i] =
-                        __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+                ((__nv_bfloat16*)p.out)[(size_t)(tile_n * BN + c) * p.ldo + tile_m * 64 + rank * half + i] =
+                    __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
             }
         }
     }
-    if (p.splits > 1) cluster_sync_all();                                  // nobody leaves while a peer may read its red
-    else __syncthreads();
+    __syncthreads();
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -287,13 +342,15 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     if (threadIdx.x == 0 && failed && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
 }
 
-template <int BN>
-static int gf_launch(const CUtensorMap& mw, const CUtensorMap& mx, const FusedParams& p, cudaStream_t stream) {
-    auto kern = gemm_fused_kernel<BN>;
-    size_t smem = (size_t)GF_STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+template <int BN, int STAGES>
+static int gf_launch_stages(const CUtensorMap& mw, const CUtensorMap& mx, const FusedParams& p, cudaStream_t stream) {
+    auto kern = gemm_fused_kernel<BN, STAGES>;
+    size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (size_t)BN * TC_BM * 4 + 1024;
     static bool set = false;
     if (!set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);    // clusters of 16
         if (e != cudaSuccess) return (int)e;
         set = true;
     }
@@ -304,19 +361,28 @@ static int gf_launch(const CUtensorMap& mw, const CUtensorMap& mx, const FusedPa
     return BG_OK;
 }
 
+// A grid that leaves SMs to spare has a CTA alone on its SM: eight stages then keep enough bytes on their way
+// from HBM (the stream of a few CTAs is bound by what they have in flight); else four, so that two CTAs share an SM.
+template <int BN>
+static int gf_launch(const CUtensorMap& mw, const CUtensorMap& mx, const FusedParams& p, cudaStream_t stream) {
+    const long long ctas = (long long)((p.n_out + TC_BM - 1) / TC_BM) * ((p.T + BN - 1) / BN) * p.splits;
+    if (BN <= 32 && ctas <= 148 && p.kb_per_split > 4) return gf_launch_stages<BN, 8>(mw, mx, p, stream);
+    return gf_launch_stages<BN, 4>(mw, mx, p, stream);
+}
+
 }  // namespace bg
 
 using namespace bg;
 
 // See the head of the file.  X (bfloat16 [T, K], row stride ldx) or xf (float [T, K], row stride ldxf, with
-// ssq_in, norm_w and eps) is the left operand; splits is 1, 2, 4 or 8.
+// ssq_in, norm_w and eps) is the left operand; splits is 1, 2, 4, 8 or 16.
 extern "C" int bg_gemm_fused(const void* W, int n_out, int K, int ldw, const void* X, int ldx, const float* xf, int ldxf,
                              const float* ssq_in, int n_ssq_in, int ssq_in_stride, const void* norm_w, float eps, int T,
                              const float* bias, int mode, void* out, int out_dtype, int ldo, float* ssq_out,
                              int ssq_out_stride, int splits, unsigned* status, cudaStream_t stream) {
     if (T <= 0 || n_out <= 0) return BG_OK;
     if (K <= 0 || T > 64) return BG_ERR_SHAPE;
-    if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return BG_ERR_SHAPE;
+    if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return BG_ERR_SHAPE;
     if ((ldw % 8) || (K % 8) || ((uintptr_t)W % 16)) return BG_ERR_ALIGN;
     if ((X == nullptr) == (xf == nullptr)) return BG_ERR_SHAPE;
     if (X && ((ldx % 8) || ((uintptr_t)X % 16))) return BG_ERR_ALIGN;

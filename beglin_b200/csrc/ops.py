@@ -23,7 +23,7 @@ _SIGNATURES = {
     "bg_add_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_float, _c_void_p, _c_int,
                        _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "bg_add_residual": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
-    "bg_swiglu": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "bg_swiglu": [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "bg_rope_table": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
     "bg_rope_kv_append": [_c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
                           _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -211,8 +211,9 @@ def add_residual(x: torch.Tensor, delta: torch.Tensor) -> None:
     _check(lib().bg_add_residual(_p(x), _p(delta), _dt(delta), x.numel(), _stream()), "add_residual")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = silu(g[t, i]) * g[t, im + i], g = gate_up or the sum of its partial sums."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
+    """out[t, i] = silu(g[t, i]) * g[t, im + i], g = gate_up or the sum of its partial sums.  With
+    `block` > 0 the columns of g are interleaved in blocks of that many: gate, up, gate, up, ..."""
     _cuda(gate_up, out)
     parts, stride = _parts(gate_up, "swiglu: gate_up")
     rows, two_im = gate_up.shape[-2:]
@@ -221,7 +222,10 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError("swiglu: gate_up must be [rows, 2*im] and out [rows, im]")
     if not gate_up.is_contiguous() or not out.is_contiguous():
         raise KernelError("swiglu: tensors must be contiguous")
-    _check(lib().bg_swiglu(_p(gate_up), _dt(gate_up), parts, stride, _p(out), _dt(out), rows, im, _stream()), "swiglu")
+    if block < 0 or (block > 0 and im % block):
+        raise KernelError(f"swiglu: blocks of {block} do not divide {im} features")
+    _check(lib().bg_swiglu(_p(gate_up), _dt(gate_up), parts, stride, _p(out), _dt(out), rows, im, block, _stream()),
+           "swiglu")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
@@ -442,7 +446,7 @@ def gemm_fused(w: torch.Tensor, out: torch.Tensor, mode: int = FUSED_PLAIN, *, x
 
     Left operand: `x` (bfloat16 [T, K]), or the float32 residual stream `xf` [T, K] normalised on the fly:
     bf16(xf * rstd * norm_weight), rstd = 1 / sqrt(sum_p ssq_in[p] / K + eps), ssq_in float32 [parts, >= T].
-    K is cut into `splits` (1, 2, 4 or 8) ranges whose CTAs add up inside a thread block cluster.
+    K is cut into `splits` (1, 2, 4, 8 or 16) ranges whose CTAs add up inside a thread block cluster.
     mode FUSED_PLAIN: out[T, N] = product (+ bias), float32 or bfloat16.
     mode FUSED_RESIDUAL: out (float32 [T, N], the residual stream) += product (+ bias); ssq_out
       [ceil(N / 128) * splits, >= T] receives partial sums of squares of the new rows.
@@ -483,6 +487,18 @@ def gemm_fused(w: torch.Tensor, out: torch.Tensor, mode: int = FUSED_PLAIN, *, x
                                _p(norm_weight), float(eps), T, _p(bias), mode, _p(out), _dt(out), out.stride(0),
                                _p(ssq_out), ssq_out.stride(0) if ssq_out is not None else 0, splits, _p(status),
                                _stream()), "gemm_fused")
+
+
+def gemm_fused_unchecked(w_ptr: int, n_out: int, k: int, ldw: int, T: int, out: torch.Tensor, mode: int, x, xf, ssq_in,
+                         norm_w_ptr, eps: float, bias_ptr, ssq_out, splits: int, status_ptr) -> None:
+    """gemm_fused for a caller that has checked the shapes once (Linear)."""
+    _check(_lib.bg_gemm_fused(w_ptr, n_out, k, ldw, None if x is None else x.data_ptr(), 0 if x is None else x.stride(0),
+                              None if xf is None else xf.data_ptr(), 0 if xf is None else xf.stride(0),
+                              None if ssq_in is None else ssq_in.data_ptr(), 0 if ssq_in is None else ssq_in.shape[0],
+                              0 if ssq_in is None else ssq_in.stride(0), norm_w_ptr, eps, T, bias_ptr, mode, out.data_ptr(),
+                              F32 if out.dtype == torch.float32 else BF16, out.stride(0),
+                              None if ssq_out is None else ssq_out.data_ptr(), 0 if ssq_out is None else ssq_out.stride(0),
+                              splits, status_ptr, _stream()), "gemm_fused")
 
 
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],

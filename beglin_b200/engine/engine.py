@@ -51,8 +51,8 @@ def require_gpu(device) -> torch.device:
 class Engine:
     def __init__(self, spec, tensors, *, dtype="bfloat16", device="cuda:0", max_tokens: int = 8192,
                  page_size: int = 64, max_requests: int = 8, max_context: Optional[int] = None,
-                 kv_split: int = 256, gemm: str = "auto", attention: str = "auto", use_graphs: bool = True,
-                 config=None, origin: str = ""):
+                 kv_split: int = 256, gemm: str = "auto", attention: str = "auto", fuse: bool = True,
+                 use_graphs: bool = True, config=None, origin: str = ""):
         """`tensors` is anything with names()/shape(name)/tensor(name): a Checkpoint or a TensorDict.
         `max_tokens` sizes the page pool: it holds that many positions (rounded up to whole pages)."""
         self.device = require_gpu(device)
@@ -60,7 +60,7 @@ class Engine:
         self.spec, self.config = spec, config
         bound = bind(spec, tensors, origin)
         self.ctx = BuildContext(device=self.device, compute_dtype=self.dtype, page_size=page_size,
-                                kv_split=kv_split, gemm=gemm, attention=attention)
+                                kv_split=kv_split, gemm=gemm, attention=attention, fuse=fuse)
         with torch.cuda.device(self.device):
             self.model = DecoderModel(spec, bound, self.ctx)
             del bound

@@ -13,6 +13,7 @@ from ..parts import registry
 from ..parts.context import BuildContext
 from ..parts.linear import Linear
 from ..parts.spec import ModelSpec
+from ..parts.stream import ResidualStream
 from ..weights.loader import layer_roles
 
 
@@ -95,12 +96,12 @@ class DecoderModel:
         qwen_infer.c:2145 skips it)."""
         x = torch.empty((batch.n_rows, self.spec.hidden), dtype=torch.float32, device=self.ctx.device)
         ops.embed_gather(self.embed, batch.token_ids, x, self.ctx.status)
-        pending = None
+        stream = ResidualStream(x)
         for si, stage in enumerate(self.spec.order):
             owner = si if stage.cache is None else stage.cache
             view = cache.view(owner, batch) if owner in cache.stage_group else None
-            pending = self.blocks[stage.layer].forward(x, pending, batch, view)
+            self.blocks[stage.layer].forward(stream, batch, view)
         if batch.n_logit_rows == 0:
             return None
-        h = self.final_norm.add_norm(x, pending, rows=batch.logit_rows, update=False)
+        h = self.final_norm.add_norm(stream.x, stream.pending, rows=batch.logit_rows, update=False)
         return self.head(h, out_dtype=torch.float32)

@@ -22,6 +22,7 @@ from .linear import Linear
 from .registry import register_mixer
 from .rope import shared_position
 from .spec import AttentionSpec, TensorRole
+from .stream import ResidualStream
 
 
 @register_mixer("gqa_attention")
@@ -68,10 +69,14 @@ class GQAAttention:
                                             ctx.page_size) for d in (False, True)}
         self.window = int(spec.window) if spec.window else 0
 
-    def forward(self, h: torch.Tensor, batch, cache: PagedKVView) -> torch.Tensor:
+    takes_stream = True        # forward takes a NormedInput and may add its result to the stream itself
+
+    def forward(self, h, batch, cache: PagedKVView, stream: Optional[ResidualStream] = None) -> Optional[torch.Tensor]:
+        """h: the normed rows, or a NormedInput.  With `stream` the result is added to it (or left owed to
+        it) and None is returned; without, the addend is returned."""
         T = batch.n_rows
-        qkv = self.qkv.partial(h)
-        q = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=h.device)
+        qkv = self.qkv.of(h)
+        q = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=qkv.device)
         ops.rope_kv_append(qkv, q, T, self.nh, self.nkv, self.hd, self.position.rotary_dim, self.position.interleaved,
                            self.position.table(batch), batch.positions, batch.row_req, cache.block_table,
                            cache.pool if self.spec.own_kv else None, cache.page_size, self.ctx.status)
@@ -80,8 +85,11 @@ class GQAAttention:
         if qblk is None and kernel != "mma_keys":
             batch.implicit_blocks = False              # this kernel wants the list
             qblk, n_qblk = batch.query_blocks(bq)
-        out = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=h.device)
+        out = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=q.device)
         ops.attention(q, q.stride(0), cache.pool, cache.block_table, batch.positions, qblk, n_qblk,
                       batch.max_position, T, self.nh, self.nkv, self.hd, self.window, self.ctx.kv_split, tile, bq,
                       self.scale, out, self.ctx.status, kernel)
-        return self.o_proj.partial(out)
+        if stream is None:
+            return self.o_proj.partial(out)
+        self.o_proj.into(out, stream)
+        return None

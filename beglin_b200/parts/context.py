@@ -17,6 +17,7 @@ class BuildContext:
     kv_split: int = 256                     # keys per attention split; fixed, so results do not depend on load
     gemm: str = "auto"                      # "auto", "library" or "tcgen05" for the bfloat16 products
     attention: str = "auto"                 # "auto", "generic" (CUDA cores) or "mma" (tensor cores) kernel
+    fuse: bool = True                       # few-token steps: norms, residual adds and SwiGLU inside the products
     status: Optional[torch.Tensor] = None   # device word in which kernels record bad ids and pages
     shared: Dict[object, object] = field(default_factory=dict)   # parts shared between layers, by spec
 

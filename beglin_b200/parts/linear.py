@@ -14,6 +14,7 @@ import torch
 from ..csrc import ops
 from . import tensor_core
 from .context import BuildContext
+from .stream import NormedInput, ResidualStream
 
 
 class Linear:
@@ -53,3 +54,46 @@ class Linear:
         takes either [T, out] or float partial sums [parts, T, out] over ranges of the inner size and
         adds them up itself."""
         return self._run(x, self.ctx.compute_dtype, True)
+
+    # ------------------------------------------------------------------ products that take over their neighbours' work
+    def fuses(self, T: int) -> bool:
+        """Whether a step of T rows runs the fused product (bfloat16, few tokens, sizes it takes)."""
+        return self._tc is not None and self._tc.fuses(T)
+
+    def _check_rows(self, x: torch.Tensor) -> None:
+        if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.shape[1] != self.in_features or x.stride(0) % 8:
+            raise ops.KernelError(f"the fused product takes contiguous bfloat16 rows of {self.in_features} features")
+
+    def of(self, inp, swiglu: bool = False) -> torch.Tensor:
+        """The product of `inp`, a tensor [T, in] or a NormedInput (a norm of the residual stream that has
+        not been computed).  Where the fused product runs, the norm is applied to the operand inside it;
+        the result is then complete ([T, out], float).  Else as `partial`.  With `swiglu` (the weight's
+        rows interleaved in blocks of 64, gate then up) the result is silu(gate) * up, [T, out / 2] in the
+        compute type, or None when this step does not run the fused product."""
+        lazy = isinstance(inp, NormedInput)
+        T = inp.rows if lazy else inp.shape[0]
+        if not self.fuses(T):
+            return None if swiglu else self.partial(inp.tensor() if lazy else inp)
+        fusion = inp.fusable() if lazy else None
+        n = self.out_features // 2 if swiglu else self.out_features
+        out = torch.empty((T, n), dtype=self.ctx.compute_dtype if swiglu else torch.float32, device=self.weight.device)
+        mode = ops.FUSED_SWIGLU if swiglu else ops.FUSED_PLAIN
+        if fusion is not None:
+            weight, eps = fusion
+            self._tc.fused(T, out, mode, xf=inp.stream.x, ssq_in=inp.stream.ssq, norm_weight=weight, eps=eps,
+                           bias=self.bias_f32)
+        else:
+            x = inp.tensor() if lazy else inp
+            self._check_rows(x)
+            self._tc.fused(T, out, mode, x=x, bias=self.bias_f32)
+        return out
+
+    def into(self, x: torch.Tensor, stream: ResidualStream) -> None:
+        """stream += x W^T (+ bias).  Where the fused product runs it adds to the stream itself and leaves
+        the sums of squares of the new rows for the next norm; else the result is owed to the stream."""
+        T = x.shape[0]
+        if self.fuses(T) and stream.pending is None:
+            self._check_rows(x)
+            stream.updated(self._tc.fused(T, stream.x, ops.FUSED_RESIDUAL, x=x, bias=self.bias_f32, want_ssq=True))
+        else:
+            stream.owe(self.partial(x))

@@ -3,7 +3,7 @@
 reference fuses them (qwen_infer.c:1368-1402)."""
 from __future__ import annotations
 
-from typing import Dict, List
+from typing import Dict, List, Optional
 
 import torch
 
@@ -12,6 +12,7 @@ from .context import BuildContext
 from .linear import Linear
 from .registry import register_feed_forward
 from .spec import SwiGLUSpec, TensorRole
+from .stream import ResidualStream
 
 
 @register_feed_forward("swiglu")
@@ -22,13 +23,31 @@ class SwiGLU:
                 TensorRole("up_proj.weight", (spec.intermediate, spec.hidden), True, True),
                 TensorRole("down_proj.weight", (spec.hidden, spec.intermediate), True, True)]
 
+    takes_stream = True        # forward takes a NormedInput and may add its result to the stream itself
+
     def __init__(self, spec: SwiGLUSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
         self.spec, self.ctx = spec, ctx
-        self.gate_up = Linear(torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0), None, ctx)
+        gate, up, im = tensors["gate_proj.weight"], tensors["up_proj.weight"], spec.intermediate
+        # Where the intermediate size allows it, the rows go in blocks of 64: gate, up, gate, up, ...  A CTA of
+        # the fused product (128 rows) then holds 64 gate features with their 64 up features and applies
+        # silu(gate) * up itself; the plain kernel reads the same layout.
+        self.block = 64 if im % 64 == 0 else 0
+        if self.block:
+            w = torch.stack([gate.reshape(im // 64, 64, -1), up.reshape(im // 64, 64, -1)], dim=1).reshape(2 * im, -1)
+        else:
+            w = torch.cat([gate, up], dim=0)
+        self.gate_up = Linear(w, None, ctx)
         self.down = Linear(tensors["down_proj.weight"], None, ctx)
 
-    def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
-        gu = self.gate_up.partial(h)
-        act = torch.empty((h.shape[0], self.spec.intermediate), dtype=self.ctx.compute_dtype, device=h.device)
-        ops.swiglu(gu, act)
-        return self.down.partial(act)
+    def forward(self, h, batch, stream: Optional[ResidualStream] = None) -> Optional[torch.Tensor]:
+        """h: the normed rows, or a NormedInput.  With `stream` the result is added to it (or left owed to
+        it) and None is returned; without, the addend is returned."""
+        act = self.gate_up.of(h, swiglu=True) if self.block else None
+        if act is None:
+            gu = self.gate_up.of(h)
+            act = torch.empty((gu.shape[-2], self.spec.intermediate), dtype=self.ctx.compute_dtype, device=gu.device)
+            ops.swiglu(gu, act, self.block)
+        if stream is None:
+            return self.down.partial(act)
+        self.down.into(act, stream)
+        return None

@@ -31,3 +31,10 @@ class RMSNorm:
         out = torch.empty((n, self.spec.size), dtype=self.ctx.compute_dtype, device=x.device)
         ops.add_rmsnorm(x, delta, self.weight, self.spec.eps, out, rows=rows, update=update and rows is None)
         return out
+
+    def fusion(self):
+        """What a product needs to apply this norm to its operand itself: (weight, eps); None when the
+        weight is not in the compute type (a checkpoint that stores it in 32-bit keeps it so)."""
+        if self.weight.dtype != self.ctx.compute_dtype:
+            return None
+        return self.weight, float(self.spec.eps)

@@ -17,6 +17,7 @@ from .context import BuildContext
 
 SM_COUNT = 148
 FEW_TOKENS = 64            # up to this many rows a product is treated as weight-streaming
+FUSED_TOKENS = 16            # steps of up to this many rows run the fused product (measured: it loses from 32 rows on)
 
 
 class TensorCoreProduct:
@@ -55,6 +56,36 @@ class TensorCoreProduct:
         want = min(want, max(1, self.k // (8 * T)))               # partial sums stay a fraction of the weight bytes
         per = -(-self.k_blocks // want)
         return -(-self.k_blocks // per)                           # no empty range
+
+    # ------------------------------------------------------------------ the fused product of few-token steps
+    def fuses(self, T: int) -> bool:
+        return self.ctx.fuse and T <= FUSED_TOKENS and self.k % 8 == 0
+
+    def fused_splits(self, T: int) -> int:
+        """1, 2, 4, 8 or 16 ranges of K (the CTAs of a tile form a cluster): enough CTAs for every SM, at
+        least two k-blocks per range, no empty range."""
+        s = self._splits.get(("fused", T))
+        if s is None:
+            want = max(1, -(-SM_COUNT // (self.tiles * -(-T // 64))))
+            s = 1
+            while s < 16 and s < want and 2 * s <= max(1, self.k_blocks // 2):
+                s *= 2
+            while s > 1 and (s - 1) * -(-self.k_blocks // s) >= self.k_blocks:
+                s //= 2
+            self._splits[("fused", T)] = s
+        return s
+
+    def fused(self, T: int, out: torch.Tensor, mode: int, x: Optional[torch.Tensor] = None,
+              xf: Optional[torch.Tensor] = None, ssq_in: Optional[torch.Tensor] = None,
+              norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, bias: Optional[torch.Tensor] = None,
+              want_ssq: bool = False) -> Optional[torch.Tensor]:
+        """ops.gemm_fused with this weight; returns the sums of squares of the new rows when asked."""
+        s = self.fused_splits(T)
+        ssq_out = torch.empty((self.tiles * s, 64), dtype=torch.float32, device=out.device) if want_ssq else None
+        ops.gemm_fused_unchecked(self._w_ptr, self.n_out, self.k, self._ldw, T, out, mode, x, xf, ssq_in,
+                                 None if norm_weight is None else norm_weight.data_ptr(), eps,
+                                 None if bias is None else bias.data_ptr(), ssq_out, s, self._status_ptr)
+        return ssq_out
 
     def __call__(self, x: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype, partial: bool) -> torch.Tensor:
         T = x.shape[0]

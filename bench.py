@@ -180,6 +180,7 @@ def main():
     ap.add_argument("--layers", type=int, default=CONFIG_1P5B["num_hidden_layers"])
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64 and the prefill")
     ap.add_argument("--gemm", default="auto")
+    ap.add_argument("--no-fuse", action="store_true", help="norms, residual adds and SwiGLU as kernels of their own")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -200,7 +201,7 @@ def main():
     max_batch = args.batch if args.no_points else max(args.batch, 64)
     page = 64
     eng = Engine.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=max_batch * args.context,
-                        page_size=page, max_requests=max_batch, max_context=args.context, gemm=args.gemm)
+                        page_size=page, max_requests=max_batch, max_context=args.context, gemm=args.gemm, fuse=not args.no_fuse)
     weight_bytes = eng.model.weight_bytes()
     kvb = kv_bytes_per_token(cfg, args.layers)
 
