@@ -314,14 +314,74 @@ extern "C" int bg_attention_partial(const void* q, int q_dtype, int q_stride, co
     return BG_OK;
 }
 
+// The same for at most 8 splits and head_dim <= 128 (decoding): the position, the maxima and sums, and the
+// partial outputs of ALL splits are asked for at once, and what lies outside the row's range is dropped when
+// the position has arrived, so the kernel is one round trip to memory instead of three.
+template <typename TO>
+__global__ void attention_merge_few_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                           const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
+                                           int T, int nh, int hd, int max_splits, int split_arg, int window) {
+    pdl_launch();
+    pdl_wait();
+    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= T * nh) return;
+    const int t = w / nh, h = w - t * nh;
+    const size_t prow = (size_t)w * max_splits;
+    const int pos = positions[t];
+    float ms[8], ls[8], v[8][4];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        const bool have = s < max_splits;
+        ms[s] = have ? part_ml[(prow + s) * 2] : -INFINITY;
+        ls[s] = have ? part_ml[(prow + s) * 2 + 1] : 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int d = i * 32 + lane;
+            v[s][i] = (have && d < hd) ? part_o[(prow + s) * hd + d] : 0.0f;
+        }
+    }
+    const int split = keys_per_split(split_arg, pos + 1, max_splits);
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int s_lo = lo / split, s_hi = pos / split;
+    float m = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        if (s < s_lo || s > s_hi) ms[s] = -INFINITY;          // not written for this row: whatever was read is dropped
+        m = fmaxf(m, ms[s]);
+    }
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, l = 0.0f;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {                             // in split order
+        if (ms[s] != -INFINITY) {
+            const float f = expf(ms[s] - m);
+            l = fmaf(ls[s], f, l);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[i] = fmaf(v[s][i], f, acc[i]);
+        }
+    }
+    const float inv = 1.0f / l;
+    TO* o = out + (size_t)t * out_stride + (size_t)h * hd;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int d = i * 32 + lane;
+        if (d < hd) o[d] = from_float<TO>(acc[i] * inv);
+    }
+}
+
 extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, const int* positions, void* out,
                                   int out_dtype, int out_stride, int T, int nh, int hd, int max_splits, int split,
                                   int window, cudaStream_t stream) {
     if (T <= 0) return BG_OK;
     long long warps = (long long)T * nh;
     unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
-    BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_kernel<TO>, dim3(blocks), dim3(256), 0, stream,
-        part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
+    if (max_splits <= 8 && hd <= 128) {
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO>, dim3(blocks), dim3(256), 0, stream,
+            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
+    } else {
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_kernel<TO>, dim3(blocks), dim3(256), 0, stream,
+            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
+    }
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

@@ -1,6 +1,7 @@
 """Small stand-alone workloads of single kernels, for timing and for profiler captures.
 
     python -m beglin_b200.csrc.microbench gemm --tokens 8 --out 17920 --inner 1536 --splits 2
+    python -m beglin_b200.csrc.microbench gemm-fused --tokens 8 --out 17920 --inner 1536 --splits 2 --norm --mode swiglu
     python -m beglin_b200.csrc.microbench attention-decode --batch 8 --context 4096
     python -m beglin_b200.csrc.microbench attention-prefill --tokens 2048
     python -m beglin_b200.csrc.microbench norm --tokens 8 --width 1536 --parts 12
@@ -55,6 +56,29 @@ def gemm(a) -> None:
     gb = N * K * 2 / 1e9
     print(f"gemm tokens={T} out={N} inner={K} splits={S} {'library' if a.library else 'tcgen05'}: {us:.1f} us  "
           f"{gb / us * 1e6:.0f} GB/s of weights  {2.0 * T * N * K / us / 1e6:.1f} TFLOP/s")
+
+
+def gemm_fused(a) -> None:
+    """The fused few-token product: --norm makes the operand from a float residual stream (RMSNorm inside),
+    --mode plain | residual | swiglu picks the epilogue."""
+    T, N, K, S = a.tokens, a.out, a.inner, a.splits
+    mode = {"plain": ops.FUSED_PLAIN, "residual": ops.FUSED_RESIDUAL, "swiglu": ops.FUSED_SWIGLU}[a.mode]
+    copies = max(2, min(48, int(300e6 // (N * K * 2)) + 1))
+    ws = [(torch.randn(N, K, device=DEV) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    x = torch.randn(T, K, device=DEV).to(torch.bfloat16)
+    xf = torch.randn(T, K, device=DEV)
+    g = torch.ones(K, device=DEV, dtype=torch.bfloat16)
+    ssq_in = (xf * xf).sum(1)[None, :].repeat(12, 1) / 12
+    ssq_in = torch.nn.functional.pad(ssq_in, (0, 64 - T)).contiguous()
+    n_cols = N // 2 if mode == ops.FUSED_SWIGLU else N
+    out = torch.zeros((T, n_cols), dtype=torch.bfloat16 if mode == ops.FUSED_SWIGLU else torch.float32, device=DEV)
+    ssq_out = torch.empty((-(-N // 128) * S, 64), device=DEV) if mode == ops.FUSED_RESIDUAL else None
+    status = ops.new_status(DEV)
+    kw = dict(xf=xf, ssq_in=ssq_in, norm_weight=g, eps=1e-6) if a.norm else dict(x=x)
+    us = _time(lambda i: ops.gemm_fused(ws[i % copies], out, mode, splits=S, ssq_out=ssq_out, status=status, **kw), a.launches)
+    ops.raise_on_status(status)
+    print(f"gemm-fused tokens={T} out={N} inner={K} splits={S} {'norm -> ' if a.norm else ''}{a.mode}: {us:.1f} us  "
+          f"{N * K * 2 / us / 1e3:.0f} GB/s of weights")
 
 
 def _filled_cache(batch: int, context: int, nkv: int, hd: int, page: int):
@@ -120,6 +144,11 @@ def main() -> None:
     g.add_argument("--tokens", type=int, default=8); g.add_argument("--out", type=int, default=17920)
     g.add_argument("--inner", type=int, default=1536); g.add_argument("--splits", type=int, default=1)
     g.add_argument("--library", action="store_true"); g.set_defaults(fn=gemm)
+    f = sub.add_parser("gemm-fused")
+    f.add_argument("--tokens", type=int, default=8); f.add_argument("--out", type=int, default=17920)
+    f.add_argument("--inner", type=int, default=1536); f.add_argument("--splits", type=int, default=2)
+    f.add_argument("--norm", action="store_true"); f.add_argument("--mode", default="plain", choices=["plain", "residual", "swiglu"])
+    f.set_defaults(fn=gemm_fused)
     d = sub.add_parser("attention-decode")
     d.add_argument("--batch", type=int, default=8); d.add_argument("--context", type=int, default=4096)
     d.set_defaults(fn=attention_decode)
@@ -133,7 +162,7 @@ def main() -> None:
     n = sub.add_parser("norm")
     n.add_argument("--tokens", type=int, default=8); n.add_argument("--width", type=int, default=1536)
     n.add_argument("--parts", type=int, default=1); n.set_defaults(fn=norm)
-    for s in (g, d, p, n):
+    for s in (g, f, d, p, n):
         s.add_argument("--launches", type=int, default=20)
     a = ap.parse_args()
     ops.lib()

@@ -152,6 +152,60 @@ def time_decode(eng, batch, context, steps, warmup, seed, e2e):
     return ms, launches, h2d / steps
 
 
+def decode_timeline(eng, batch, context, seed):
+    """The kernels of ONE decode step as the device ran them (CUPTI records through torch.profiler): for
+    every kernel its start and end relative to the step's first kernel, in microseconds.  Under
+    programmatic dependent launch a kernel starts while the one before it still runs and then waits, so
+    what a kernel adds to the step is the difference between its end and the end of the kernel before."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    rids = [("timeline", batch, i) for i in range(batch)]
+    fill_cache(eng, rids, context - 16, seed)
+    toks = torch.randint(0, eng.vocab, (batch,), generator=torch.Generator().manual_seed(seed)).tolist()
+    eng.decode(rids, toks, read_back=False)
+    for _ in range(4):
+        eng.decode(rids, None, read_back=False)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(2):
+            eng.decode(rids, None, read_back=False)
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+          and "memcpy" not in e.name.lower() and "memset" not in e.name.lower()]
+    ev.sort(key=lambda e: e.time_range.start)
+    first = [i for i, e in enumerate(ev) if "embed_gather" in e.name][-1]
+    step = ev[first:]
+    t0 = step[0].time_range.start
+    for r in rids:
+        eng.release(r)
+
+    def short(name):
+        return name.replace("void bg::", "").replace("bg::", "").split("<")[0].split("(")[0]
+    return [(short(e.name), e.time_range.start - t0, e.time_range.end - t0) for e in step]
+
+
+def print_timeline(rows, layers):
+    print(f"{len(rows)} kernels, {rows[-1][2]:.1f} us from the first kernel's start to the last one's end")
+    print("  #  kernel                               start      end   adds")
+    prev = 0.0
+    shown = list(range(min(len(rows), 24))) + list(range(max(24, len(rows) - 6), len(rows)))
+    for i, (name, s, e) in enumerate(rows):
+        if i in shown:
+            print(f"{i:4d} {name[:34]:34s} {s:8.1f} {e:8.1f} {e - prev:6.1f}")
+        elif i == 24:
+            print("     ...")
+        prev = max(prev, e)
+    adds, prev = {}, 0.0
+    for name, s, e in rows:
+        a = adds.setdefault(name, [0, 0.0])
+        a[0] += 1
+        a[1] += max(0.0, e - prev)
+        prev = max(prev, e)
+    print("what each kind of kernel adds to the step (its end minus the end of the kernel before it):")
+    for name, (n, t) in sorted(adds.items(), key=lambda kv: -kv[1][1]):
+        print(f"  {name[:40]:40s} x{n:<4d} {t:8.1f} us  ({t / n:5.1f} us each)")
+
+
 def time_prefill(eng, T, reps, seed):
     import torch
     g = torch.Generator().manual_seed(seed)
@@ -181,6 +235,8 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64 and the prefill")
     ap.add_argument("--gemm", default="auto")
     ap.add_argument("--no-fuse", action="store_true", help="norms, residual adds and SwiGLU as kernels of their own")
+    ap.add_argument("--timeline", action="store_true",
+                    help="instead of the measurement: print the kernels of one decode step with their device times")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -202,6 +258,9 @@ def main():
     page = 64
     eng = Engine.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=max_batch * args.context,
                         page_size=page, max_requests=max_batch, max_context=args.context, gemm=args.gemm, fuse=not args.no_fuse)
+    if args.timeline:
+        print_timeline(decode_timeline(eng, args.batch, args.context, seed=1), args.layers)
+        return 0
     weight_bytes = eng.model.weight_bytes()
     kvb = kv_bytes_per_token(cfg, args.layers)
 
