@@ -157,7 +157,7 @@ def main() -> None:
     p.add_argument("--kernel", default="auto", choices=["auto", "mma", "tcgen05", "generic"])
     for s in (d, p):
         s.add_argument("--heads", type=int, default=12); s.add_argument("--kv-heads", type=int, default=2)
-        s.add_argument("--head-dim", type=int, default=128); s.add_argument("--page", type=int, default=16)
+        s.add_argument("--head-dim", type=int, default=128); s.add_argument("--page", type=int, default=64)
         s.add_argument("--split", type=int, default=256)
     n = sub.add_parser("norm")
     n.add_argument("--tokens", type=int, default=8); n.add_argument("--width", type=int, default=1536)

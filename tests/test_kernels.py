@@ -92,6 +92,23 @@ def test_swiglu(ops, dtype):
     assert (out2.double() - want).abs().max() <= tol * want.abs().max()
 
 
+@pytest.mark.parametrize("dtype,block,im", [(torch.float32, 64, 192), (torch.bfloat16, 64, 128), (torch.float32, 5, 35),
+                                            (torch.bfloat16, 8, 200)])
+def test_swiglu_interleaved_blocks(ops, dtype, block, im):
+    """Columns in blocks: gate, up, gate, up, ... (the layout of the fused product's weight)."""
+    g, u = rnd(7, im, dtype=dtype, seed=21, scale=2.0), rnd(7, im, dtype=dtype, seed=22, scale=2.0)
+    gu = torch.stack([g.reshape(7, im // block, block), u.reshape(7, im // block, block)], dim=2).reshape(7, 2 * im).contiguous()
+    want = plain.swiglu(g.double(), u.double())
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    out = torch.empty((7, im), dtype=dtype, device=DEV)
+    ops.swiglu(gu, out, block)
+    assert (out.double() - want).abs().max() <= tol * want.abs().max()
+    parts = torch.stack([0.25 * gu.float(), 0.75 * gu.float()]).contiguous()
+    out2 = torch.empty((7, im), dtype=dtype, device=DEV)
+    ops.swiglu(parts, out2, block)
+    assert (out2.double() - want).abs().max() <= tol * want.abs().max()
+
+
 def test_gemm_f32_is_true_float_and_row_invariant(ops):
     M, N, K = 37, 203, 301
     a = rnd(M, K, seed=6)

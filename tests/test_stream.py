@@ -1,0 +1,58 @@
+"""The residual stream's bookkeeping (host logic only): what is owed, when sums of squares are valid, and
+when a norm may be applied inside a product."""
+import torch
+
+from beglin_b200.parts.stream import NormedInput, ResidualStream
+
+
+class FakeNorm:
+    def __init__(self, fusable=True):
+        self.calls = []
+        self._fusable = fusable
+
+    def add_norm(self, x, delta):
+        self.calls.append(None if delta is None else delta.clone())
+        if delta is not None:
+            x += delta
+        return x * 2.0
+
+    def fusion(self):
+        return ("weight", 1e-6) if self._fusable else None
+
+
+def test_owed_addend_is_added_by_the_next_norm_and_invalidates_the_squares():
+    s = ResidualStream(torch.ones(3, 4))
+    s.updated(torch.full((2, 64), 0.5))
+    assert s.pending is None and s.ssq is not None
+    s.owe(torch.full((3, 4), 2.0))
+    assert s.ssq is None                                   # x is no longer what the squares describe
+    norm = FakeNorm()
+    h = NormedInput(s, norm)
+    assert h.fusable() is None                             # an addend is owed: the norm kernel has to add it
+    out = h.tensor()
+    assert torch.equal(s.x, torch.full((3, 4), 3.0)) and torch.equal(out, torch.full((3, 4), 6.0))
+    assert s.pending is None and len(norm.calls) == 1
+    assert h.tensor() is out and len(norm.calls) == 1      # computed once
+
+
+def test_norm_is_left_to_the_product_only_with_valid_squares_and_a_willing_norm():
+    s = ResidualStream(torch.ones(2, 8))
+    assert NormedInput(s, FakeNorm()).fusable() is None    # nothing is known about x's rows yet
+    s.updated(torch.ones(1, 64))
+    assert NormedInput(s, FakeNorm()).fusable() == ("weight", 1e-6)
+    assert NormedInput(s, FakeNorm(fusable=False)).fusable() is None
+    assert NormedInput(s, object()).fusable() is None      # a norm without `fusion`
+    h = NormedInput(s, FakeNorm())
+    h.tensor()
+    assert h.fusable() is None                             # already computed: use the tensor
+    assert s.ssq is not None                               # x did not change, the squares still hold
+
+
+def test_decode_splits_make_one_wave():
+    from beglin_b200.csrc.ops import decode_splits
+    for streams in (1, 2, 7, 16, 32, 100, 148, 500):
+        for context in (1, 200, 256, 257, 4096, 100000):
+            n = decode_splits(streams, context)
+            assert n >= 1 and (streams * n <= 148 or n == 1)
+            assert n <= max(1, -(-context // 256))
+    assert decode_splits(16, 4096) == 9 and decode_splits(2, 4096) == 16 and decode_splits(128, 4096) == 1
