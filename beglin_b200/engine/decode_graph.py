@@ -18,6 +18,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from ..cache.manager import CacheError, OutOfPages
 from ..csrc import ops
 
 
@@ -80,13 +81,20 @@ class DecodeGraph:
         self.ring = [_Staging(n, cache) for _ in range(self.RING)]
         self.turn = 0
         self.h_out = torch.zeros(n, dtype=torch.int32).pin_memory()
+        self.h_in = torch.zeros(n, dtype=torch.int32).pin_memory()
+        self.h_in_np = self.h_in.numpy()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        # the same step with the host's tokens copied in at its head and the sampled ones copied out at its
+        # tail, for a caller that feeds every step from the host and reads every result: one launch per step
+        self.graph_fed: Optional[torch.cuda.CUDAGraph] = None
         self.launches = 0
         self.h2d_bytes = 0                     # bytes uploaded by the last step
         self._rids: Optional[tuple] = None     # what the device buffers describe
         self._positions: Optional[List[int]] = None
         self._tables: Dict[int, np.ndarray] = {}
         self._sampling = False
+        self._ahead = None                     # ((rids), positions) whose pages and tables are in place already
+        self._ahead_bytes = 0
 
     def _body(self) -> None:
         b = self.batch
@@ -97,7 +105,13 @@ class DecodeGraph:
         b.positions.add_(1)                    # the next step of the same requests needs no upload
         self.logits = logits
 
-    def _capture(self) -> None:
+    def _body_fed(self) -> None:
+        self.batch.token_ids.copy_(self.h_in, non_blocking=True)
+        self._body()
+        self.h_out.copy_(self.out_tokens, non_blocking=True)
+
+    def _capture(self, fed: bool = False) -> None:
+        body = self._body_fed if fed else self._body
         side = torch.cuda.Stream(device=self.engine.device)
         side.wait_stream(torch.cuda.current_stream())
         saved_tokens, saved_pos = self.batch.token_ids.clone(), self.batch.positions.clone()
@@ -110,9 +124,55 @@ class DecodeGraph:
         before = ops.launch_count()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            self._body()
+            body()
         self.launches = ops.launch_count() - before
-        self.graph = g
+        if fed:
+            self.graph_fed = g
+        else:
+            self.graph = g
+
+    def _upload_tables(self, rids, st) -> int:
+        """Upload the block tables that differ from what the device holds; returns the bytes sent."""
+        cache, sent = self.engine.cache, 0
+        for gi, h in st.tables.items():
+            table = cache.block_table(gi, rids)
+            last = self._tables.get(gi)
+            if last is None or not np.array_equal(last, table):
+                h.copy_(torch.from_numpy(table))
+                self.batch.block_tables[gi].copy_(h, non_blocking=True)
+                self._tables[gi] = table
+                sent += table.size * 4
+        return sent
+
+    def _look_ahead(self, key, rids) -> None:
+        """While the device runs this step, do the host's part of the next step of the same requests: make
+        room for one more position each and, when a request got a new page, upload its block table (the
+        copy is queued behind this step's graph).  If the next call is for other requests, or there is no
+        room, nothing is lost: that call does its own bookkeeping."""
+        cache = self.engine.cache
+        self._ahead, self._ahead_bytes = None, 0
+        nxt = [p + 1 for p in self._positions]
+        if any(n > cache.max_context for n in nxt):
+            return
+        try:
+            cache.reserve(list(zip(rids, nxt)))
+        except (OutOfPages, CacheError):
+            return
+        st = self.ring[self.turn]              # the staging set of the next call
+        if st.event is not None:
+            st.event.synchronize()
+        sent = self._upload_tables(rids, st)
+        if sent:
+            st.event = torch.cuda.Event()
+            st.event.record()
+        self._ahead, self._ahead_bytes = (key, list(self._positions)), sent
+
+    def prepared(self, rids: Sequence[Hashable]) -> bool:
+        """Whether the last step has already made room for the next step of exactly these requests."""
+        if self._ahead is None or self._ahead[0] != tuple(rids):
+            return False
+        cache = self.engine.cache
+        return all(cache.length(r) == p for r, p in zip(rids, self._ahead[1]))
 
     def step(self, rids: Sequence[Hashable], tokens: Optional[Sequence[int]], temperatures: Optional[Sequence[float]] = None,
              uniforms: Optional[Sequence[float]] = None, read_back: bool = True):
@@ -137,7 +197,11 @@ class DecodeGraph:
             b.slots.copy_(st.meta[1], non_blocking=True)
             sent += 8 * n
             self._rids = key
-        if tokens is not None:
+        fed = tokens is not None and read_back     # the copies in and out are part of the replayed graph
+        if fed:
+            self.h_in_np[:] = tokens               # safe: the last fed step was waited for before it returned
+            sent += 4 * n
+        elif tokens is not None:
             st.tokens.copy_(torch.as_tensor(list(tokens), dtype=torch.int32))
             b.token_ids.copy_(st.tokens, non_blocking=True)
             sent += 4 * n
@@ -151,26 +215,27 @@ class DecodeGraph:
         elif self._sampling:
             self.temperature.zero_()
             self._sampling = False
-        for gi, h in st.tables.items():
-            table = cache.block_table(gi, rids)
-            last = self._tables.get(gi)
-            if last is None or not np.array_equal(last, table):
-                h.copy_(torch.from_numpy(table))
-                b.block_tables[gi].copy_(h, non_blocking=True)
-                self._tables[gi] = table
-                sent += table.size * 4
-        if sent:
+        if self._ahead != (key, positions):    # else the last step has brought the tables up to date already
+            sent += self._upload_tables(rids, st)
+        if sent > (4 * n if fed else 0):
             st.event = torch.cuda.Event()
             st.event.record()
-        self.h2d_bytes = sent
-        if self.graph is None:
-            self._capture()
-        self.graph.replay()
+        self.h2d_bytes = sent + self._ahead_bytes
+        if fed:
+            if self.graph_fed is None:
+                self._capture(fed=True)
+            self.graph_fed.replay()
+        else:
+            if self.graph is None:
+                self._capture()
+            self.graph.replay()
         ops.count_launches(self.launches)
         cache.commit([(r, p + 1) for r, p in zip(rids, positions)])
         self._positions = [p + 1 for p in positions]
+        self._look_ahead(key, rids)
         if read_back:
-            self.h_out.copy_(self.out_tokens, non_blocking=True)
+            if not fed:
+                self.h_out.copy_(self.out_tokens, non_blocking=True)
             torch.cuda.current_stream().synchronize()
             return self.h_out.tolist()
         return self.out_tokens

@@ -176,9 +176,11 @@ class Engine:
         """One decoding step for live requests, one token each, run as a replayed CUDA graph:
         `tokens` (host ids; None feeds what the last step sampled, kept on the device) in, the
         sampled tokens out (greedy unless temperatures and uniform numbers are given)."""
-        self.cache.reserve([(r, self.cache.length(r) + 1) for r in rids])
+        g = self.decode_graph(len(rids))
+        if not g.prepared(rids):               # else the last step made room while the device was busy
+            self.cache.reserve([(r, self.cache.length(r) + 1) for r in rids])
         with torch.cuda.device(self.device):
-            return self.decode_graph(len(rids)).step(rids, tokens, temperatures, uniforms, read_back)
+            return g.step(rids, tokens, temperatures, uniforms, read_back)
 
     # ------------------------------------------------------------------ generation
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Union[int, Sequence[int]] = 32,
