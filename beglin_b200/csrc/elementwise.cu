@@ -175,6 +175,15 @@ __global__ void add_residual_kernel(float* __restrict__ x, const TD* __restrict_
 // product, [parts][rows][2 im].  With block > 0 the columns of gu are interleaved in blocks of that
 // many features, gate then up, gate then up (the layout that lets one CTA of the fused product hold
 // both): gate i is column (i / block) * 2 block + i % block and its up lies `block` columns on.
+// silu(g) * u.  For a bfloat16 result (8 bits of mantissa) the exponential and the reciprocal are the hardware's
+// approximations (ex2.approx and the approximate division: relative error about 2^-21), which makes the kernel bound by memory
+// instead of by these two functions; a float result is computed with expf and a division.
+template <typename TO> __device__ __forceinline__ float silu_mul(float g, float u);
+template <> __device__ __forceinline__ float silu_mul<float>(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+template <> __device__ __forceinline__ float silu_mul<__nv_bfloat16>(float g, float u) {
+    return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, int parts, size_t part_stride, TO* __restrict__ out,
                               int rows, int im, int block) {
@@ -189,7 +198,7 @@ __global__ void swiglu_kernel(const TI* __restrict__ gu, int parts, size_t part_
     const TI* gp = gu + t * 2 * (size_t)im + col;
     float g = sum_parts(gp, parts, part_stride);
     float u = sum_parts(gp + (block > 0 ? block : im), parts, part_stride);
-    out[idx] = from_float<TO>((g / (1.0f + expf(-g))) * u);
+    out[idx] = from_float<TO>(silu_mul<TO>(g, u));
 }
 
 // One tensor (no partial sums), im a multiple of 8: eight features per thread, 16-byte accesses.
@@ -208,7 +217,7 @@ __global__ void swiglu_vec8_kernel(const TI* __restrict__ gu, TO* __restrict__ o
     load8(gu + t * 2 * (size_t)im + col, g);
     load8(gu + t * 2 * (size_t)im + col + (block > 0 ? block : im), u);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) g[i] = (g[i] / (1.0f + expf(-g[i]))) * u[i];
+    for (int i = 0; i < 8; ++i) g[i] = silu_mul<TO>(g[i], u[i]);
     store8(out + t * (size_t)im + 8 * c, g);
 }
 
