@@ -38,3 +38,31 @@ def test_fused_swiglu_needs_blocks_of_64(model_root):
         folder = make_model(model_root, name, seed=3, dtype=torch.bfloat16)
         eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=128, page_size=TINY[name][2], max_requests=1)
         assert eng.model.blocks[0].feed_forward.block == block
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_pages_of_64_positions(model_root, dtype):
+    """The engine's default page size (a page is a tile of the attention kernels and comes in one TMA box):
+    a prompt in portions, then token by token across a page's edge, with a second request in between."""
+    from beglin_b200 import Engine
+    from helpers import TOL_F32
+    cfg, _, _ = TINY["D"]
+    stored = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    folder = make_model(model_root, "D", seed=13, dtype=stored)
+    ids = {"a": seeded_ids(150, cfg["vocab_size"], 7), "b": seeded_ids(70, cfg["vocab_size"], 8)}
+    want = {r: plain_logits(folder, ids[r]) for r in ids}
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=256, max_requests=2)       # 4 pages of 64
+    assert eng.cache.page_size == 64
+    rl.poison(eng)
+    got = {"a": [], "b": []}
+    got["a"].append(eng.step([("a", ids["a"][:60], list(range(60)))]))
+    got["b"].append(eng.step([("b", ids["b"][:3], [0, 1, 2])]))
+    for t in range(60, 70):                                    # across the edge at 64, beside the other request
+        out = eng.step([("a", ids["a"][t:t + 1], [0]), ("b", ids["b"][t - 57:t - 56], [0])])
+        got["a"].append(out[:1]); got["b"].append(out[1:])
+    got["a"].append(eng.step([("a", ids["a"][70:150], list(range(80)))], end=["a"]))   # a third page; then its pages go back
+    got["b"].append(eng.step([("b", ids["b"][13:70], list(range(57)))], end=["b"]))
+    tol = TOL_BF16 if dtype == "bfloat16" else TOL_F32
+    for r in ids:
+        assert rel_err(torch.cat(got[r]).cpu(), want[r]) < tol, r
+    eng.cache.check()
