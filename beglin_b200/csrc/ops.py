@@ -312,7 +312,9 @@ def decode_splits(n_streams: int, context: int) -> int:
     longer ranges.  No more than one CTA per 256 keys of `context` (a stage of 64 for each of the four
     warps).  Each request's keys are spread evenly over its CTAs by the kernel itself, by the
     request's own length, so the count depends on the shapes of the step only."""
-    return max(1, min(148 // max(1, n_streams), -(-context // 256)))
+    want = max(1, min(148 // max(1, n_streams), -(-context // 256)))
+    per = -(-(-(-context // want)) // 256) * 256          # what the kernel makes of it: whole multiples of 256 keys
+    return -(-context // per)                             # no CTA without keys
 
 
 def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table: torch.Tensor,

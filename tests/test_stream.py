@@ -55,4 +55,4 @@ def test_decode_splits_make_one_wave():
             n = decode_splits(streams, context)
             assert n >= 1 and (streams * n <= 148 or n == 1)
             assert n <= max(1, -(-context // 256))
-    assert decode_splits(16, 4096) == 9 and decode_splits(2, 4096) == 16 and decode_splits(128, 4096) == 1
+    assert decode_splits(16, 4096) == 8 and decode_splits(2, 4096) == 16 and decode_splits(128, 4096) == 1
