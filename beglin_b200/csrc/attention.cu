@@ -314,10 +314,10 @@ extern "C" int bg_attention_partial(const void* q, int q_dtype, int q_stride, co
     return BG_OK;
 }
 
-// The same for at most 8 splits and head_dim <= 128 (decoding): the position, the maxima and sums, and the
+// The same for at most NS (8 or 16) splits and head_dim <= 128 (decoding): the position, the maxima and sums, and the
 // partial outputs of ALL splits are asked for at once, and what lies outside the row's range is dropped when
 // the position has arrived, so the kernel is one round trip to memory instead of three.
-template <typename TO>
+template <typename TO, int NS>
 __global__ void attention_merge_few_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
                                            int T, int nh, int hd, int max_splits, int split_arg, int window) {
@@ -329,9 +329,9 @@ __global__ void attention_merge_few_kernel(const float* __restrict__ part_o, con
     const int t = w / nh, h = w - t * nh;
     const size_t prow = (size_t)w * max_splits;
     const int pos = positions[t];
-    float ms[8], ls[8], v[8][4];
+    float ms[NS], ls[NS], v[NS][4];
 #pragma unroll
-    for (int s = 0; s < 8; ++s) {
+    for (int s = 0; s < NS; ++s) {
         const bool have = s < max_splits;
         ms[s] = have ? part_ml[(prow + s) * 2] : -INFINITY;
         ls[s] = have ? part_ml[(prow + s) * 2 + 1] : 0.0f;
@@ -346,13 +346,13 @@ __global__ void attention_merge_few_kernel(const float* __restrict__ part_o, con
     const int s_lo = lo / split, s_hi = pos / split;
     float m = -INFINITY;
 #pragma unroll
-    for (int s = 0; s < 8; ++s) {
+    for (int s = 0; s < NS; ++s) {
         if (s < s_lo || s > s_hi) ms[s] = -INFINITY;          // not written for this row: whatever was read is dropped
         m = fmaxf(m, ms[s]);
     }
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, l = 0.0f;
 #pragma unroll
-    for (int s = 0; s < 8; ++s) {                             // in split order
+    for (int s = 0; s < NS; ++s) {                             // in split order
         if (ms[s] != -INFINITY) {
             const float f = expf(ms[s] - m);
             l = fmaf(ls[s], f, l);
@@ -376,7 +376,10 @@ extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, con
     long long warps = (long long)T * nh;
     unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
     if (max_splits <= 8 && hd <= 128) {
-        BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO>, dim3(blocks), dim3(256), 0, stream,
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 8>, dim3(blocks), dim3(256), 0, stream,
+            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
+    } else if (max_splits <= 16 && hd <= 128) {
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 16>, dim3(blocks), dim3(256), 0, stream,
             part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
     } else {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_kernel<TO>, dim3(blocks), dim3(256), 0, stream,
