@@ -540,6 +540,10 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
                     acc = fmaf(o_sh[((size_t)w * 16 + r) * HD + d], f, acc);
                     l = fmaf(ml_sh[(w * 16 + r) * 2 + 1], f, l);
                 }
+                if (p.out) {                                   // the only range of its request: the finished row
+                    p.out[(size_t)row0 * p.out_stride + (size_t)(kvh * group + r) * HD + d] = __float2bfloat16_rn(acc / l);
+                    continue;
+                }
                 size_t prow = ((size_t)row0 * p.nh + (size_t)kvh * group + r) * p.max_splits + sp;
                 p.part_o[prow * HD + d] = acc;
                 if (d == 0) { p.part_ml[prow * 2 + 0] = m * AM_LN2; p.part_ml[prow * 2 + 1] = l; }
@@ -595,7 +599,7 @@ extern "C" int bg_attention_mma_partial(const void* q, int q_stride, const void*
                                         int nh, int nkv, int hd, int window, int split, int by_keys, float scale,
                                         void* direct_out, int out_stride, unsigned* status, cudaStream_t stream) {
     if (n_qblk <= 0 || n_splits_launch <= 0) return BG_OK;
-    if (direct_out && (by_keys || n_splits_launch != 1 || (out_stride % 2) != 0)) return BG_ERR_SHAPE;
+    if (direct_out && (n_splits_launch != 1 || (out_stride % 2) != 0)) return BG_ERR_SHAPE;
     if (nh % nkv != 0 || split % AM_STAGE_KEYS != 0 || (split <= 0 && !by_keys)) return BG_ERR_SHAPE;
     if (n_splits_launch > max_splits || n_splits_launch > 65535 || nkv > 65535) return BG_ERR_SHAPE;
     if ((q_stride % 8) != 0 || ((uintptr_t)q % 16) != 0 || ((uintptr_t)kv_pool % 16) != 0) return BG_ERR_ALIGN;

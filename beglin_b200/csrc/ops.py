@@ -360,6 +360,14 @@ def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table
         return
     if kernel == "mma_keys":
         split, n_splits = 0, decode_splits(n_qblk * nkv, max_position + 1)
+        if n_splits == 1:                        # one CTA walks all keys of its (request, kv head) and writes the rows
+            if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+                raise KernelError("attention: the tensor-core kernel takes bfloat16 queries, caches and outputs")
+            _check(L.bg_attention_mma_partial(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
+                                              block_table.shape[1], _p(positions), _p(qblk) if qblk is not None else None,
+                                              n_qblk, None, None, 1, 1, nh, nkv, hd, window, 0, 1, float(scale), _p(out),
+                                              out.stride(0), _p(status), _stream()), "attention_mma_keys")
+            return
     else:
         n_splits = max_position // split + 1
     part_o = torch.empty((n_rows * nh * n_splits, hd), dtype=torch.float32, device=q.device)
