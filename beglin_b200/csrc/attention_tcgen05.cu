@@ -175,7 +175,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
 
     pdl_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-    const int qb = blockIdx.x, kvh = blockIdx.y;
+    // the blocks with the most keys (the last ones of a prompt) are handed out first, for every kv head, so that
+    // the short ones fill the machine's last wave
+    const int kvh = blockIdx.x, qb = (int)gridDim.y - 1 - (int)blockIdx.y;
     if (tid == 0) {
         for (int s = 0; s < AT_STAGES; ++s) {
             at_mbar_init(&k_full[s], 1); at_mbar_init(&k_empty[s], 1); at_mbar_init(&v_full[s], 1); at_mbar_init(&v_empty[s], 1);
@@ -482,7 +484,7 @@ static int at_launch(const CUtensorMap& map, const AttnTcParams& p, int n_qblk, 
     const size_t smem = (size_t)(HD / 64) * AT_BM * 128 + (size_t)2 * AT_STAGES * (HD / 64) * AT_BK * 128 + 2 * AT_BM * 128 + 1024;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    e = launch(kern, dim3(n_qblk, p.nkv), dim3(AT_THREADS), smem, stream, map, p);
+    e = launch(kern, dim3(p.nkv, n_qblk), dim3(AT_THREADS), smem, stream, map, p);
     if (e != cudaSuccess) return (int)e;
     return BG_OK;
 }
@@ -507,7 +509,7 @@ extern "C" int bg_attention_tc(const void* q, int q_stride, const void* kv_pool,
     if (nh % nkv != 0 || (hd != 64 && hd != 128) || nh / nkv > 128 || !(scale > 0.0f)) return BG_ERR_UNSUPPORTED;
     if (page_size < 1 || page_size > 64 || 64 % page_size != 0) return BG_ERR_UNSUPPORTED;
     if ((q_stride % 8) || (out_stride % 8) || ((uintptr_t)q % 16) || ((uintptr_t)kv_pool % 16) || ((uintptr_t)out % 16)) return BG_ERR_ALIGN;
-    if (nkv > 65535) return BG_ERR_SHAPE;
+    if (n_qblk > 65535) return BG_ERR_SHAPE;                 // the query blocks are the grid's second dimension
     AttnTcParams p;
     p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.kv_pool = (const __nv_bfloat16*)kv_pool;
     p.num_pages = num_pages; p.page_size = page_size; p.page_shift = -1;
