@@ -20,7 +20,11 @@
 //          64 keys (stage s lands in buffer s % 4, which is warp s % 4's), walks it alone, and the four
 //          partial results are joined in shared memory at the end (decoding: a stage is a long chain of
 //          dependent steps for one warp, so four of them run side by side, each with 64 keys' worth of
-//          independent MMAs, and no barrier of the CTA stands between two stages).
+//          independent MMAs, and no barrier of the CTA stands between two stages).  With at most 8 heads
+//          per kv head the products are turned around (SWAP): the 16 keys of a block are the M side of
+//          the instruction and the heads the N side of 8, S^T = K Q^T and O^T = V^T P^T, which halves
+//          the MMAs of a stage (the heads fill 6 of 8 columns instead of 6 of 16 rows); P^T reaches its
+//          operand layout through movmatrix.
 #include "page_tma.cuh"
 
 namespace bg {
@@ -84,6 +88,12 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+// transposes an 8x8 matrix of 16-bit values held one 32-bit register (two values) per lane
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
+    unsigned d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -96,7 +106,7 @@ __device__ __forceinline__ int swz_kv(int row, int c) {
     return (c >> 3) * (AM_STAGE_KEYS * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4);
 }
 
-template <int HD, bool BY_KEYS, int AM_STAGES>
+template <int HD, bool BY_KEYS, int AM_STAGES, bool SWAP>
 __global__ void __launch_bounds__(AM_ALL)
 attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_constant__ CUtensorMap map_page, AttnMmaParams p) {
     constexpr int CH = HD / 8;                 // 16-byte columns per row
@@ -316,6 +326,25 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
     float o[NT_O][4];
 #pragma unroll
     for (int t = 0; t < NT_O; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f; }
+    // SWAP: the heads are the N side.  This lane's heads are r0 = 2 (lane % 4) and r0 + 1; qsw holds Q as the B
+    // operand, ot the transposed output: ot[db][e] is feature db * 16 + lane / 4 + 8 (e >> 1) of head r0 + (e & 1).
+    unsigned qsw[KSTEPS][2];
+    float ot[HD / 16][4];
+    int koff_a[KSTEPS], voff_a[HD / 16];
+    if (SWAP) {
+#pragma unroll
+        for (int ks2 = 0; ks2 < KSTEPS / 2; ++ks2) {
+            unsigned r4[4];
+            ldmatrix_x4(r4, q_s + swz<HD>(lane & 7, ks2 * 4 + (lane >> 3)));
+            qsw[2 * ks2][0] = r4[0]; qsw[2 * ks2][1] = r4[1]; qsw[2 * ks2 + 1][0] = r4[2]; qsw[2 * ks2 + 1][1] = r4[3];
+        }
+#pragma unroll
+        for (int db = 0; db < HD / 16; ++db) { ot[db][0] = ot[db][1] = ot[db][2] = ot[db][3] = 0.0f; }
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) koff_a[ks] = swz_kv((lane & 7) + (((lane >> 3) & 1) << 3), ks * 2 + (lane >> 4));
+#pragma unroll
+        for (int db = 0; db < HD / 16; ++db) voff_a[db] = swz_kv((lane & 7) + ((lane >> 4) << 3), db * 2 + ((lane >> 3) & 1));
+    }
 
     constexpr int KB = 4;                               // 16-key blocks of a stage
     constexpr int BLOCK_BYTES = 16 * 128;               // 16 keys further down, in every block of 64 features
@@ -377,7 +406,77 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
         const int w_key0 = stage_key0;
         const int vis_lo = max(max(w_key0, k_begin), warp_lo);                   // keys some row of the warp sees
         const int vis_hi = min(min(w_key0 + 16 * KB, k_end), warp_pos_hi + 1);
-        if (vis_lo < vis_hi) {                                                   // warp-uniform
+        if (SWAP && vis_lo < vis_hi) {
+            // ---- S^T = K Q^T: per block of 16 keys a 16 x 8 tile; c[kb][e]: key kb * 16 + lane / 4 + 8 (e >> 1), head r0 + (e & 1)
+            float c[KB][4];
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) { c[kb][0] = c[kb][1] = c[kb][2] = c[kb][3] = 0.0f; }
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb) {
+                    unsigned a[4];
+                    ldmatrix_x4(a, kt + kb * BLOCK_BYTES + koff_a[ks]);
+                    mma_bf16(c[kb], a, qsw[ks][0], qsw[ks][1]);
+                }
+            }
+            const int r0 = 2 * (lane & 3);
+            const int pos = pos_first, lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+            const bool all_seen = w_key0 >= k_begin && w_key0 + 16 * KB <= k_end && w_key0 >= lo && w_key0 + 16 * KB - 1 <= pos;
+            float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = w_key0 + kb * 16 + (lane >> 2) + 8 * (e >> 1);
+                    const bool ok = all_seen || (key <= pos && key >= lo && key >= k_begin && key < k_end);
+                    const float v = (ok && r0 + (e & 1) < n_rows) ? c[kb][e] * p.scale_log2 : -INFINITY;
+                    c[kb][e] = v;
+                    tmax[e & 1] = fmaxf(tmax[e & 1], v);
+                }
+            float corr[2], m_use[2], psum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {                                        // the keys of a head lie across lane / 4
+                tmax[j] = fmaxf(tmax[j], __shfl_xor_sync(0xffffffffu, tmax[j], 4));
+                tmax[j] = fmaxf(tmax[j], __shfl_xor_sync(0xffffffffu, tmax[j], 8));
+                tmax[j] = fmaxf(tmax[j], __shfl_xor_sync(0xffffffffu, tmax[j], 16));
+                const float m_new = fmaxf(m_r[j], tmax[j]);
+                m_use[j] = (m_new == -INFINITY) ? 0.0f : m_new;
+                corr[j] = ex2(m_r[j] - m_use[j]);
+                m_r[j] = m_new;
+            }
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    c[kb][e] = ex2(c[kb][e] - m_use[e & 1]);
+                    psum[e & 1] += c[kb][e];
+                }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                psum[j] += __shfl_xor_sync(0xffffffffu, psum[j], 4);
+                psum[j] += __shfl_xor_sync(0xffffffffu, psum[j], 8);
+                psum[j] += __shfl_xor_sync(0xffffffffu, psum[j], 16);
+                l_r[j] = l_r[j] * corr[j] + psum[j];
+            }
+#pragma unroll
+            for (int db = 0; db < HD / 16; ++db) {
+                ot[db][0] *= corr[0]; ot[db][1] *= corr[1]; ot[db][2] *= corr[0]; ot[db][3] *= corr[1];
+            }
+            // ---- O^T += V^T P^T: P^T of a block as the B operand (keys x heads) through a transpose of the packed tile
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+                const unsigned b0 = movmatrix_trans(pack_bf16(c[kb][0], c[kb][1]));
+                const unsigned b1 = movmatrix_trans(pack_bf16(c[kb][2], c[kb][3]));
+#pragma unroll
+                for (int db = 0; db < HD / 16; ++db) {
+                    unsigned a[4];
+                    ldmatrix_x4_trans(a, vt + kb * BLOCK_BYTES + voff_a[db]);
+                    mma_bf16(ot[db], a, b0, b1);
+                }
+            }
+        }
+        if (!SWAP && vis_lo < vis_hi) {                                          // warp-uniform
             // ---- scores of 16 rows x 16*KB keys
             // (k-step outermost, so the 2*KB accumulators form independent chains of dependent MMAs)
             float sc[2 * KB][4];
@@ -512,8 +611,20 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
         compute_sync();
         float* o_sh = reinterpret_cast<float*>(k_s);               // [4][16][HD]
         float* ml_sh = o_sh + 4 * 16 * HD;                         // [4][16][2]
+        if (SWAP) {
+            const int r0 = 2 * (lane & 3);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+            for (int db = 0; db < HD / 16; ++db)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    o_sh[((size_t)warp * 16 + r0 + (e & 1)) * HD + db * 16 + (lane >> 2) + 8 * (e >> 1)] = ot[db][e];
+            if (lane < 4) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) { ml_sh[(warp * 16 + r0 + j) * 2 + 0] = m_r[j]; ml_sh[(warp * 16 + r0 + j) * 2 + 1] = l_r[j]; }
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2 && !SWAP; ++h) {
             int r = (lane >> 2) + h * 8;
             float* dst = o_sh + ((size_t)warp * 16 + r) * HD;
 #pragma unroll
@@ -557,9 +668,9 @@ static size_t am_smem_bytes() {
     return (size_t)(BY_KEYS ? 16 : 64) * HD * 2 + (size_t)2 * STAGES * AM_STAGE_KEYS * HD * 2 + 1024;
 }
 
-template <int HD, bool BY_KEYS, int STAGES>
+template <int HD, bool BY_KEYS, int STAGES, bool SWAP = false>
 static int am_launch_stages(const CUtensorMap& map, const CUtensorMap& map5, const AttnMmaParams& p, int n_qblk, int n_splits, cudaStream_t stream) {
-    auto kern = attention_mma_kernel<HD, BY_KEYS, STAGES>;
+    auto kern = attention_mma_kernel<HD, BY_KEYS, STAGES, SWAP>;
     size_t smem = am_smem_bytes<HD, BY_KEYS, STAGES>();
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -571,6 +682,7 @@ static int am_launch_stages(const CUtensorMap& map, const CUtensorMap& map5, con
 
 template <int HD, bool BY_KEYS>
 static int am_launch(const CUtensorMap& map, const CUtensorMap& map5, const AttnMmaParams& p, int n_qblk, int n_splits, cudaStream_t stream) {
+    if (BY_KEYS && p.group <= 8) return am_launch_stages<HD, BY_KEYS, AM_THREADS / 32, BY_KEYS>(map, map5, p, n_qblk, n_splits, stream);
     if (BY_KEYS) return am_launch_stages<HD, BY_KEYS, AM_THREADS / 32>(map, map5, p, n_qblk, n_splits, stream);   // a buffer per warp
     return am_launch_stages<HD, BY_KEYS, 3>(map, map5, p, n_qblk, n_splits, stream);
 }
