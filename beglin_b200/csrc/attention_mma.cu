@@ -124,7 +124,11 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
     __shared__ int gave_up;
 
     pdl_launch();
-    pdl_wait();
+    // Decoding (keys arrangement): the kernel before this one wrote the step's queries and the ONE new key
+    // and value of every request; positions, block tables and all older keys and values are from earlier
+    // steps.  So everything up to the first copies of old pages happens before the wait for that kernel, and
+    // when it has finished the data is already on its way (or here).
+    if (!BY_KEYS) pdl_wait();
     const int qb = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
     // without a list of query blocks, block i is row i of request i (a step of single tokens)
     const int req = p.qblk ? p.qblk[qb * 3 + 0] : qb, row0 = p.qblk ? p.qblk[qb * 3 + 1] : qb;
@@ -139,15 +143,18 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
     // (rows beyond n_rows are zero) ...
     const int pos_first = p.positions[row0];
     const int pos_last = p.positions[row0 + nq - 1];
-    for (int idx = tid; idx < Q_ROWS * CH; idx += AM_ALL) {
-        int r = idx / CH, c = idx - r * CH;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < n_rows) {
-            int qi = BY_KEYS ? 0 : r / group, g = r - qi * group;
-            v = *reinterpret_cast<const uint4*>(p.q + (size_t)(row0 + qi) * p.q_stride + (size_t)(kvh * group + g) * HD + c * 8);
+    auto load_queries = [&](int first, int step) {
+        for (int idx = first; idx < Q_ROWS * CH; idx += step) {
+            int r = idx / CH, c = idx - r * CH;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < n_rows) {
+                int qi = BY_KEYS ? 0 : r / group, g = r - qi * group;
+                v = *reinterpret_cast<const uint4*>(p.q + (size_t)(row0 + qi) * p.q_stride + (size_t)(kvh * group + g) * HD + c * 8);
+            }
+            *reinterpret_cast<uint4*>(q_s + swz<HD>(r, c)) = v;
         }
-        *reinterpret_cast<uint4*>(q_s + swz<HD>(r, c)) = v;
-    }
+    };
+    if (!BY_KEYS) load_queries(tid, AM_ALL);
     // ... and the block-table entries of 128 pages at a time, kept in shared memory so that a stage's
     // copies start without a table load of their own (a stage of 64 keys never straddles two such groups).
     // The group fetched here is the one the first keys of this CTA's range lie in when there is no window.
@@ -177,8 +184,13 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
     const int last_page = (k_end - 1) / p.page_size;
     int table_group = (first_stage_key / p.page_size) / AM_TABLE;
     if (table_group != pre_group) table_group = -1;               // a window moved the range: fetched by the loader
-    __syncthreads();                           // q_s and table_s are complete
+    __syncthreads();                           // table_s and the barriers are ready (and q_s, rows arrangement)
     auto compute_sync = [] { asm volatile("bar.sync 1, %0;\n" ::"n"(AM_THREADS) : "memory"); };   // the four computing warps
+    if (BY_KEYS && warp < AM_THREADS / 32) {
+        pdl_wait();                            // the queries come from the kernel before this one
+        load_queries(tid, AM_THREADS);
+        compute_sync();
+    }
     if (warp == AM_THREADS / 32) {
         // ---- the copying warp.  A page of a stage is 2 * HD / 64 boxes (keys and values, 64 features each);
         // box o of the stage is lane o's, so that one instruction of the warp asks for up to 32 boxes (what
@@ -194,8 +206,12 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
             if (s >= n_stage || o >= n_box || key_lo >= k_end || key_lo + ps <= k_begin || (key_lo >> shift) >= p.max_pages) return -1;
             return table[key_lo >> shift];
         };
+        // stages of old keys only may be asked for before the kernel ahead has finished: all but the one that
+        // holds the newest position
+        const int n_early = BY_KEYS ? min(AM_STAGES, k_end == pos_last + 1 ? n_stage - 1 : n_stage) : 0;
         int next_page = page_of(0, p.whole_pages ? lane * PER_PAGE : lane);
         for (int s = 0; s < n_stage; ++s) {
+            if (BY_KEYS && s == n_early) pdl_wait();
             const int buf = s % AM_STAGES;
             int page = next_page;
             next_page = page_of(s + 1, p.whole_pages ? lane * PER_PAGE : lane);   // fetched while this stage's copies go out
@@ -609,15 +625,17 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
         // join the four warps' results: o_w, m_w, l_w -> shared memory (over the stage buffers, once every
         // warp has read its last keys and values from them)
         compute_sync();
-        float* o_sh = reinterpret_cast<float*>(k_s);               // [4][16][HD]
-        float* ml_sh = o_sh + 4 * 16 * HD;                         // [4][16][2]
+        constexpr int HP = HD + 4;                                 // rows four floats apart from a multiple of 128 bytes:
+        float* o_sh = reinterpret_cast<float*>(k_s);               // [4][16][HP]  the stores below meet no bank twice
+        float* ml_sh = o_sh + 4 * 16 * HP;                         // [4][16][2]
+        float* fac_sh = ml_sh + 4 * 16 * 2;                        // [16][4] weights of the warps' parts, then [16][2] m and l
         if (SWAP) {
             const int r0 = 2 * (lane & 3);
 #pragma unroll
             for (int db = 0; db < HD / 16; ++db)
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                    o_sh[((size_t)warp * 16 + r0 + (e & 1)) * HD + db * 16 + (lane >> 2) + 8 * (e >> 1)] = ot[db][e];
+                    o_sh[((size_t)warp * 16 + r0 + (e & 1)) * HP + db * 16 + (lane >> 2) + 8 * (e >> 1)] = ot[db][e];
             if (lane < 4) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) { ml_sh[(warp * 16 + r0 + j) * 2 + 0] = m_r[j]; ml_sh[(warp * 16 + r0 + j) * 2 + 1] = l_r[j]; }
@@ -626,7 +644,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
 #pragma unroll
         for (int h = 0; h < 2 && !SWAP; ++h) {
             int r = (lane >> 2) + h * 8;
-            float* dst = o_sh + ((size_t)warp * 16 + r) * HD;
+            float* dst = o_sh + ((size_t)warp * 16 + r) * HP;
 #pragma unroll
             for (int t = 0; t < NT_O; ++t) {
                 dst[t * 8 + (lane & 3) * 2 + 0] = o[t][h * 2 + 0];
@@ -638,26 +656,40 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
         const int pos = pos_first;
         const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
         if (!(pos < sp * split || lo >= (sp + 1) * split)) {
-            for (int idx = tid; idx < n_rows * HD; idx += AM_THREADS) {
-                int r = idx / HD, d = idx - r * HD;
+            // the weights of the four warps' parts, row by row (16 threads), then every thread one feature of all rows
+            if (tid < n_rows) {
+                const int r = tid;
                 float m = -INFINITY;
 #pragma unroll
                 for (int w = 0; w < 4; ++w) m = fmaxf(m, ml_sh[(w * 16 + r) * 2]);
-                float acc = 0.0f, l = 0.0f;
+                float l = 0.0f;
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
-                    float mw = ml_sh[(w * 16 + r) * 2];
-                    float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
-                    acc = fmaf(o_sh[((size_t)w * 16 + r) * HD + d], f, acc);
+                    const float mw = ml_sh[(w * 16 + r) * 2];
+                    const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
+                    fac_sh[r * 4 + w] = f;
                     l = fmaf(ml_sh[(w * 16 + r) * 2 + 1], f, l);
                 }
-                if (p.out) {                                   // the only range of its request: the finished row
-                    p.out[(size_t)row0 * p.out_stride + (size_t)(kvh * group + r) * HD + d] = __float2bfloat16_rn(acc / l);
-                    continue;
+                fac_sh[64 + r * 2 + 0] = m;
+                fac_sh[64 + r * 2 + 1] = l;
+            }
+            compute_sync();
+            if (tid < HD) {
+                const int d = tid;
+#pragma unroll 4
+                for (int r = 0; r < n_rows; ++r) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) acc = fmaf(o_sh[((size_t)w * 16 + r) * HP + d], fac_sh[r * 4 + w], acc);
+                    if (p.out) {                               // the only range of its request: the finished row
+                        p.out[(size_t)row0 * p.out_stride + (size_t)(kvh * group + r) * HD + d] =
+                            __float2bfloat16_rn(acc / fac_sh[64 + r * 2 + 1]);
+                    } else {
+                        const size_t prow = ((size_t)row0 * p.nh + (size_t)kvh * group + r) * p.max_splits + sp;
+                        p.part_o[prow * HD + d] = acc;
+                        if (d == 0) { p.part_ml[prow * 2 + 0] = fac_sh[64 + r * 2] * AM_LN2; p.part_ml[prow * 2 + 1] = fac_sh[64 + r * 2 + 1]; }
+                    }
                 }
-                size_t prow = ((size_t)row0 * p.nh + (size_t)kvh * group + r) * p.max_splits + sp;
-                p.part_o[prow * HD + d] = acc;
-                if (d == 0) { p.part_ml[prow * 2 + 0] = m * AM_LN2; p.part_ml[prow * 2 + 1] = l; }
             }
         }
     }
