@@ -385,18 +385,20 @@ __global__ void rope_kv_append_heads_kernel(const TS* __restrict__ src, int src_
                                             TC* __restrict__ kv_pool, int num_pages, int page_size,
                                             int nh, int nkv, int hd, int rot, int interleaved, unsigned* status) {
     pdl_launch();
-    pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y, i = threadIdx.x;
     if (i >= hd) return;
     const int half = rot >> 1;
     const bool is_v = h >= nh + nkv;
     const TS* head = src + (size_t)t * src_stride + (size_t)h * hd;
+    // where the key or value goes is known before the step began (positions and block tables are not written
+    // by the kernels of a step): this chain of two loads runs while the kernel ahead finishes
     int page = 0, slot = 0;
     if (h >= nh) {
         const int pos = positions[t];
         page = block_table[(size_t)row_req[t] * max_pages + pos / page_size];
         slot = pos % page_size;
     }
+    pdl_wait();
     float val = sum_parts(head + i, parts, part_stride);
     if (!is_v && i < rot) {
         int pi, partner;
