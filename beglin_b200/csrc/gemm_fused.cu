@@ -106,6 +106,10 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     tc_fence_after();
     const unsigned tmem_base = tmem_base_sh;
 
+    // What the reduction at the end adds to the product (the bias of this thread's row; in residual mode the
+    // stream's values that it will update) is asked for while the main loop still runs: up to four values.
+    float pre_bias = 0.0f, pre_x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+
     if (warp == 0) {
         // ---------------- TMA producer: the weights (requested before the kernel ahead has finished) and,
         // when they come by TMA, the activations
@@ -228,6 +232,21 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 }
             }
         }
+        {
+            const int S = p.splits, rows_per = TC_BM / S, half = rows_per / 2;
+            const int rl = te & (rows_per - 1);
+            const int row = p.mode == GF_SWIGLU ? (rl < half ? split * half + rl : 64 + split * half + (rl - half)) : split * rows_per + rl;
+            const int n = tile_m * TC_BM + row;
+            if (p.bias && n < p.n_out) pre_bias = p.bias[n];
+            if (p.mode == GF_RESIDUAL && n < p.n_out) {
+                const int t_real = min(BN, p.T - tile_n * BN);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int c = te / rows_per + i * S;
+                    if (c < t_real) pre_x[i] = ((const float*)p.out)[(size_t)(tile_n * BN + c) * p.ldo + n];
+                }
+            }
+        }
         if (ok && n_kb > 0) {
             ok = mbar_wait(&acc_bar, 0);
             if (!ok) atomicExch(&failed, 1);
@@ -276,7 +295,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         const int rl = te & (rows_per - 1);
         const int row = p.mode == GF_SWIGLU ? (rl < half ? rank * half + rl : 64 + rank * half + (rl - half)) : rank * rows_per + rl;
         const int n = tile_m * TC_BM + row;
-        const float bias = (p.bias && n < p.n_out) ? p.bias[n] : 0.0f;
+        const float bias = pre_bias;
         const int c0 = te / rows_per;
         const int part = BN * rows_per;                                    // floats between two ranks' parts
         // the sum over the ranks, in rank order (the loads go out together; S is 1, 2, 4, 8 or 16)
@@ -304,8 +323,20 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             }
         } else if (p.mode == GF_RESIDUAL) {
             float* po = (float*)p.out + (size_t)(tile_n * BN + c0) * p.ldo + n;
-#pragma unroll 4
-            for (int c = c0; c < t_real; c += S, po += (size_t)S * p.ldo) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {                                  // the values asked for ahead
+                const int c = c0 + i * S;
+                if (c < t_real) {
+                    float x = 0.0f;
+                    if (n < p.n_out) {
+                        x = pre_x[i] + total(c);
+                        po[(size_t)i * S * p.ldo] = x;
+                    }
+                    sq[c * rows_per + rl] = x * x;
+                }
+            }
+            po += (size_t)4 * S * p.ldo;
+            for (int c = c0 + 4 * S; c < t_real; c += S, po += (size_t)S * p.ldo) {
                 float x = 0.0f;
                 if (n < p.n_out) {
                     x = *po + total(c);
