@@ -324,31 +324,43 @@ rope_kv_append_bf16_kernel(const __nv_bfloat16* __restrict__ src, int src_stride
                            __nv_bfloat16* __restrict__ kv_pool, int num_pages, int page_size, int nh, int nkv, int hd,
                            unsigned* status) {
     pdl_launch();
-    pdl_wait();
     const int t = blockIdx.x;
     const int half = hd >> 1, chunks = half >> 3;              // 8-feature chunks per half head
     const __nv_bfloat16* row = src + (size_t)t * src_stride;
     const float2* cs = cos_sin + (size_t)t * half;
-    int page = -1, slot = 0;
-    if (kv_pool) {
-        const int pos = positions[t];
-        page = block_table[(size_t)row_req[t] * max_pages + pos / page_size];
-        slot = pos % page_size;
-        if (page < 0 || page >= num_pages) {
-            if (threadIdx.x == 0 && status) atomicOr(status, BG_STATUS_BAD_PAGE);
-            page = -1;
+    // where this token's key and value go: position and request are asked for before the wait for the kernel
+    // ahead, the block-table entry once the first features are on their way, so that the chain of dependent
+    // loads runs beside them instead of before them
+    int pos = 0, rq = 0;
+    if (kv_pool) { pos = positions[t]; rq = row_req[t]; }
+    pdl_wait();
+    int page = -2, slot = 0;                                   // -2: not looked up yet
+    auto look_up = [&] {
+        if (page != -2) return;
+        page = -1;
+        if (kv_pool) {
+            page = block_table[(size_t)rq * max_pages + pos / page_size];
+            slot = pos % page_size;
+            if (page < 0 || page >= num_pages) {
+                if (threadIdx.x == 0 && status) atomicOr(status, BG_STATUS_BAD_PAGE);
+                page = -1;
+            }
         }
-    }
+    };
     const int n_heads = nh + (kv_pool ? nkv : 0);
     for (int item = threadIdx.x; item < n_heads * chunks; item += blockDim.x) {
         const int h = item / chunks, c = item - h * chunks;
         float a[8], b[8];
         load8(row + (size_t)h * hd + 8 * c, a);
         load8(row + (size_t)h * hd + half + 8 * c, b);
+        float4 f4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f4[i] = reinterpret_cast<const float4*>(cs + 8 * c)[i];
+        look_up();
         float ra[8], rb[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const float2 f = cs[8 * c + i];
+            const float2 f = (i & 1) ? make_float2(f4[i >> 1].z, f4[i >> 1].w) : make_float2(f4[i >> 1].x, f4[i >> 1].y);
             ra[i] = rope_rotate(a[i], b[i], f, true);
             rb[i] = rope_rotate(b[i], a[i], f, false);
         }
@@ -362,6 +374,7 @@ rope_kv_append_bf16_kernel(const __nv_bfloat16* __restrict__ src, int src_stride
         store8(dst + 8 * c, ra);
         store8(dst + half + 8 * c, rb);
     }
+    look_up();
     if (kv_pool && page >= 0) {                                  // v: a plain copy
         const __nv_bfloat16* v = row + (size_t)(nh + nkv) * hd;
         __nv_bfloat16* vdst = kv_pool + ((size_t)page * 2 + 1) * nkv * page_size * hd;

@@ -28,27 +28,29 @@ class StepBatch:
         self.entries = list(entries)
         self.device = torch.device(device)
         self.n_req = len(self.entries)
-        ids: List[int] = []
-        pos: List[int] = []
-        req: List[int] = []
-        rows: List[int] = []
         self.row_start: List[int] = []
-        for i, (e, s) in enumerate(zip(self.entries, starts)):
-            self.row_start.append(len(ids))
-            n = len(e.tokens)
-            ids.extend(int(t) for t in e.tokens)
-            pos.extend(range(s, s + n))
-            req.extend([i] * n)
-            rows.extend(self.row_start[-1] + int(w) for w in e.want)
-        self.n_rows = len(ids)
-        self.starts = list(starts)
         self.lens = [len(e.tokens) for e in self.entries]
-        self.max_position = max(pos) if pos else 0
+        self.starts = [int(s) for s in starts]
+        ids_parts, pos_parts, req_parts, rows = [], [], [], []
+        n_rows = 0
+        for i, (e, s, n) in enumerate(zip(self.entries, self.starts, self.lens)):
+            self.row_start.append(n_rows)
+            t64 = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+            if t64.size and (t64.min() < 0 or t64.max() > 0x7fffffff):
+                t64 = np.where((t64 < 0) | (t64 > 0x7fffffff), -1, t64)      # the embedding kernel reports these
+            ids_parts.append(t64.astype(np.int32))
+            pos_parts.append(np.arange(s, s + n, dtype=np.int32))
+            req_parts.append(np.full(n, i, dtype=np.int32))
+            rows.extend(n_rows + int(w) for w in e.want)
+            n_rows += n
+        cat = lambda parts: np.concatenate(parts) if parts else np.zeros(0, dtype=np.int32)
+        self.n_rows = n_rows
+        self.max_position = max((s + n - 1 for s, n in zip(self.starts, self.lens) if n > 0), default=0)
         self.decode_only = all(n == 1 for n in self.lens)      # every request brings a single token
         self.n_logit_rows = len(rows)
-        self.token_ids = self._to_device(np.asarray(ids, dtype=np.int32))
-        self.positions = self._to_device(np.asarray(pos, dtype=np.int32))
-        self.row_req = self._to_device(np.asarray(req, dtype=np.int32))
+        self.token_ids = self._to_device(cat(ids_parts))
+        self.positions = self._to_device(cat(pos_parts))
+        self.row_req = self._to_device(cat(req_parts))
         self.logit_rows = self._to_device(np.asarray(rows, dtype=np.int32)) if rows else None
         self.block_tables: Dict[int, torch.Tensor] = {}
         self.slots: Optional[torch.Tensor] = None
@@ -71,11 +73,12 @@ class StepBatch:
         (request, first row, number of rows)."""
         hit = self._qblk.get(bq)
         if hit is None:
-            blocks = []
+            parts = []
             for i, (r0, n) in enumerate(zip(self.row_start, self.lens)):
-                for b in range(0, n, bq):
-                    blocks.append((i, r0 + b, min(bq, n - b)))
-            arr = np.asarray(blocks, dtype=np.int32).reshape(-1, 3)
-            hit = (self._to_device(arr), len(blocks))
+                first = np.arange(0, n, bq, dtype=np.int32)
+                parts.append(np.stack([np.full(first.size, i, dtype=np.int32), r0 + first,
+                                       np.minimum(bq, n - first).astype(np.int32)], axis=1))
+            arr = np.concatenate(parts).reshape(-1, 3) if parts else np.zeros((0, 3), dtype=np.int32)
+            hit = (self._to_device(arr), int(arr.shape[0]))
             self._qblk[bq] = hit
         return hit
