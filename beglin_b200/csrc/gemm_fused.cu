@@ -47,9 +47,13 @@ struct FusedParams {
     unsigned* status;
 };
 
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+// (nothing that this thread wrote has to be visible to the peers at the first use of the barrier)
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    cluster_arrive();
+    cluster_wait();
 }
 // the address, in the cluster's shared window, of this CTA's shared-memory address in the CTA of the given rank
 __device__ __forceinline__ unsigned peer_addr(unsigned local_addr, unsigned rank) {
@@ -90,6 +94,9 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const bool make_x = p.xf != nullptr;
 
     pdl_launch();
+    // The cluster's barrier is used twice.  First: every thread arrives here and waits before anything is stored
+    // into a peer's shared memory, so that every CTA of the cluster is known to be running by then.
+    if (p.splits > 1) cluster_arrive_relaxed();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], make_x ? 5 : 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&acc_bar, 1);
@@ -265,6 +272,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             owner = m_local / rows_per; rl = m_local & (rows_per - 1);
         }
         const int t_real = min(BN, p.T - tile_n * BN);                     // columns beyond it are padding
+        if (S > 1) cluster_wait();                                         // the peers run (first use of the barrier)
         // where token 0 of this row goes: the owner's recv[rank][0][rl] (one token further is rows_per floats on)
         const unsigned dst0 = peer_addr(smem_u32(recv) + (unsigned)(rank * BN * rows_per + rl) * 4u, (unsigned)owner);
 #pragma unroll 1
@@ -283,8 +291,12 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         }
         tc_fence_before();
     }
-    if (p.splits > 1) cluster_sync_all();                                  // every rank has what the others sent it
-    else __syncthreads();
+    if (p.splits > 1) {
+        if (warp < 2) cluster_wait();                                      // (these warps' half of the first use)
+        cluster_sync_all();                                                // second: every rank has what the others sent it
+    } else {
+        __syncthreads();
+    }
 
     if (warp >= 2) {
         const int te = threadIdx.x - 64;
