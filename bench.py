@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine at Qwen2.5-1.5B layer sizes, random weights, bf16.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers N]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers N] [--sizes 1.5b]
     python bench.py --impl reference ...      # prints the reference arm's `unavailable` line
 
 A step is one decoding step of `batch` requests, each holding close to `context` positions in the
@@ -30,6 +30,18 @@ CONFIG_1P5B = {
     "intermediate_size": 8960, "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
     "tie_word_embeddings": True, "use_sliding_window": False, "hidden_act": "silu",
     "max_position_embeddings": 32768,
+}
+# Other layer sizes of the same architecture, for measurements beside the default one (--sizes).
+_BIG = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "rope_theta": 1000000.0, "use_sliding_window": False,
+        "hidden_act": "silu", "max_position_embeddings": 32768, "tie_word_embeddings": False, "vocab_size": 152064}
+SIZES = {
+    "1.5b": ("Qwen2.5-1.5B", CONFIG_1P5B),
+    "0.5b": ("Qwen2.5-0.5B", dict(CONFIG_1P5B, num_hidden_layers=24, hidden_size=896, num_attention_heads=14,
+                                  intermediate_size=4864)),
+    "7b": ("Qwen2.5-7B", dict(_BIG, num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+                              intermediate_size=18944, rms_norm_eps=1e-6)),
+    "14b": ("Qwen2.5-14B", dict(_BIG, num_hidden_layers=48, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                                intermediate_size=13824, rms_norm_eps=1e-5)),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
@@ -231,7 +243,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=CONFIG_1P5B["num_hidden_layers"])
+    ap.add_argument("--sizes", default="1.5b", choices=sorted(SIZES), help="layer sizes (default: the baseline record's)")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (default: all)")
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64 and the prefill")
     ap.add_argument("--gemm", default="auto")
     ap.add_argument("--no-fuse", action="store_true", help="norms, residual adds and SwiGLU as kernels of their own")
@@ -253,7 +266,9 @@ def main():
     import torch
     from beglin_b200 import Engine
     pk = peaks()
-    cfg = dict(CONFIG_1P5B, num_hidden_layers=args.layers)
+    model_name, full = SIZES[args.sizes]
+    args.layers = args.layers or full["num_hidden_layers"]
+    cfg = dict(full, num_hidden_layers=args.layers)
     max_batch = args.batch if args.no_points else max(args.batch, 64)
     page = 64
     eng = Engine.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=max_batch * args.context,
@@ -275,14 +290,14 @@ def main():
     step_bytes = weight_bytes + args.batch * ctx_mid * kvb
     achieved = step_bytes / (ms * 1e-3) / 1e9
     out = {
-        "metric": "decode tok/s @ batch 8; Qwen2.5-1.5B bf16", "value": round(value, 1), "unit": "tok/s",
+        "metric": f"decode tok/s @ batch {args.batch}; {model_name} bf16", "value": round(value, 1), "unit": "tok/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (seeded uniform token ids, random weights)",
-        "config": {"model": "Qwen2.5-1.5B sizes", "layers": args.layers, "layers_of_config": CONFIG_1P5B["num_hidden_layers"],
+        "config": {"model": f"{model_name} sizes", "layers": args.layers, "layers_of_config": full["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"],
-                   "vocab": cfg["vocab_size"], "tied_head": True, "global_batch": args.batch, "seq_len": args.context,
+                   "vocab": cfg["vocab_size"], "tied_head": bool(cfg["tie_word_embeddings"]), "global_batch": args.batch, "seq_len": args.context,
                    "page_size": page, "parallelism": "single GPU", "weights": "random, seeded",
                    "l2": "inputs larger than L2 (weights and cache read once per step)",
                    "peaks": pk["source"]},
