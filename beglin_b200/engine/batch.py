@@ -21,10 +21,22 @@ class Entry:
     tokens: Sequence[int]
     want: Sequence[int] = ()
 
+    def ids(self) -> np.ndarray:
+        """The tokens as an int64 array, converted once."""
+        a = self.__dict__.get("_ids")
+        if a is None:
+            a = self.__dict__["_ids"] = np.asarray(self.tokens, dtype=np.int64).reshape(-1)
+        return a
+
+
+ALIGN = 32      # every array of a step starts on a multiple of this many int32 values (128 bytes) of the one buffer
+
 
 class StepBatch:
     def __init__(self, entries: Sequence[Entry], starts: Sequence[int], device, cache=None):
-        """`starts[i]` is the position of the first token of entry i (the request's length so far)."""
+        """`starts[i]` is the position of the first token of entry i (the request's length so far).
+        All the step's integer arrays are laid out in ONE host buffer and go to the device in one copy;
+        the device arrays are views of it."""
         self.entries = list(entries)
         self.device = torch.device(device)
         self.n_req = len(self.entries)
@@ -35,7 +47,7 @@ class StepBatch:
         n_rows = 0
         for i, (e, s, n) in enumerate(zip(self.entries, self.starts, self.lens)):
             self.row_start.append(n_rows)
-            t64 = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+            t64 = e.ids()
             if t64.size and (t64.min() < 0 or t64.max() > 0x7fffffff):
                 t64 = np.where((t64 < 0) | (t64 > 0x7fffffff), -1, t64)      # the embedding kernel reports these
             ids_parts.append(t64.astype(np.int32))
@@ -48,19 +60,33 @@ class StepBatch:
         self.max_position = max((s + n - 1 for s, n in zip(self.starts, self.lens) if n > 0), default=0)
         self.decode_only = all(n == 1 for n in self.lens)      # every request brings a single token
         self.n_logit_rows = len(rows)
-        self.token_ids = self._to_device(cat(ids_parts))
-        self.positions = self._to_device(cat(pos_parts))
-        self.row_req = self._to_device(cat(req_parts))
-        self.logit_rows = self._to_device(np.asarray(rows, dtype=np.int32)) if rows else None
-        self.block_tables: Dict[int, torch.Tensor] = {}
-        self.slots: Optional[torch.Tensor] = None
+        arrays = {"token_ids": cat(ids_parts), "positions": cat(pos_parts), "row_req": cat(req_parts)}
+        if rows:
+            arrays["logit_rows"] = np.asarray(rows, dtype=np.int32)
         if cache is not None:
             rids = [e.rid for e in self.entries]
             for gi in range(len(cache.kv_groups)):
-                self.block_tables[gi] = self._to_device(cache.block_table(gi, rids))
-            self.slots = self._to_device(cache.slot_ids(rids))
+                arrays[("block_table", gi)] = cache.block_table(gi, rids)
+            arrays["slots"] = cache.slot_ids(rids)
+        dev = self._to_device_packed(arrays)
+        self.token_ids, self.positions, self.row_req = dev["token_ids"], dev["positions"], dev["row_req"]
+        self.logit_rows = dev.get("logit_rows")
+        self.block_tables: Dict[int, torch.Tensor] = {k[1]: v for k, v in dev.items() if isinstance(k, tuple)}
+        self.slots: Optional[torch.Tensor] = dev.get("slots")
         self.scratch: Dict[object, object] = {}       # per-step tables made by parts (rotary tables)
         self._qblk: Dict[int, Tuple[torch.Tensor, int]] = {}
+
+    def _to_device_packed(self, arrays: Dict[object, np.ndarray]) -> Dict[object, torch.Tensor]:
+        """int32 arrays -> device tensors of the same shapes, through one buffer and one copy."""
+        offsets, total = {}, 0
+        for k, a in arrays.items():
+            offsets[k] = total
+            total += -(-a.size // ALIGN) * ALIGN
+        host = np.zeros(max(total, ALIGN), dtype=np.int32)
+        for k, a in arrays.items():
+            host[offsets[k]:offsets[k] + a.size] = np.asarray(a, dtype=np.int32).reshape(-1)
+        buf = self._to_device(host)
+        return {k: buf[offsets[k]:offsets[k] + a.size].view(a.shape) for k, a in arrays.items()}
 
     def _to_device(self, a: np.ndarray) -> torch.Tensor:
         t = torch.from_numpy(np.ascontiguousarray(a))

@@ -112,9 +112,10 @@ class Engine:
             seen.add(e.rid)
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.rid!r} brings no tokens")
-            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab]
-            if bad:
-                raise ValueError(f"request {e.rid!r}: token id {bad[0]} is outside the vocabulary [0, {self.vocab})")
+            ids = e.ids()
+            if ids.min() < 0 or ids.max() >= self.vocab:
+                bad = int(ids[(ids < 0) | (ids >= self.vocab)][0])
+                raise ValueError(f"request {e.rid!r}: token id {bad} is outside the vocabulary [0, {self.vocab})")
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise ValueError(f"request {e.rid!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
