@@ -201,6 +201,35 @@ __global__ void swiglu_kernel(const TI* __restrict__ gu, int parts, size_t part_
     out[idx] = from_float<TO>(silu_mul<TO>(g, u));
 }
 
+// Float partial sums, im and block multiples of 4: four features per thread, 16-byte loads, the parts added in
+// index order as above.
+template <typename TO>
+__global__ void swiglu_parts_vec4_kernel(const float* __restrict__ gu, int parts, size_t part_stride, TO* __restrict__ out,
+                                         int rows, int im, int block) {
+    pdl_launch();
+    pdl_wait();
+    const int im4 = im >> 2;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * im4) return;
+    size_t t = idx / im4;
+    const int i = 4 * (int)(idx - t * im4);
+    const int col = block > 0 ? (i / block) * 2 * block + i % block : i;
+    const float4* gp = reinterpret_cast<const float4*>(gu + t * 2 * (size_t)im + col);
+    const float4 g = sum_parts4(gp, parts, part_stride / 4);
+    const float4 u = sum_parts4(gp + (block > 0 ? block : im) / 4, parts, part_stride / 4);
+    const float r[4] = {silu_mul<TO>(g.x, u.x), silu_mul<TO>(g.y, u.y), silu_mul<TO>(g.z, u.z), silu_mul<TO>(g.w, u.w)};
+    TO* o = out + t * (size_t)im + i;
+    if constexpr (std::is_same<TO, float>::value) {
+        *reinterpret_cast<float4*>(o) = make_float4(r[0], r[1], r[2], r[3]);
+    } else {
+        uint2 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+        h[0] = __floats2bfloat162_rn(r[0], r[1]);
+        h[1] = __floats2bfloat162_rn(r[2], r[3]);
+        *reinterpret_cast<uint2*>(o) = raw;
+    }
+}
+
 // One tensor (no partial sums), im a multiple of 8: eight features per thread, 16-byte accesses.
 template <typename TI, typename TO>
 __global__ void swiglu_vec8_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int rows, int im, int block) {
@@ -516,6 +545,12 @@ static int swiglu_in(const void* gu, int parts, size_t part_stride, void* out, i
         unsigned blocks = (unsigned)((total + 255) / 256);
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_vec8_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream,
             (const TI*)gu, (TO*)out, rows, im, block));
+    } else if (std::is_same<TI, float>::value && (im % 4 == 0) && (block % 4 == 0) && (part_stride % 4 == 0) &&
+               ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
+        size_t total = (size_t)rows * (im / 4);
+        unsigned blocks = (unsigned)((total + 255) / 256);
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_parts_vec4_kernel<TO>, dim3(blocks), dim3(256), 0, stream,
+            (const float*)gu, parts, part_stride, (TO*)out, rows, im, block));
     } else {
         size_t total = (size_t)rows * im;
         unsigned blocks = (unsigned)((total + 255) / 256);
