@@ -262,6 +262,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.steps + args.warmup + 2 > args.context:          # every timed step decodes one more position
+        args.context = args.steps + args.warmup + 64
 
     import torch
     from beglin_b200 import Engine
