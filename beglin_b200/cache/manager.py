@@ -189,22 +189,27 @@ class CacheManager:
         """(page indexes to give back, number of page indexes to add) for one group."""
         table = g.tables[rid]
         first = g.first_needed_page(first_query_pos, self.page_size)
-        drop = [i for i in range(min(first, len(table))) if table[i] >= 0]
+        drop = [i for i in range(min(first, len(table))) if table[i] >= 0] if first > 0 else ()
         want_pages = -(-new_len // self.page_size)
         add = max(0, want_pages - len(table))
         return drop, add
 
+    def _plans(self, plan: Sequence[tuple]):
+        """For every group, the (give back, add) of every entry of the plan."""
+        return [[self._plan(g, rid, new_len, self.lengths[rid]) for rid, new_len in plan] for g in self.kv_groups]
+
+    @staticmethod
+    def _short(groups, plans) -> int:
+        short = 0
+        for g, per_request in zip(groups, plans):
+            need = sum(add - len(drop) for drop, add in per_request)
+            short = max(short, need - g.pool.num_free)
+        return max(0, short)
+
     def pages_short(self, plan: Sequence[tuple]) -> int:
         """How many pages the fullest pool lacks for `plan` = [(request, new length), ...], counting
         what the plan itself gives back.  0 means the plan fits."""
-        short = 0
-        for g in self.kv_groups:
-            need = 0
-            for rid, new_len in plan:
-                drop, add = self._plan(g, rid, new_len, self.lengths[rid])
-                need += add - len(drop)
-            short = max(short, need - g.pool.num_free)
-        return max(0, short)
+        return self._short(self.kv_groups, self._plans(plan))
 
     def reserve(self, plan: Sequence[tuple]) -> None:
         """Make room for every (request, new length) of a step, or raise OutOfPages and change
@@ -218,19 +223,20 @@ class CacheManager:
                                  f"limit {self.max_context}")
             if new_len < self.lengths[rid]:
                 raise CacheError(f"request {rid!r} cannot shrink from {self.lengths[rid]} to {new_len}")
-        short = self.pages_short(plan)
+        plans = self._plans(plan)
+        short = self._short(self.kv_groups, plans)
         if short:
             raise OutOfPages(f"the step needs {short} more pages than are free")
-        for g in self.kv_groups:
-            for rid, new_len in plan:
-                drop, add = self._plan(g, rid, new_len, self.lengths[rid])
-                table = g.tables[rid]
-                g.pool.free([table[i] for i in drop])
-                for i in drop:
-                    table[i] = -1
-            for rid, new_len in plan:
-                _, add = self._plan(g, rid, new_len, self.lengths[rid])
-                g.tables[rid].extend(g.pool.alloc(add))
+        for g, per_request in zip(self.kv_groups, plans):
+            for (rid, _), (drop, _) in zip(plan, per_request):      # first everything that is given back,
+                if drop:
+                    table = g.tables[rid]
+                    g.pool.free([table[i] for i in drop])
+                    for i in drop:
+                        table[i] = -1
+            for (rid, _), (_, add) in zip(plan, per_request):       # then what is added (a table's length does not change above)
+                if add:
+                    g.tables[rid].extend(g.pool.alloc(add))
 
     def commit(self, plan: Sequence[tuple]) -> None:
         """Record the new lengths after the step has run."""
