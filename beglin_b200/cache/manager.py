@@ -196,7 +196,14 @@ class CacheManager:
 
     def _plans(self, plan: Sequence[tuple]):
         """For every group, the (give back, add) of every entry of the plan."""
-        return [[self._plan(g, rid, new_len, self.lengths[rid]) for rid, new_len in plan] for g in self.kv_groups]
+        out, ps = [], self.page_size
+        for g in self.kv_groups:
+            if g.need.window is None:          # nothing is ever given back before the request ends
+                tables = g.tables
+                out.append([((), max(0, -(-new_len // ps) - len(tables[rid]))) for rid, new_len in plan])
+            else:
+                out.append([self._plan(g, rid, new_len, self.lengths[rid]) for rid, new_len in plan])
+        return out
 
     @staticmethod
     def _short(groups, plans) -> int:
