@@ -27,6 +27,7 @@
 namespace bg {
 
 constexpr int GF_PLAIN = 0, GF_RESIDUAL = 1, GF_SWIGLU = 2;
+constexpr int SSQ_AHEAD = 24;        // partial sums of squares that a thread of the norm prologue asks for at a time
 
 struct FusedParams {
     // the operand made from the residual stream (xf == null: X comes by TMA)
@@ -174,16 +175,18 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 #pragma unroll
             for (int j = 0; j < CHUNKS; ++j) {
                 // the eight threads of a token share the parts of its sum of squares: thread c8 adds parts c8,
-                // c8 + 8, ... (four loads on their way at a time), then the eight sums meet in a fixed order
+                // c8 + 8, ... (SSQ_AHEAD loads on their way at a time: the parts that a product over 16 ranges of K and
+                // 12 tiles leaves come in one trip to L2), then the eight sums meet in a fixed order
                 const int t = tile_n * BN + (te + j * 128) / 8;
                 float ssq = 0.0f;
                 if (t < p.T) {
-                    for (int q = c8; q < p.n_ssq_in; q += 32) {
-                        float a[4];
+                    for (int q = c8; q < p.n_ssq_in; q += 8 * SSQ_AHEAD) {
+                        float a[SSQ_AHEAD];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u)
+                        for (int u = 0; u < SSQ_AHEAD; ++u)
                             a[u] = q + 8 * u < p.n_ssq_in ? p.ssq_in[(size_t)(q + 8 * u) * p.ssq_in_stride + t] : 0.0f;
-                        ssq += (a[0] + a[1]) + (a[2] + a[3]);
+#pragma unroll
+                        for (int u = 0; u < SSQ_AHEAD; u += 4) ssq += (a[u] + a[u + 1]) + (a[u + 2] + a[u + 3]);
                     }
                 }
                 ssq += __shfl_xor_sync(0xffffffffu, ssq, 1);
