@@ -275,7 +275,7 @@ TC_ROWS_FOR = ("auto", "tcgen05")
 
 
 def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, decode_only: bool = False,
-                   prefer: str = "auto", page_size: int = 16) -> Tuple[str, int, int]:
+                   prefer: str = "auto", page_size: int = 64) -> Tuple[str, int, int]:
     """(kernel, rows per query block, keys per tile) for these sizes.  Kernels: "mma_keys" (tensor
     cores, one token per block, for steps of single tokens), "mma_rows" (tensor cores, up to 64 rows
     per block) and "generic" (CUDA cores, every size up to head_dim 256, float or bfloat16)."""
