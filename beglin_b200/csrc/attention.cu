@@ -190,10 +190,12 @@ attention_partial_kernel(AttnParams p) {
 }
 
 // out[t, h, :] = sum_s o_s * exp(m_s - m) / sum_s l_s * exp(m_s - m), over the splits the row sees,
-// in split order.  One warp per (row, head): the lanes first take one split each to find the maximum
-// and the weights (so these loads are in flight together), then every lane sums its output features
-// over the splits.
-template <typename TO>
+// in split order.  One warp per (row, head): the lanes first take one split each (of up to 32 * MERGE_GROUPS
+// at once) to find the maximum and the weights, so these loads are in flight together and are made once; then
+// every lane sums its output features over the splits, BATCH splits' loads on their way at a time.  DPL is the
+// number of output features per lane (head_dim <= 32 DPL).
+constexpr int MERGE_GROUPS = 4;
+template <typename TO, int DPL, int BATCH>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
                                        int T, int nh, int hd, int max_splits, int split_arg, int window) {
@@ -208,43 +210,57 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int s_lo = lo / split, s_hi = pos / split;
     const size_t prow = (size_t)w * max_splits;
-    float m = -INFINITY;
-    for (int s = s_lo + lane; s <= s_hi; s += 32) m = fmaxf(m, part_ml[(prow + s) * 2]);
-    m = warp_max(m);
-    float acc[ATT_MAX_DPL];
+    // the maxima and sums of the first 32 * MERGE_GROUPS splits of the row: lane j holds split s_lo + 32 g + j
+    float ms_r[MERGE_GROUPS], ls_r[MERGE_GROUPS];
 #pragma unroll
-    for (int i = 0; i < ATT_MAX_DPL; ++i) acc[i] = 0.0f;
+    for (int g = 0; g < MERGE_GROUPS; ++g) {
+        const int sidx = s_lo + 32 * g + lane;
+        const float2 ml = sidx <= s_hi ? *reinterpret_cast<const float2*>(part_ml + (prow + sidx) * 2) : make_float2(-INFINITY, 0.0f);
+        ms_r[g] = ml.x; ls_r[g] = ml.y;
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int g = 0; g < MERGE_GROUPS; ++g) m = fmaxf(m, ms_r[g]);
+    for (int sidx = s_lo + 32 * MERGE_GROUPS + lane; sidx <= s_hi; sidx += 32) m = fmaxf(m, part_ml[(prow + sidx) * 2]);
+    m = warp_max(m);
+    float acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
     float l = 0.0f;
-    for (int s0 = s_lo; s0 <= s_hi; s0 += 32) {
+    int grp = 0;
+    for (int s0 = s_lo; s0 <= s_hi; s0 += 32, ++grp) {
         // this lane's split of the group of 32: its weight and its share of the sum
         const int mine = s0 + lane;
-        float f_mine = 0.0f, l_mine = 0.0f;
-        if (mine <= s_hi) {
-            const float ms = part_ml[(prow + mine) * 2];
-            f_mine = (ms == -INFINITY) ? 0.0f : expf(ms - m);
+        float ms = -INFINITY, l_mine = 0.0f;
+        if (grp < MERGE_GROUPS) {
+#pragma unroll
+            for (int g = 0; g < MERGE_GROUPS; ++g) if (g == grp) { ms = ms_r[g]; l_mine = ls_r[g]; }
+        } else if (mine <= s_hi) {
+            ms = part_ml[(prow + mine) * 2];
             l_mine = part_ml[(prow + mine) * 2 + 1];
         }
+        const float f_mine = (ms == -INFINITY) ? 0.0f : expf(ms - m);
         const int n = min(32, s_hi - s0 + 1);
-        for (int j0 = 0; j0 < n; j0 += 4) {
-            // the loads of four splits go out together, then they are added in split order
-            float v[4][ATT_MAX_DPL];
+        for (int j0 = 0; j0 < n; j0 += BATCH) {
+            // the loads of BATCH splits go out together, then they are added in split order
+            float v[BATCH][DPL];
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
+            for (int jj = 0; jj < BATCH; ++jj) {
                 const float* po = part_o + (prow + s0 + j0 + jj) * hd;
 #pragma unroll
-                for (int i = 0; i < ATT_MAX_DPL; ++i) {
+                for (int i = 0; i < DPL; ++i) {
                     int d = i * 32 + lane;
                     v[jj][i] = (j0 + jj < n && d < hd) ? po[d] : 0.0f;
                 }
             }
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
+            for (int jj = 0; jj < BATCH; ++jj) {
                 const float f = __shfl_sync(0xffffffffu, f_mine, (j0 + jj) & 31);
                 const float lj = __shfl_sync(0xffffffffu, l_mine, (j0 + jj) & 31);
                 if (j0 + jj < n) {
                     l = fmaf(lj, f, l);
 #pragma unroll
-                    for (int i = 0; i < ATT_MAX_DPL; ++i) acc[i] = fmaf(v[jj][i], f, acc[i]);
+                    for (int i = 0; i < DPL; ++i) acc[i] = fmaf(v[jj][i], f, acc[i]);
                 }
             }
         }
@@ -252,7 +268,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
     const float inv = 1.0f / l;
     TO* o = out + (size_t)t * out_stride + (size_t)h * hd;
 #pragma unroll
-    for (int i = 0; i < ATT_MAX_DPL; ++i) {
+    for (int i = 0; i < DPL; ++i) {
         int d = i * 32 + lane;
         if (d < hd) o[d] = from_float<TO>(acc[i] * inv);
     }
@@ -381,8 +397,11 @@ extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, con
     } else if (max_splits <= 16 && hd <= 128) {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 16>, dim3(blocks), dim3(256), 0, stream,
             part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
+    } else if (hd <= 128) {
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_kernel<TO, 4, 16>, dim3(blocks), dim3(256), 0, stream,
+            part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
     } else {
-        BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_kernel<TO>, dim3(blocks), dim3(256), 0, stream,
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_kernel<TO, ATT_MAX_DPL, 4>, dim3(blocks), dim3(256), 0, stream,
             part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
     }
     BG_LAUNCH_CHECK();

@@ -211,7 +211,7 @@ def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64, prefe
     if decode_only:
         ctx = [(37, 1), (150, 1), (0, 1), (63, 1), (64, 1), (127, 1), (200, 1)]
     if long:                                         # many key tiles: every pipeline stage is reused several times
-        ctx = [(517, 90), (1000, 1), (0, 333)] if not decode_only else [(517, 1), (1000, 1), (0, 1), (2100, 1)]
+        ctx = [(517, 90), (1000, 1), (0, 333)] if not decode_only else [(517, 1), (1000, 1), (0, 1), (2100, 1), (4400, 1)]
     total = [c + n for c, n in ctx]
     n_pages_each = [-(-t // page) for t in total]
     n_pages = sum(n_pages_each) + 5
@@ -242,6 +242,8 @@ def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64, prefe
     positions, row_req, qblk = [], [], []
     kernel, bq, tile = ops.attention_plan(group, hd, dtype, decode_only, prefer, page)
     assert kernel == {"generic": "generic", "mma": "mma_keys" if decode_only else "mma_rows", "tcgen05": "tc_rows"}[prefer]
+    if kernel == "generic" and split < tile:         # ranges of 32 keys: tiles of 32 (less shared memory than planned)
+        tile = split
     r0 = 0
     for r, (c, n) in enumerate(ctx):
         positions += list(range(c, c + n)); row_req += [r] * n
@@ -483,3 +485,17 @@ def test_gemm_fused_swiglu(ops, T, im, K, splits):
                    status=status)
     ops.raise_on_status(status)
     assert (out.double().cpu() - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("nh,nkv,hd,page,dtype,split", [(4, 2, 64, 16, torch.float32, 32), (6, 2, 128, 64, torch.bfloat16, 32),
+                                                        (2, 1, 256, 32, torch.float32, 32), (3, 1, 32, 8, torch.float32, 64)])
+@pytest.mark.parametrize("decode_only", [False, True])
+def test_attention_merge_of_many_ranges(ops, nh, nkv, hd, page, dtype, split, decode_only):
+    """Keys cut into far more ranges than the one-trip merge takes (up to 138 of 32 keys): the general merge,
+    whose lanes hold the first 128 ranges' maxima and read the rest again."""
+    got, want = _attention_case(ops, nh, nkv, hd, page, dtype, None, seed=hd + split, split=split, prefer="generic",
+                                decode_only=decode_only, long=True)
+    assert torch.isfinite(got).all()
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert (got - want).abs().max() < tol * max(1.0, float(want.abs().max()))
