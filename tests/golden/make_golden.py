@@ -87,7 +87,9 @@ def case_folder(root: str, name: str, seed: int, dtype: str) -> str:
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path of the reference tree>")
+    ref = sys.argv[1]
     with tempfile.TemporaryDirectory() as tmp:
         tools = build_tools(ref, tmp)
         for name, seed, dtype in CASES:

@@ -1,8 +1,8 @@
 """This framework's readers and the plain implementation against outputs of the reference's own C
 code (no GPU): the fields hf_config.c reads from config.json, the per-tensor checksums of
 safetensors_load.c + safetensors_quants.c, and the frequency ratios of rope_llama3_scale.h.  The
-golden files were made by tests/golden/make_golden.py; where the reference tree and gcc are present
-the programs are also compiled and run afresh."""
+golden files were made by tests/golden/make_golden.py; where the variable BEGLIN_REFERENCE names the
+reference tree and gcc is present, the programs are also compiled and run afresh."""
 import json
 import os
 import shutil
@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 import make_golden as mg  # noqa: E402
 
-REF = os.environ.get("BEGLIN_REFERENCE", "/root/reference")
+REF = os.environ.get("BEGLIN_REFERENCE", "")           # the reference tree, when the caller has one
 
 
 def golden(kind, name):
