@@ -492,7 +492,10 @@ static int add_rmsnorm_launch(float* x, const void* delta, int parts, size_t par
     } else if (vec) {
         auto kern = add_rmsnorm_vec8_kernel<TD, TW, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        int threads = d / 8 >= 512 ? 512 : (d / 8 >= 256 ? 256 : (d / 8 >= 128 ? 128 : 64));
+        // as few trips through a row as 512 threads allow, and no thread without a chunk in the last trip
+        const int d8 = d / 8, trips = (d8 + 511) / 512;
+        int threads = (((d8 + trips - 1) / trips) + 31) / 32 * 32;
+        if (threads < 64) threads = 64;
         launch(kern, dim3(n_rows), dim3(threads), smem, stream, x, (const TD*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out,
                                                 rows, d, update);
     } else {

@@ -218,6 +218,43 @@ def print_timeline(rows, layers):
         print(f"  {name[:40]:40s} x{n:<4d} {t:8.1f} us  ({t / n:5.1f} us each)")
 
 
+def prefill_timeline(eng, T, seed):
+    """The kernels of ONE prompt step of T tokens as the device ran them: (name, start, end) in microseconds
+    from the step's first kernel, library kernels included."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, eng.vocab, (T,), generator=g).tolist()
+    for _ in range(3):
+        eng.step([("timeline", ids, [T - 1])], end=["timeline"], check=False)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        eng.step([("timeline", ids, [T - 1])], end=["timeline"], check=False)
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+          and "memcpy" not in e.name.lower() and "memset" not in e.name.lower()]
+    ev.sort(key=lambda e: e.time_range.start)
+    t0 = ev[0].time_range.start
+
+    def short(name):
+        return name.replace("void bg::", "").replace("bg::", "").split("<")[0].split("(")[0]
+    return [(short(e.name), e.time_range.start - t0, e.time_range.end - t0) for e in ev]
+
+
+def print_busy(rows):
+    """Per kind of kernel the time it ran (not what it adds), and the time in which the device ran nothing."""
+    busy, idle, prev = {}, 0.0, 0.0
+    for name, s, e in rows:
+        b = busy.setdefault(name, [0, 0.0])
+        b[0] += 1
+        b[1] += e - s
+        idle += max(0.0, s - prev)
+        prev = max(prev, e)
+    print(f"the device ran nothing for {idle:.1f} us of the step; time each kind of kernel ran:")
+    for name, (n, t) in sorted(busy.items(), key=lambda kv: -kv[1][1]):
+        print(f"  {name[:40]:40s} x{n:<4d} {t:8.1f} us  ({t / n:6.1f} us each)")
+
+
 def time_prefill(eng, T, reps, seed):
     import torch
     g = torch.Generator().manual_seed(seed)
@@ -248,8 +285,9 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64 and the prefill")
     ap.add_argument("--gemm", default="auto")
     ap.add_argument("--no-fuse", action="store_true", help="norms, residual adds and SwiGLU as kernels of their own")
-    ap.add_argument("--timeline", action="store_true",
-                    help="instead of the measurement: print the kernels of one decode step with their device times")
+    ap.add_argument("--timeline", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
+                    help="instead of the measurement: print the kernels of one decode step (or of one prompt step of "
+                         "2,048 tokens) with their device times")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -275,6 +313,11 @@ def main():
     page = 64
     eng = Engine.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=max_batch * args.context,
                         page_size=page, max_requests=max_batch, max_context=args.context, gemm=args.gemm, fuse=not args.no_fuse)
+    if args.timeline == "prefill":
+        rows = prefill_timeline(eng, 2048, seed=3)
+        print_timeline(rows, args.layers)
+        print_busy(rows)
+        return 0
     if args.timeline:
         print_timeline(decode_timeline(eng, args.batch, args.context, seed=1), args.layers)
         return 0
