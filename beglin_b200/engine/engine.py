@@ -22,6 +22,7 @@ from ..sampling.sampler import Sampler, uniform
 from ..weights import Checkpoint, TensorDict, bind, random_tensors
 from .batch import Entry, StepBatch
 from .model import DecoderModel
+from .portion_graph import PortionGraphs
 from .scheduler import Request, Scheduler
 
 _DTYPES = {"float32": torch.float32, "fp32": torch.float32, "f32": torch.float32,
@@ -52,9 +53,11 @@ class Engine:
     def __init__(self, spec, tensors, *, dtype="bfloat16", device="cuda:0", max_tokens: int = 8192,
                  page_size: int = 64, max_requests: int = 8, max_context: Optional[int] = None,
                  kv_split: int = 256, gemm: str = "auto", attention: str = "auto", fuse: bool = True,
-                 use_graphs: bool = True, config=None, origin: str = ""):
+                 use_graphs: bool = True, portion_graph_rows: int = 256, config=None, origin: str = ""):
         """`tensors` is anything with names()/shape(name)/tensor(name): a Checkpoint or a TensorDict.
-        `max_tokens` sizes the page pool: it holds that many positions (rounded up to whole pages)."""
+        `max_tokens` sizes the page pool: it holds that many positions (rounded up to whole pages).
+        With `use_graphs`, decoding steps and portions of one request of at least `portion_graph_rows`
+        tokens whose shape comes again are replayed as CUDA graphs."""
         self.device = require_gpu(device)
         self.dtype = parse_dtype(dtype)
         self.spec, self.config = spec, config
@@ -74,6 +77,7 @@ class Engine:
         self.vocab = spec.vocab
         self.use_graphs = use_graphs
         self._graphs = {}
+        self.portions = PortionGraphs(self, min_rows=portion_graph_rows)
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -145,8 +149,13 @@ class Engine:
         record the new lengths."""
         with torch.cuda.device(self.device):
             starts = [self.cache.length(e.rid) for e in ents]
-            batch = StepBatch(ents, starts, self.device, self.cache)
-            logits = self.model.forward(batch, self.cache)
+            key = self.portions.key_of(ents, starts) if self.use_graphs else None
+            graph = self.portions.get(key) if key is not None else None
+            if graph is not None:              # a portion of one request in a shape that came before
+                logits = self.portions.step(graph, ents[0], starts[0])
+            else:
+                batch = StepBatch(ents, starts, self.device, self.cache)
+                logits = self.model.forward(batch, self.cache)
         self.cache.commit(plan)
         return logits
 
