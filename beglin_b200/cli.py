@@ -13,7 +13,7 @@ and model.safetensors), QWEN_PROMPT (file of little-endian int32 token ids; defa
 (live requests, default 8), QWEN_CB_REQS (default 12), QWEN_CB_REPS (default 3),
 QWEN_CB_PREFILL_BUDGET (prompt tokens per step, default 16), QWEN_CB_STOP_EXTRA (an extra stop id).
 Added: QWEN_DTYPE (bf16 | fp32, default bf16), QWEN_TEMPERATURE and QWEN_SEED (sampling),
-QWEN_PAGE_SIZE (default 16), QWEN_NUM_PAGES, QWEN_RANDOM (a seed: write random weights for
+QWEN_PAGE_SIZE (default 64), QWEN_NUM_PAGES, QWEN_RANDOM (a seed: write random weights for
 <QWEN_BASE>/config.json first, if the folder has no model.safetensors), QWEN_DUMP_DIR.
 """
 from __future__ import annotations

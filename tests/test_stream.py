@@ -56,3 +56,38 @@ def test_decode_splits_make_one_wave():
             assert n >= 1 and (streams * n <= 148 or n == 1)
             assert n <= max(1, -(-context // 256))
     assert decode_splits(16, 4096) == 8 and decode_splits(2, 4096) == 16 and decode_splits(128, 4096) == 1
+
+
+def test_which_steps_a_portion_graph_stands_for_and_which_graphs_are_kept():
+    """Host logic of the portion graphs: one request, enough rows, few wanted places; the bound on positions
+    grows in steps; a shape is captured at its second sighting; the graph used least recently goes first."""
+    from types import SimpleNamespace
+    from beglin_b200.engine import portion_graph as pg
+    from beglin_b200.engine.batch import Entry
+
+    engine = SimpleNamespace(cache=SimpleNamespace(max_context=10000))
+    graphs = pg.PortionGraphs(engine, min_rows=16, max_wanted=2, keep=2)
+    e = lambda n, w=(): Entry("r", list(range(n)), list(w))
+    assert graphs.key_of([e(16), e(16)], [0, 0]) is None                    # two requests
+    assert graphs.key_of([e(15)], [0]) is None                              # too few rows
+    assert graphs.key_of([e(16, (0, 1, 2))], [0]) is None                   # too many wanted places
+    assert graphs.key_of([e(16, (15,))], [0]) == (16, 1, 4095)
+    assert graphs.key_of([e(16)], [4080]) == (16, 0, 4095)                  # the last position is 4095
+    assert graphs.key_of([e(16)], [4081]) == (16, 0, 8191)
+    assert graphs.key_of([e(16)], [9000]) == (16, 0, 9999)                  # never beyond the context limit
+
+    made = []
+    pg_class, pg.PortionGraph = pg.PortionGraph, lambda eng, *key: made.append(key) or ("graph", key)
+    try:
+        a, b, c = (16, 0, 4095), (32, 0, 4095), (48, 1, 4095)
+        assert graphs.get(a) is None and made == []                         # first sighting: no graph yet
+        assert graphs.get(a) == ("graph", a) and made == [a]
+        assert graphs.get(a) == ("graph", a) and made == [a]                # kept
+        assert graphs.get(b) is None and graphs.get(b) == ("graph", b)
+        assert graphs.get(a) == ("graph", a)                                # a is now the one used last
+        assert graphs.get(c) is None and graphs.get(c) == ("graph", c)      # b goes
+        assert list(graphs.graphs) == [a, c]
+        assert graphs.get(b) == ("graph", b) and made == [a, b, c, b]       # seen before: made again at once
+        assert list(graphs.graphs) == [c, b]
+    finally:
+        pg.PortionGraph = pg_class
