@@ -586,7 +586,12 @@ static int rope_kv_cache(const void* src, int src_stride, int parts, size_t part
                          const float* cos_sin, const int* positions, const int* row_req, const int* block_table,
                          int max_pages, void* kv_pool, int cache_dtype, int num_pages, int page_size, int T, int nh,
                          int nkv, int hd, int rot, int interleaved, unsigned* status, cudaStream_t stream) {
-    if (T <= 64 && hd <= 1024) {
+    // one block per token stages the token's whole q/k/v row in shared memory; a row that does not fit there
+    // (many wide heads in float) goes head by head, like the steps of few tokens
+    const size_t smem = (size_t)(nh + 2 * nkv) * hd * sizeof(float);
+    const bool row_fits = smem <= 200 * 1024;
+    if (!row_fits && hd > 1024) return BG_ERR_SHAPE;
+    if ((T <= 64 || !row_fits) && hd <= 1024) {
         dim3 grid(T, nh + (kv_pool ? 2 * nkv : 0));
         BG_DISPATCH_DTYPE(cache_dtype, TC, launch(rope_kv_append_heads_kernel<TS, TQ, TC>, grid, dim3((hd + 31) / 32 * 32), 0,
             stream, (const TS*)src, src_stride, parts, part_stride, (TQ*)q_out, q_stride, (const float2*)cos_sin, positions,
@@ -594,8 +599,10 @@ static int rope_kv_cache(const void* src, int src_stride, int parts, size_t part
         BG_LAUNCH_CHECK();
         return BG_OK;
     }
-    const size_t smem = (size_t)(nh + 2 * nkv) * hd * sizeof(float);
-    if (smem > 48 * 1024) return BG_ERR_SHAPE;
+    if (smem > 48 * 1024) {
+        BG_DISPATCH_DTYPE(cache_dtype, TC, cudaFuncSetAttribute(rope_kv_append_kernel<TS, TQ, TC>,
+            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
     BG_DISPATCH_DTYPE(cache_dtype, TC, launch(rope_kv_append_kernel<TS, TQ, TC>, dim3(T), dim3(256), smem, stream,
         (const TS*)src, src_stride, parts, part_stride, (TQ*)q_out, q_stride, (const float2*)cos_sin, positions, row_req,
         block_table, max_pages, (TC*)kv_pool, num_pages, page_size, nh, nkv, hd, rot, interleaved, status));

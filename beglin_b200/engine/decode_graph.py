@@ -20,6 +20,7 @@ import torch
 
 from ..cache.manager import CacheError, OutOfPages
 from ..csrc import ops
+from .capture import no_collection
 
 
 class _StaticBatch:
@@ -123,7 +124,7 @@ class DecodeGraph:
         torch.cuda.synchronize()
         before = ops.launch_count()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        with no_collection(), torch.cuda.graph(g):
             body()
         self.launches = ops.launch_count() - before
         if fed:

@@ -23,6 +23,7 @@ import torch
 
 from ..csrc import ops
 from .batch import ALIGN
+from .capture import no_collection
 
 
 class _StaticPortion:
@@ -93,7 +94,7 @@ class PortionGraph:
         torch.cuda.synchronize()
         before = ops.launch_count()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        with no_collection(), torch.cuda.graph(g):
             self._body()
         self.launches = ops.launch_count() - before
         self.graph = g

@@ -200,6 +200,45 @@ def test_rope_table_and_kv_append(ops, interleaved, dtype, hd, rot):
         ops.raise_on_status(status)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("nh,nkv,hd,dtype", [(5, 1, 48, torch.float32), (48, 3, 256, torch.float32), (64, 4, 256, torch.float32),
+                                             (200, 4, 256, torch.float32), (12, 2, 128, torch.bfloat16), (48, 3, 256, torch.bfloat16)])
+def test_rope_and_kv_append_of_many_tokens(ops, nh, nkv, hd, dtype):
+    """A portion of 100 tokens (one block per token, its q/k/v row staged in shared memory): rows of up to 48 KB, rows that
+    need the larger shared-memory carve-out (55 and 73 KB) and a row that fits no SM (213 KB: head by head)."""
+    T, page, rot = 100, 16, hd
+    positions = torch.arange(3, 3 + T, dtype=torch.int32, device=DEV)
+    row_req = torch.zeros(T, dtype=torch.int32, device=DEV)
+    inv = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -(2 * torch.arange(rot // 2, dtype=torch.float64)) / rot).float().to(DEV)
+    table = torch.empty((T, rot // 2, 2), device=DEV)
+    ops.rope_table(positions, inv, table)
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=nh)
+    n_pages = 9
+    bt = torch.tensor([[5, 2, 8, 0, 7, 3, 1, -1]], dtype=torch.int32, device=DEV)       # positions 3..102 lie in 7 pages
+    pool = torch.full((n_pages, 2, nkv, page, hd), float("nan"), dtype=dtype, device=DEV)
+    q_out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    status = ops.new_status(DEV)
+    ops.rope_kv_append(qkv, q_out, T, nh, nkv, hd, rot, False, table, positions, row_req, bt, pool, page, status)
+    ops.raise_on_status(status)
+    c, s_ = table[..., 0].double().cpu()[:, None, :], table[..., 1].double().cpu()[:, None, :]
+    o = qkv.double().cpu().reshape(T, nh + 2 * nkv, hd)
+
+    def rotate(v):                                                     # v [T, heads, hd]
+        a, b = v[..., :hd // 2], v[..., hd // 2:]
+        return torch.cat([a * c - b * s_, b * c + a * s_], dim=-1)
+
+    tol = 4e-6 if dtype == torch.float32 else 8e-2
+    assert (q_out.double().cpu().reshape(T, nh, hd) - rotate(o[:, :nh])).abs().max() < tol
+    k, v = rotate(o[:, nh:nh + nkv]), o[:, nh + nkv:]
+    for t in range(T):
+        p_ = 3 + t
+        pg, sl = int(bt[0, p_ // page]), p_ % page
+        assert (pool[pg, 0, :, sl].double().cpu() - k[t]).abs().max() < tol
+        assert (pool[pg, 1, :, sl].double().cpu() - v[t]).abs().max() < tol
+    held = torch.isfinite(pool[:, 0, 0, :, 0].float()).cpu().sum()
+    assert int(held) == T                                              # nothing else was written
+
+
 def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64, prefer="generic", decode_only=False,
                     long=False):
     """Three requests in one step: a long prompt portion on top of earlier context, a decoded token

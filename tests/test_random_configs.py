@@ -60,3 +60,39 @@ def test_random_configuration_mixed_replay(model_root, case):
         assert torch.isfinite(rows).all(), (rid, cfg)
         assert rel_err(rows, plain_logits(folder, ids)) < tol, (rid, cfg, dtype, page)
     eng.cache.check()
+
+
+@pytest.mark.parametrize("case", [1, 3, 7, 12, 270, 526, 537, 565])
+def test_random_configuration_prompts_then_single_tokens(model_root, case):
+    """Several prompts whole in one step, then steps in which every request brings one token: through the step
+    function and through `Engine.decode` (the replayed graph), both against the plain implementation.  Cases 270
+    and 526 have q/k/v rows wider than 48 KB in float32; 537 has an intermediate size that the tcgen05 product
+    does not take (no multiple of 8), so the library product runs inside the graph."""
+    from beglin_b200 import Engine
+    cfg, dtype, page, _, std = random_config(case)
+    rng = random.Random(99 + case)
+    n_req, n_dec = rng.choice([1, 2, 3, 5, 8]), rng.choice([8, 20, 40])
+    prompt = [rng.randint(1, 200) for _ in range(n_req)]
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    tol = TOL_F32 if dtype == "float32" else TOL_BF16
+    folder = make_model(model_root, f"random{case}", seed=case, dtype=stored, config=cfg, std=std, bias_std=0.05)
+    ids = [seeded_ids(p + n_dec, cfg["vocab_size"], 1000 * case + i) for i, p in enumerate(prompt)]
+    want = [plain_logits(folder, x) for x in ids]
+    for through_graph in (False, True):
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=sum(-(-len(x) // 64) * 64 for x in ids),
+                                 page_size=page, max_requests=n_req)
+        rl.poison(eng)
+        out = eng.step([(i, ids[i][:prompt[i]], [prompt[i] - 1]) for i in range(n_req)])
+        for i in range(n_req):
+            assert rel_err(out[i:i + 1], want[i][[prompt[i] - 1]]) < tol, (case, "prompt", i)
+        for k in range(n_dec):
+            tokens = [ids[i][prompt[i] + k] for i in range(n_req)]
+            if through_graph:
+                eng.decode(list(range(n_req)), tokens, read_back=True)
+                out = eng.decode_graph(n_req).logits
+            else:
+                out = eng.step([(i, [tokens[i]], [0]) for i in range(n_req)])
+            assert torch.isfinite(out).all()
+            for i in range(n_req):
+                assert rel_err(out[i:i + 1], want[i][[prompt[i] + k]]) < tol, (case, through_graph, k, i)
+        eng.cache.check()

@@ -91,3 +91,41 @@ def test_which_steps_a_portion_graph_stands_for_and_which_graphs_are_kept():
         assert list(graphs.graphs) == [c, b]
     finally:
         pg.PortionGraph = pg_class
+
+
+def test_no_collection_collects_first_and_keeps_the_collector_off():
+    """A dropped cycle (an engine and its graphs are one) is collected before the block begins, not inside it."""
+    import gc
+    from beglin_b200.engine.capture import no_collection
+
+    freed = []
+
+    class Node:
+        def __del__(self):
+            freed.append(gc.isenabled())
+
+    def cycle():
+        a, b = Node(), Node()
+        a.other, b.other = b, a
+
+    assert gc.isenabled()
+    gc.disable()
+    cycle()                                   # garbage that only the collector can free
+    gc.enable()
+    with no_collection():
+        assert len(freed) == 2                # gone before the block began
+        assert not gc.isenabled()
+        cycle()
+        for _ in range(3):
+            [[] for _ in range(100000)]       # enough allocations to start the collector if it were on
+        assert len(freed) == 2
+    assert gc.isenabled()
+    gc.collect()
+    assert len(freed) == 4
+    gc.disable()
+    try:
+        with no_collection():
+            pass
+        assert not gc.isenabled()             # left as it was found
+    finally:
+        gc.enable()
