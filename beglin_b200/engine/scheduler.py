@@ -18,6 +18,7 @@ Pure host code: it talks to the cache manager's accounting and is tested without
 """
 from __future__ import annotations
 
+import time
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, Hashable, List, Optional, Sequence, Set, Tuple
@@ -42,6 +43,7 @@ class Request:
     finish_reason: Optional[str] = None
     admitted_at: int = -1
     preemptions: int = 0
+    last_token_at: Optional[float] = None     # when the step that gave its newest token was recorded
 
 
 @dataclass
@@ -63,11 +65,24 @@ class Counters:
     decode_rows: int = 0
     prefill_rows: int = 0
     preemptions: int = 0
+    # time between consecutive tokens of one request, from its first token on (the reference's inter-token gap,
+    # qwen_infer.c:20731-20742: taken once per step, so that a request which gets nothing while others' prompts
+    # run, or which is recomputed after a preemption, shows as a long gap)
+    gaps: int = 0
+    gap_sum_s: float = 0.0
+    gap_max_s: float = 0.0
+
+    def utilisation(self, batch: int) -> float:
+        """Decoding rows per step over the live-request limit (qwen_infer.c:20879)."""
+        return self.decode_rows / (self.steps * batch) if self.steps and batch else 0.0
+
+    def gap_mean_s(self) -> float:
+        return self.gap_sum_s / self.gaps if self.gaps else 0.0
 
 
 class Scheduler:
     def __init__(self, cache: CacheManager, max_batch: int = 8, max_step_tokens: int = 2048,
-                 prefill_budget: Optional[int] = None, max_context: Optional[int] = None):
+                 prefill_budget: Optional[int] = None, max_context: Optional[int] = None, now=time.perf_counter):
         """max_batch: live requests (the reference's QWEN_BATCH, default 8, qwen_infer.c:20617);
         prefill_budget: prompt tokens per step (QWEN_CB_PREFILL_BUDGET, qwen_infer.c:20691), by
         default whatever max_step_tokens leaves after the decoding rows."""
@@ -81,6 +96,7 @@ class Scheduler:
         self.finished: List[Request] = []
         self.counters = Counters()
         self._clock = 0
+        self._now = now                          # the clock of the inter-token gaps
 
     # ------------------------------------------------------------------ queue
     def add(self, req: Request) -> None:
@@ -208,7 +224,14 @@ class Scheduler:
         for r, take, last in plan.prefill:
             r.done_prompt += take
         ended = []
+        now, c = self._now(), self.counters
         for r, tok in zip(self.wanted(plan), tokens):
+            if r.last_token_at is not None:
+                gap = now - r.last_token_at
+                c.gaps += 1
+                c.gap_sum_s += gap
+                c.gap_max_s = max(c.gap_max_s, gap)
+            r.last_token_at = now
             r.output.append(int(tok))
             r.phase = "decode"
             length = self.cache.length(r.rid)

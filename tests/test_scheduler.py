@@ -160,3 +160,34 @@ def test_repeats_are_identical():
         steps = run(s, reqs)
         outs.append(([r.output for r in reqs], [[(e.rid, tuple(e.tokens)) for e in p.entries] for p in steps]))
     assert outs[0] == outs[1]
+
+
+def test_inter_token_gaps_and_utilisation_are_counted_as_the_reference_counts_them():
+    """One clock reading per step; a request's gap runs from the step that gave its previous token to the
+    step that gives the next one, its first token starting the clock; a request that waits while another's
+    prompt runs alone shows a longer gap (qwen_infer.c:20731-20742)."""
+    ticks = iter(range(1000))
+    c = cache()
+    s = Scheduler(c, max_batch=2, max_step_tokens=64, prefill_budget=4, now=lambda: float(next(ticks)))
+    reqs = [Request(0, [1, 2, 3], 4), Request(1, list(range(20, 28)), 2)]
+    steps = run(s, reqs)
+    # step 0: request 0 whole (3 tokens) and the first token of request 1's prompt (budget 4); request 0 then
+    # decodes in every step, so its three gaps are one tick each; request 1 needs two more steps of prompt,
+    # gets its first token at the end of step 2 and its second one step later: one gap of one tick
+    assert [[(e.rid, len(e.tokens)) for e in p.entries] for p in steps[:3]] == [[(0, 3), (1, 1)], [(0, 1), (1, 4)], [(0, 1), (1, 3)]]
+    k = s.counters
+    assert k.gaps == 3 + 1 and k.gap_max_s == 1.0 and k.gap_mean_s() == 1.0
+    assert k.steps == len(steps) == 4 and k.decode_rows == 3 + 1
+    assert k.utilisation(2) == 4 / (4 * 2)
+    assert reqs[0].output == expected_output([1, 2, 3], 4) and reqs[1].output == expected_output(range(20, 28), 2)
+
+
+def test_a_preempted_request_shows_its_recomputation_as_a_gap():
+    ticks = iter(range(1000))
+    c = cache(pages=5, page=4, reqs=4)
+    s = Scheduler(c, max_batch=2, max_step_tokens=64, now=lambda: float(next(ticks)))
+    reqs = [Request(0, list(range(7)), 12), Request(1, list(range(50, 57)), 6)]
+    run(s, reqs)
+    assert s.counters.preemptions >= 1
+    assert s.counters.gap_max_s > 1.0                     # the victim's next token came more than a step later
+    assert s.counters.gaps == (12 - 1) + (6 - 1)          # every token but a request's first closes a gap
