@@ -2,7 +2,8 @@
 environment variables (qwen_infer.c:20108-20128).
 
 Modes kept: `greedy` (default; N new tokens, default 32, no stop on EOS, output `greedy: id id ...`,
-qwen_infer.c:20412-20429), `bench` (prefill, 8 warm-up tokens, N timed decode tokens, best of 3,
+qwen_infer.c:20412-20429), `ppl` (teacher-forced perplexity over the first N, default 12, token files
+<QWEN_BASE>/eval/ppl_work/w0.i32, w1.i32, ..., output `ppl P tokens T`, :20488-20504), `bench` (prefill, 8 warm-up tokens, N timed decode tokens, best of 3,
 output `tok_s ... ms_tok ...`, :20430-20462), `dump` (last logits of the prompt to a file,
 :20405-20411) and `cbatch` (continuous batching over prompts cut from the loaded one, output one
 `cbatch req...` line per request and an `agg_tok_s` line with the reference's `util`, `avg_active`,
@@ -48,8 +49,8 @@ def main(argv: List[str]) -> int:
     if mode in ("-h", "--help"):
         print(__doc__)
         return 0
-    if mode not in ("greedy", "bench", "dump", "cbatch"):
-        return _err(f"unknown mode '{mode}'; modes: greedy, bench, dump, cbatch")
+    if mode not in ("greedy", "bench", "dump", "ppl", "cbatch"):
+        return _err(f"unknown mode '{mode}'; modes: greedy, bench, dump, ppl, cbatch")
     base = os.environ.get("QWEN_BASE")
     if not base:
         return _err("QWEN_BASE is not set (the model folder with config.json and model.safetensors)")
@@ -76,12 +77,14 @@ def main(argv: List[str]) -> int:
                            dtype=torch.float32 if dtype in ("fp32", "float32") else torch.bfloat16)
 
     prompt_path = os.environ.get("QWEN_PROMPT") or os.path.join(base, "ref", "prompt_ids.i32")
-    try:
-        prompt = load_ids(prompt_path, maxseq)
-    except OSError as e:
-        return _err(f"could not read prompt ids from {prompt_path} ({e.strerror})")
-    if len(prompt) < 1:
-        return _err(f"no prompt ids (np={len(prompt)})")
+    prompt: List[int] = []
+    if mode != "ppl":                                        # ppl reads its own token files (qwen_infer.c:20402)
+        try:
+            prompt = load_ids(prompt_path, maxseq)
+        except OSError as e:
+            return _err(f"could not read prompt ids from {prompt_path} ({e.strerror})")
+        if len(prompt) < 1:
+            return _err(f"no prompt ids (np={len(prompt)})")
 
     live = batch if mode == "cbatch" else 1
     num_pages = _env_int("QWEN_NUM_PAGES", live * -(-maxseq // page))
@@ -105,6 +108,35 @@ def main(argv: List[str]) -> int:
         os.makedirs(out_dir, exist_ok=True)
         logits[0].cpu().numpy().astype("<f4").tofile(os.path.join(out_dir, "c_logits_last.f32"))
         print(f"[engine] dumped, argmax={int(eng.sampler.greedy(logits)[0])}", file=sys.stderr)
+        return 0
+
+    if mode == "ppl":
+        n_win = int(argv[2]) if len(argv) > 2 else 12
+        tot_nll, tot, rows = 0.0, 0, 256                     # the logits of 256 places at a time
+        for wi in range(n_win):
+            try:
+                ids = load_ids(os.path.join(base, "eval", "ppl_work", f"w{wi}.i32"), maxseq)
+            except OSError:
+                continue
+            if len(ids) < 2:
+                continue
+            for lo in range(0, len(ids), rows):
+                part = ids[lo:lo + rows]
+                want = [i for i in range(len(part)) if lo + i < len(ids) - 1]      # every place but the window's last
+                logits = eng.step([("ppl", part, want)], end=["ppl"] if lo + rows >= len(ids) else [])
+                if want:
+                    nxt = torch.tensor(ids[lo + 1:lo + 1 + len(want)], device=logits.device)
+                    lg = logits.double()
+                    nll = torch.logsumexp(lg, dim=1) - lg.gather(1, nxt[:, None])[:, 0]
+                    tot_nll += float(nll.sum())
+                    tot += len(want)
+            print(f"[ppl] window {wi} done ({tot} toks)", file=sys.stderr)
+        if tot == 0:
+            return _err("no ppl tokens (missing eval/ppl_work?)")
+        import math
+        ppl = math.exp(tot_nll / tot)
+        print(f"[ppl] {dtype} ppl {ppl:.4f} over {tot} tokens", file=sys.stderr)
+        print(f"ppl {ppl:.4f} tokens {tot}")
         return 0
 
     if mode == "greedy":

@@ -1,6 +1,7 @@
 """Generation through the entry points: greedy against the plain implementation, temperature
 sampling reproducible and independent of the batch, few pages (preemption and recomputation), and
 the command line."""
+import math
 import os
 import subprocess
 import sys
@@ -131,5 +132,21 @@ def test_command_line_greedy_and_cbatch(model_root, tmp_path):
         head, toks = line.split(":")
         assert head == f"cbatch req{i} plen {plen[i]} maxnew {maxnew[i]} nout {maxnew[i]}"
         assert [int(t) for t in toks.split()] == plain.greedy_generate(cfg, w, prompt[:plen[i]], maxnew[i])
+    # ppl: teacher-forced perplexity over the token files of <QWEN_BASE>/eval/ppl_work (one is missing, one too short)
+    work = os.path.join(folder, "eval", "ppl_work")
+    os.makedirs(work, exist_ok=True)
+    windows = {0: seeded_ids(90, 256, 21), 2: seeded_ids(33, 256, 22), 3: [5]}
+    for wi, ids_w in windows.items():
+        np.asarray(ids_w, dtype="<i4").tofile(os.path.join(work, f"w{wi}.i32"))
+    r = subprocess.run(exe + ["ppl", "4"], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    nll, n = 0.0, 0
+    for ids_w in (windows[0], windows[2]):
+        logp = torch.log_softmax(plain.forward(cfg, w, ids_w)[:-1], dim=-1)
+        nll -= float(logp[torch.arange(len(ids_w) - 1), torch.tensor(ids_w[1:])].sum())
+        n += len(ids_w) - 1
+    word, value, word2, count = r.stdout.split()
+    assert (word, word2, int(count)) == ("ppl", "tokens", n)
+    assert abs(float(value) / math.exp(nll / n) - 1.0) < 1e-4
     r = subprocess.run(exe + ["greedy"], env=dict(env, QWEN_BASE=str(tmp_path)), capture_output=True, text=True, timeout=600)
     assert r.returncode == 1 and "FATAL" in r.stderr and "arch config" in r.stderr
