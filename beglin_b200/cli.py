@@ -3,8 +3,9 @@ environment variables (qwen_infer.c:20108-20128).
 
 Modes kept: `greedy` (default; N new tokens, default 32, no stop on EOS, output `greedy: id id ...`,
 qwen_infer.c:20412-20429), `ppl` (teacher-forced perplexity over the first N, default 12, token files
-<QWEN_BASE>/eval/ppl_work/w0.i32, w1.i32, ..., output `ppl P tokens T`, :20488-20504), `bench` (prefill, 8 warm-up tokens, N timed decode tokens, best of 3,
-output `tok_s ... ms_tok ...`, :20430-20462), `dump` (last logits of the prompt to a file,
+<QWEN_BASE>/eval/ppl_work/w0.i32, w1.i32, ..., output `ppl P tokens T`, :20488-20504), `bench` (prefill,
+8 warm-up tokens, N timed decode tokens, best of 3, output `tok_s ... ms_tok ...`, :20430-20462), `dump`
+(last logits of the prompt to a file,
 :20405-20411) and `cbatch` (continuous batching over prompts cut from the loaded one, output one
 `cbatch req...` line per request and an `agg_tok_s` line with the reference's `util`, `avg_active`,
 `steps`, `msteps`, `pfonly`, `pf_cols`, `tbt_max_ms` and `tbt_mean_ms` fields, :20611-20912).
