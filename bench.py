@@ -55,7 +55,7 @@ def peaks():
         if "bf16_tflops_sustained" in p:
             out["bf16_tflops_sustained"] = float(p["bf16_tflops_sustained"])
         return out
-    except (OSError, KeyError, ValueError):
+    except (OSError, KeyError, ValueError, TypeError):
         return dict(FALLBACK_PEAKS)
 
 
