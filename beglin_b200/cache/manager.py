@@ -127,15 +127,35 @@ class CacheManager:
         self.lengths: Dict[Hashable, int] = {}
         self.slots: Dict[Hashable, int] = {}
         self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
+        # Every start of a request gets a number of its own, so that whoever remembers what the device holds
+        # for a request (a replayed graph's block tables and positions) can tell a request from a later one
+        # of the same name.
+        self.births: Dict[Hashable, int] = {}
+        self._born = 0
+        # One page and one state slot more than are ever handed out: rows that pad a batch of fixed shape
+        # write their keys, values and state there, where no request reads.
+        self.dump_page = num_pages
+        self.dump_slot = max_requests
 
     # ---------------------------------------------------------------- device side
     def allocate(self, device, dtype: torch.dtype) -> None:
         for g in self.kv_groups:
-            g.device_pool = torch.empty((len(g.stages), self.num_pages, 2, g.need.n_kv_heads, self.page_size,
+            g.device_pool = torch.empty((len(g.stages), self.num_pages + 1, 2, g.need.n_kv_heads, self.page_size,
                                          g.need.head_dim), dtype=dtype, device=device)
+            g.device_pool[:, self.dump_page].zero_()
         for g in self.state_groups:
-            g.slab = torch.zeros((len(g.stages), self.max_requests) + tuple(g.need.shape),
+            g.slab = torch.zeros((len(g.stages), self.max_requests + 1) + tuple(g.need.shape),
                                  dtype=getattr(torch, g.need.dtype), device=device)
+
+    def snapshot_state(self) -> list:
+        """Copies of the fixed-state slabs, for a caller that has to run a step twice (a warm-up before a
+        stream capture) and must not advance the state twice."""
+        return [g.slab.clone() if g.slab is not None else None for g in self.state_groups]
+
+    def restore_state(self, saved: list) -> None:
+        for g, s in zip(self.state_groups, saved):
+            if s is not None:
+                g.slab.copy_(s)
 
     def device_bytes(self) -> int:
         total = 0
@@ -168,6 +188,8 @@ class CacheManager:
         slot = self._free_slots.pop()
         self.lengths[rid] = 0
         self.slots[rid] = slot
+        self._born += 1
+        self.births[rid] = self._born
         for g in self.kv_groups:
             g.tables[rid] = []
         for g in self.state_groups:
@@ -183,6 +205,24 @@ class CacheManager:
             g.pool.free([p for p in g.tables.pop(rid) if p >= 0])
         self._free_slots.append(self.slots.pop(rid))
         del self.lengths[rid]
+        del self.births[rid]
+
+    def identity(self, rids: Sequence[Hashable]) -> tuple:
+        """(request, number of its start) for each: equal only for the same live requests."""
+        return tuple((r, self.births[r]) for r in rids)
+
+    def trim(self, rids: Sequence[Hashable]) -> None:
+        """Give back the pages that lie beyond each request's recorded length: what a reservation took for
+        a step that did not happen."""
+        for rid in rids:
+            if rid not in self.lengths:
+                continue
+            keep = -(-self.lengths[rid] // self.page_size)
+            for g in self.kv_groups:
+                table = g.tables[rid]
+                if len(table) > keep:
+                    g.pool.free([p for p in table[keep:] if p >= 0])
+                    del table[keep:]
 
     # ---------------------------------------------------------------- pages
     def _plan(self, g: _KVGroup, rid: Hashable, new_len: int, first_query_pos: int):

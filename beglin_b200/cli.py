@@ -44,6 +44,27 @@ def load_ids(path: str, limit: int) -> List[int]:
     return np.fromfile(path, dtype="<i4")[:limit].astype(np.int64).tolist()
 
 
+def describe(spec) -> str:
+    """The reference's arch line (qwen_infer.c:19489-19490) from a model's description: the sizes are read
+    off the parts of the first layer, whatever architecture built the description; a size that the layer's
+    parts do not have is left out."""
+    first = spec.layers[0].parts if spec.layers else {}
+    mixer, ff = first.get("mixer"), first.get("feed_forward")
+    fields = [("NL", len(spec.layers)), ("NH", getattr(mixer, "n_heads", None)), ("NKV", getattr(mixer, "n_kv_heads", None)),
+              ("D", spec.hidden), ("HD", getattr(mixer, "head_dim", None)), ("IM", getattr(ff, "intermediate", None)),
+              ("VOCAB", spec.vocab)]
+    position = getattr(mixer, "position", None)
+    theta = getattr(position, "theta", None)
+    if theta is not None:
+        fields.append(("THETA", f"{theta:.1f}"))
+    fields.append(("EPS", f"{spec.final_norm.eps:g}"))
+    if getattr(mixer, "qkv_bias", None) is not None:
+        fields.append(("QKV_BIAS", int(mixer.qkv_bias)))
+    if getattr(mixer, "n_heads", None) and getattr(mixer, "n_kv_heads", None):
+        fields.append(("GROUP", mixer.n_heads // mixer.n_kv_heads))
+    return " ".join(f"{k}={v}" for k, v in fields if v is not None)
+
+
 def main(argv: List[str]) -> int:
     mode = argv[1] if len(argv) > 1 else "greedy"
     n_gen = int(argv[2]) if len(argv) > 2 else 32
@@ -94,12 +115,7 @@ def main(argv: List[str]) -> int:
                                  max_requests=live, max_context=maxseq)
     except Exception as e:                                   # one line, as the reference's FATALs
         return _err(str(e))
-    cfg = eng.config
-    print(f"[engine] arch config ({base}): NL={cfg.num_hidden_layers} NH={cfg.num_attention_heads} "
-          f"NKV={cfg.num_key_value_heads} D={cfg.hidden_size} HD={cfg.head_dim} IM={cfg.intermediate_size} "
-          f"VOCAB={cfg.vocab_size} THETA={cfg.rope_theta:.1f} EPS={cfg.rms_norm_eps:g} MAXSEQ={maxseq} "
-          f"QKV_BIAS={int(cfg.qkv_bias)} GROUP={cfg.num_attention_heads // cfg.num_key_value_heads} "
-          f"DTYPE={dtype}", file=sys.stderr)
+    print(f"[engine] arch config ({base}): {describe(eng.spec)} MAXSEQ={maxseq} DTYPE={dtype}", file=sys.stderr)
     temperature = float(os.environ.get("QWEN_TEMPERATURE", "0"))
     seed = _env_int("QWEN_SEED", 0)
 

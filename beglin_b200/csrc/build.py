@@ -52,7 +52,7 @@ def sources() -> List[str]:
 
 def _source_hash() -> str:
     h = hashlib.sha1()
-    for path in sources() + sorted(glob.glob(os.path.join(HERE, "*.cuh"))):
+    for path in sources() + sorted(glob.glob(os.path.join(HERE, "*.cuh"))) + sorted(glob.glob(os.path.join(HERE, "*.h"))):
         h.update(os.path.basename(path).encode())
         with open(path, "rb") as f:
             h.update(f.read())

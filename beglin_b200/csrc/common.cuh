@@ -46,6 +46,19 @@ inline int& pdl_enabled() {
     return on;
 }
 
+// The number of SMs of the current device, read from the device once per device.
+inline int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};

@@ -412,7 +412,7 @@ static int gf_launch_stages(const CUtensorMap& mw, const CUtensorMap& mx, const 
 template <int BN>
 static int gf_launch(const CUtensorMap& mw, const CUtensorMap& mx, const FusedParams& p, cudaStream_t stream) {
     const long long ctas = (long long)((p.n_out + TC_BM - 1) / TC_BM) * ((p.T + BN - 1) / BN) * p.splits;
-    if (BN <= 32 && ctas <= 148 && p.kb_per_split > 4) return gf_launch_stages<BN, 8>(mw, mx, p, stream);
+    if (BN <= 32 && ctas <= sm_count() && p.kb_per_split > 4) return gf_launch_stages<BN, 8>(mw, mx, p, stream);
     return gf_launch_stages<BN, 4>(mw, mx, p, stream);
 }
 

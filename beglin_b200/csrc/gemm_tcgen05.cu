@@ -222,7 +222,7 @@ extern "C" int bg_gemm_bf16_tn(const void* W, int n_out, int K, int ldw, const v
             // a CTA under half of an SM's shared memory, so two CTAs share the SM and one's epilogue overlaps
             // the other's MMAs; a grid that does not fill the machine gets the deeper pipeline instead.
             const long long ctas = (long long)((n_out + TC_BM - 1) / TC_BM) * ((T + 255) / 256) * splits;
-            if (ctas > 148) return tc_launch<256, 2>(mw, mx, p, splits, stream);
+            if (ctas > sm_count()) return tc_launch<256, 2>(mw, mx, p, splits, stream);
             return tc_launch<256, 4>(mw, mx, p, splits, stream);
         }
     }

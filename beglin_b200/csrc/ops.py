@@ -305,14 +305,31 @@ def attention_plan(group: int, hd: int, dtype: torch.dtype = torch.float32, deco
     return "generic", bq.value, tile.value
 
 
-def decode_splits(n_streams: int, context: int) -> int:
+_sm_counts = {}
+
+
+def sm_count(device=None) -> int:
+    """The number of SMs of `device` (default: the current CUDA device), read from the device once."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    n = _sm_counts.get(index)
+    if n is None:
+        n = _sm_counts[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return n
+
+
+def decode_splits(n_streams: int, context: int, sms: Optional[int] = None) -> int:
     """How many CTAs share the keys of one (request, kv head) stream in the decoding kernel.  A CTA has
     a shared-memory buffer per warp and is alone on its SM, so the streams are cut to make one wave
-    of CTAs (148 SMs): more CTAs wait for a second wave, fewer leave SMs idle while the others walk
-    longer ranges.  No more than one CTA per 256 keys of `context` (a stage of 64 for each of the four
-    warps).  Each request's keys are spread evenly over its CTAs by the kernel itself, by the
-    request's own length, so the count depends on the shapes of the step only."""
-    want = max(1, min(148 // max(1, n_streams), -(-context // 256)))
+    of CTAs (one per SM; `sms` defaults to the current device's count): more CTAs wait for a second
+    wave, fewer leave SMs idle while the others walk longer ranges.  No more than one CTA per 256 keys
+    of `context` (a stage of 64 for each of the four warps).  Each request's keys are spread evenly
+    over its CTAs by the kernel itself, by the request's own length, so the count depends on the
+    shapes of the step only."""
+    if sms is None:
+        sms = sm_count()
+    want = max(1, min(sms // max(1, n_streams), -(-context // 256)))
     per = -(-(-(-context // want)) // 256) * 256          # what the kernel makes of it: whole multiples of 256 keys
     return -(-context // per)                             # no CTA without keys
 

@@ -7,9 +7,16 @@ tables, state slots, temperatures and uniform numbers.  The sampled tokens are a
 into the token buffer on the device, so a caller that does not need them on the host can decode
 without a round trip.
 
-The attention kernel is launched for as many key splits as the context limit has; splits beyond a
-request's length return at once.  The split boundaries are fixed positions, so a replayed step
-computes every row exactly as the uncaptured step function does.
+A graph stands for a batch of up to `n` requests, n one of `BUCKETS`: a step of fewer requests pads
+the batch with rows that belong to nobody (token 0 at position 0, keys, values and state written to
+the cache manager's spare page and spare slot, results dropped), so that requests which end one by
+one go through at most a handful of graphs.
+
+The attention kernels are launched for the context limit, not for the longest live request: the
+float32 kernel cuts the keys at fixed positions, so a replayed float32 step computes every row
+bitwise as the uncaptured step function does; the bfloat16 decoding kernel spreads a request's keys
+over a number of CTAs that depends on the batch's size and the context limit, so there a replayed
+step agrees with the uncaptured one up to rounding only.
 """
 from __future__ import annotations
 
@@ -21,6 +28,19 @@ import torch
 from ..cache.manager import CacheError, OutOfPages
 from ..csrc import ops
 from .capture import no_collection
+
+
+BUCKETS = (1, 2, 4, 8, 16, 32, 64)
+
+
+def bucket(n: int) -> int:
+    """The batch size of the graph that serves a step of n requests: the next of BUCKETS, and beyond
+    the largest the next multiple of it."""
+    for b in BUCKETS:
+        if n <= b:
+            return b
+    top = BUCKETS[-1]
+    return -(-n // top) * top
 
 
 class _StaticBatch:
@@ -59,7 +79,7 @@ class _Staging:
     has taken them."""
 
     def __init__(self, n: int, cache):
-        self.meta = torch.zeros((2, n), dtype=torch.int32).pin_memory()          # positions, slots
+        self.meta = torch.zeros((3, n), dtype=torch.int32).pin_memory()          # positions, slots, live rows
         self.tokens = torch.zeros(n, dtype=torch.int32).pin_memory()
         self.floats = torch.zeros((2, n), dtype=torch.float32).pin_memory()      # temperatures, uniforms
         self.tables = {gi: torch.zeros((n, cache.max_pages), dtype=torch.int32).pin_memory()
@@ -75,6 +95,7 @@ class DecodeGraph:
         dev = engine.device
         cache = engine.cache
         self.batch = _StaticBatch(n, cache, dev)
+        self.advance = torch.ones(n, dtype=torch.int32, device=dev)      # 1 for a live row, 0 for a row that pads
         self.temperature = torch.zeros(n, dtype=torch.float32, device=dev)
         self.uniform = torch.zeros(n, dtype=torch.float32, device=dev)
         self.out_tokens = torch.zeros(n, dtype=torch.int32, device=dev)
@@ -103,7 +124,7 @@ class DecodeGraph:
         logits = self.engine.model.forward(b, self.engine.cache)
         ops.sample(logits, self.temperature, self.uniform, self.out_tokens)
         b.token_ids.copy_(self.out_tokens)
-        b.positions.add_(1)                    # the next step of the same requests needs no upload
+        b.positions.add_(self.advance)         # the next step of the same requests needs no upload
         self.logits = logits
 
     def _body_fed(self) -> None:
@@ -117,7 +138,12 @@ class DecodeGraph:
         side.wait_stream(torch.cuda.current_stream())
         saved_tokens, saved_pos = self.batch.token_ids.clone(), self.batch.positions.clone()
         with torch.cuda.stream(side):
-            self._body()                       # warm-up outside the capture (library handles, allocations)
+            # Warm-up outside the capture (library handles, allocations).  The replay that follows runs the
+            # same step again: keys and values are written twice with the same contents, and state of fixed
+            # size, which a mixer reads, changes and writes, is put back as it was.
+            saved_state = self.engine.cache.snapshot_state()
+            self._body()
+            self.engine.cache.restore_state(saved_state)
             self.batch.token_ids.copy_(saved_tokens)
             self.batch.positions.copy_(saved_pos)
         torch.cuda.current_stream().wait_stream(side)
@@ -133,10 +159,13 @@ class DecodeGraph:
             self.graph = g
 
     def _upload_tables(self, rids, st) -> int:
-        """Upload the block tables that differ from what the device holds; returns the bytes sent."""
-        cache, sent = self.engine.cache, 0
+        """Upload the block tables that differ from what the device holds; returns the bytes sent.  The
+        rows beyond the live requests hold the spare page at position 0 and nothing else."""
+        cache, sent, m = self.engine.cache, 0, len(rids)
         for gi, h in st.tables.items():
-            table = cache.block_table(gi, rids)
+            table = np.full((self.n, cache.max_pages), -1, dtype=np.int32)
+            table[:m] = cache.block_table(gi, rids)
+            table[m:, 0] = cache.dump_page
             last = self._tables.get(gi)
             if last is None or not np.array_equal(last, table):
                 h.copy_(torch.from_numpy(table))
@@ -170,9 +199,9 @@ class DecodeGraph:
 
     def prepared(self, rids: Sequence[Hashable]) -> bool:
         """Whether the last step has already made room for the next step of exactly these requests."""
-        if self._ahead is None or self._ahead[0] != tuple(rids):
-            return False
         cache = self.engine.cache
+        if self._ahead is None or not all(cache.has(r) for r in rids) or self._ahead[0] != cache.identity(rids):
+            return False
         return all(cache.length(r) == p for r, p in zip(rids, self._ahead[1]))
 
     def step(self, rids: Sequence[Hashable], tokens: Optional[Sequence[int]], temperatures: Optional[Sequence[float]] = None,
@@ -183,32 +212,39 @@ class DecodeGraph:
         the last step is uploaded: positions advance on the device, block tables change when a request
         gets a new page."""
         cache, n, b = self.engine.cache, self.n, self.batch
-        assert len(rids) == n
+        m = len(rids)
+        assert 1 <= m <= n
         st = self.ring[self.turn]
         self.turn = (self.turn + 1) % self.RING
         if st.event is not None:
             st.event.synchronize()             # the device has read this set's last contents
         sent = 0
         positions = [cache.length(r) for r in rids]
-        key = tuple(rids)
+        key = cache.identity(rids)             # a request that ended and one that began under its name differ
         if key != self._rids or positions != self._positions:
-            st.meta[0] = torch.as_tensor(positions, dtype=torch.int32)
-            st.meta[1] = torch.from_numpy(cache.slot_ids(rids))
+            meta = st.meta.numpy()
+            meta[0, :m], meta[0, m:] = positions, 0
+            meta[1, :m], meta[1, m:] = cache.slot_ids(rids), cache.dump_slot
+            meta[2, :m], meta[2, m:] = 1, 0
             b.positions.copy_(st.meta[0], non_blocking=True)
             b.slots.copy_(st.meta[1], non_blocking=True)
-            sent += 8 * n
+            self.advance.copy_(st.meta[2], non_blocking=True)
+            sent += 12 * n
             self._rids = key
         fed = tokens is not None and read_back     # the copies in and out are part of the replayed graph
         if fed:
-            self.h_in_np[:] = tokens               # safe: the last fed step was waited for before it returned
+            self.h_in_np[:m] = tokens              # safe: the last fed step was waited for before it returned
+            self.h_in_np[m:] = 0
             sent += 4 * n
         elif tokens is not None:
-            st.tokens.copy_(torch.as_tensor(list(tokens), dtype=torch.int32))
+            h = st.tokens.numpy()
+            h[:m], h[m:] = list(tokens), 0
             b.token_ids.copy_(st.tokens, non_blocking=True)
             sent += 4 * n
         if temperatures is not None and any(t > 0.0 for t in temperatures):
-            st.floats[0] = torch.as_tensor(list(temperatures), dtype=torch.float32)
-            st.floats[1] = torch.as_tensor(list(uniforms), dtype=torch.float32)
+            f = st.floats.numpy()
+            f[0, :m], f[0, m:] = list(temperatures), 0.0
+            f[1, :m], f[1, m:] = list(uniforms), 0.0
             self.temperature.copy_(st.floats[0], non_blocking=True)
             self.uniform.copy_(st.floats[1], non_blocking=True)
             sent += 8 * n
@@ -238,5 +274,5 @@ class DecodeGraph:
             if not fed:
                 self.h_out.copy_(self.out_tokens, non_blocking=True)
             torch.cuda.current_stream().synchronize()
-            return self.h_out.tolist()
-        return self.out_tokens
+            return self.h_out[:m].tolist()
+        return self.out_tokens[:m]

@@ -136,7 +136,15 @@ class Engine:
                     if self.cache.has(rid):
                         self.cache.release(rid)
                 raise
-            logits = self.run(ents, plan)
+            try:
+                logits = self.run(ents, plan)
+            except Exception:
+                # the step did not happen: what was reserved for it goes back, and a request that came with
+                # this step is gone again
+                for rid in new:
+                    self.cache.release(rid)
+                self.cache.trim([e.rid for e in ents])
+                raise
             if check:
                 ops.raise_on_status(self.ctx.status)
         for rid in end:
@@ -173,11 +181,14 @@ class Engine:
 
     # ------------------------------------------------------------------ decoding as a CUDA graph
     def decode_graph(self, n: int):
-        from .decode_graph import DecodeGraph
-        g = self._graphs.get(n)
+        """The graph that serves decoding steps of n requests: one per bucket of batch sizes (1, 2, 4, ...),
+        so requests that end one by one go through a handful of graphs, not one per count."""
+        from .decode_graph import DecodeGraph, bucket
+        size = bucket(n)
+        g = self._graphs.get(size)
         if g is None:
             with torch.cuda.device(self.device):
-                g = self._graphs[n] = DecodeGraph(self, n)
+                g = self._graphs[size] = DecodeGraph(self, size)
         return g
 
     def decode(self, rids: Sequence[Hashable], tokens: Optional[Sequence[int]] = None,
@@ -233,10 +244,10 @@ class Engine:
                         tokens = self.decode_graph(len(wanted)).step(
                             [r.rid for r in wanted], [r.output[-1] for r in wanted], temps, us)
                 else:
-                    logits = self.run(plan.entries, sched._plan_lengths)
+                    logits = self.run(plan.entries, plan.lengths)
                     if wanted:
                         tokens = self.sampler.sample(logits, temps, us)
-                sched.update(plan, tokens)
+                sched.update(plan, tokens, committed=True)      # the step functions above have recorded the lengths
             ops.raise_on_status(self.ctx.status)
         finally:
             for r in list(sched.running):

@@ -14,7 +14,6 @@ from ..parts.context import BuildContext
 from ..parts.linear import Linear
 from ..parts.spec import ModelSpec
 from ..parts.stream import ResidualStream
-from ..weights.loader import layer_roles
 
 
 class DecoderModel:
@@ -26,23 +25,16 @@ class DecoderModel:
             ctx.status = ops.new_status(ctx.device)
         self.embed = ctx.matrix(tensors[spec.embed_name])
         self.blocks = []
-        self.mixers = []
         for layer in spec.layers:
             parts = {}
-            for prefix, cls, pspec in (
-                    ("mixer_norm", registry.norm_class(layer.mixer_norm.kind), layer.mixer_norm),
-                    ("mixer", registry.mixer_class(layer.mixer.kind), layer.mixer),
-                    ("feed_forward_norm", registry.norm_class(layer.feed_forward_norm.kind), layer.feed_forward_norm),
-                    ("feed_forward", registry.feed_forward_class(layer.feed_forward.kind), layer.feed_forward)):
+            for slot, _, cls, pspec in registry.layer_slots(layer):
                 mine = {}
                 for role in cls.expected_tensors(pspec):
-                    name = layer.names[f"{prefix}.{role.name}"]
+                    name = layer.names[f"{slot}.{role.name}"]
                     if name in tensors:
                         mine[role.name] = tensors[name]
-                parts[prefix] = cls(pspec, mine, ctx)
-            self.mixers.append(parts["mixer"])
-            self.blocks.append(registry.block_class(layer.block)(parts["mixer_norm"], parts["mixer"],
-                                                                 parts["feed_forward_norm"], parts["feed_forward"]))
+                parts[slot] = cls(pspec, mine, ctx)
+            self.blocks.append(registry.block_class(layer.block)(**parts))
         self.final_norm = registry.norm_class(spec.final_norm.kind)(
             spec.final_norm, {"weight": tensors[spec.final_norm_name]}, ctx)
         if spec.head_name is None:
@@ -55,11 +47,11 @@ class DecoderModel:
         """The cache need of every stage of the run order (None for a stage that reads another's)."""
         needs = []
         for stage in self.spec.order:
-            layer = self.spec.layers[stage.layer]
-            cls = registry.mixer_class(layer.mixer.kind)
-            need = cls.cache_need(layer.mixer)
-            if stage.cache is not None:
-                need = None
+            need = None
+            if stage.cache is None:
+                for _, family, cls, pspec in registry.layer_slots(self.spec.layers[stage.layer]):
+                    if family == "mixer":
+                        need = cls.cache_need(pspec)
             needs.append(need)
         return needs
 

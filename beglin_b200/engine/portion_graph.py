@@ -89,8 +89,12 @@ class PortionGraph:
         side = torch.cuda.Stream(device=self.engine.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            self._body()                       # warm-up outside the capture (library handles, allocations); it
-        torch.cuda.current_stream().wait_stream(side)      # writes the same keys and values the replay will
+            # warm-up outside the capture (library handles, allocations); it writes the same keys and values
+            # the replay will, and state of fixed size is put back as it was
+            saved_state = self.engine.cache.snapshot_state()
+            self._body()
+            self.engine.cache.restore_state(saved_state)
+        torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         before = ops.launch_count()
         g = torch.cuda.CUDAGraph()

@@ -51,6 +51,7 @@ class StepPlan:
     entries: List[Entry]
     decode: List[Request]             # requests whose entry is one decoded token, in entry order
     prefill: List[Tuple[Request, int, bool]]   # (request, tokens taken, reaches the prompt's end)
+    lengths: List[Tuple[Hashable, int]] = field(default_factory=list)   # (request, length after the step): what was reserved
 
     @property
     def n_tokens(self) -> int:
@@ -202,7 +203,7 @@ class Scheduler:
             for r, take, last in prefill:
                 toks = r.tokens_in[r.done_prompt:r.done_prompt + take]
                 entries.append(Entry(r.rid, toks, [take - 1] if last else []))
-            self._plan_lengths = plan
+            lengths = plan
             c = self.counters
             c.steps += 1
             c.decode_rows += len(decode)
@@ -211,16 +212,18 @@ class Scheduler:
                 c.mixed_steps += 1
             if not decode:
                 c.prefill_only_steps += 1
-            return StepPlan(entries, decode, prefill)
+            return StepPlan(entries, decode, prefill, lengths)
 
     def wanted(self, plan: StepPlan) -> List[Request]:
         """The requests that get a new token from this step, in the order of the step's logit rows."""
         return list(plan.decode) + [r for r, _, last in plan.prefill if last]
 
-    def update(self, plan: StepPlan, tokens: Sequence[int]) -> List[Request]:
-        """Record the step: new lengths, the sampled token of every request in `wanted(plan)`, phase
-        changes and endings.  Returns the requests that ended."""
-        self.cache.commit(self._plan_lengths)
+    def update(self, plan: StepPlan, tokens: Sequence[int], committed: bool = False) -> List[Request]:
+        """Record the step: new lengths (unless the step function that ran the plan has `committed` them to
+        the cache already), the sampled token of every request in `wanted(plan)`, phase changes and endings.
+        Returns the requests that ended."""
+        if not committed:
+            self.cache.commit(plan.lengths)
         for r, take, last in plan.prefill:
             r.done_prompt += take
         ended = []

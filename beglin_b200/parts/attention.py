@@ -36,11 +36,11 @@ class GQAAttention:
             roles += [TensorRole("k_proj.weight", (kvd, spec.hidden), True, True),
                       TensorRole("v_proj.weight", (kvd, spec.hidden), True, True)]
         if spec.qkv_bias:
-            roles.append(TensorRole("q_proj.bias", (qd,)))
+            roles.append(TensorRole("q_proj.bias", (qd,), role="bias"))
             if spec.own_kv:
-                roles += [TensorRole("k_proj.bias", (kvd,)), TensorRole("v_proj.bias", (kvd,))]
+                roles += [TensorRole("k_proj.bias", (kvd,), role="bias"), TensorRole("v_proj.bias", (kvd,), role="bias")]
         if spec.out_bias:
-            roles.append(TensorRole("o_proj.bias", (spec.hidden,)))
+            roles.append(TensorRole("o_proj.bias", (spec.hidden,), role="bias"))
         return roles
 
     @staticmethod

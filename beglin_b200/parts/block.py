@@ -12,6 +12,10 @@ from .stream import NormedInput, ResidualStream
 
 @register_block("prenorm")
 class PreNormBlock:
+    # the slots of a layer of this kind, in the order they are built: (slot name, family of the part).  A
+    # block is constructed with one keyword argument per slot.
+    SLOTS = (("mixer_norm", "norm"), ("mixer", "mixer"), ("feed_forward_norm", "norm"), ("feed_forward", "feed_forward"))
+
     def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward):
         self.mixer_norm, self.mixer = mixer_norm, mixer
         self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward

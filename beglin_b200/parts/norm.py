@@ -17,7 +17,7 @@ from .spec import NormSpec, TensorRole
 class RMSNorm:
     @staticmethod
     def expected_tensors(spec: NormSpec) -> List[TensorRole]:
-        return [TensorRole("weight", (spec.size,))]
+        return [TensorRole("weight", (spec.size,), role="scale")]
 
     def __init__(self, spec: NormSpec, tensors: Dict[str, torch.Tensor], ctx: BuildContext):
         self.spec, self.ctx = spec, ctx

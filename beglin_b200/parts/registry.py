@@ -58,3 +58,34 @@ def position_class(kind: str) -> type:
 
 def block_class(kind: str) -> type:
     return lookup(BLOCKS, kind, "block")
+
+
+FAMILIES = {"mixer": (MIXERS, "mixer"), "feed_forward": (FEED_FORWARDS, "feed-forward"), "norm": (NORMS, "norm")}
+
+
+def part_class(family: str, kind: str) -> type:
+    """The class of a part of one of the families a block's slots are made of."""
+    try:
+        table, what = FAMILIES[family]
+    except KeyError:
+        raise KeyError(f"no family of parts called '{family}'; families: {', '.join(FAMILIES)}") from None
+    return lookup(table, kind, what)
+
+
+def layer_slots(layer) -> list:
+    """(slot name, family, part class, part spec) for every slot that the layer's block kind declares,
+    in the block's order.  A slot the layer's spec does not fill, or a part the block has no slot for,
+    is an error."""
+    block = block_class(layer.block)
+    slots = getattr(block, "SLOTS", None)
+    if slots is None:
+        raise TypeError(f"block kind '{layer.block}' declares no SLOTS")
+    declared = [name for name, _ in slots]
+    missing = [name for name in declared if name not in layer.parts]
+    extra = [name for name in layer.parts if name not in declared]
+    if missing or extra:
+        raise KeyError(f"a layer of block kind '{layer.block}' has slots {declared}; "
+                       f"the spec lacks {missing} and has {extra} besides")
+    if sum(1 for _, family in slots if family == "mixer") > 1:
+        raise TypeError(f"block kind '{layer.block}' declares more than one mixer slot; a stage has one cache")
+    return [(name, family, part_class(family, layer.parts[name].kind), layer.parts[name]) for name, family in slots]

@@ -14,13 +14,19 @@ from typing import Dict, List, Optional, Tuple
 
 @dataclass(frozen=True)
 class TensorRole:
-    """One tensor a part wants: its name inside the part, its shape, whether it may be absent, and
+    """One tensor a part wants: its name inside the part, its shape, whether it may be absent,
     whether it is a matrix of a matrix product (kept in the compute dtype) or a small vector or
-    table (kept as stored)."""
+    table (kept as stored), and what it is for.  `role` decides how random weights are drawn:
+    "matrix" and "vector" around zero, "bias" around zero with a deviation of its own, "scale" (a
+    norm's weight, which multiplies) around one.  Empty means "matrix" or "vector" by `matrix`."""
     name: str
     shape: Tuple[int, ...]
     required: bool = True
     matrix: bool = False
+    role: str = ""
+
+    def init_role(self) -> str:
+        return self.role or ("matrix" if self.matrix else "vector")
 
 
 @dataclass(frozen=True)
@@ -68,16 +74,40 @@ class SwiGLUSpec:
     kind: str = "swiglu"
 
 
-@dataclass(frozen=True)
 class LayerSpec:
-    """One decoder layer.  `names` maps each part's own tensor names to checkpoint names, e.g.
-    {"mixer.q_proj.weight": "model.layers.3.self_attn.q_proj.weight"}."""
-    mixer: object
-    feed_forward: object
-    mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
-    names: Dict[str, str]
-    block: str = "prenorm"
+    """One decoder layer: the kind of its block, and the spec of the part in every slot that the block
+    kind declares (`parts`: slot name -> part spec; the block class's `SLOTS` says which slots there are
+    and of which family each is).  `names` maps each part's own tensor names, qualified by the slot, to
+    checkpoint names, e.g. {"mixer.q_proj.weight": "model.layers.3.self_attn.q_proj.weight"}.
+
+    The slots may also be given as keywords (`LayerSpec(mixer=..., feed_forward=..., names=...)`) and
+    read as attributes (`layer.mixer`); `with_parts` returns a copy with some slots, the names or the
+    block kind replaced."""
+
+    def __init__(self, parts: Optional[Dict[str, object]] = None, names: Optional[Dict[str, str]] = None,
+                 block: str = "prenorm", **slots):
+        merged = dict(parts or {})
+        merged.update(slots)
+        object.__setattr__(self, "parts", merged)
+        object.__setattr__(self, "names", dict(names or {}))
+        object.__setattr__(self, "block", block)
+
+    def __getattr__(self, slot):
+        parts = self.__dict__.get("parts", {})
+        if slot in parts:
+            return parts[slot]
+        raise AttributeError(f"the layer has no slot '{slot}' (slots: {', '.join(parts) or 'none'})")
+
+    def __setattr__(self, key, value):
+        raise AttributeError("a LayerSpec is not changed in place; use with_parts()")
+
+    def with_parts(self, names: Optional[Dict[str, str]] = None, block: Optional[str] = None, **slots) -> "LayerSpec":
+        parts = dict(self.parts)
+        parts.update(slots)
+        return LayerSpec(parts, self.names if names is None else names, self.block if block is None else block)
+
+    def __repr__(self):
+        return f"LayerSpec(block={self.block!r}, parts={self.parts!r})"
 
 
 @dataclass(frozen=True)

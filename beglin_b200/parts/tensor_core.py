@@ -15,7 +15,6 @@ import torch
 from ..csrc import ops
 from .context import BuildContext
 
-SM_COUNT = 148
 FEW_TOKENS = 64            # up to this many rows a product is treated as weight-streaming
 FUSED_TOKENS = 16            # steps of up to this many rows run the fused product (measured: it loses from 32 rows on)
 
@@ -30,6 +29,7 @@ class TensorCoreProduct:
         self._w_ptr, self._ldw = weight.data_ptr(), weight.stride(0)
         self._status_ptr = None if ctx.status is None else ctx.status.data_ptr()
         self._splits = {}
+        self.sms = ops.sm_count(weight.device)
 
     @staticmethod
     def takes(weight: torch.Tensor) -> bool:
@@ -51,7 +51,7 @@ class TensorCoreProduct:
     def _choose_splits(self, T: int) -> int:
         if T > FEW_TOKENS:
             return 1
-        want = max(1, -(-SM_COUNT // self.tiles))                 # enough CTAs for every SM
+        want = max(1, -(-self.sms // self.tiles))                 # enough CTAs for every SM
         want = min(want, max(1, self.k_blocks // 2))              # at least two k-blocks per range
         want = min(want, max(1, self.k // (8 * T)))               # partial sums stay a fraction of the weight bytes
         per = -(-self.k_blocks // want)
@@ -66,7 +66,7 @@ class TensorCoreProduct:
         least two k-blocks per range, no empty range."""
         s = self._splits.get(("fused", T))
         if s is None:
-            want = max(1, -(-SM_COUNT // (self.tiles * -(-T // 64))))
+            want = max(1, -(-self.sms // (self.tiles * -(-T // 64))))
             s = 1
             while s < 16 and s < want and 2 * s <= max(1, self.k_blocks // 2):
                 s *= 2

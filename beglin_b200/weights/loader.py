@@ -34,15 +34,12 @@ class WeightError(ValueError):
 
 
 def layer_roles(layer) -> List[Tuple[str, TensorRole]]:
-    """(part-qualified name, role) of every tensor a layer's parts want."""
+    """(slot-qualified name, role) of every tensor a layer's parts want: the slots are those its block
+    kind declares."""
     out: List[Tuple[str, TensorRole]] = []
-    parts = (("mixer_norm", registry.norm_class(layer.mixer_norm.kind), layer.mixer_norm),
-             ("mixer", registry.mixer_class(layer.mixer.kind), layer.mixer),
-             ("feed_forward_norm", registry.norm_class(layer.feed_forward_norm.kind), layer.feed_forward_norm),
-             ("feed_forward", registry.feed_forward_class(layer.feed_forward.kind), layer.feed_forward))
-    for prefix, cls, spec in parts:
+    for slot, _, cls, spec in registry.layer_slots(layer):
         for role in cls.expected_tensors(spec):
-            out.append((f"{prefix}.{role.name}", role))
+            out.append((f"{slot}.{role.name}", role))
     return out
 
 

@@ -1,7 +1,8 @@
 """Random weights for a configuration: in memory, or as a model folder (config.json and
 model.safetensors) that every loader of the framework reads like a downloaded one.
 
-Matrices and biases are N(0, std) and N(0, bias_std); norm weights are 1 + N(0, norm_std).  Each
+Matrices and biases are N(0, std) and N(0, bias_std); norm weights are 1 + N(0, norm_std); which
+of these a tensor is says the `role` of the part's `TensorRole`, never its name.  Each
 tensor has a generator of its own, seeded from (seed, tensor name), so the values do not depend on
 the order or on which other tensors exist.  The reference has no such mode in its engine; its tests
 write a seeded three-tensor fixture (tests/regression/mk_tiny_st.py:21-45).
@@ -20,14 +21,6 @@ from .loader import expected_tensors
 from .safetensors_io import write_safetensors
 
 
-def _kind(name: str) -> str:
-    if name.endswith("bias"):
-        return "bias"
-    if "norm" in name.rsplit(".", 2)[-2] or name.endswith("norm.weight"):
-        return "norm"
-    return "matrix"
-
-
 def random_tensors(spec: ModelSpec, seed: int, std: float = 0.02, bias_std: Optional[float] = None,
                    norm_std: float = 0.02, dtype: torch.dtype = torch.bfloat16,
                    device: str = "cpu") -> Dict[str, torch.Tensor]:
@@ -36,7 +29,7 @@ def random_tensors(spec: ModelSpec, seed: int, std: float = 0.02, bias_std: Opti
     for name, role in expected_tensors(spec).items():
         gen = torch.Generator(device=device)
         gen.manual_seed((int(seed) * 1000003 + zlib.crc32(name.encode())) % (2**63))
-        kind = "matrix" if role.matrix else _kind(name)
+        kind = role.init_role()            # what the part says the tensor is for; the checkpoint's name plays no part
         if role.matrix and device != "cpu" and len(role.shape) == 2 and role.shape[0] * role.shape[1] > (1 << 26):
             # large tables are filled in row blocks so the float32 draw never doubles their footprint
             t = torch.empty(role.shape, dtype=dtype, device=device)
@@ -47,7 +40,7 @@ def random_tensors(spec: ModelSpec, seed: int, std: float = 0.02, bias_std: Opti
             out[name] = t
             continue
         x = torch.randn(role.shape, generator=gen, dtype=torch.float32, device=device)
-        if kind == "norm":
+        if kind == "scale":
             x = 1.0 + norm_std * x
         elif kind == "bias":
             x = bias_std * x

@@ -67,8 +67,17 @@ class SafetensorsFile:
         (hlen,) = struct.unpack("<Q", self._mm[:8])
         if hlen > size - 8:
             raise SafetensorsError(f"{path}: header length {hlen} exceeds the file ({size} bytes)")
+        def no_duplicates(pairs):
+            # two entries of one name: the reference stops (qwen_infer.c:345-350); Python's parser would keep the last
+            seen = {}
+            for k, v in pairs:
+                if k in seen:
+                    raise SafetensorsError(f"{path}: duplicate tensor name in the header: {k}")
+                seen[k] = v
+            return seen
+
         try:
-            header = json.loads(self._mm[8:8 + hlen].decode("utf-8"))
+            header = json.loads(self._mm[8:8 + hlen].decode("utf-8"), object_pairs_hook=no_duplicates)
         except (UnicodeDecodeError, json.JSONDecodeError) as e:
             raise SafetensorsError(f"{path}: header is not valid JSON: {e}") from e
         if not isinstance(header, dict):

@@ -4,7 +4,9 @@ It rests on the formulas of popixoxipop-collab/beglin's `qwen_infer.c` (each fun
 lines it restates): that file needs Apple's Accelerate and ARM NEON headers and does not compile on
 an x86 Linux host, so the model math cannot be compared with the reference's own binary here.
 
-Whole sequences, no cache, one function per part, CPU tensors.  It shares no code with the
+Whole sequences, no cache, one function per part, plain tensor arithmetic on whatever device the
+weights lie (the CPU by default; long sequences may be given weights on a GPU, in float64 still).
+It shares no code with the
 `beglin_b200` package: it reads the model folder with the `json` module and the `safetensors`
 library and computes in float64 by default (float32 on request), so a fault of the engine's loader,
 cache, batching or kernels cannot be mirrored here.
@@ -62,7 +64,7 @@ def layer_window(cfg: dict, layer: int) -> Optional[int]:
 # ----------------------------------------------------------------------------- parts
 def embed(table: torch.Tensor, ids: Sequence[int]) -> torch.Tensor:
     """x = E[id], a row gather without scaling (qwen_infer.c:1438-1439, :2067)."""
-    return table[torch.as_tensor(list(ids), dtype=torch.long)]
+    return table[torch.as_tensor(list(ids), dtype=torch.long, device=table.device)]
 
 
 def rmsnorm(x: torch.Tensor, g: torch.Tensor, eps: float) -> torch.Tensor:
@@ -111,13 +113,14 @@ def rope_angles(positions: Sequence[int], rot: int, theta: float, dtype,
     if scale is not None:
         inv = inv * scale
     pos = torch.as_tensor(list(positions), dtype=torch.float64)
-    return (pos[:, None] * inv[None, :]).to(dtype)
+    return (pos[:, None] * inv[None, :]).to(dtype)            # on the CPU; `rope_split_half` moves it to its operand
 
 
 def rope_split_half(v: torch.Tensor, ang: torch.Tensor) -> torch.Tensor:
     """Pairs (i, i+hd/2): v[i] = a*c - b*s; v[i+hd/2] = b*c + a*s (qwen_infer.c:782-790, the
     split-half branch).  v is [T, heads, hd], ang is [T, hd/2]."""
     half = v.shape[-1] // 2
+    ang = ang.to(v.device)
     c = torch.cos(ang)[:, None, :]
     s = torch.sin(ang)[:, None, :]
     a, b = v[..., :half], v[..., half:]
@@ -144,23 +147,28 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group: int,
     return out.reshape(T, nh * hd)
 
 
-def attention_fast(q, k, v, group, window=None):
-    """The same sums as `attention`, as matrix products with a mask (for long sequences)."""
+def attention_fast(q, k, v, group, window=None, rows_at_a_time: int = 1024):
+    """The same sums as `attention`, as matrix products with a mask (for long sequences), a block of
+    query rows at a time so that the scores of a long sequence need not be held all at once."""
     T, nh, hd = q.shape
     scale = 1.0 / math.sqrt(float(hd))
     kk = k.repeat_interleave(group, dim=1)          # head h reads kv head h // group
     vv = v.repeat_interleave(group, dim=1)
-    s = torch.einsum("phd,thd->hpt", q, kk) * scale
-    p_idx = torch.arange(T)[:, None]
-    t_idx = torch.arange(T)[None, :]
-    ok = t_idx <= p_idx
-    if window is not None:
-        ok = ok & (t_idx > p_idx - window)
-    s = s.masked_fill(~ok[None], float("-inf"))
-    s = s - s.max(dim=-1, keepdim=True).values
-    e = torch.exp(s)
-    pr = e / e.sum(dim=-1, keepdim=True)
-    return torch.einsum("hpt,thd->phd", pr, vv).reshape(T, nh * hd)
+    out = torch.empty(T, nh, hd, dtype=q.dtype, device=q.device)
+    t_idx = torch.arange(T, device=q.device)[None, :]
+    for lo in range(0, T, rows_at_a_time):
+        hi = min(T, lo + rows_at_a_time)
+        s = torch.einsum("phd,thd->hpt", q[lo:hi], kk[:hi]) * scale
+        p_idx = torch.arange(lo, hi, device=q.device)[:, None]
+        ok = t_idx[:, :hi] <= p_idx
+        if window is not None:
+            ok = ok & (t_idx[:, :hi] > p_idx - window)
+        s = s.masked_fill(~ok[None], float("-inf"))
+        s = s - s.max(dim=-1, keepdim=True).values
+        e = torch.exp(s)
+        pr = e / e.sum(dim=-1, keepdim=True)
+        out[lo:hi] = torch.einsum("hpt,thd->phd", pr, vv[:hi])
+    return out.reshape(T, nh * hd)
 
 
 def swiglu(g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:

@@ -135,3 +135,45 @@ def test_random_orders_lose_nothing(seed):
         m.release(rid)
     m.check()
     assert m.free_pages() == 12
+
+
+def test_a_request_that_starts_again_under_its_name_is_another_request():
+    """Whoever remembers what the device holds for a request (a replayed graph) compares identities, not
+    names: the same name after a release is a new request, with other pages in another order."""
+    m = manager(pages=8, page=4, reqs=2)
+    m.add_request("r"); m.add_request("s")
+    m.reserve([("r", 5), ("s", 3)]); m.commit([("r", 5), ("s", 3)])
+    first = m.identity(["r", "s"])
+    assert m.identity(["r", "s"]) == first
+    table = m.block_table(0, ["r"]).tolist()
+    m.release("r")
+    m.release("s")
+    m.add_request("r")
+    m.reserve([("r", 5)]); m.commit([("r", 5)])
+    assert m.length("r") == 5 and m.identity(["r"]) != first[:1]        # same name, same length, another request
+    assert m.block_table(0, ["r"]).tolist() != table                     # and its pages lie elsewhere
+    m.check()
+
+
+def test_trim_gives_back_what_a_step_that_did_not_happen_had_reserved():
+    m = manager(window=6, pages=8, page=4, reqs=2)
+    m.add_request("r")
+    m.reserve([("r", 6)]); m.commit([("r", 6)])
+    free = [g.pool.num_free for g in m.kv_groups]
+    m.reserve([("r", 19)])                       # reserved for a step ...
+    assert [g.pool.num_free for g in m.kv_groups] != free
+    m.trim(["r", "not live"])                    # ... that failed
+    assert [g.pool.num_free for g in m.kv_groups] == free and m.length("r") == 6
+    m.check()
+    m.reserve([("r", 7)]); m.commit([("r", 7)])  # and the request goes on
+    m.check()
+
+
+def test_spare_page_and_slot_are_never_handed_out():
+    m = manager(pages=3, page=4, reqs=2, extra=[FixedStateNeed((2,))])
+    for i in range(2):
+        m.add_request(i)
+    m.reserve([(0, 8), (1, 4)])
+    held = {p for g in m.kv_groups for t in g.tables.values() for p in t}
+    assert m.dump_page == 3 and m.dump_page not in held and max(held) < 3
+    assert m.dump_slot == 2 and m.dump_slot not in m.slots.values()

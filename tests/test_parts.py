@@ -182,10 +182,10 @@ def toy_spec(cfg_json, order=None, share=False):
     l1 = spec.layers[1]
     names = {k: v for k, v in l1.names.items() if not k.startswith("mixer.")}
     names["mixer.w.weight"] = "model.layers.1.toy.w.weight"
-    spec.layers[1] = dataclasses.replace(l1, mixer=DecaySpec(hidden=cfg.hidden_size, decay=0.5), names=names)
+    spec.layers[1] = l1.with_parts(mixer=DecaySpec(hidden=cfg.hidden_size, decay=0.5), names=names)
     if share:
         l2 = spec.layers[2]
-        spec.layers[2] = dataclasses.replace(l2, mixer=dataclasses.replace(l2.mixer, own_kv=False))
+        spec.layers[2] = l2.with_parts(mixer=dataclasses.replace(l2.mixer, own_kv=False))
     if order is not None:
         spec.order = [Stage(*o) if isinstance(o, tuple) else Stage(o) for o in order]
     return spec, cfg

@@ -50,12 +50,14 @@ def test_norm_is_left_to_the_product_only_with_valid_squares_and_a_willing_norm(
 
 def test_decode_splits_make_one_wave():
     from beglin_b200.csrc.ops import decode_splits
-    for streams in (1, 2, 7, 16, 32, 100, 148, 500):
-        for context in (1, 200, 256, 257, 4096, 100000):
-            n = decode_splits(streams, context)
-            assert n >= 1 and (streams * n <= 148 or n == 1)
-            assert n <= max(1, -(-context // 256))
-    assert decode_splits(16, 4096) == 8 and decode_splits(2, 4096) == 16 and decode_splits(128, 4096) == 1
+    for sms in (148, 132, 20):
+        for streams in (1, 2, 7, 16, 32, 100, 148, 500):
+            for context in (1, 200, 256, 257, 4096, 100000):
+                n = decode_splits(streams, context, sms=sms)
+                assert n >= 1 and (streams * n <= sms or n == 1)
+                assert n <= max(1, -(-context // 256))
+    assert decode_splits(16, 4096, sms=148) == 8 and decode_splits(2, 4096, sms=148) == 16
+    assert decode_splits(128, 4096, sms=148) == 1
 
 
 def test_which_steps_a_portion_graph_stands_for_and_which_graphs_are_kept():

@@ -188,7 +188,7 @@ def test_toy_routed_feed_forward_in_one_layer():
     names = {k: v for k, v in l1.names.items() if not k.startswith("feed_forward.")}
     roles = register_toy_routed().expected_tensors(rs)
     names.update({"feed_forward." + r.name: "model.layers.1.toy." + r.name for r in roles})
-    spec.layers[1] = dataclasses.replace(l1, feed_forward=rs, names=names)
+    spec.layers[1] = l1.with_parts(feed_forward=rs, names=names)
     tensors = random_tensors(spec, 11, std=0.05, dtype=torch.float32)
     assert "model.layers.1.mlp.gate_proj.weight" not in tensors and "model.layers.1.toy.experts.4.down.weight" in tensors
     # a router that spreads the tokens: larger logits than the random draw gives
@@ -214,7 +214,7 @@ def test_toy_position_encoding_in_one_layer(dtype, tol):
     spec = arch.build_spec(cfg)
     ps = PhaseSpec(rotary_dim=8, step=0.37, phase=(0.1, -0.7, 1.9, 0.4))
     l0 = spec.layers[0]
-    spec.layers[0] = dataclasses.replace(l0, mixer=dataclasses.replace(l0.mixer, position=ps))
+    spec.layers[0] = l0.with_parts(mixer=dataclasses.replace(l0.mixer, position=ps))
     tensors = random_tensors(spec, 12, std=0.08, bias_std=0.05, dtype=torch.float32)
     if dtype == "bfloat16":
         tensors = {k: v.to(torch.bfloat16) for k, v in tensors.items()}
@@ -223,3 +223,102 @@ def test_toy_position_encoding_in_one_layer(dtype, tol):
     ids = {"a": seeded_ids(37, 256, 5), "b": seeded_ids(21, 256, 6)}
     want = {r: plain_forward(TINY_A, w, ids[r], phase={0: ps}) for r in ids}
     whole_and_cut(eng, ids, want, tol)
+
+
+# ------------------------------------------------------------------------------------------------
+# Two block arrangements the framework does not have.  "toy_parallel": one norm, the mixer and the
+# feed-forward both read it, x += mixer(h) + feed_forward(h): three slots.  "toy_ff_post": no mixer at
+# all and the norm AFTER the part, x += norm(feed_forward(x_bf)): two slots, one of them a norm that is
+# applied to the part's result instead of to the stream.
+
+def register_toy_blocks():
+    from beglin_b200.parts import register_block
+
+    @register_block("toy_parallel")
+    class ParallelBlock:
+        SLOTS = (("norm", "norm"), ("mixer", "mixer"), ("feed_forward", "feed_forward"))
+
+        def __init__(self, norm, mixer, feed_forward):
+            self.norm, self.mixer, self.feed_forward = norm, mixer, feed_forward
+
+        def forward(self, stream, batch, cache):
+            h = self.norm.add_norm(stream.x, stream.pending)      # adds what is owed, then norms
+            stream.pending = stream.ssq = None
+            a = self.mixer.forward(h, batch, cache)
+            m = self.feed_forward.forward(h, batch)
+
+            def whole(t):                                          # a product may return partial sums over ranges of K
+                return (t.sum(dim=0) if t.dim() == 3 else t).float()
+            stream.owe(whole(a) + whole(m))
+
+    @register_block("toy_ff_post")
+    class FeedForwardPostNormBlock:
+        SLOTS = (("feed_forward", "feed_forward"), ("post_norm", "norm"))
+
+        def __init__(self, feed_forward, post_norm):
+            self.feed_forward, self.post_norm = feed_forward, post_norm
+
+        def forward(self, stream, batch, cache):
+            assert cache is None                                   # a layer without a mixer has no cache
+            if stream.pending is not None:
+                p = stream.pending
+                stream.x += (p.sum(dim=0) if p.dim() == 3 else p).float()
+                stream.pending = stream.ssq = None
+            m = self.feed_forward.forward(stream.x.to(self.feed_forward.ctx.compute_dtype), batch)
+            m = (m.sum(dim=0) if m.dim() == 3 else m).float().contiguous()
+            stream.owe(self.post_norm.add_norm(m, None, update=False).float())
+
+
+def plain_toy_blocks_forward(cfg, w, ids):
+    """Layer 0: the reference's block.  Layer 1: parallel.  Layer 2: feed-forward only, norm after it."""
+    sz = plain.sizes(cfg)
+    eps, theta = cfg["rms_norm_eps"], cfg["rope_theta"]
+    x = plain.embed(w["model.embed_tokens.weight"], ids)
+    p = "model.layers.0."
+    h = plain.rmsnorm(x, w[p + "input_layernorm.weight"], eps)
+    x = x + plain.attention_block(h, w, p + "self_attn.", sz, theta, None, fast=True)
+    h = plain.rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps)
+    x = x + plain.mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    p = "model.layers.1."
+    h = plain.rmsnorm(x, w[p + "input_layernorm.weight"], eps)
+    x = x + plain.attention_block(h, w, p + "self_attn.", sz, theta, None, fast=True) \
+        + plain.mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    p = "model.layers.2."
+    m = plain.mlp(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    x = x + plain.rmsnorm(m, w[p + "after.weight"], eps)
+    return plain.head(x, w, cfg)
+
+
+def test_toy_blocks_with_other_slots():
+    """A block kind declares its slots; the loader asks exactly those parts for their tensors and the model
+    builds exactly those parts.  Three layers with three arrangements (four slots, three, two; one without a
+    mixer and therefore without a cache) run whole and cut against the plain computation written out by hand."""
+    from beglin_b200 import Engine
+    from beglin_b200.config import load_config
+    from beglin_b200.parts import LayerSpec
+    from beglin_b200.weights import TensorDict, expected_tensors, random_tensors
+    register_toy_blocks()
+    arch, cfg = load_config(TINY_B)
+    spec = arch.build_spec(cfg)
+    l1, l2 = spec.layers[1], spec.layers[2]
+    names1 = {k: v for k, v in l1.names.items() if not k.endswith("_norm.weight")}
+    names1["norm.weight"] = "model.layers.1.input_layernorm.weight"
+    spec.layers[1] = LayerSpec({"norm": l1.mixer_norm, "mixer": l1.mixer, "feed_forward": l1.feed_forward},
+                               names1, block="toy_parallel")
+    names2 = {k: v for k, v in l2.names.items() if k.startswith("feed_forward.")}
+    names2["post_norm.weight"] = "model.layers.2.after.weight"
+    spec.layers[2] = LayerSpec({"feed_forward": l2.feed_forward, "post_norm": l2.feed_forward_norm}, names2,
+                               block="toy_ff_post")
+    wanted = set(expected_tensors(spec))
+    assert "model.layers.1.post_attention_layernorm.weight" not in wanted
+    assert "model.layers.2.after.weight" in wanted and not any(".2.self_attn." in n for n in wanted)
+    with pytest.raises(KeyError, match="lacks"):
+        expected_tensors(dataclasses.replace(spec, layers=[spec.layers[0], spec.layers[1],
+                                                           LayerSpec({"feed_forward": l2.feed_forward}, names2, "toy_ff_post")]))
+    tensors = random_tensors(spec, 13, std=0.05, bias_std=0.05, dtype=torch.float32)
+    eng = Engine(spec, TensorDict(tensors), dtype="float32", max_tokens=256, page_size=16, max_requests=3, kv_split=64)
+    assert [type(n).__name__ if n is not None else None for n in eng.model.cache_needs()] == ["PagedKVNeed", "PagedKVNeed", None]
+    w = {k: v.double() for k, v in tensors.items()}
+    ids = {"a": seeded_ids(41, 384, 7), "b": seeded_ids(22, 384, 8)}
+    want = {r: plain_toy_blocks_forward(TINY_B, w, ids[r]) for r in ids}
+    whole_and_cut(eng, ids, want, TOL_F32)

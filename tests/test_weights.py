@@ -59,6 +59,22 @@ def test_random_weights_are_seeded_and_independent_of_order():
     assert abs(float(a["model.layers.1.mlp.up_proj.weight"].std()) - 0.02) < 0.003
 
 
+def test_random_weights_follow_the_role_not_the_name():
+    """How a tensor is drawn is what its part says it is for.  A model whose checkpoint calls a projection
+    matrix "...norm.bias" and a norm's weight "...matrix" still gets a matrix around zero and a scale around one."""
+    spec = spec_of(TINY_A)
+    layer = spec.layers[0]
+    names = dict(layer.names)
+    names["mixer.o_proj.weight"] = "odd.names.out_norm.bias"
+    names["mixer_norm.weight"] = "odd.names.first.matrix"
+    names["mixer.q_proj.bias"] = "odd.names.q_norm.weight"
+    spec.layers[0] = layer.with_parts(names=names)
+    t = random_tensors(spec, 7, std=0.02, bias_std=0.3, norm_std=0.02, dtype=torch.float32)
+    assert abs(float(t["odd.names.out_norm.bias"].mean())) < 0.005 and abs(float(t["odd.names.out_norm.bias"].std()) - 0.02) < 0.004
+    assert abs(float(t["odd.names.first.matrix"].mean()) - 1.0) < 0.02
+    assert abs(float(t["odd.names.q_norm.weight"].std()) - 0.3) < 0.08 and abs(float(t["odd.names.q_norm.weight"].mean())) < 0.15
+
+
 def test_one_error_lists_missing_unexpected_and_wrong_shapes():
     spec = spec_of(TINY_A)
     t = random_tensors(spec, 0, dtype=torch.float32)
@@ -121,6 +137,13 @@ def test_container_faults_are_refused(tmp_path):
         Checkpoint(p)
     with pytest.raises(SafetensorsError, match="could not open"):
         Checkpoint(str(tmp_path / "none.safetensors"))
+    # one name twice in the header: refused, as the reference refuses it (qwen_infer.c:345-350)
+    entry = '{"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}'
+    text = ('{"t": ' + entry + ', "u": ' + entry + ', "t": ' + entry + '}').encode()
+    with open(p, "wb") as f:
+        f.write(struct.pack("<Q", len(text)) + text + b"\0" * 8)
+    with pytest.raises(SafetensorsError, match="duplicate tensor name in the header: t"):
+        Checkpoint(p)
 
 
 def test_sharded_folder(tmp_path):
