@@ -14,7 +14,12 @@ Variables kept, with the reference's meanings: QWEN_BASE (here: the model folder
 and model.safetensors), QWEN_PROMPT (file of little-endian int32 token ids; default
 <QWEN_BASE>/ref/prompt_ids.i32), QWEN_SAFETENSORS_MAXSEQ (context cap, default 2048), QWEN_BATCH
 (live requests, default 8), QWEN_CB_REQS (default 12), QWEN_CB_REPS (default 3),
-QWEN_CB_PREFILL_BUDGET (prompt tokens per step, default 16), QWEN_CB_STOP_EXTRA (an extra stop id).
+QWEN_CB_PREFILL_BUDGET (prompt tokens per step, default 16), QWEN_CB_STOP_EXTRA (an extra stop id),
+QWEN_CB_MIXED (default 1; 0 runs every prompt in steps of its own while the decoding requests wait, for the
+comparison of the two orders, qwen_infer.c:20690), QWEN_HF_CONFIG (a config.json that stands elsewhere than in
+the model folder, :20121), QWEN_PROF (1: in `bench` and `greedy`, device time per kernel class from CUDA events,
+printed with the share of the total that the classes add up to, :1224-1235 and :20463-20486; the steps then
+run kernel by kernel, not as replayed graphs).
 Added: QWEN_DTYPE (bf16 | fp32, default bf16), QWEN_TEMPERATURE and QWEN_SEED (sampling),
 QWEN_PAGE_SIZE (default 64), QWEN_NUM_PAGES, QWEN_RANDOM (a seed: write random weights for
 <QWEN_BASE>/config.json first, if the folder has no model.safetensors), QWEN_DUMP_DIR.
@@ -42,6 +47,39 @@ def _err(msg: str) -> int:
 def load_ids(path: str, limit: int) -> List[int]:
     """Raw little-endian int32 ids (qwen_infer.c:2168-2170)."""
     return np.fromfile(path, dtype="<i4")[:limit].astype(np.int64).tolist()
+
+
+class PhaseReport:
+    """QWEN_PROF: device time per kernel class between its making and `close`, measured with CUDA events
+    around every launch of the class, against the device time of the whole stretch.  The classes do not add
+    up to the total: what is missing is the time in which no kernel of the package ran (launch gaps of steps
+    that run kernel by kernel, library products of steps of many rows).  The closing line says how much they
+    cover, as the reference's does (qwen_infer.c:20463-20467)."""
+
+    def __init__(self, ops):
+        import torch
+        self.ops, self.torch = ops, torch
+        self.t0, self.t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ops.profile_begin()
+        self.t0.record()
+        self.phases = None
+
+    def close(self) -> None:
+        if self.phases is None:
+            self.t1.record()
+            self.phases = self.ops.profile_end()
+            self.total_ms = self.t0.elapsed_time(self.t1)
+
+    def print(self, ctx: int, n: int, unit: str) -> None:
+        self.close()
+        total = self.total_ms / n
+        covered = sum(ms for ms, _ in self.phases.values()) / n
+        print(f"[prof] ctx~{ctx} total={total:.3f}ms/{unit} sum(phases)={covered:.3f}ms/{unit} "
+              f"closure={100.0 * covered / total if total > 0 else 0.0:.1f}%", file=sys.stderr)
+        for name, (ms, count) in self.phases.items():
+            print(f"[prof]   {name:14s} {ms / n:.4f} ms ({100.0 * ms / n / total if total > 0 else 0.0:.2f}%) in {count} brackets",
+                  file=sys.stderr)
+        print(f"PROF ctx {ctx} total_ms {total:.4f} " + " ".join(f"{k} {ms / n:.4f}" for k, (ms, _) in self.phases.items()))
 
 
 def describe(spec) -> str:
@@ -76,8 +114,10 @@ def main(argv: List[str]) -> int:
     base = os.environ.get("QWEN_BASE")
     if not base:
         return _err("QWEN_BASE is not set (the model folder with config.json and model.safetensors)")
-    if not os.path.exists(os.path.join(base, "config.json")):
-        return _err(f"{base}: no arch config (config.json) found")
+    config_path = os.environ.get("QWEN_HF_CONFIG") or os.path.join(base, "config.json")
+    if not os.path.exists(config_path):
+        return _err(f"{config_path}: no arch config (config.json) found")
+    prof = bool(_env_int("QWEN_PROF", 0))
 
     import torch
     from .engine.engine import Engine
@@ -92,7 +132,7 @@ def main(argv: List[str]) -> int:
             and not os.path.exists(os.path.join(base, "model.safetensors.index.json")):
         import json
         from .weights import write_random_model
-        with open(os.path.join(base, "config.json")) as f:
+        with open(config_path) as f:
             cfg_json = json.load(f)
         print(f"[engine] writing random weights (seed {seed_random}) to {base}", file=sys.stderr)
         write_random_model(base, cfg_json, int(seed_random),
@@ -111,11 +151,11 @@ def main(argv: List[str]) -> int:
     live = batch if mode == "cbatch" else 1
     num_pages = _env_int("QWEN_NUM_PAGES", live * -(-maxseq // page))
     try:
-        eng = Engine.from_folder(base, dtype=dtype, max_tokens=num_pages * page, page_size=page,
-                                 max_requests=live, max_context=maxseq)
+        eng = Engine.from_folder(base, config_path=config_path, dtype=dtype, max_tokens=num_pages * page, page_size=page,
+                                 max_requests=live, max_context=maxseq, use_graphs=not prof)
     except Exception as e:                                   # one line, as the reference's FATALs
         return _err(str(e))
-    print(f"[engine] arch config ({base}): {describe(eng.spec)} MAXSEQ={maxseq} DTYPE={dtype}", file=sys.stderr)
+    print(f"[engine] arch config ({config_path}): {describe(eng.spec)} MAXSEQ={maxseq} DTYPE={dtype}", file=sys.stderr)
     temperature = float(os.environ.get("QWEN_TEMPERATURE", "0"))
     seed = _env_int("QWEN_SEED", 0)
 
@@ -158,8 +198,11 @@ def main(argv: List[str]) -> int:
 
     if mode == "greedy":
         room = maxseq - len(prompt)
-        out = eng.generate([prompt], max_new_tokens=min(n_gen, max(room, 0) + 1), temperature=temperature,
-                           seed=seed, stop_ids=())[0]
+        n_new = min(n_gen, max(room, 0) + 1)
+        timer = PhaseReport(ops) if prof else None
+        out = eng.generate([prompt], max_new_tokens=n_new, temperature=temperature, seed=seed, stop_ids=())[0]
+        if timer:
+            timer.print(len(prompt) + len(out), max(1, len(prompt) + len(out) - 1), "tok (prompt and new)")
         print("greedy:" + "".join(f" {t}" for t in out))
         return 0
 
@@ -178,13 +221,21 @@ def main(argv: List[str]) -> int:
                 logits = eng.step([("b", [int(tok[0])], [0])])
                 tok = eng.sampler.greedy(logits)
             torch.cuda.synchronize()
+            timer = PhaseReport(ops) if prof else None
             t0 = time.perf_counter()
             for _ in range(N):
                 logits = eng.step([("b", [int(tok[0])], [0])], check=False)
                 tok = eng.sampler.greedy(logits)
             torch.cuda.synchronize()
-            best = min(best, time.perf_counter() - t0)
+            took = time.perf_counter() - t0
+            if timer:
+                timer.close()
+                if took < best:
+                    best_timer = timer
+            best = min(best, took)
             eng.release("b")
+        if prof:
+            best_timer.print(len(prompt) + 8, N, "tok")
         ms = best / N * 1e3
         print(f"[bench] {dtype} N={N} pos~{len(prompt) + 8}: {ms:.3f} ms/tok = {1000.0 / ms:.2f} tok/s", file=sys.stderr)
         print(f"tok_s {1000.0 / ms:.3f} ms_tok {ms:.2f}")
@@ -195,6 +246,7 @@ def main(argv: List[str]) -> int:
     reps = max(1, _env_int("QWEN_CB_REPS", 3))
     budget = max(1, _env_int("QWEN_CB_PREFILL_BUDGET", 16))
     stop_extra = _env_int("QWEN_CB_STOP_EXTRA", -1)
+    mixed = bool(_env_int("QWEN_CB_MIXED", 1))
     spread = n_gen if n_gen > 1 else 27
     plen = [min(len(prompt), 4 + (r * 13) % 37) for r in range(R)]
     maxnew = [6 + (r * 7) % spread for r in range(R)]
@@ -204,7 +256,7 @@ def main(argv: List[str]) -> int:
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         reqs = eng.generate([prompt[:n] for n in plen], max_new_tokens=maxnew, temperature=temperature, seed=seed,
-                            stop_ids=stops, max_batch=batch, prefill_budget=budget, return_requests=True)
+                            stop_ids=stops, max_batch=batch, prefill_budget=budget, return_requests=True, mixed=mixed)
         torch.cuda.synchronize()
         wall = time.perf_counter() - t0
         if wall < best_wall:
@@ -219,7 +271,7 @@ def main(argv: List[str]) -> int:
         print(f"cbatch req{i} plen {plen[i]} maxnew {maxnew[i]} nout {len(r.output)}:" + "".join(f" {t}" for t in r.output))
     print(f"agg_tok_s {tot / best_wall:.3f} wall_s {best_wall:.3f} util {c.utilisation(batch):.4f} "
           f"avg_active {c.decode_rows / max(1, c.steps):.3f} B {batch} R {R} tok {tot} reps_identical "
-          f"{int(identical)} mixed 1 steps {c.steps} msteps {c.mixed_steps} pfonly {c.prefill_only_steps} "
-          f"pf_cols {c.prefill_rows} tbt_max_ms {c.gap_max_s * 1e3:.3f} tbt_mean_ms {c.gap_mean_s() * 1e3:.3f} "
+          f"{int(identical)} mixed {int(mixed)} steps {c.steps} msteps {c.mixed_steps} pfonly {c.prefill_only_steps} "
+          f"pstall {c.prefill_stalls} pf_cols {c.prefill_rows} tbt_max_ms {c.gap_max_s * 1e3:.3f} tbt_mean_ms {c.gap_mean_s() * 1e3:.3f} "
           f"preemptions {c.preemptions}")
     return 0

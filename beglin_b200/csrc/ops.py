@@ -106,6 +106,81 @@ def _check(rc: int, name: str) -> None:
     raise KernelError(f"{name}: CUDA error {rc} at launch")
 
 
+# ------------------------------------------------------------------------------------------------
+# Phase timers (the reference's QWEN_PROF, qwen_infer.c:1224-1235): while a profile is open, every kernel
+# class is bracketed by two CUDA events on the launching stream; `profile_end` adds up the device time
+# between them per class.  Closed, `phase` hands out one shared do-nothing context.
+class _NoPhase:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+class _Phase:
+    __slots__ = ("name", "start")
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        self.start = torch.cuda.Event(enable_timing=True)
+        self.start.record()
+
+    def __exit__(self, *exc):
+        end = torch.cuda.Event(enable_timing=True)
+        end.record()
+        _profile.append((self.name, self.start, end))
+        return False
+
+
+_NO_PHASE = _NoPhase()
+_profile = None            # None: closed; a list of (class, start event, end event) while open
+_depth = 0
+
+
+def phase(name: str):
+    """Context for the launches of one kernel class.  Phases do not nest: inside an open phase an inner
+    one is part of it."""
+    if _profile is None:
+        return _NO_PHASE
+    return _Outer(name)
+
+
+class _Outer(_Phase):
+    def __enter__(self):
+        global _depth
+        _depth += 1
+        if _depth == 1:
+            super().__enter__()
+
+    def __exit__(self, *exc):
+        global _depth
+        if _depth == 1:
+            super().__exit__(*exc)
+        _depth -= 1
+        return False
+
+
+def profile_begin() -> None:
+    global _profile, _depth
+    _profile, _depth = [], 0
+
+
+def profile_end() -> dict:
+    """Close the profile: {kernel class: (device milliseconds, brackets)} in order of first use.  Waits for
+    the device."""
+    global _profile
+    records, _profile = _profile or [], None
+    torch.cuda.synchronize()
+    out = {}
+    for name, start, end in records:
+        ms, n = out.get(name, (0.0, 0))
+        out[name] = (ms + start.elapsed_time(end), n + 1)
+    return out
+
+
 def _dt(t: torch.Tensor) -> int:
     if t.dtype == torch.float32:
         return F32
@@ -167,8 +242,9 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stat
     T, d = ids.numel(), table.shape[1]
     if out.dtype != torch.float32 or tuple(out.shape) != (T, d) or not out.is_contiguous() or not table.is_contiguous():
         raise KernelError("embed_gather: out must be contiguous float32 [T, d] and the table contiguous")
-    _check(lib().bg_embed_gather(_p(table), _dt(table), _p(ids), _p(out), T, d, table.shape[0], _p(status), _stream()),
-           "embed_gather")
+    with phase("emb_gather"):
+        _check(lib().bg_embed_gather(_p(table), _dt(table), _p(ids), _p(out), T, d, table.shape[0], _p(status), _stream()),
+               "embed_gather")
 
 
 def _parts(t: torch.Tensor, what: str):
@@ -199,16 +275,18 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
             raise KernelError("add_rmsnorm: delta must be contiguous and shaped like x")
     if rows is not None:
         _i32(rows, "rows")
-    _check(lib().bg_add_rmsnorm(_p(x), _p(delta), _dt(delta) if delta is not None else F32, parts, stride, _p(weight),
-                                _dt(weight), float(eps), _p(out), _dt(out), _p(rows), n, d, 1 if update else 0,
-                                _stream()), "add_rmsnorm")
+    with phase("rmsnorm"):
+        _check(lib().bg_add_rmsnorm(_p(x), _p(delta), _dt(delta) if delta is not None else F32, parts, stride, _p(weight),
+                                    _dt(weight), float(eps), _p(out), _dt(out), _p(rows), n, d, 1 if update else 0,
+                                    _stream()), "add_rmsnorm")
 
 
 def add_residual(x: torch.Tensor, delta: torch.Tensor) -> None:
     _cuda(x, delta)
     if x.dtype != torch.float32 or x.shape != delta.shape or not x.is_contiguous() or not delta.is_contiguous():
         raise KernelError("add_residual: x must be contiguous float32 and delta shaped like it")
-    _check(lib().bg_add_residual(_p(x), _p(delta), _dt(delta), x.numel(), _stream()), "add_residual")
+    with phase("residuals"):
+        _check(lib().bg_add_residual(_p(x), _p(delta), _dt(delta), x.numel(), _stream()), "add_residual")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
@@ -224,8 +302,9 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
         raise KernelError("swiglu: tensors must be contiguous")
     if block < 0 or (block > 0 and im % block):
         raise KernelError(f"swiglu: blocks of {block} do not divide {im} features")
-    _check(lib().bg_swiglu(_p(gate_up), _dt(gate_up), parts, stride, _p(out), _dt(out), rows, im, block, _stream()),
-           "swiglu")
+    with phase("swiglu"):
+        _check(lib().bg_swiglu(_p(gate_up), _dt(gate_up), parts, stride, _p(out), _dt(out), rows, im, block, _stream()),
+               "swiglu")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
@@ -236,7 +315,8 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tenso
     if inv_freq.dtype != torch.float32 or out.dtype != torch.float32 or tuple(out.shape) != (T, half, 2) \
             or not out.is_contiguous() or not inv_freq.is_contiguous():
         raise KernelError("rope_table: inv_freq float32 [half], out contiguous float32 [T, half, 2]")
-    _check(lib().bg_rope_table(_p(positions), _p(inv_freq), _p(out), T, half, _stream()), "rope_table")
+    with phase("rope"):
+        _check(lib().bg_rope_table(_p(positions), _p(inv_freq), _p(out), T, half, _stream()), "rope_table")
 
 
 def rope_kv_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh: int, nkv: int, hd: int, rot: int,
@@ -262,11 +342,12 @@ def rope_kv_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh: int,
         num_pages = kv_pool.shape[0]
     if rot > 0 and (cos_sin is None or cos_sin.shape[0] < n_rows or cos_sin.shape[1] != rot // 2 or cos_sin.dtype != torch.float32):
         raise KernelError("rope_kv_append: cos_sin must be float32 [T, rot/2, 2]")
-    _check(lib().bg_rope_kv_append(_p(src), _dt(src), src.stride(-2), parts, stride, _p(q_out), _dt(q_out),
-                                   q_out.stride(0), _p(cos_sin), _p(positions), _p(row_req), _p(block_table),
-                                   block_table.shape[1], _p(kv_pool), _dt(kv_pool) if kv_pool is not None else F32,
-                                   num_pages, page_size, n_rows, nh, nkv, hd, rot, 1 if interleaved else 0,
-                                   _p(status), _stream()), "rope_kv_append")
+    with phase("rope+kv_write"):
+        _check(lib().bg_rope_kv_append(_p(src), _dt(src), src.stride(-2), parts, stride, _p(q_out), _dt(q_out),
+                                       q_out.stride(0), _p(cos_sin), _p(positions), _p(row_req), _p(block_table),
+                                       block_table.shape[1], _p(kv_pool), _dt(kv_pool) if kv_pool is not None else F32,
+                                       num_pages, page_size, n_rows, nh, nkv, hd, rot, 1 if interleaved else 0,
+                                       _p(status), _stream()), "rope_kv_append")
 
 
 
@@ -334,7 +415,13 @@ def decode_splits(n_streams: int, context: int, sms: Optional[int] = None) -> in
     return -(-context // per)                             # no CTA without keys
 
 
-def attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table: torch.Tensor,
+def attention(*args, **kwargs) -> None:
+    """`_attention` under the phase timer of its kernel class (the partial kernel and its merge together)."""
+    with phase("attn"):
+        _attention(*args, **kwargs)
+
+
+def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_table: torch.Tensor,
               positions: torch.Tensor, qblk: torch.Tensor, n_qblk: int, max_position: int, n_rows: int, nh: int,
               nkv: int, hd: int, window: int, split: int, tile: int, bq: int, scale: float, out: torch.Tensor,
               status: Optional[torch.Tensor], kernel: str = "generic") -> None:
@@ -541,6 +628,7 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: O
         if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
             raise KernelError("sample: temperature and uniform must be float32 [n]")
     scratch = torch.empty(n * 64 * 3, dtype=torch.float32, device=logits.device)
-    _check(lib().bg_sample(_p(logits), n, V, _p(temperature), _p(uniform), _p(out), _p(scratch), _stream()), "sample")
+    with phase("sample"):
+        _check(lib().bg_sample(_p(logits), n, V, _p(temperature), _p(uniform), _p(out), _p(scratch), _stream()), "sample")
     global _launches
     _launches += 1            # two kernels

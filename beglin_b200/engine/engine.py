@@ -81,10 +81,12 @@ class Engine:
 
     # ------------------------------------------------------------------ construction
     @classmethod
-    def from_folder(cls, folder: str, **kw) -> "Engine":
+    def from_folder(cls, folder: str, config_path: Optional[str] = None, **kw) -> "Engine":
+        """`config_path` names a config.json that stands elsewhere than in the folder (the reference's
+        QWEN_HF_CONFIG, qwen_infer.c:20121)."""
         ckpt = Checkpoint(folder)
         try:
-            arch, cfg = load_config(folder, tensor_names=ckpt.names())
+            arch, cfg = load_config(config_path or folder, tensor_names=ckpt.names())
             return cls(arch.build_spec(cfg), ckpt, config=cfg, origin=folder, **kw)
         finally:
             ckpt.close()
@@ -207,17 +209,18 @@ class Engine:
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Union[int, Sequence[int]] = 32,
                  temperature: float = 0.0, seed: int = 0, stop_ids: Optional[Sequence[int]] = None,
                  max_batch: Optional[int] = None, max_step_tokens: int = 2048,
-                 prefill_budget: Optional[int] = None, return_requests: bool = False):
+                 prefill_budget: Optional[int] = None, return_requests: bool = False, mixed: bool = True):
         """Generate for every prompt (lists of token ids on the host) and return the new token ids
         per prompt (the stop token included, as the reference records it, qwen_infer.c:2032-2039).
         `stop_ids` defaults to the configuration's eos ids; pass () to run to the token limit, as
-        the reference's `greedy` mode does."""
+        the reference's `greedy` mode does.  `mixed` False runs every prompt in steps of its own while the
+        decoding requests wait (the reference's QWEN_CB_MIXED=0); the tokens are the same."""
         if stop_ids is None:
             stop_ids = tuple(self.spec.eos_ids)
         if isinstance(max_new_tokens, int):
             max_new_tokens = [max_new_tokens] * len(prompts)
         sched = Scheduler(self.cache, max_batch=max_batch or self.cache.max_requests,
-                          max_step_tokens=max_step_tokens, prefill_budget=prefill_budget)
+                          max_step_tokens=max_step_tokens, prefill_budget=prefill_budget, mixed=mixed)
         reqs = []
         for i, (p, n) in enumerate(zip(prompts, max_new_tokens)):
             bad = [t for t in p if not 0 <= int(t) < self.vocab]

@@ -38,9 +38,9 @@ class DecoderModel:
         self.final_norm = registry.norm_class(spec.final_norm.kind)(
             spec.final_norm, {"weight": tensors[spec.final_norm_name]}, ctx)
         if spec.head_name is None:
-            self.head = Linear(self.embed, None, ctx)      # ctx.matrix is a no-op on the table: one copy
+            self.head = Linear(self.embed, None, ctx, label="head_gemv")      # ctx.matrix is a no-op on the table: one copy
         else:
-            self.head = Linear(tensors[spec.head_name], None, ctx)
+            self.head = Linear(tensors[spec.head_name], None, ctx, label="head_gemv")
 
     # ------------------------------------------------------------------ cache
     def cache_needs(self) -> List[Optional[object]]:

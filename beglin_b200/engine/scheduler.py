@@ -66,6 +66,7 @@ class Counters:
     decode_rows: int = 0
     prefill_rows: int = 0
     preemptions: int = 0
+    prefill_stalls: int = 0           # sequential prefill only: prompt steps that ran while decoding requests sat idle
     # time between consecutive tokens of one request, from its first token on (the reference's inter-token gap,
     # qwen_infer.c:20731-20742: taken once per step, so that a request which gets nothing while others' prompts
     # run, or which is recomputed after a preemption, shows as a long gap)
@@ -83,11 +84,18 @@ class Counters:
 
 class Scheduler:
     def __init__(self, cache: CacheManager, max_batch: int = 8, max_step_tokens: int = 2048,
-                 prefill_budget: Optional[int] = None, max_context: Optional[int] = None, now=time.perf_counter):
+                 prefill_budget: Optional[int] = None, max_context: Optional[int] = None, now=time.perf_counter,
+                 mixed: bool = True):
         """max_batch: live requests (the reference's QWEN_BATCH, default 8, qwen_infer.c:20617);
         prefill_budget: prompt tokens per step (QWEN_CB_PREFILL_BUDGET, qwen_infer.c:20691), by
-        default whatever max_step_tokens leaves after the decoding rows."""
+        default whatever max_step_tokens leaves after the decoding rows.
+        mixed (QWEN_CB_MIXED, qwen_infer.c:20690): True puts prompt portions beside the decoding rows of
+        a step.  False is the reference's older order (qwen_infer.c:20759-20782): while any admitted request
+        still has prompt left, a step carries ONE request's next portion and nothing else, and the decoding
+        requests wait; it exists so that the two can be compared (worst gap between a request's tokens,
+        steps in which decoding stalled), and both give every request the same tokens."""
         self.cache = cache
+        self.mixed = mixed
         self.max_batch = min(max_batch, cache.max_requests)
         self.max_step_tokens = max_step_tokens
         self.prefill_budget = prefill_budget
@@ -176,13 +184,20 @@ class Scheduler:
                 budget = min(budget, self.prefill_budget)
             if not decode:
                 budget = max(budget, 1)             # progress guarantee (qwen_infer.c:20815-20817)
+            stalled: List[Request] = []
+            if not self.mixed and any(r.phase == "prefill" for r in self.running):
+                # sequential prefill: this step is one request's portion alone; the decoding requests keep
+                # their pages (made sure of above) and wait
+                stalled, decode, plan = decode, [], []
+                budget = max(1, self.prefill_budget if self.prefill_budget is not None else self.max_step_tokens)
             prefill: List[Tuple[Request, int, bool]] = []
             for r in self.running:
-                if r.phase != "prefill" or budget <= 0:
+                if r.phase != "prefill" or budget <= 0 or (prefill and not self.mixed):
                     continue
                 have = self.cache.length(r.rid)
                 take = min(len(r.tokens_in) - r.done_prompt, budget)
-                while take > 0 and self.cache.pages_short(plan + [(r.rid, have + take)]) > 0:
+                held = [(q.rid, self.cache.length(q.rid) + 1) for q in stalled]     # room the waiting rows will need
+                while take > 0 and self.cache.pages_short(held + plan + [(r.rid, have + take)]) > 0:
                     # give up the portion's last page: shorten it to the previous page boundary
                     take = ((have + take - 1) // self.cache.page_size) * self.cache.page_size - have
                 if take <= 0:
@@ -190,6 +205,11 @@ class Scheduler:
                 plan.append((r.rid, have + take))
                 prefill.append((r, take, r.done_prompt + take == len(r.tokens_in)))
                 budget -= take
+            if stalled and not prefill:
+                # sequential order, and no portion fits beside the room the decoding requests need next: they
+                # decode after all, and what they free when they end lets the prompt go on
+                decode, stalled = stalled, []
+                plan = [(r.rid, self.cache.length(r.rid) + 1) for r in decode]
             if not decode and not prefill:
                 # nothing fits: free the pages of the request admitted last, or give up on the only one
                 victim = max(self.running, key=lambda r: r.admitted_at)
@@ -212,6 +232,8 @@ class Scheduler:
                 c.mixed_steps += 1
             if not decode:
                 c.prefill_only_steps += 1
+            if stalled:
+                c.prefill_stalls += 1
             return StepPlan(entries, decode, prefill, lengths)
 
     def wanted(self, plan: StepPlan) -> List[Request]:

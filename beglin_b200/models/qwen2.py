@@ -185,20 +185,26 @@ class Qwen2Config:
 def llama3_frequency_scale(theta: float, rot: int, r: RopeScaling) -> Tuple[float, ...]:
     """Per-frequency ratio of rope_type "llama3" (rope_llama3_scale.h:18-28): wavelengths above
     orig/low_freq_factor are divided by `factor`, those below orig/high_freq_factor are kept, and
-    the band between is blended."""
+    the band between is blended.  The reference computes the ratio in 32-bit, operation by operation;
+    so does this (with `powf` as the correctly rounded power), and the ratios come out bit for bit."""
+    import numpy as np
+    f = np.float32
+    theta32, factor, low, high = f(theta), f(r.factor), f(r.low_freq_factor), f(r.high_freq_factor)
+    orig = f(r.original_max_position_embeddings)
     out = []
-    low_wl = r.original_max_position_embeddings / r.low_freq_factor
-    high_wl = r.original_max_position_embeddings / r.high_freq_factor
+    low_wl = orig / low
+    high_wl = orig / high
     for i in range(rot // 2):
-        inv = theta ** (-(2.0 * i) / rot)
-        wl = 2.0 * math.pi / inv
+        exponent = -(f(2.0) * f(i)) / f(rot)
+        inv = f(np.float64(theta32) ** np.float64(exponent))
+        wl = (f(2.0) * f(math.pi)) / inv
         if wl > low_wl:
-            out.append(1.0 / r.factor)
+            out.append(float(f(1.0) / factor))
         elif wl < high_wl:
             out.append(1.0)
         else:
-            smooth = (r.original_max_position_embeddings / wl - r.low_freq_factor) / (r.high_freq_factor - r.low_freq_factor)
-            out.append((1.0 - smooth) / r.factor + smooth)
+            smooth = (orig / wl - low) / (high - low)
+            out.append(float((f(1.0) - smooth) / factor + smooth))
     return tuple(out)
 
 

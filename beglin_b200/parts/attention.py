@@ -60,8 +60,9 @@ class GQAAttention:
         names = ["q_proj"] + (["k_proj", "v_proj"] if spec.own_kv else [])
         w = torch.cat([tensors[n + ".weight"] for n in names], dim=0)
         b = torch.cat([tensors[n + ".bias"].float() for n in names], dim=0) if spec.qkv_bias else None
-        self.qkv = Linear(w, b, ctx)
-        self.o_proj = Linear(tensors["o_proj.weight"], tensors.get("o_proj.bias") if spec.out_bias else None, ctx)
+        self.qkv = Linear(w, b, ctx, label="proj_qkv")
+        self.o_proj = Linear(tensors["o_proj.weight"], tensors.get("o_proj.bias") if spec.out_bias else None, ctx,
+                             label="proj_o")
         self.position = shared_position(spec.position, ctx)
         scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(float(self.hd))
         self.scale = float(np.float32(scale))

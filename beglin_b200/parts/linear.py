@@ -18,8 +18,10 @@ from .stream import NormedInput, ResidualStream
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor], ctx: BuildContext):
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor], ctx: BuildContext, label: str = "proj"):
+        """`label` names the product's kernel class for the phase timers (ops.phase)."""
         self.ctx = ctx
+        self.label = label
         self.weight = ctx.matrix(weight)
         self.out_features, self.in_features = self.weight.shape
         self.bias_f32 = None if bias is None else bias.to(device=ctx.device, dtype=torch.float32).contiguous()
@@ -29,6 +31,10 @@ class Linear:
         self._tc_always = ctx.gemm == "tcgen05"
 
     def _run(self, x: torch.Tensor, out_dtype: torch.dtype, partial: bool) -> torch.Tensor:
+        with ops.phase(self.label):
+            return self._product(x, out_dtype, partial)
+
+    def _product(self, x: torch.Tensor, out_dtype: torch.dtype, partial: bool) -> torch.Tensor:
         T = x.shape[0]
         if self.f32:
             out = torch.empty((T, self.out_features), dtype=torch.float32, device=x.device)
@@ -80,12 +86,14 @@ class Linear:
         mode = ops.FUSED_SWIGLU if swiglu else ops.FUSED_PLAIN
         if fusion is not None:
             weight, eps = fusion
-            self._tc.fused(T, out, mode, xf=inp.stream.x, ssq_in=inp.stream.ssq, norm_weight=weight, eps=eps,
-                           bias=self.bias_f32)
+            with ops.phase(self.label):
+                self._tc.fused(T, out, mode, xf=inp.stream.x, ssq_in=inp.stream.ssq, norm_weight=weight, eps=eps,
+                               bias=self.bias_f32)
         else:
             x = inp.tensor() if lazy else inp
             self._check_rows(x)
-            self._tc.fused(T, out, mode, x=x, bias=self.bias_f32)
+            with ops.phase(self.label):
+                self._tc.fused(T, out, mode, x=x, bias=self.bias_f32)
         return out
 
     def into(self, x: torch.Tensor, stream: ResidualStream) -> None:
@@ -94,6 +102,7 @@ class Linear:
         T = x.shape[0]
         if self.fuses(T) and stream.pending is None:
             self._check_rows(x)
-            stream.updated(self._tc.fused(T, stream.x, ops.FUSED_RESIDUAL, x=x, bias=self.bias_f32, want_ssq=True))
+            with ops.phase(self.label):
+                stream.updated(self._tc.fused(T, stream.x, ops.FUSED_RESIDUAL, x=x, bias=self.bias_f32, want_ssq=True))
         else:
             stream.owe(self.partial(x))

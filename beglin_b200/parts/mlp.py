@@ -36,8 +36,8 @@ class SwiGLU:
             w = torch.stack([gate.reshape(im // 64, 64, -1), up.reshape(im // 64, 64, -1)], dim=1).reshape(2 * im, -1)
         else:
             w = torch.cat([gate, up], dim=0)
-        self.gate_up = Linear(w, None, ctx)
-        self.down = Linear(tensors["down_proj.weight"], None, ctx)
+        self.gate_up = Linear(w, None, ctx, label="proj_gate_up")
+        self.down = Linear(tensors["down_proj.weight"], None, ctx, label="proj_down")
 
     def forward(self, h, batch, stream: Optional[ResidualStream] = None) -> Optional[torch.Tensor]:
         """h: the normed rows, or a NormedInput.  With `stream` the result is added to it (or left owed to

@@ -1,7 +1,13 @@
 """Rotary position encoding.  Frequency i is theta^(-2i/rot) * scale_i; the angle of a token is its
 position times the frequency, as a float product, and its cosine and sine are computed once per
 step for all layers and heads (qwen_infer.c:757-794).  The table is made by the `rope_table`
-kernel; the rotation itself is fused into the cache append (`rope_kv_append`)."""
+kernel; the rotation itself is fused into the cache append (`rope_kv_append`).
+
+The frequencies are 32-bit numbers made the way the reference makes them (qwen_infer.c:791):
+`powf(theta, -(2.0f*i)/hd)` of the 32-bit theta and the 32-bit exponent, times the 32-bit scale.
+`powf` is taken as correctly rounded (the power in 64-bit of the 32-bit operands, rounded once), so
+that the same bits come out on every host; at position 30,000 one unit in a frequency's last place
+moves the angle by 0.002."""
 from __future__ import annotations
 
 import numpy as np
@@ -22,12 +28,12 @@ class RotaryPosition:
             raise ValueError(f"unknown rotary pairing '{spec.pairing}'")
         self.spec, self.ctx = spec, ctx
         half = spec.rotary_dim // 2
-        i = np.arange(half, dtype=np.float64)
-        inv = np.power(float(spec.theta), -(2.0 * i) / spec.rotary_dim)
+        exponent = -(np.float32(2.0) * np.arange(half, dtype=np.float32)) / np.float32(spec.rotary_dim)
+        inv = np.power(np.float64(np.float32(spec.theta)), exponent.astype(np.float64)).astype(np.float32)
         if spec.freq_scale is not None:
             if len(spec.freq_scale) != half:
                 raise ValueError("freq_scale must have rotary_dim/2 entries")
-            inv = inv * np.asarray(spec.freq_scale, dtype=np.float64)
+            inv = inv * np.asarray(spec.freq_scale, dtype=np.float32)
         self.inv_freq = torch.from_numpy(inv.astype(np.float32)).to(ctx.device)
         self.rotary_dim = spec.rotary_dim
         self.interleaved = spec.pairing == "interleaved"

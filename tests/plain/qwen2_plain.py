@@ -1,8 +1,12 @@
 """Plain, slow implementation of the Qwen2 dense decoder, used only as the oracle of the tests.
 
-It rests on the formulas of popixoxipop-collab/beglin's `qwen_infer.c` (each function cites the
-lines it restates): that file needs Apple's Accelerate and ARM NEON headers and does not compile on
-an x86 Linux host, so the model math cannot be compared with the reference's own binary here.
+It restates the formulas of popixoxipop-collab/beglin's `qwen_infer.c` (each function cites the
+lines it restates).  That file needs Apple's Accelerate and ARM NEON headers and does not compile
+whole on an x86 Linux host, but the functions of its arithmetic do when they are cut out by their
+lines and given a shim of the Accelerate loops: tests/golden/make_golden.py compiles them into a
+driver that runs tiny random models token by token, and tests/test_golden.py holds this file
+against the driver's committed outputs (logits, greedy tokens, rotation tables up to position
+32,767, frequency ratios).
 
 Whole sequences, no cache, one function per part, plain tensor arithmetic on whatever device the
 weights lie (the CPU by default; long sequences may be given weights on a GPU, in float64 still).
@@ -84,35 +88,44 @@ def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -
 
 def frequency_scale(cfg: dict, rot: int) -> Optional[torch.Tensor]:
     """The per-frequency ratio s_i of config.json's rope_scaling of rope_type "llama3"
-    (rope_llama3_scale.h:18-28); None (all ones) without that key (qwen_infer.c:757-764)."""
+    (rope_llama3_scale.h:18-28); None (all ones) without that key (qwen_infer.c:757-764).  The header
+    computes in 32-bit floats throughout, and so does this, one rounded operation after the other."""
     rs = cfg.get("rope_scaling")
     if not rs:
         return None
-    theta = float(cfg["rope_theta"])
-    factor, low, high = float(rs["factor"]), float(rs["low_freq_factor"]), float(rs["high_freq_factor"])
-    orig = float(rs["original_max_position_embeddings"])
+    f32 = lambda v: torch.tensor(float(v), dtype=torch.float32)
+    theta, factor, low, high = f32(cfg["rope_theta"]), f32(rs["factor"]), f32(rs["low_freq_factor"]), f32(rs["high_freq_factor"])
+    orig = f32(rs["original_max_position_embeddings"])
     out = []
     for i in range(rot // 2):
-        inv = theta ** (-(2.0 * i) / rot)
-        wavelen = 2.0 * math.pi / inv
+        exponent = -(f32(2.0) * f32(i)) / f32(rot)
+        inv = torch.pow(theta.double(), exponent.double()).float()          # powf, correctly rounded
+        wavelen = (f32(2.0) * f32(math.pi)) / inv
         if wavelen > orig / low:
-            out.append(1.0 / factor)
+            out.append(f32(1.0) / factor)
         elif wavelen < orig / high:
-            out.append(1.0)
+            out.append(f32(1.0))
         else:
             smooth = (orig / wavelen - low) / (high - low)
-            out.append((1.0 - smooth) / factor + smooth)
-    return torch.tensor(out, dtype=torch.float64)
+            out.append((f32(1.0) - smooth) / factor + smooth)
+    return torch.stack(out).double()
 
 
 def rope_angles(positions: Sequence[int], rot: int, theta: float, dtype,
                 scale: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """ang[p, i] = pos * theta^(-2i/rot) * s_i for i < rot/2 (qwen_infer.c:791-794)."""
-    i = torch.arange(rot // 2, dtype=torch.float64)
-    inv = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -(2.0 * i) / rot)
+    """ang[p, i] = pos * inv_i, inv_i = theta^(-2i/rot) * s_i for i < rot/2 (qwen_infer.c:791-794).
+
+    The reference makes these numbers in 32-bit: `float inv = powf(theta, -(2.0f*i)/hd); inv *= scale[i];
+    float ang = pos*inv;`.  They are restated so: theta, the exponent, the frequency and the angle are
+    32-bit values, `powf` correctly rounded (the 64-bit power of the 32-bit operands, rounded once).  Only
+    the cosine and sine that follow are taken in `dtype`.  A 64-bit angle would be another function of the
+    position: at position 4,000 the 32-bit product is 0.0002 off it."""
+    i = torch.arange(rot // 2, dtype=torch.float32)
+    exponent = -(2.0 * i) / torch.tensor(float(rot), dtype=torch.float32)
+    inv = torch.pow(torch.tensor(float(theta), dtype=torch.float32).double(), exponent.double()).float()
     if scale is not None:
-        inv = inv * scale
-    pos = torch.as_tensor(list(positions), dtype=torch.float64)
+        inv = inv * scale.float()
+    pos = torch.as_tensor(list(positions), dtype=torch.float32)
     return (pos[:, None] * inv[None, :]).to(dtype)            # on the CPU; `rope_split_half` moves it to its operand
 
 

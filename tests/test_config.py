@@ -106,3 +106,17 @@ def test_json_roundtrip_of_typed_config():
     _, cfg = load_config(TINY_C)
     _, again = load_config(cfg.to_json_dict())
     assert again == cfg
+
+
+def test_command_line_takes_the_configuration_from_qwen_hf_config(tmp_path, monkeypatch, capsys):
+    """QWEN_HF_CONFIG names the config.json (qwen_infer.c:20121); a path that does not exist is reported with
+    that path, before anything is loaded."""
+    from beglin_b200 import cli
+    monkeypatch.setenv("QWEN_BASE", str(tmp_path))
+    monkeypatch.setenv("QWEN_HF_CONFIG", str(tmp_path / "elsewhere" / "cfg.json"))
+    assert cli.main(["qwen_infer", "greedy", "4"]) == 1
+    err = capsys.readouterr().err
+    assert "FATAL" in err and "elsewhere/cfg.json" in err and "arch config" in err
+    monkeypatch.delenv("QWEN_HF_CONFIG")
+    assert cli.main(["qwen_infer", "greedy", "4"]) == 1
+    assert str(tmp_path / "config.json") in capsys.readouterr().err

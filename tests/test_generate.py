@@ -150,3 +150,61 @@ def test_command_line_greedy_and_cbatch(model_root, tmp_path):
     assert abs(float(value) / math.exp(nll / n) - 1.0) < 1e-4
     r = subprocess.run(exe + ["greedy"], env=dict(env, QWEN_BASE=str(tmp_path)), capture_output=True, text=True, timeout=600)
     assert r.returncode == 1 and "FATAL" in r.stderr and "arch config" in r.stderr
+
+
+def test_command_line_kept_variables(model_root, tmp_path):
+    """QWEN_CB_MIXED=0 (prompts in steps of their own: the same tokens, stalls counted), QWEN_HF_CONFIG (the
+    configuration from another place than the model folder) and QWEN_PROF=1 (time per kernel class with the
+    share of the total they cover)."""
+    import shutil
+    folder = make_model(model_root, "A", seed=3, dtype=torch.float32)
+    cfg, w = plain_model(folder)
+    prompt = seeded_ids(40, 256, 8)
+    ids = tmp_path / "prompt.i32"
+    np.asarray(prompt, dtype="<i4").tofile(ids)
+    # a folder with the weights only; its config.json lies elsewhere
+    bare = tmp_path / "weights_only"
+    bare.mkdir()
+    shutil.copy(os.path.join(folder, "model.safetensors"), bare / "model.safetensors")
+    elsewhere = tmp_path / "the_config.json"
+    shutil.copy(os.path.join(folder, "config.json"), elsewhere)
+    env = dict(os.environ, QWEN_BASE=str(bare), QWEN_PROMPT=str(ids), QWEN_DTYPE="fp32", QWEN_SAFETENSORS_MAXSEQ="128",
+               QWEN_PAGE_SIZE="8", QWEN_HF_CONFIG=str(elsewhere))
+    exe = [sys.executable, os.path.join(ROOT, "bin", "qwen_infer")]
+    want = plain.greedy_generate(cfg, w, prompt, 6)
+    r = subprocess.run(exe + ["greedy", "6"], env=dict(env, QWEN_PROF="1"), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.strip().splitlines()[-1] == "greedy:" + "".join(f" {t}" for t in want)
+    assert str(elsewhere) in r.stderr
+    closure = [l for l in r.stderr.splitlines() if l.startswith("[prof] ctx~")]
+    assert len(closure) == 1 and "closure=" in closure[0]
+    share = float(closure[0].split("closure=")[1].rstrip("%"))
+    assert 1.0 < share <= 100.5                       # the classes are part of the total and never more than it
+    classes = [l.split()[1] for l in r.stderr.splitlines() if l.startswith("[prof]   ")]
+    for name in ("emb_gather", "rmsnorm", "proj_qkv", "rope+kv_write", "attn", "proj_o", "proj_gate_up", "swiglu", "proj_down",
+                 "head_gemv", "sample"):
+        assert name in classes, (name, classes)
+    fields = r.stdout.strip().splitlines()[0].split()
+    assert fields[0] == "PROF" and fields[3] == "total_ms"
+    total = float(fields[4])
+    parts = sum(float(v) for v in fields[6::2])
+    assert abs(parts / total * 100.0 - share) < 0.5    # the machine-readable line says the same
+    r = subprocess.run(exe + ["bench", "5"], env=dict(env, QWEN_PROF="1"), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "closure=" in r.stderr and r.stdout.strip().splitlines()[-1].startswith("tok_s ")
+    # the two orders of cbatch give every request the same tokens; the sequential one counts its stalls
+    outs = {}
+    for mixed in ("1", "0"):
+        r = subprocess.run(exe + ["cbatch", "5"], env=dict(env, QWEN_CB_REQS="6", QWEN_BATCH="3", QWEN_CB_REPS="1",
+                                                            QWEN_CB_PREFILL_BUDGET="8", QWEN_CB_MIXED=mixed),
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        lines = r.stdout.strip().splitlines()
+        outs[mixed] = lines[:6]
+        agg = lines[-1].split()
+        field = lambda k: agg[agg.index(k) + 1]
+        assert field("mixed") == mixed
+        assert (int(field("pstall")) > 0) == (mixed == "0") and (int(field("msteps")) > 0) == (mixed == "1")
+    assert outs["1"] == outs["0"]
+    r = subprocess.run(exe + ["greedy"], env=dict(env, QWEN_HF_CONFIG=str(tmp_path / "missing.json")), capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 1 and "missing.json" in r.stderr and "arch config" in r.stderr

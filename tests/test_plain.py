@@ -39,7 +39,11 @@ def test_rotation_keeps_norms_and_relative_angles():
     # feature i pairs with i + 16: rotating (1, 0) by the angle gives (cos, sin)
     e = torch.zeros(1, 1, 32, dtype=torch.float64)
     e[0, 0, 3] = 1.0
-    a3 = 7 * 10000.0 ** (-(2 * 3) / 32)
+    # the angle is the reference's 32-bit number: 32-bit frequency times 32-bit position (qwen_infer.c:791)
+    import numpy as np
+    inv3 = np.float32(np.float64(np.float32(10000.0)) ** np.float64(-(np.float32(2.0) * np.float32(3)) / np.float32(32)))
+    a3 = float(np.float32(7) * inv3)
+    assert abs(a3 - 7 * 10000.0 ** (-(2 * 3) / 32)) < 1e-6
     r = plain.rope_split_half(e, plain.rope_angles([7], 32, 10000.0, torch.float64))
     assert abs(r[0, 0, 3] - math.cos(a3)) < 1e-12 and abs(r[0, 0, 19] - math.sin(a3)) < 1e-12
 

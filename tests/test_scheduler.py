@@ -191,3 +191,41 @@ def test_a_preempted_request_shows_its_recomputation_as_a_gap():
     assert s.counters.preemptions >= 1
     assert s.counters.gap_max_s > 1.0                     # the victim's next token came more than a step later
     assert s.counters.gaps == (12 - 1) + (6 - 1)          # every token but a request's first closes a gap
+
+
+def test_sequential_prefill_gives_the_same_tokens_and_shows_the_stalls():
+    """QWEN_CB_MIXED=0, the reference's older order (qwen_infer.c:20759-20782): a request's whole prompt runs in
+    steps of its own while the decoding requests wait.  Every request gets the tokens it gets in the mixed
+    order (the reference's gate, qwen_infer.c:20641-20645); what differs is what the counters show: steps in
+    which decoding stalled, no mixed steps, and a longer worst gap between a request's tokens."""
+    def workload():
+        return [Request(i, list(range(100 * i, 100 * i + n)), m) for i, (n, m) in
+                enumerate([(5, 9), (23, 4), (3, 12), (40, 3), (9, 6), (17, 5)])]
+    results = {}
+    for mixed in (True, False):
+        ticks = iter(range(100000))
+        s = Scheduler(cache(), max_batch=3, max_step_tokens=64, prefill_budget=8, mixed=mixed, now=lambda: float(next(ticks)))
+        reqs = workload()
+        steps = run(s, reqs)
+        for r in reqs:
+            assert r.output == expected_output(r.prompt, r.max_new_tokens) and r.finish_reason == "length"
+        results[mixed] = (s.counters, steps, [r.output for r in reqs])
+    assert results[True][2] == results[False][2]
+    mixed_c, seq_c = results[True][0], results[False][0]
+    assert mixed_c.mixed_steps > 0 and mixed_c.prefill_stalls == 0
+    assert seq_c.mixed_steps == 0 and seq_c.prefill_stalls > 0
+    assert seq_c.gap_max_s > mixed_c.gap_max_s                # a 40-token prompt in portions of 8 holds the decoders up
+    for p in results[False][1]:                               # a step is either one request's portion or decoding rows
+        kinds = {len(e.tokens) == 1 and e.rid in [r.rid for r in p.decode] for e in p.entries}
+        assert len(kinds) == 1 and (kinds == {True} or len(p.entries) == 1)
+        assert p.n_tokens <= 8 or all(len(e.tokens) == 1 for e in p.entries)
+
+
+def test_sequential_prefill_with_few_pages_still_ends():
+    """When no portion fits beside the room the waiting decoders need, they decode after all; nobody starves."""
+    s = Scheduler(cache(pages=7, page=4), max_batch=3, max_step_tokens=64, prefill_budget=8, mixed=False)
+    reqs = [Request("a", list(range(8)), 10), Request("b", list(range(20, 31)), 6), Request("c", list(range(40, 45)), 4)]
+    run(s, reqs)
+    for r in reqs:
+        assert r.output == expected_output(r.prompt, r.max_new_tokens), r.rid
+    assert s.cache.free_pages() == 7
