@@ -538,3 +538,63 @@ def test_attention_merge_of_many_ranges(ops, nh, nkv, hd, page, dtype, split, de
     assert torch.isfinite(got).all()
     tol = 1e-5 if dtype == torch.float32 else 1e-2
     assert (got - want).abs().max() < tol * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("dtype,page,batch", [(torch.bfloat16, 64, 8), (torch.bfloat16, 16, 8), (torch.float32, 64, 8),
+                                              (torch.bfloat16, 64, 64), (torch.bfloat16, 32, 3)])
+def test_decoding_attention_under_a_bound_finds_every_needle(ops, dtype, page, batch):
+    """Decoding steps that are replayed as a graph launch the attention for the context limit, not for the
+    longest request: requests of 40 to 4,000 keys side by side under `max_position` 4095, so that for the short
+    ones most CTAs of the fixed grid have nothing to do.  One key of every request is made to win its softmax
+    (its value row is a marker), and it is moved through the places where a kernel can lose a key: the first and
+    the newest, the two sides of a page's edge and of a 256-key stage, the middle.  Every row must come out as
+    its marker; the other keys are noise."""
+    nh, nkv, hd = 12, 2, 128
+    lengths = ([40, 700, 1500, 4000, 63, 1023, 255, 2049] * 8)[:batch]
+    if batch == 64:
+        lengths = [1 + (97 * i) % 4000 for i in range(64)]
+    torch.manual_seed(batch + page)
+    n_pages_each = [-(-t // page) for t in lengths]
+    n_pages = sum(n_pages_each) + 3
+    perm = iter(torch.randperm(n_pages).tolist())
+    max_pages = 4096 // page
+    bt = torch.full((batch, max_pages), -1, dtype=torch.int32)
+    pool = torch.full((n_pages, 2, nkv, page, hd), float("nan"), dtype=dtype)
+    for r, t in enumerate(lengths):
+        k = (torch.randn(t, nkv, hd) * 0.5).to(dtype)
+        v = torch.randn(t, nkv, hd).to(dtype)
+        for pi in range(n_pages_each[r]):
+            pg = next(perm)
+            bt[r, pi] = pg
+            n = min(page, t - pi * page)
+            pool[pg, 0, :, :n] = k[pi * page:pi * page + n].transpose(0, 1)
+            pool[pg, 1, :, :n] = v[pi * page:pi * page + n].transpose(0, 1)
+    pool = pool.to(DEV)
+    q = torch.zeros(batch, nh, hd)
+    q[:, :, 5] = 16.0                                   # a needle's score is 16 * 16 / sqrt(128) = 22.6; noise stays under 3
+    qd = q.reshape(batch, nh * hd).to(dtype).to(DEV).contiguous()
+    positions = torch.tensor([t - 1 for t in lengths], dtype=torch.int32, device=DEV)
+    kernel, bq, tile = ops.attention_plan(nh // nkv, hd, dtype, True, "auto", page)
+    assert kernel == ("mma_keys" if dtype == torch.bfloat16 else "generic")
+    qblk = torch.tensor([(r, r, 1) for r in range(batch)], dtype=torch.int32, device=DEV)
+    status = ops.new_status(DEV)
+    places = [lambda t: 0, lambda t: t - 1, lambda t: min(t - 1, 63), lambda t: min(t - 1, 64), lambda t: min(t - 1, 255),
+              lambda t: min(t - 1, 256), lambda t: t // 2, lambda t: max(0, t - 2), lambda t: (t - 1) // 256 * 256,
+              lambda t: max(0, (t - 1) // page * page - 1)]
+    for place in places:
+        changed = []
+        for r, t in enumerate(lengths):
+            at = place(t)
+            pg, sl = int(bt[r, at // page]), at % page
+            changed.append((pg, sl, pool[pg, :, :, sl].clone()))
+            pool[pg, 0, :, sl, 5] = 16.0
+            pool[pg, 1, :, sl, :] = 100.0 + r
+        out = torch.full((batch, nh * hd), float("nan"), dtype=dtype, device=DEV)
+        ops.attention(qd, qd.stride(0), pool, bt.to(DEV), positions, qblk, batch, 4095, batch, nh, nkv, hd, 0, 256, tile, bq,
+                      1.0 / math.sqrt(hd), out, status, kernel)
+        ops.raise_on_status(status)
+        got = out.float().cpu()
+        for r, t in enumerate(lengths):
+            assert (got[r] - (100.0 + r)).abs().max() < 1.0, (r, t, place(t), got[r][:4])
+        for pg, sl, old in changed:
+            pool[pg, :, :, sl] = old
