@@ -62,3 +62,41 @@ def test_real_widths_whole_portions_and_single_tokens(model_root, dtype):
     eng.release("a"); eng.release("b")
     new = eng.generate([ids["b"][:20]], max_new_tokens=4, stop_ids=())[0]
     follows_plain(folder, ids["b"][:20], new, tol)
+
+
+# The same widths with a vocabulary cut to 3,001 tokens, so that the float64 oracle runs six requests in
+# seconds: the four ways of cutting of the replay tests, the mixed one on a pool so small that pages come back.
+WIDE_SMALL_VOCAB = dict(WIDE, vocab_size=3001)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_widths_four_ways_of_cutting(model_root, dtype):
+    """Each request alone and whole; most of it in one step and the last 32 tokens one by one; portions of
+    changing size down to two tokens; and mixed, up to four live requests with portions of some beside single
+    tokens of others, every page poisoned first.  float32: every row bitwise the same in the four ways (what a
+    request computes does not depend on who shares its step, the reference's gate, qwen_infer.c:2040-2048, or
+    on how it was cut) and right against the oracle; bfloat16: right against the oracle."""
+    from beglin_b200 import Engine
+    from test_replay import check_against_plain
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = make_model(model_root, "wide3001", seed=6, dtype=stored, config=WIDE_SMALL_VOCAB, std=0.02, bias_std=0.02)
+    reqs = {f"r{i}": seeded_ids(n, 3001, 300 + i) for i, n in enumerate([150, 41, 290, 97, 64, 200])}
+    tol = TOL_F32 if dtype == "float32" else TOL_BF16
+    mixed_steps, peak = rl.mixed(reqs, seed=8)
+    assert peak < sum(-(-len(v) // 64) * 64 for v in reqs.values())       # the pool cannot hold all at once
+    results = {}
+    for way, steps, max_tokens in (("whole", rl.whole(reqs), 320), ("tail", rl.last_one_by_one(reqs), 320),
+                                   ("portions", rl.portions(reqs), 320), ("mixed", mixed_steps, peak)):
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=max_tokens, page_size=16, max_requests=4)
+        rl.poison(eng)
+        got = rl.run_in_process(eng, steps)
+        eng.cache.check()
+        assert eng.cache.free_pages() == eng.cache.num_pages and not eng.cache.live()
+        worst = check_against_plain(got, folder, reqs, tol)
+        print(f"real widths {dtype} {way}: worst relative error {worst:.3g} (limit {tol:g})")
+        results[way] = got
+        del eng
+    if dtype == "float32":
+        for way in ("tail", "portions", "mixed"):
+            for key, row in results["whole"].items():
+                assert torch.equal(row, results[way][key]), (way, key)
