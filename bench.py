@@ -10,7 +10,12 @@ replayed as a CUDA graph, sampled tokens fed back on the device); `e2e` is the s
 Python entry point `Engine.decode`, host token ids in from pinned memory and sampled ids read back
 every step; `prefill` is one 2,048-token prompt in one step; `roofline` sets the bytes a decoding
 step has to read (every weight once and the cache of the live requests) against the measured copy
-bandwidth; `points` holds decoding at batch 1 and 64.
+bandwidth; `points` holds decoding at batch 1 and 64, and the other configurations of the baseline
+record, each with its own engine, built and freed in turn: `decode_b8_page16` (the headline sizes with
+pages of 16 positions), `gen_7b_*` (Qwen2.5-7B sizes, context 8192: 32 requests with seeded prompt lengths
+of 128 to 2,048 tokens and 256 new tokens each through `Engine.generate`) and `decode_14b_b64` (Qwen2.5-14B
+sizes, 64 prompts of 4,096 tokens, context limit 16384), the decoding points with milliseconds per step and
+their fraction of the copy bandwidth.  `--no-big` leaves the 7B and 14B points out.
 """
 import argparse
 import json
@@ -125,13 +130,15 @@ def fill_cache(eng, rids, length, seed, chunk=2048):
     torch.cuda.synchronize()
 
 
-def time_decode(eng, batch, context, steps, warmup, seed, e2e):
+def time_decode(eng, batch, context, steps, warmup, seed, e2e, start_len=None):
     """(ms per step on the device, launches of this package's kernels in the timed region).  With
-    `e2e` every step takes its tokens from the host and reads the sampled ones back."""
+    `e2e` every step takes its tokens from the host and reads the sampled ones back.  The requests hold
+    `start_len` positions before the first step (default: so that the last timed step ends at `context`)."""
     import torch
     from beglin_b200.csrc import ops
     rids = [("bench", batch, i) for i in range(batch)]
-    start_len = context - (warmup + steps) - 1
+    if start_len is None:
+        start_len = context - (warmup + steps) - 1
     fill_cache(eng, rids, start_len, seed)
     g = torch.Generator().manual_seed(seed + 1)
     toks = torch.randint(0, eng.vocab, (batch,), generator=g).tolist()
@@ -272,6 +279,65 @@ def time_prefill(eng, T, reps, seed):
     return best
 
 
+def free_engine(eng):
+    """Drop an engine and everything it holds on the device (its graphs refer back to it, so the cycle
+    collector has to run before the memory is free)."""
+    import gc
+    import torch
+    eng._graphs.clear()
+    eng.portions.graphs.clear()
+    del eng
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
+def decode_point(cfg, pk, batch, context, start_len, steps, warmup, page, max_context=None, seed=5):
+    """One decoding measurement with an engine of its own: tokens a second, milliseconds a step, the bytes a
+    step has to read and their fraction of the copy bandwidth."""
+    from beglin_b200 import Engine
+    layers = cfg["num_hidden_layers"]
+    eng = Engine.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=batch * (context + 2 * page), page_size=page,
+                        max_requests=batch, max_context=max_context or context)
+    weight_bytes = eng.model.weight_bytes()
+    ms, _, _ = time_decode(eng, batch, context, steps, warmup, seed=seed, e2e=False, start_len=start_len)
+    free_engine(eng)
+    first = start_len if start_len is not None else context - (warmup + steps) - 1
+    mid = first + warmup + steps / 2.0
+    step_bytes = weight_bytes + batch * mid * kv_bytes_per_token(cfg, layers)
+    gbs = step_bytes / (ms * 1e-3) / 1e9
+    return {"tok_s": round(batch * 1000.0 / ms, 1), "ms": round(ms, 4), "gb": round(step_bytes / 1e9, 3),
+            "frac": round(gbs / pk["hbm_gbs"], 4), "steps": steps}
+
+
+def generate_point(cfg, requests=32, new_tokens=256, context=8192, seed=11):
+    """The mixed workload of the baseline record's fourth configuration through `Engine.generate`: `requests`
+    prompts of seeded lengths 128..2,048 (seeded uniform token ids), `new_tokens` new tokens each, all live at
+    once, host token ids in and out.  The first run captures the graphs; the second is timed on the host's
+    clock between two device synchronisations."""
+    import torch
+    from beglin_b200 import Engine
+    g = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(128, 2049, (requests,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lengths]
+    eng = Engine.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=requests * (2048 + new_tokens + 64),
+                        page_size=64, max_requests=requests, max_context=context)
+    out = {}
+    for timed in (False, True):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs = eng.generate(prompts, max_new_tokens=new_tokens, stop_ids=(), max_batch=requests, max_step_tokens=4096)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        c = eng.last_counters
+        new = sum(len(o) for o in outs)
+        out = {"new_tok_s": round(new / wall, 1), "tok_s_with_prompts": round((new + sum(lengths)) / wall, 1),
+               "wall_s": round(wall, 3), "prompt_tokens": sum(lengths), "new_tokens": new, "steps": c.steps,
+               "mixed_steps": c.mixed_steps, "preemptions": c.preemptions,
+               "tbt_max_ms": round(c.gap_max_s * 1e3, 2), "tbt_mean_ms": round(c.gap_mean_s() * 1e3, 3)}
+    free_engine(eng)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -283,6 +349,7 @@ def main():
     ap.add_argument("--sizes", default="1.5b", choices=sorted(SIZES), help="layer sizes (default: the baseline record's)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (default: all)")
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64 and the prefill")
+    ap.add_argument("--no-big", action="store_true", help="skip the points with engines of their own (page 16, 7B, 14B)")
     ap.add_argument("--gemm", default="auto")
     ap.add_argument("--no-fuse", action="store_true", help="norms, residual adds and SwiGLU as kernels of their own")
     ap.add_argument("--timeline", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
@@ -365,6 +432,19 @@ def main():
         flops = prefill_flops(cfg, args.layers, T)
         out["prefill"] = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
                           "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        if not args.no_big and args.sizes == "1.5b" and args.layers == full["num_hidden_layers"]:
+            free_engine(eng)
+            del eng
+            # the headline sizes with the page size the baseline record states
+            p16 = decode_point(cfg, pk, args.batch, args.context, None, min(args.steps, 32), args.warmup, page=16)
+            points.update({"decode_b8_page16": p16["tok_s"], "decode_b8_page16_ms": p16["ms"], "decode_b8_page16_frac": p16["frac"]})
+            # Qwen2.5-7B sizes: the mixed workload through Engine.generate
+            gen = generate_point(SIZES["7b"][1])
+            points.update({"gen_7b_" + k: v for k, v in gen.items()})
+            # Qwen2.5-14B sizes: 64 prompts of 4,096 tokens under a context limit of 16384
+            big = decode_point(SIZES["14b"][1], pk, 64, 4096 + 64, 4096, 8, 3, page=64, max_context=16384)
+            points.update({"decode_14b_b64": big["tok_s"], "decode_14b_b64_ms": big["ms"], "decode_14b_b64_gb": big["gb"],
+                           "decode_14b_b64_frac": big["frac"], "decode_14b_b64_steps": big["steps"]})
     print(json.dumps(out))
     return 0
 
