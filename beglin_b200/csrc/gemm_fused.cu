@@ -48,23 +48,6 @@ struct FusedParams {
     unsigned* status;
 };
 
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
-// (nothing that this thread wrote has to be visible to the peers at the first use of the barrier)
-__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void cluster_sync_all() {
-    cluster_arrive();
-    cluster_wait();
-}
-// the address, in the cluster's shared window, of this CTA's shared-memory address in the CTA of the given rank
-__device__ __forceinline__ unsigned peer_addr(unsigned local_addr, unsigned rank) {
-    unsigned a;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(a) : "r"(local_addr), "r"(rank));
-    return a;
-}
-__device__ __forceinline__ void st_cluster(unsigned addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
-}
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }   // warps 2..5
 
 template <int BN, int STAGES>

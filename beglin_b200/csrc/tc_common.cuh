@@ -68,6 +68,25 @@ __device__ __forceinline__ void tc_ld16(unsigned taddr, unsigned (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
+// Thread block clusters: the cluster-wide barrier (every thread of every CTA arrives) and stores into a
+// peer CTA's shared memory.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+// (nothing that this thread wrote has to be visible to the peers at the first use of the barrier)
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_sync_all() {
+    cluster_arrive();
+    cluster_wait();
+}
+// the address, in the cluster's shared window, of this CTA's shared-memory address in the CTA of the given rank
+__device__ __forceinline__ unsigned peer_addr(unsigned local_addr, unsigned rank) {
+    unsigned a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(a) : "r"(local_addr), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void st_cluster(unsigned addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
+}
 // Shared-memory operand descriptor: K-major tile whose rows are 128 bytes, 128-byte swizzle; groups
 // of 8 rows are 1024 bytes apart.
 __device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned smem_addr) {
