@@ -49,6 +49,8 @@ _SIGNATURES = {
                       _c_void_p, _c_float, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
                       _c_void_p, _c_void_p],
     "bg_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "bg_sample_feed": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                       _c_void_p],
 }
 
 _lib = None
@@ -616,10 +618,18 @@ def gemm_fused_unchecked(w_ptr: int, n_out: int, k: int, ldw: int, T: int, out: 
 
 
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],
-           out: torch.Tensor) -> None:
+           out: torch.Tensor, feed_tokens: Optional[torch.Tensor] = None, feed_positions: Optional[torch.Tensor] = None,
+           advance: Optional[torch.Tensor] = None) -> None:
     """out[r] = first argmax of logits[r] when temperature[r] <= 0 (or temperature is None), else the
-    index where the cumulative softmax(logits[r] / temperature[r]) first exceeds uniform[r]."""
-    _cuda(logits, temperature, uniform, out)
+    index where the cumulative softmax(logits[r] / temperature[r]) first exceeds uniform[r].  For a decoding
+    step that is replayed on the device: the token also goes to feed_tokens[r] (the step's input buffer), and
+    feed_positions[r] grows by advance[r] (by 1 without `advance`)."""
+    _cuda(logits, temperature, uniform, out, feed_tokens, feed_positions, advance)
+    for t in (feed_tokens, feed_positions, advance):
+        if t is not None:
+            _i32(t, "feed_tokens, feed_positions and advance")
+            if t.numel() != logits.shape[0]:
+                raise KernelError("sample: feed_tokens, feed_positions and advance have one value per row")
     n, V = logits.shape
     if logits.dtype != torch.float32 or not logits.is_contiguous():
         raise KernelError("sample: logits must be contiguous float32 [n, V]")
@@ -629,6 +639,7 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: O
             raise KernelError("sample: temperature and uniform must be float32 [n]")
     scratch = torch.empty(n * 64 * 3, dtype=torch.float32, device=logits.device)
     with phase("sample"):
-        _check(lib().bg_sample(_p(logits), n, V, _p(temperature), _p(uniform), _p(out), _p(scratch), _stream()), "sample")
+        _check(lib().bg_sample_feed(_p(logits), n, V, _p(temperature), _p(uniform), _p(out), _p(scratch), _p(feed_tokens),
+                                    _p(feed_positions), _p(advance), _stream()), "sample")
     global _launches
     _launches += 1            # two kernels

@@ -94,7 +94,8 @@ sample_stage1_kernel(const float* __restrict__ logits, int V, const float* __res
 __global__ void __launch_bounds__(STAGE_THREADS)
 sample_stage2_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
                      const float* __restrict__ uniform, const float* __restrict__ c_max, const int* __restrict__ c_arg,
-                     const float* __restrict__ c_sum, int* __restrict__ out) {
+                     const float* __restrict__ c_sum, int* __restrict__ out, int* __restrict__ feed_tokens,
+                     int* __restrict__ feed_positions, const int* __restrict__ advance) {
     __shared__ float s_part[STAGE_THREADS];
     __shared__ float s_gmax, s_target, s_before;
     __shared__ int s_chunk, s_pick;
@@ -102,6 +103,13 @@ sample_stage2_kernel(const float* __restrict__ logits, int V, const float* __res
     pdl_wait();
     const int r = blockIdx.x;
     const float T = temperature ? temperature[r] : 0.0f;
+    // The chosen token; for a decoding loop that runs on the device it also becomes the row's next input token, and
+    // the row's position moves on by advance[r] (0 for a row that pads the batch).
+    auto emit = [&](int token) {
+        out[r] = token;
+        if (feed_tokens) feed_tokens[r] = token;
+        if (feed_positions) feed_positions[r] += advance ? advance[r] : 1;
+    };
     if (threadIdx.x == 0) {
         float g = -INFINITY;
         int arg = 0;
@@ -136,7 +144,7 @@ sample_stage2_kernel(const float* __restrict__ logits, int V, const float* __res
     }
     __syncthreads();
     if (!(T > 0.0f) || s_chunk < 0) {
-        if (threadIdx.x == 0) out[r] = s_pick;
+        if (threadIdx.x == 0) emit(s_pick);
         return;
     }
     const float* row = logits + (size_t)r * V;
@@ -167,7 +175,7 @@ sample_stage2_kernel(const float* __restrict__ logits, int V, const float* __res
             run += pe;
             if (run > s_target) { pick = i; break; }
         }
-        out[r] = pick >= 0 ? pick : lastnz;
+        emit(pick >= 0 ? pick : lastnz);
     }
 }
 
@@ -177,9 +185,11 @@ sample_stage2_kernel(const float* __restrict__ logits, int V, const float* __res
 extern "C" long long bg_sample_scratch_bytes(int n) { return (long long)n * bg::SAMPLE_CHUNKS * 12; }
 
 // temperature may be null (all rows greedy); uniform may be null only then.  scratch holds
-// bg_sample_scratch_bytes(n) bytes.
-extern "C" int bg_sample(const float* logits, int n, int V, const float* temperature, const float* uniform, int* out,
-                         void* scratch, cudaStream_t stream) {
+// bg_sample_scratch_bytes(n) bytes.  feed_tokens [n] and feed_positions [n] (either may be null) are the input buffers
+// of a decoding step that is replayed: the chosen token is also written to feed_tokens[r], and feed_positions[r]
+// grows by advance[r] (by 1 where advance is null).
+extern "C" int bg_sample_feed(const float* logits, int n, int V, const float* temperature, const float* uniform, int* out,
+                              void* scratch, int* feed_tokens, int* feed_positions, const int* advance, cudaStream_t stream) {
     if (n <= 0) return BG_OK;
     if (V <= 0) return BG_ERR_SHAPE;
     if (temperature && !uniform) return BG_ERR_SHAPE;
@@ -190,7 +200,13 @@ extern "C" int bg_sample(const float* logits, int n, int V, const float* tempera
     dim3 grid(n, bg::SAMPLE_CHUNKS);
     bg::launch(bg::sample_stage1_kernel, grid, dim3(bg::STAGE_THREADS), 0, stream, logits, V, temperature, c_max, c_arg, c_sum);
     BG_LAUNCH_CHECK();
-    bg::launch(bg::sample_stage2_kernel, dim3(n), dim3(bg::STAGE_THREADS), 0, stream, logits, V, temperature, uniform, c_max, c_arg, c_sum, out);
+    bg::launch(bg::sample_stage2_kernel, dim3(n), dim3(bg::STAGE_THREADS), 0, stream, logits, V, temperature, uniform, c_max, c_arg, c_sum, out,
+               feed_tokens, feed_positions, advance);
     BG_LAUNCH_CHECK();
     return BG_OK;
+}
+
+extern "C" int bg_sample(const float* logits, int n, int V, const float* temperature, const float* uniform, int* out,
+                         void* scratch, cudaStream_t stream) {
+    return bg_sample_feed(logits, n, V, temperature, uniform, out, scratch, nullptr, nullptr, nullptr, stream);
 }

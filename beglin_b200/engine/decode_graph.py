@@ -122,9 +122,10 @@ class DecodeGraph:
         b = self.batch
         b.scratch.clear()
         logits = self.engine.model.forward(b, self.engine.cache)
-        ops.sample(logits, self.temperature, self.uniform, self.out_tokens)
-        b.token_ids.copy_(self.out_tokens)
-        b.positions.add_(self.advance)         # the next step of the same requests needs no upload
+        # the sampled tokens become the next step's input and the positions move on inside the sampling kernel, so
+        # the next step of the same requests needs no upload and the graph holds no kernel but the package's own
+        ops.sample(logits, self.temperature, self.uniform, self.out_tokens, feed_tokens=b.token_ids,
+                   feed_positions=b.positions, advance=self.advance)
         self.logits = logits
 
     def _body_fed(self) -> None:

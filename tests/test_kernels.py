@@ -383,6 +383,17 @@ def test_sample_greedy_takes_the_first_maximum(ops):
     out = torch.empty(4, dtype=torch.int32, device=DEV)
     ops.sample(logits, None, None, out)
     assert out.tolist() == [300, 999, 0, 0]
+    # for a decoding loop on the device: the tokens also go to the step's input buffer, and the positions move on
+    # (not for a row that pads the batch); greedy rows and a sampled row alike
+    feed = torch.full((4,), -1, dtype=torch.int32, device=DEV)
+    positions = torch.tensor([7, 0, 41, 5], dtype=torch.int32, device=DEV)
+    advance = torch.tensor([1, 1, 1, 0], dtype=torch.int32, device=DEV)
+    temp = torch.tensor([0.0, 0.0, 0.7, 0.0], device=DEV)
+    u = torch.tensor([0.0, 0.0, 0.999, 0.0], device=DEV)
+    out2 = torch.empty(4, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temp, u, out2, feed_tokens=feed, feed_positions=positions, advance=advance)
+    assert out2.tolist()[:2] == [300, 999] and out2.tolist()[3] == 0
+    assert feed.tolist() == out2.tolist() and positions.tolist() == [8, 1, 42, 5]
 
 
 def test_sample_temperature_inverts_the_cumulative_distribution(ops):
