@@ -1,21 +1,30 @@
 // Attention of prompt portions on the fifth-generation tensor cores (bfloat16, head size 64 or 128).
 //
 // One CTA takes a query block of up to 128 rows (consecutive tokens of one request x the query heads
-// of one kv head) and walks all keys the block sees, 64 at a time:
-//   S = Q K^T      tcgen05.mma, Q and the key tile in shared memory (K-major, 128-byte swizzle),
-//                  S in tensor memory (two buffers of 64 columns);
-//   softmax        128 threads, one per row: tcgen05.ld of the row's 64 scores, scale, mask, running
-//                  maximum and sum in float, P = exp2(S - m) as bfloat16 into shared memory;
-//   O += P V       tcgen05.mma, P K-major, the value tile as it lies in the cache (N-major), O in
-//                  tensor memory (head_dim columns); when a row's maximum grows, its O is rescaled
-//                  by tcgen05.ld / tcgen05.st before the product is issued.
+// of one kv head) and walks all keys the block sees, 128 at a time:
+//   S = Q K^T      tcgen05.mma with 128 key columns (an MMA of 64 columns costs its issuer and the tensor
+//                  cores as much as one of 128), Q and the key tile in shared memory (K-major, 128-byte
+//                  swizzle), S in tensor memory (128 columns);
+//   softmax        one thread per row, the tile's scores in two halves of 64: tcgen05.ld of the row's 64
+//                  scores, scale, mask, running maximum and sum in float, P = exp2(S - m) as bfloat16
+//                  into shared memory;
+//   O += P V       tcgen05.mma, one half at a time: P K-major, the value tile as it lies in the cache
+//                  (N-major), O in tensor memory (head_dim columns); when a row's maximum grows, its O is
+//                  rescaled by tcgen05.ld / tcgen05.st before the product is issued.
+// The softmax of a tile is a chain of latencies (the load from tensor memory, the maximum, the
+// exponentials, the store of P) that one warp per SM sub-partition cannot hide, and it is what a tile
+// waits for.  So the key tiles are dealt to TWO groups of four softmax warps, the even tiles to one
+// and the odd tiles to the other: each group has a score buffer, keeps a running maximum, a sum and an accumulator O in
+// tensor memory of its own, as if the keys had been cut into two interleaved sets, and the two are
+// joined when all tiles are done (O = (O_e 2^(m_e - m) + O_o 2^(m_o - m)) / (l_e 2^(m_e - m) + l_o 2^(m_o - m))).
+// While one group is busy with tile i the other works on tile i + 1, and the tensor cores serve both.
 // Keys and values come from the pages by TMA (cp.async.bulk.tensor over the page pool seen as a 2-D
 // tensor [rows, head_dim], boxes of one page x 64 features, 128-byte swizzle), each through a ring of
-// three stages of its own: the keys' stage is free as soon as the scores are done, the values' only
-// after the second product.  Issuing an asynchronous operation (a copy, an MMA, a commit) costs the
+// two stages of 128 keys of its own: the keys' stage is free as soon as the scores are done, the values'
+// only after the second product.  Issuing an asynchronous operation (a copy, an MMA, a commit) costs the
 // issuing thread on the order of a hundred cycles, so the roles are spread over warps: warp 0 issues
 // S = Q K^T, warp 6 issues O += P V, warp 5 copies keys, warp 7 copies values, warps 1-4 are the
-// softmax.  A tile of values at the ragged end of the keys is completed by its loader (rows that the
+// softmax of the even tiles and warps 8-11 that of the odd tiles.  A tile of values at the ragged end of the keys is completed by its loader (rows that the
 // block must not see are zeroed, so that 0 * garbage cannot be NaN) before it is released.
 // Every wait on an mbarrier is bounded in time and records BG_STATUS_TIMEOUT.
 //
@@ -25,9 +34,15 @@
 namespace bg {
 
 constexpr int AT_BM = 128;                 // rows per CTA
-constexpr int AT_BK = 64;                  // keys per tile
-constexpr int AT_STAGES = 3;
-constexpr int AT_THREADS = 256;            // warps 0 and 6: MMA issue; warps 1-4: softmax; warps 5 and 7: loaders
+// From this many keys on, tiles of 128 keys (BEGLIN_B200_ATTN_WIDE_FROM overrides the measured default).
+inline int at_wide_from() {
+    static int v = [] { const char* e = getenv("BEGLIN_B200_ATTN_WIDE_FROM"); return (e && atoi(e) > 0) ? atoi(e) : 5120; }();
+    return v;
+}
+// Keys per tile: 128 for long contexts (an MMA of 64 key columns costs as much as one of 128), 64 for short ones
+// (a block's keys are walked in whole tiles, and with few tiles a tile that is mostly masked weighs more).  A tile
+// is cut into two halves, one for each group of softmax warps.  Stages of the key and value rings: 256 keys each.
+constexpr int AT_THREADS = 384;            // warps 0 and 6: MMA issue; warps 1-4 and 8-11: softmax; warps 5 and 7: loaders
 constexpr unsigned long long AT_WAIT_NS = 1000000000ull;
 constexpr float AT_LOG2E = 1.4426950408889634f;
 
@@ -94,6 +109,11 @@ __device__ __forceinline__ void at_mma(unsigned tmem_d, unsigned long long a, un
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
 }
+// The same with the left operand in tensor memory (row i in lane i, two bfloat16 of consecutive k a column).
+__device__ __forceinline__ void at_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long b, unsigned idesc, unsigned acc) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
 __device__ __forceinline__ void at_ld32(unsigned taddr, float (&v)[32]) {
     unsigned r[32];
     asm volatile(
@@ -108,6 +128,27 @@ __device__ __forceinline__ void at_ld32(unsigned taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 64 consecutive columns: both loads are on their way before the one wait.
+__device__ __forceinline__ void at_ld64(unsigned taddr, float (&v)[64]) {
+    unsigned r[64];
+#define BG_LD32(base, off)                                                                                                  \
+    asm volatile(                                                                                                           \
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"                   \
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"                                        \
+        : "=r"(r[off + 0]), "=r"(r[off + 1]), "=r"(r[off + 2]), "=r"(r[off + 3]), "=r"(r[off + 4]), "=r"(r[off + 5]),       \
+          "=r"(r[off + 6]), "=r"(r[off + 7]), "=r"(r[off + 8]), "=r"(r[off + 9]), "=r"(r[off + 10]), "=r"(r[off + 11]),     \
+          "=r"(r[off + 12]), "=r"(r[off + 13]), "=r"(r[off + 14]), "=r"(r[off + 15]), "=r"(r[off + 16]), "=r"(r[off + 17]), \
+          "=r"(r[off + 18]), "=r"(r[off + 19]), "=r"(r[off + 20]), "=r"(r[off + 21]), "=r"(r[off + 22]), "=r"(r[off + 23]), \
+          "=r"(r[off + 24]), "=r"(r[off + 25]), "=r"(r[off + 26]), "=r"(r[off + 27]), "=r"(r[off + 28]), "=r"(r[off + 29]), \
+          "=r"(r[off + 30]), "=r"(r[off + 31])                                                                              \
+        : "r"(base))
+    BG_LD32(taddr, 0);
+    BG_LD32(taddr + 32, 32);
+#undef BG_LD32
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void at_st32(unsigned taddr, const float (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
@@ -120,6 +161,15 @@ __device__ __forceinline__ void at_st32(unsigned taddr, const float (&v)[32]) {
           "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
           "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
           "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+__device__ __forceinline__ void at_st16(unsigned taddr, const float (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
         : "memory");
 }
 __device__ __forceinline__ float at_ex2(float x) {
@@ -152,24 +202,27 @@ __host__ __device__ constexpr unsigned at_idesc(int m, int n, int b_nmajor) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)b_nmajor << 16) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
 
-template <int HD>
+template <int HD, int AT_BK>
 __global__ void __launch_bounds__(AT_THREADS)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParams p) {
+    constexpr int AT_HALF = AT_BK / 2, AT_STAGES = 256 / AT_BK;
     constexpr int CB = HD / 64;                          // 64-feature column blocks of a row
     constexpr int Q_BYTES = CB * AT_BM * 128;
     constexpr int KV_BLOCK = AT_BK * 128;                // one column block of a key or value tile
     constexpr int KV_BYTES = CB * KV_BLOCK;
-    constexpr int P_BYTES = AT_BM * 128;
-    constexpr unsigned TMEM_COLS = 256;                  // S: 2 x 64, O: HD (<= 128)
-    constexpr unsigned O_COL = 128;
+    // tensor memory: S in two buffers of 128 columns (columns 0..63 of a buffer are the first group's keys, 64..127
+    // the second group's; a group's P, two bfloat16 a column, takes the first 32 columns of its half), and an
+    // accumulator O of 128 columns for each group
+    constexpr unsigned TMEM_COLS = 512;
+    constexpr unsigned O_COL = 256;
     extern __shared__ unsigned char at_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)at_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = base;
     unsigned char* k_s = q_s + Q_BYTES;
     unsigned char* v_s = k_s + AT_STAGES * KV_BYTES;
-    unsigned char* p_s = v_s + AT_STAGES * KV_BYTES;     // two buffers
     __shared__ __align__(8) unsigned long long k_full[AT_STAGES], k_empty[AT_STAGES], v_full[AT_STAGES], v_empty[AT_STAGES], kv_landed[AT_STAGES];
-    __shared__ __align__(8) unsigned long long s_full[2], s_empty[2], p_full[2], p_empty[2], o_ready;
+    __shared__ __align__(8) unsigned long long s_full[2], p_full[4], pv_done[4], o_ready;    // [buffer], [2 buffer + group]
+    __shared__ float2 ml_other[AT_BM];                   // the second group's running maximum and sum of every row, for the join
     __shared__ unsigned tmem_sh;
     __shared__ int failed;
 
@@ -183,10 +236,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             at_mbar_init(&k_full[s], 1); at_mbar_init(&k_empty[s], 1); at_mbar_init(&v_full[s], 1); at_mbar_init(&v_empty[s], 1);
             at_mbar_init(&kv_landed[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            at_mbar_init(&s_full[b], 1); at_mbar_init(&s_empty[b], 128);
-            at_mbar_init(&p_full[b], 128); at_mbar_init(&p_empty[b], 1);
-        }
+        for (int b = 0; b < 2; ++b) at_mbar_init(&s_full[b], 1);
+        for (int b = 0; b < 4; ++b) { at_mbar_init(&p_full[b], 128); at_mbar_init(&pv_done[b], 1); }
         at_mbar_init(&o_ready, 1);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -226,7 +277,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
     if (warp == 0 || warp == 6) {
         // ------------------------------------------------------------------ MMA issuers: warp 0 the scores, warp 6 the values
         // The whole warp runs the loop and one elected lane issues: addresses and descriptors then stay in
-        // uniform registers, which keeps the issue of one small MMA to a few cycles.
+        // uniform registers, which keeps the issue of one small MMA to a few cycles.  P, the left operand of the
+        // second product, lies in tensor memory, so that MMA reads only its value tile from shared memory (with
+        // both operands there, a 128 x 128 x 16 MMA asks for all of an SM's shared-memory bandwidth).
         constexpr unsigned idesc_qk = at_idesc(AT_BM, AT_BK, 0);
         constexpr unsigned idesc_pv = at_idesc(AT_BM, HD, 1);
         const unsigned q_addr = at_smem(q_s);
@@ -235,11 +288,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             return __all_sync(0xffffffffu, at_mbar_wait(bar, parity)) != 0;
         };
         if (warp == 0) {
-            // scores: S[b] = Q K(i)^T as soon as the keys have landed and the buffer has been read
+            // scores: S[b] = Q K(i)^T as soon as the keys have landed and both groups' P of the buffer's last tile
+            // have been used up
             for (int i = 0; i < n_tiles && ok; ++i) {
                 const int st = i % AT_STAGES, b = i & 1;
                 ok = wait_all(&k_full[st], (i / AT_STAGES) & 1);
-                if (ok && i >= 2) ok = wait_all(&s_empty[b], ((i >> 1) - 1) & 1);
+                if (ok && i >= 2) ok = wait_all(&pv_done[2 * b], ((i >> 1) - 1) & 1) && wait_all(&pv_done[2 * b + 1], ((i >> 1) - 1) & 1);
                 if (!ok) break;
                 at_tc_after();
                 const unsigned k_addr = at_smem(k_s + st * KV_BYTES);
@@ -247,7 +301,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
 #pragma unroll
                     for (int ks = 0; ks < HD / 16; ++ks) {
                         const unsigned off = (ks & 3) * 32;
-                        at_mma(tmem + (unsigned)b * 64, at_desc_kmajor(q_addr + (ks >> 2) * (AT_BM * 128) + off),
+                        at_mma(tmem + (unsigned)b * AT_BK, at_desc_kmajor(q_addr + (ks >> 2) * (AT_BM * 128) + off),
                                at_desc_kmajor(k_addr + (ks >> 2) * KV_BLOCK + off), idesc_qk, ks > 0 ? 1u : 0u);
                     }
                     at_commit(&s_full[b]);
@@ -256,30 +310,36 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                 __syncwarp();
             }
         } else {
-            // values: O += P(i) V(i) once the softmax warps have written P(i)
+            // values: O[g] += P(i, g) V(i, g) once group g's softmax warps have written their half of P
             for (int i = 0; i < n_tiles && ok; ++i) {
                 const int st = i % AT_STAGES, b = i & 1;
-                ok = wait_all(&v_full[st], (i / AT_STAGES) & 1) && wait_all(&p_full[b], (i >> 1) & 1);
-                if (!ok) break;
-                at_tc_after();
-                const unsigned p_addr = at_smem(p_s + b * P_BYTES);
+                ok = wait_all(&v_full[st], (i / AT_STAGES) & 1);
                 const unsigned v_addr = at_smem(v_s + st * KV_BYTES);
-                if (at_elect()) {
+                for (int g = 0; g < 2 && ok; ++g) {
+                    ok = wait_all(&p_full[2 * b + g], (i >> 1) & 1);
+                    if (!ok) break;
+                    at_tc_after();
+                    if (at_elect()) {
 #pragma unroll
-                    for (int ks = 0; ks < AT_BK / 16; ++ks)
-                        at_mma(tmem + O_COL, at_desc_kmajor(p_addr + ks * 32), at_desc_nmajor(v_addr + ks * 2048, KV_BLOCK, 1024),
-                               idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
-                    at_commit(&v_empty[st]);
-                    at_commit(&p_empty[b]);
+                        for (int ks = 0; ks < AT_HALF / 16; ++ks)
+                            at_mma_ts(tmem + O_COL + 128u * (unsigned)g, tmem + (unsigned)b * AT_BK + (unsigned)g * AT_HALF + (unsigned)ks * 8,
+                                      at_desc_nmajor(v_addr + (g * (AT_HALF / 16) + ks) * 2048, KV_BLOCK, 1024), idesc_pv,
+                                      (i > 0 || ks > 0) ? 1u : 0u);
+                        at_commit(&pv_done[2 * b + g]);
+                        if (g == 1) at_commit(&v_empty[st]);
+                    }
+                    __syncwarp();
                 }
-                __syncwarp();
             }
             if (ok) { if (at_elect()) at_commit(&o_ready); }
             __syncwarp();
         }
         if (!ok && lane == 0) atomicExch(&failed, 1);
-    } else if (warp <= 4) {
-        // ------------------------------------------------------------------ softmax: one thread per row
+    } else if (warp <= 4 || warp >= 8) {
+        // ------------------------------------------------------------------ softmax: one thread per row, in each of two groups;
+        // group 0 (warps 1-4) takes the first 64 keys of every tile, group 1 (warps 8-11) the last 64
+        const int grp = warp >= 8 ? 1 : 0;
+        const unsigned o_col = O_COL + 128u * (unsigned)grp;
         const int quarter = warp & 3;                    // the tensor-memory lanes this warp may touch
         const int r = quarter * 32 + lane;
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
@@ -292,34 +352,26 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
         bool ok = true;
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int b = i & 1;
-            const int key0 = (tile0 + i) * AT_BK;
+            const unsigned s_col = (unsigned)b * AT_BK + (unsigned)grp * AT_HALF;     // this group's scores of the tile, and its P
+            const int key0 = (tile0 + i) * AT_BK + grp * AT_HALF;
             ok = at_mbar_wait(&s_full[b], (i >> 1) & 1);
             if (!ok) break;
             at_tc_after();
-            float s[64];
-            {
-                float t[32];
-                at_ld32(tmem + lane_addr + (unsigned)b * 64, t);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) s[j] = t[j];
-                at_ld32(tmem + lane_addr + (unsigned)b * 64 + 32, t);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) s[32 + j] = t[j];
-            }
-            at_tc_before();
-            at_mbar_arrive(&s_empty[b]);                 // the scores are in registers
-            // only a tile that some row of the warp sees in part is masked element by element
+            float s[AT_HALF];
+            if constexpr (AT_HALF == 64) at_ld64(tmem + lane_addr + s_col, s);
+            else at_ld32(tmem + lane_addr + s_col, s);
+            // only a half that some row of the warp sees in part is masked element by element
             float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            if (key0 + AT_BK - 1 > warp_pos_min || key0 < warp_lo_max) {
+            if (key0 + AT_HALF - 1 > warp_pos_min || key0 < warp_lo_max) {
 #pragma unroll
-                for (int j = 0; j < 64; ++j) {
-                    const int key = key0 + j;
-                    s[j] = (key <= pos && key >= lo) ? s[j] : -INFINITY;
-                    tm[j & 3] = fmaxf(tm[j & 3], s[j]);
+                for (int q = 0; q < AT_HALF; ++q) {
+                    const int key = key0 + q;
+                    s[q] = (key <= pos && key >= lo) ? s[q] : -INFINITY;
+                    tm[q & 3] = fmaxf(tm[q & 3], s[q]);
                 }
             } else {
 #pragma unroll
-                for (int j = 0; j < 64; ++j) tm[j & 3] = fmaxf(tm[j & 3], s[j]);
+                for (int q = 0; q < AT_HALF; ++q) tm[q & 3] = fmaxf(tm[q & 3], s[q]);
             }
             const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3])) * p.scale_log2;   // the scale is positive
             // The reference maximum m moves only when some row of the warp outgrows it by more than 8 (a factor
@@ -330,62 +382,66 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
             const float corr = grow ? at_ex2(m - m_use) : 1.0f;
             float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            if (i >= 2) { ok = at_mbar_wait(&p_empty[b], ((i >> 1) - 1) & 1); if (!ok) break; }
-            unsigned char* prow = p_s + b * P_BYTES + r * 128;
+            float pk[AT_HALF / 2];                       // P: two keys a column
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                float e[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) { e[j] = at_ex2(fmaf(s[c * 8 + j], p.scale_log2, -m_use)); sums[j & 3] += e[j]; }
-                uint4 pk;
-                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(e[2 * j], e[2 * j + 1]);
-                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = pk;
+            for (int c = 0; c < AT_HALF / 2; ++c) {
+                const float e0 = at_ex2(fmaf(s[2 * c], p.scale_log2, -m_use)), e1 = at_ex2(fmaf(s[2 * c + 1], p.scale_log2, -m_use));
+                sums[c & 3] += e0 + e1;
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(e0, e1);
+                pk[c] = __uint_as_float(*reinterpret_cast<const unsigned*>(&h2));
             }
             const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
             l = l * corr + sum;
             m = m_new;
-            // rows whose maximum grew: O *= corr, once the previous product has landed
+            // rows whose maximum grew: O *= corr, once this group's product of the tile before has landed
             if (i > 0 && grow) {
-                ok = at_mbar_wait(&p_empty[(i - 1) & 1], ((i - 1) >> 1) & 1);
+                ok = at_mbar_wait(&pv_done[2 * (b ^ 1) + grp], ((i - 1) >> 1) & 1);
                 if (!ok) break;
                 at_tc_after();
 #pragma unroll
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     float t[32];
-                    at_ld32(tmem + lane_addr + O_COL + c0, t);
+                    at_ld32(tmem + lane_addr + o_col + c0, t);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) t[j] *= corr;
-                    at_st32(tmem + lane_addr + O_COL + c0, t);
+                    for (int q = 0; q < 32; ++q) t[q] *= corr;
+                    at_st32(tmem + lane_addr + o_col + c0, t);
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-                at_tc_before();
             }
-            at_fence_async();                            // P (written through the generic proxy) for the MMA
-            at_mbar_arrive(&p_full[b]);
+            if constexpr (AT_HALF == 64) at_st32(tmem + lane_addr + s_col, pk);       // over the first half of the scores it came from
+            else at_st16(tmem + lane_addr + s_col, pk);
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            at_tc_before();
+            at_mbar_arrive(&p_full[2 * b + grp]);
         }
         if (ok && n_tiles > 0) ok = at_mbar_wait(&o_ready, 0);
         if (!ok) atomicExch(&failed, 1);
-        if (ok && real && n_tiles > 0) {
+        // the join of the two groups: the second hands its maximum and sum over, the first group's thread of the
+        // same row (the same lanes of tensor memory) reads both accumulators
+        if (grp == 1) ml_other[r] = make_float2(m, l);
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        if (grp == 0 && ok && n_tiles > 0) {
             at_tc_after();
-        }
-        if (ok && n_tiles > 0) {
-            at_tc_after();
-            const float inv = real ? 1.0f / l : 0.0f;
+            const float2 other = ml_other[r];
+            const float m_all = fmaxf(m, other.x);
+            const float m_ref = (m_all == -INFINITY) ? 0.0f : m_all;
+            const float a0 = at_ex2(m - m_ref), a1 = at_ex2(other.x - m_ref);
+            const float l_all = l * a0 + other.y * a1;
+            const float inv = (real && l_all > 0.0f) ? 1.0f / l_all : 0.0f;
+            const float w0 = a0 * inv, w1 = a1 * inv;
             const int qi = real ? r / group : 0, g = real ? r - qi * group : 0;
             __nv_bfloat16* o = p.out + (size_t)(row0 + qi) * p.out_stride + (size_t)(kvh * group + g) * HD;
 #pragma unroll
             for (int c0 = 0; c0 < HD; c0 += 32) {
-                float t[32];
+                float t[32], u[32];
                 at_ld32(tmem + lane_addr + O_COL + c0, t);        // all lanes take part; only real rows store
+                at_ld32(tmem + lane_addr + O_COL + 128u + c0, u);
                 if (real) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
+                    for (int q = 0; q < 32; q += 8) {
                         float v8[8];
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) v8[k] = t[j + k] * inv;
-                        store8(o + c0 + j, v8);
+                        for (int k = 0; k < 8; ++k) v8[k] = t[q + k] * w0 + u[q + k] * w1;
+                        store8(o + c0 + q, v8);
                     }
                 }
             }
@@ -401,10 +457,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
         const int n_pg = AT_BK / ps;                     // pages per tile (page_size divides 64)
         bool ok = true;
         unsigned landed_phase = 0;                       // bit s: parity of stage s's "landed" barrier
-        auto fetch_pages = [&](int i, int (&pg)[2]) {
+        constexpr int ROUNDS = AT_BK / 32;               // a lane holds the page of up to ROUNDS of a tile's pages (pages of one key)
+        auto fetch_pages = [&](int i, int (&pg)[ROUNDS]) {
             const int key0 = (tile0 + i) * AT_BK;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < ROUNDS; ++h) {
                 const int k = h * 32 + lane;
                 const int pi = key0 / ps + k;
                 pg[h] = -1;
@@ -412,7 +469,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                     pg[h] = p.block_table[(size_t)req * p.max_pages + pi];
             }
         };
-        int pg_next[2];
+        int pg_next[ROUNDS];
         fetch_pages(0, pg_next);
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int st = i % AT_STAGES;
@@ -422,14 +479,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             }
             const int key0 = (tile0 + i) * AT_BK;
             unsigned char* dst = ring + st * KV_BYTES;
-            // page numbers of the tile (fetched one tile ahead): lanes 0..n_pg-1 hold one each, in two rounds
-            int pg[2] = {pg_next[0], pg_next[1]};
-            fetch_pages(i + 1, pg_next);
+            // page numbers of the tile (fetched one tile ahead): lanes 0..n_pg-1 hold one each, in rounds of 32
+            int pg[ROUNDS];
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int h = 0; h < ROUNDS; ++h) pg[h] = pg_next[h];
+            fetch_pages(i + 1, pg_next);
+            unsigned have[ROUNDS];
+            int n_have = 0;
+#pragma unroll
+            for (int h = 0; h < ROUNDS; ++h) {
                 if (pg[h] >= p.num_pages) { if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE); pg[h] = -1; }
-            const unsigned have0 = __ballot_sync(0xffffffffu, pg[0] >= 0), have1 = __ballot_sync(0xffffffffu, pg[1] >= 0);
-            const int n_have = __popc(have0) + __popc(have1);
+                have[h] = __ballot_sync(0xffffffffu, pg[h] >= 0);
+                n_have += __popc(have[h]);
+            }
             // Key rows that no query may see need no care (their scores are masked, whatever they are); value rows
             // do: 0 * garbage can be NaN.  So a ragged tile of values lands on a barrier of its own, the rows
             // outside the range or in pages that are not held are zeroed, and only then is the tile released.
@@ -441,7 +503,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             }
             __syncwarp();
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < ROUNDS; ++h) {
                 if (pg[h] >= 0) {
                     const int row = ((pg[h] * 2 + which) * p.nkv + kvh) * ps;
 #pragma unroll
@@ -456,11 +518,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                     if (!ok) break;
                 }
                 for (int idx = lane; idx < AT_BK * (HD / 8); idx += 32) {
-                    const int j = idx / (HD / 8), c = idx - j * (HD / 8);
-                    const int key = key0 + j, k = j / ps;
-                    const int held = k < 32 ? ((have0 >> k) & 1) : ((have1 >> (k - 32)) & 1);
+                    const int jrow = idx / (HD / 8), c = idx - jrow * (HD / 8);
+                    const int key = key0 + jrow, k = jrow / ps;
+                    unsigned mask = have[0];
+#pragma unroll
+                    for (int h = 1; h < ROUNDS; ++h) mask = (k >> 5) == h ? have[h] : mask;
+                    const int held = (mask >> (k & 31)) & 1;
                     if (!held || key < k_begin || key >= k_end)
-                        *reinterpret_cast<uint4*>(dst + (c >> 3) * KV_BLOCK + j * 128 + (((c & 7) ^ (j & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(dst + (c >> 3) * KV_BLOCK + jrow * 128 + (((c & 7) ^ (jrow & 7)) << 4)) = make_uint4(0, 0, 0, 0);
                 }
                 at_fence_async();
                 __syncwarp();
@@ -478,10 +543,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
     if (tid == 0 && failed && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
 }
 
-template <int HD>
+template <int HD, int BK>
 static int at_launch(const CUtensorMap& map, const AttnTcParams& p, int n_qblk, cudaStream_t stream) {
-    auto kern = attention_tcgen05_kernel<HD>;
-    const size_t smem = (size_t)(HD / 64) * AT_BM * 128 + (size_t)2 * AT_STAGES * (HD / 64) * AT_BK * 128 + 2 * AT_BM * 128 + 1024;
+    auto kern = attention_tcgen05_kernel<HD, BK>;
+    // Q, and two rings (keys, values) of 256 keys each
+    const size_t smem = (size_t)(HD / 64) * AT_BM * 128 + (size_t)2 * 256 * (HD / 64) * 128 + 1024;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     e = launch(kern, dim3(p.nkv, n_qblk), dim3(AT_THREADS), smem, stream, map, p);
@@ -503,7 +569,7 @@ extern "C" int bg_attention_tc_plan(int group, int hd, int page_size, int* bq_ou
 
 extern "C" int bg_attention_tc(const void* q, int q_stride, const void* kv_pool, int num_pages, int page_size,
                                const int* block_table, int max_pages, const int* positions, const int* qblk, int n_qblk,
-                               void* out, int out_stride, int nh, int nkv, int hd, int window, float scale,
+                               void* out, int out_stride, int nh, int nkv, int hd, int window, float scale, int max_position,
                                unsigned* status, cudaStream_t stream) {
     if (n_qblk <= 0) return BG_OK;
     if (nh % nkv != 0 || (hd != 64 && hd != 128) || nh / nkv > 128 || !(scale > 0.0f)) return BG_ERR_UNSUPPORTED;
@@ -520,5 +586,8 @@ extern "C" int bg_attention_tc(const void* q, int q_stride, const void* kv_pool,
     CUtensorMap map;
     int rc = pt_pool_map(&map, kv_pool, num_pages, nkv, page_size, hd);
     if (rc != BG_OK) return rc;
-    return hd == 128 ? at_launch<128>(map, p, n_qblk, stream) : at_launch<64>(map, p, n_qblk, stream);
+    // tiles of 128 keys where a block may walk many of them (max_position bounds the positions of the step's rows)
+    const bool wide = (window > 0 ? (window < max_position + 1 ? window : max_position + 1) : max_position + 1) >= at_wide_from();
+    if (hd == 128) return wide ? at_launch<128, 128>(map, p, n_qblk, stream) : at_launch<128, 64>(map, p, n_qblk, stream);
+    return wide ? at_launch<64, 128>(map, p, n_qblk, stream) : at_launch<64, 64>(map, p, n_qblk, stream);
 }

@@ -40,7 +40,7 @@ _SIGNATURES = {
                                  _c_int, _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p],
     "bg_attention_tc_plan": [_c_int, _c_int, _c_int, ctypes.POINTER(_c_int)],
     "bg_attention_tc": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
-                        _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+                        _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p],
     "bg_gemm_f32_nt": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_void_p],
     "bg_gemm_bf16_tn": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
@@ -454,7 +454,7 @@ def _attention(q: torch.Tensor, q_stride: int, kv_pool: torch.Tensor, block_tabl
             raise KernelError("attention: the tcgen05 kernel takes bfloat16 queries, caches and outputs")
         _check(L.bg_attention_tc(_p(q), q_stride, _p(kv_pool), num_pages, page_size, _p(block_table),
                                  block_table.shape[1], _p(positions), _p(qblk), n_qblk, _p(out), out.stride(0), nh, nkv,
-                                 hd, window, float(scale), _p(status), _stream()), "attention_tcgen05")
+                                 hd, window, float(scale), int(max_position), _p(status), _stream()), "attention_tcgen05")
         return
     if kernel == "mma_rows":
         if q.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:

@@ -251,6 +251,8 @@ def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64, prefe
         ctx = [(37, 1), (150, 1), (0, 1), (63, 1), (64, 1), (127, 1), (200, 1)]
     if long:                                         # many key tiles: every pipeline stage is reused several times
         ctx = [(517, 90), (1000, 1), (0, 333)] if not decode_only else [(517, 1), (1000, 1), (0, 1), (2100, 1), (4400, 1)]
+    if long == "wide":                               # beyond 5,120 keys the tcgen05 kernel walks tiles of 128 keys
+        ctx = [(6144, 2048), (5300, 1), (0, 333)]
     total = [c + n for c, n in ctx]
     n_pages_each = [-(-t // page) for t in total]
     n_pages = sum(n_pages_each) + 5
@@ -358,6 +360,17 @@ def test_attention_tcgen05_kernel(ops, nh, nkv, hd, page, window):
 def test_attention_long_contexts(ops, prefer, decode_only, nh, nkv, hd, page, window):
     got, want = _attention_case(ops, nh, nkv, hd, page, torch.bfloat16, window, seed=9, split=256, prefer=prefer,
                                 decode_only=decode_only, long=True)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(2, 1, 128, 64, None), (3, 1, 64, 16, None), (2, 2, 128, 32, 700)])
+def test_attention_tcgen05_wide_tiles(ops, nh, nkv, hd, page, window):
+    """2,048 rows on top of 6,144 positions of context (8,192 keys), a decoded token at 5,300 and a fresh prompt, in
+    one step: with this many keys the kernel walks tiles of 128 keys, each cut between its two groups of softmax
+    warps, whose accumulators are joined at the end.  Against the plain attention."""
+    got, want = _attention_case(ops, nh, nkv, hd, page, torch.bfloat16, window, seed=17, split=256, prefer="tcgen05",
+                                long="wide")
     assert torch.isfinite(got).all()
     assert (got - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
 
