@@ -385,6 +385,95 @@ __global__ void attention_merge_few_kernel(const float* __restrict__ part_o, con
     }
 }
 
+// The same for many splits of few rows (decoding a long context at a small batch, where a request's keys are
+// spread over up to a whole wave of CTAs): a CTA of eight warps per (row, head).  The splits are taken in groups
+// of eight consecutive ABSOLUTE split numbers; warp w owns the groups w, w + 8, ...: it asks for the eight partial
+// outputs of a group at once (a lane holds four features), joins them in split order around the group's own
+// maximum, and joins its groups in ascending order; the eight warps' results are joined in warp order through
+// shared memory.  The grouping depends on the split numbers alone, so a row's result depends on nothing but its
+// own range of splits.  One trip to memory per group instead of one per 16 splits of a single warp.
+constexpr int MERGE_WARPS = 8;
+template <typename TO>
+__global__ void __launch_bounds__(32 * MERGE_WARPS)
+attention_merge_block_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                             const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
+                             int T, int nh, int hd, int max_splits, int split_arg, int window) {
+    __shared__ float4 acc_s[MERGE_WARPS][32];
+    __shared__ float2 ml_s[MERGE_WARPS];
+    pdl_launch();
+    pdl_wait();
+    const int w = blockIdx.x;                                   // (row, head)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = w / nh, h = w - t * nh;
+    const int pos = positions[t];
+    const int split = keys_per_split(split_arg, pos + 1, max_splits);
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int s_lo = lo / split, s_hi = pos / split;
+    const size_t prow = (size_t)w * max_splits;
+    const int d = lane * 4;
+    const bool live = d < hd;                                   // hd is a multiple of 4
+    float m = -INFINITY, l = 0.0f;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int g = (s_lo >> 3) + ((warp - (s_lo >> 3)) & (MERGE_WARPS - 1)); g * 8 <= s_hi; g += MERGE_WARPS) {
+        float ms[8], ls[8];
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int sidx = g * 8 + j;
+            const bool have = sidx >= s_lo && sidx <= s_hi;
+            const float2 ml = have ? *reinterpret_cast<const float2*>(part_ml + (prow + sidx) * 2) : make_float2(-INFINITY, 0.0f);
+            ms[j] = ml.x; ls[j] = ml.y;
+            v[j] = (have && live) ? *reinterpret_cast<const float4*>(part_o + (prow + sidx) * hd + d)
+                                  : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+        float mg = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mg = fmaxf(mg, ms[j]);
+        if (mg == -INFINITY) continue;
+        float lg = 0.0f;
+        float4 ag = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {                           // in split order
+            if (ms[j] != -INFINITY) {
+                const float f = expf(ms[j] - mg);
+                lg = fmaf(ls[j], f, lg);
+                ag.x = fmaf(v[j].x, f, ag.x); ag.y = fmaf(v[j].y, f, ag.y);
+                ag.z = fmaf(v[j].z, f, ag.z); ag.w = fmaf(v[j].w, f, ag.w);
+            }
+        }
+        const float mn = fmaxf(m, mg);
+        const float fo = (m == -INFINITY) ? 0.0f : expf(m - mn), fg = expf(mg - mn);
+        l = l * fo + lg * fg;
+        acc.x = acc.x * fo + ag.x * fg; acc.y = acc.y * fo + ag.y * fg;
+        acc.z = acc.z * fo + ag.z * fg; acc.w = acc.w * fo + ag.w * fg;
+        m = mn;
+    }
+    acc_s[warp][lane] = acc;
+    if (lane == 0) ml_s[warp] = make_float2(m, l);
+    __syncthreads();
+    if (warp != 0) return;
+    float mt = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MERGE_WARPS; ++i) mt = fmaxf(mt, ml_s[i].x);
+    float lt = 0.0f;
+    float4 at = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < MERGE_WARPS; ++i) {                     // in warp order
+        const float2 ml = ml_s[i];
+        if (ml.x != -INFINITY) {
+            const float f = expf(ml.x - mt);
+            const float4 a = acc_s[i][lane];
+            lt = fmaf(ml.y, f, lt);
+            at.x = fmaf(a.x, f, at.x); at.y = fmaf(a.y, f, at.y); at.z = fmaf(a.z, f, at.z); at.w = fmaf(a.w, f, at.w);
+        }
+    }
+    if (!live) return;
+    const float inv = 1.0f / lt;
+    TO* o = out + (size_t)t * out_stride + (size_t)h * hd + d;
+    o[0] = from_float<TO>(at.x * inv); o[1] = from_float<TO>(at.y * inv);
+    o[2] = from_float<TO>(at.z * inv); o[3] = from_float<TO>(at.w * inv);
+}
+
 extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, const int* positions, void* out,
                                   int out_dtype, int out_stride, int T, int nh, int hd, int max_splits, int split,
                                   int window, cudaStream_t stream) {
@@ -397,6 +486,11 @@ extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, con
     } else if (max_splits <= 16 && hd <= 128) {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 16>, dim3(blocks), dim3(256), 0, stream,
             part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
+    } else if (hd <= 128 && hd % 4 == 0 && out_dtype == BG_DTYPE_BF16 && warps <= 4096) {
+        // bfloat16 rows of few requests with many splits each (the float path keeps one order of summation for
+        // every shape of a step, so that its rows do not depend on the batch)
+        launch(attention_merge_block_kernel<__nv_bfloat16>, dim3((unsigned)warps), dim3(32 * MERGE_WARPS), 0, stream,
+               part_o, part_ml, positions, (__nv_bfloat16*)out, out_stride, T, nh, hd, max_splits, split, window);
     } else if (hd <= 128) {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_kernel<TO, 4, 16>, dim3(blocks), dim3(256), 0, stream,
             part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));

@@ -564,24 +564,41 @@ def test_attention_merge_of_many_ranges(ops, nh, nkv, hd, page, dtype, split, de
     assert (got - want).abs().max() < tol * max(1.0, float(want.abs().max()))
 
 
-@pytest.mark.parametrize("dtype,page,batch", [(torch.bfloat16, 64, 8), (torch.bfloat16, 16, 8), (torch.float32, 64, 8),
-                                              (torch.bfloat16, 64, 64), (torch.bfloat16, 32, 3)])
-def test_decoding_attention_under_a_bound_finds_every_needle(ops, dtype, page, batch):
+@pytest.mark.gpu
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(6, 2, 128, 64, 300), (4, 2, 64, 16, 1000), (3, 1, 48, 16, 77)])
+@pytest.mark.parametrize("decode_only", [False, True])
+def test_attention_merge_of_many_ranges_behind_a_window(ops, nh, nkv, hd, page, window, decode_only):
+    """bfloat16 rows over ranges of 32 keys with a window: a row's ranges begin at any number, not at 0, so the
+    wide merge's groups of eight ranges are cut at both ends."""
+    got, want = _attention_case(ops, nh, nkv, hd, page, torch.bfloat16, window, seed=window, split=32, prefer="generic",
+                                decode_only=decode_only, long=True)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("dtype,page,batch,bound", [(torch.bfloat16, 64, 8, 4095), (torch.bfloat16, 16, 8, 4095),
+                                                    (torch.float32, 64, 8, 4095), (torch.bfloat16, 64, 64, 4095),
+                                                    (torch.bfloat16, 32, 3, 4095), (torch.bfloat16, 64, 2, 32767),
+                                                    (torch.bfloat16, 64, 1, 20479)])
+def test_decoding_attention_under_a_bound_finds_every_needle(ops, dtype, page, batch, bound):
     """Decoding steps that are replayed as a graph launch the attention for the context limit, not for the
     longest request: requests of 40 to 4,000 keys side by side under `max_position` 4095, so that for the short
     ones most CTAs of the fixed grid have nothing to do.  One key of every request is made to win its softmax
     (its value row is a marker), and it is moved through the places where a kernel can lose a key: the first and
     the newest, the two sides of a page's edge and of a 256-key stage, the middle.  Every row must come out as
-    its marker; the other keys are noise."""
+    its marker; the other keys are noise.  Under a bound of tens of thousands of positions a request's keys are
+    spread over dozens of CTAs, whose partial results the wide merge joins."""
     nh, nkv, hd = 12, 2, 128
     lengths = ([40, 700, 1500, 4000, 63, 1023, 255, 2049] * 8)[:batch]
     if batch == 64:
         lengths = [1 + (97 * i) % 4000 for i in range(64)]
+    if bound > 4095:
+        lengths = [20000, 300][:batch]
     torch.manual_seed(batch + page)
     n_pages_each = [-(-t // page) for t in lengths]
     n_pages = sum(n_pages_each) + 3
     perm = iter(torch.randperm(n_pages).tolist())
-    max_pages = 4096 // page
+    max_pages = (bound + 1) // page
     bt = torch.full((batch, max_pages), -1, dtype=torch.int32)
     pool = torch.full((n_pages, 2, nkv, page, hd), float("nan"), dtype=dtype)
     for r, t in enumerate(lengths):
@@ -614,7 +631,7 @@ def test_decoding_attention_under_a_bound_finds_every_needle(ops, dtype, page, b
             pool[pg, 0, :, sl, 5] = 16.0
             pool[pg, 1, :, sl, :] = 100.0 + r
         out = torch.full((batch, nh * hd), float("nan"), dtype=dtype, device=DEV)
-        ops.attention(qd, qd.stride(0), pool, bt.to(DEV), positions, qblk, batch, 4095, batch, nh, nkv, hd, 0, 256, tile, bq,
+        ops.attention(qd, qd.stride(0), pool, bt.to(DEV), positions, qblk, batch, bound, batch, nh, nkv, hd, 0, 256, tile, bq,
                       1.0 / math.sqrt(hd), out, status, kernel)
         ops.raise_on_status(status)
         got = out.float().cpu()
