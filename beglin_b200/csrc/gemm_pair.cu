@@ -1,0 +1,328 @@
+// out[t, n] = sum_k X[t, k] * W[n, k] for steps of many tokens (prompt portions), on the fifth-generation tensor
+// cores with PAIRS of CTAs: a persistent kernel, one pair (a thread block cluster of two, on the two SMs of a
+// TPC) per tile of 256 tokens x 256 output features.
+//
+//   tokens are the M side here and the weights the N side (the reverse of gemm_tcgen05.cu, which streams the
+//   weights once for a handful of tokens): a thread of the epilogue then owns a token's row of consecutive
+//   features, so SwiGLU (gate and up features interleaved in blocks of 64 rows of the weight) is a thread's own
+//   business, and rows go out as whole 128-byte lines.
+//   One thread of the pair's first CTA issues tcgen05.mma.cta_group::2 (M = 256, N = 256): each CTA brings its own
+//   128 tokens and HALF of the tile's weight rows into its shared memory (32 KB a stage instead of 48), the
+//   instruction reads both halves, and each CTA's tensor memory receives the accumulator of its own 128 tokens.
+//   That halving of the shared-memory traffic per flop is what lets the tensor pipe run near its peak.
+//   The accumulator is double-buffered in tensor memory (2 x 256 columns): the four epilogue warps of each CTA
+//   drain tile i (tcgen05.ld, convert, stage in shared memory, TMA store) while the MMAs of tile i + 1 run.
+//
+// Barriers (mbarriers; a wait is bounded and records BG_STATUS_TIMEOUT):
+//   full[s]       in the first CTA: one arrival (its producer's expect_tx of BOTH CTAs' bytes) + the bytes; the second
+//                 CTA's copies complete on the first CTA's barrier (cp.async.bulk.tensor with .cta_group::2)
+//   empty[s]      in both CTAs: tcgen05.commit (multicast to the pair) when the stage's MMAs have read it
+//   acc_full[b]   in both CTAs: tcgen05.commit (multicast) after a tile's last MMA
+//   acc_empty[b]  in the first CTA: 8 arrivals, one per epilogue warp of the pair, when the warp has read buffer b
+// No copy here is a multicast copy: each CTA fetches its own operands.
+#include "tc_common.cuh"
+
+namespace bg {
+
+constexpr int GP_BM = 128;                 // tokens per CTA (256 per pair)
+constexpr int GP_BN = 256;                 // output features per tile; a CTA loads 128 rows of the weight
+constexpr int GP_HALF_N = GP_BN / 2;
+constexpr int GP_THREADS = 192;            // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
+constexpr unsigned GP_A_BYTES = GP_BM * TC_BK * 2;
+constexpr unsigned GP_B_BYTES = GP_HALF_N * TC_BK * 2;
+constexpr unsigned GP_STAGE_BYTES = GP_A_BYTES + GP_B_BYTES;          // 32 KB
+constexpr unsigned GP_OUT_BYTES = GP_BM * 128;                        // a staging buffer: 128 rows of 64 bfloat16
+constexpr int GP_MODE_PLAIN = 0;           // out[t, n] (+ bias[n]) as bfloat16
+constexpr int GP_MODE_SWIGLU = 1;          // out[t, j] = silu(gate) * up, the weight's rows interleaved in blocks of 64
+
+struct PairParams {
+    const float* bias;      // [n_out] or null
+    int n_out, T, K;
+    int tiles_m, tiles_n;   // tiles of 256 tokens and of 256 features
+    unsigned* status;
+};
+
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// A TMA load whose completion is counted on a barrier of the pair's first CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, unsigned bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+                 ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(smem_u32(bar)), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                            unsigned accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+// 16 bytes into a staging buffer of 128 rows x 128 bytes in the 128-byte swizzle of the store's tensor map
+__device__ __forceinline__ void stage_store16(unsigned char* buf, int row, int chunk, uint4 v) {
+    *reinterpret_cast<uint4*>(buf + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
+}
+
+template <int STAGES, int MODE>
+__global__ void __launch_bounds__(GP_THREADS)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                 const __grid_constant__ CUtensorMap map_out, PairParams p) {
+    extern __shared__ unsigned char gp_smem_raw[];
+    unsigned char* tiles = (unsigned char*)(((uintptr_t)gp_smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* staging = tiles + (size_t)STAGES * GP_STAGE_BYTES;
+    __shared__ __align__(8) unsigned long long full_bar[STAGES];
+    __shared__ __align__(8) unsigned long long empty_bar[STAGES];
+    __shared__ __align__(8) unsigned long long acc_full[2];
+    __shared__ __align__(8) unsigned long long acc_empty[2];
+    __shared__ unsigned tmem_base_sh;
+    __shared__ int failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster_rank();
+    const int n_pairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
+    const int n_tiles = p.tiles_m * p.tiles_n;
+    const int n_kb = (p.K + TC_BK - 1) / TC_BK;
+
+    pdl_launch();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(&tmem_base_sh)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                     // the peer's barriers are initialised before anything is signalled there
+    tc_fence_after();
+    const unsigned tmem_base = tmem_base_sh;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (in both CTAs: own tokens, own half of the weight rows)
+        if (lane == 0) {
+            pdl_wait();
+            int it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                const int row_x = tm * (2 * GP_BM) + (int)rank * GP_BM;
+                const int row_w = tn * GP_BN + (int)rank * GP_HALF_N;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1)) { ok = false; break; }
+                    unsigned char* a = tiles + (size_t)s * GP_STAGE_BYTES;
+                    if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * GP_STAGE_BYTES);
+                    const unsigned bar = peer_addr(smem_u32(&full_bar[s]), 0);
+                    tma_load_2d_pair(a, &map_x, kb * TC_BK, row_x, bar);
+                    tma_load_2d_pair(a + GP_A_BYTES, &map_w, kb * TC_BK, row_w, bar);
+                }
+            }
+            if (!ok) atomicExch(&failed, 1);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: one thread of the pair's first CTA
+        if (lane == 0 && rank == 0) {
+            constexpr unsigned idesc = instr_desc_bf16(2 * GP_BM, GP_BN);
+            int it = 0, t_idx = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++t_idx) {
+                const int b = t_idx & 1;
+                if (t_idx >= 2 && !mbar_wait(&acc_empty[b], ((t_idx >> 1) - 1) & 1)) { ok = false; break; }
+                tc_fence_after();
+                const unsigned d = tmem_base + (unsigned)(b * GP_BN);
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    const unsigned a_addr = smem_u32(tiles + (size_t)s * GP_STAGE_BYTES);
+                    const unsigned b_addr = a_addr + GP_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        tc_mma_pair(d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                                    (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit_pair(&empty_bar[s]);      // the stage is free in both CTAs once these MMAs have read it
+                }
+                if (ok) tc_commit_pair(&acc_full[b]);   // both CTAs' epilogues: every MMA of the tile is complete
+            }
+            if (!ok) atomicExch(&failed, 1);
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) .. + 31, a token each
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const bool elected = (warp == 2 && lane == 0);
+        const unsigned acc_empty_first = peer_addr(smem_u32(&acc_empty[0]), 0);
+        int t_idx = 0, q = 0;
+        bool ok = true;
+        pdl_wait();
+        for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++t_idx) {
+            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            const int b = t_idx & 1;
+            if (!mbar_wait(&acc_full[b], (t_idx >> 1) & 1)) { ok = false; break; }
+            tc_fence_after();
+            const unsigned t_addr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(b * GP_BN);
+            const int row0 = tm * (2 * GP_BM) + (int)rank * GP_BM;
+            constexpr int CHUNKS = MODE == GP_MODE_SWIGLU ? 2 : 4;
+#pragma unroll 1
+            for (int c = 0; c < CHUNKS; ++c, ++q) {
+                unsigned char* buf = staging + (size_t)(q & 1) * GP_OUT_BYTES;
+                if (elected) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");     // the store that read this buffer two chunks ago is done
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    unsigned g[32], u[32];
+                    float o[32];
+                    if (MODE == GP_MODE_SWIGLU) {
+                        tc_ld32(t_addr + (unsigned)(c * 128 + h * 32), g);
+                        tc_ld32(t_addr + (unsigned)(c * 128 + 64 + h * 32), u);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
+                            o[j] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+                        }
+                    } else {
+                        tc_ld32(t_addr + (unsigned)(c * 64 + h * 32), g);
+                        tc_wait_ld();
+                        const int n0 = tn * GP_BN + c * 64 + h * 32;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            o[j] = __uint_as_float(g[j]) + ((p.bias && n0 + j < p.n_out) ? __ldg(p.bias + n0 + j) : 0.0f);
+                    }
+                    if (c == CHUNKS - 1 && h == 1) {
+                        // the buffer of tensor memory has been read: the MMAs of the tile after next may overwrite it
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(acc_empty_first + (unsigned)(b * sizeof(unsigned long long)));
+                    }
+#pragma unroll
+                    for (int v = 0; v < 4; ++v)
+                        stage_store16(buf, row, h * 4 + v,
+                                      make_uint4(pack_bf16(o[8 * v], o[8 * v + 1]), pack_bf16(o[8 * v + 2], o[8 * v + 3]),
+                                                 pack_bf16(o[8 * v + 4], o[8 * v + 5]), pack_bf16(o[8 * v + 6], o[8 * v + 7])));
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                if (elected) {
+                    const int col0 = MODE == GP_MODE_SWIGLU ? tn * (GP_BN / 2) + c * 64 : tn * GP_BN + c * 64;
+                    tma_store_2d(&map_out, buf, col0, row0);
+                    asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                }
+            }
+        }
+        if (elected) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
+        if (!ok) atomicExch(&failed, 1);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                     // neither CTA frees tensor memory or leaves while its peer may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+    if (threadIdx.x == 0 && failed && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
+}
+
+template <int STAGES, int MODE>
+static int gp_launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const PairParams& p, cudaStream_t stream) {
+    auto kern = gemm_pair_kernel<STAGES, MODE>;
+    const size_t smem = (size_t)STAGES * GP_STAGE_BYTES + 2 * GP_OUT_BYTES + 1024;
+    static bool set = false;
+    if (!set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        set = true;
+    }
+    const int n_tiles = p.tiles_m * p.tiles_n;
+    int pairs = sm_count() / 2;
+    if (pairs > n_tiles) pairs = n_tiles;
+    if (pairs < 1) return BG_ERR_UNSUPPORTED;
+    // a kernel that issues cta_group::2 instructions is launched with its pairs along x (a launch with the cluster
+    // along z is refused as a misconfigured cluster)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(GP_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 2; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
+    ++n;
+    cfg.attrs = attr; cfg.numAttrs = n;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mx, mw, mo, p);
+    if (e != cudaSuccess) return (int)e;
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+}  // namespace bg
+
+using namespace bg;
+
+// out[t, n] = sum_k X[t, k] W[n, k] (+ bias[n]) as bfloat16 [T, ldo] (mode 0), or, with the rows of W being
+// gate and up features interleaved in blocks of 64 (n_out = 2 * inner), out[t, j] = silu(gate_j) * up_j as
+// bfloat16 [T, ldo] with n_out / 2 columns (mode 1).
+//   W: [n_out, K] bfloat16, row stride ldw; X: [T, K] bfloat16, row stride ldx; strides multiples of 8 elements,
+//   bases 16-byte aligned.  Mode 1 wants n_out a multiple of 128.
+extern "C" int bg_gemm_pair(const void* W, int n_out, int K, int ldw, const void* X, int T, int ldx, const float* bias,
+                            void* out, int ldo, int mode, unsigned* status, cudaStream_t stream) {
+    if (T <= 0 || n_out <= 0) return BG_OK;
+    if (K <= 0) return BG_ERR_SHAPE;
+    if ((ldw % 8) || (ldx % 8) || (ldo % 8) || ((uintptr_t)W % 16) || ((uintptr_t)X % 16) || ((uintptr_t)out % 16)) return BG_ERR_ALIGN;
+    if (mode != GP_MODE_PLAIN && mode != GP_MODE_SWIGLU) return BG_ERR_UNSUPPORTED;
+    if (mode == GP_MODE_SWIGLU && (n_out % 128 || bias)) return BG_ERR_SHAPE;
+    PairParams p;
+    p.bias = bias; p.n_out = n_out; p.T = T; p.K = K; p.status = status;
+    p.tiles_m = (T + 2 * GP_BM - 1) / (2 * GP_BM);
+    p.tiles_n = (n_out + GP_BN - 1) / GP_BN;
+    CUtensorMap mw, mx, mo;
+    int rc = weight_map(&mw, W, n_out, K, ldw);
+    if (rc != BG_OK) return rc;
+    rc = make_map(&mx, X, T, K, ldx, GP_BM);
+    if (rc != BG_OK) return rc;
+    rc = make_map(&mo, out, T, mode == GP_MODE_SWIGLU ? n_out / 2 : n_out, ldo, GP_BM);
+    if (rc != BG_OK) return rc;
+    static int stages = [] { const char* e = getenv("BEGLIN_B200_PAIR_STAGES"); return e ? atoi(e) : 6; }();
+    if (mode == GP_MODE_SWIGLU) {
+        if (stages == 4) return gp_launch<4, GP_MODE_SWIGLU>(mx, mw, mo, p, stream);
+        if (stages == 5) return gp_launch<5, GP_MODE_SWIGLU>(mx, mw, mo, p, stream);
+        return gp_launch<6, GP_MODE_SWIGLU>(mx, mw, mo, p, stream);
+    }
+    if (stages == 4) return gp_launch<4, GP_MODE_PLAIN>(mx, mw, mo, p, stream);
+    if (stages == 5) return gp_launch<5, GP_MODE_PLAIN>(mx, mw, mo, p, stream);
+    return gp_launch<6, GP_MODE_PLAIN>(mx, mw, mo, p, stream);
+}

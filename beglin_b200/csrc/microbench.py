@@ -90,6 +90,29 @@ def _filled_cache(batch: int, context: int, nkv: int, hd: int, page: int):
     return pool, bt
 
 
+def gemm_pair(a) -> None:
+    T, N, K = a.tokens, a.out, a.inner
+    copies = max(2, min(48, int(300e6 // (N * K * 2)) + 1))
+    ws = [(torch.randn(N, K, device=DEV) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    x = torch.randn(T, K, device=DEV).to(torch.bfloat16)
+    status = ops.new_status(DEV)
+    swiglu = a.mode == "swiglu"
+    out = torch.empty((T, N // 2 if swiglu else N), dtype=torch.bfloat16, device=DEV)
+    if a.library:
+        tmp = torch.empty((T, N), dtype=torch.bfloat16, device=DEV)
+        def fn(i):
+            torch.mm(x, ws[i % copies].t(), out=tmp)
+            if swiglu:
+                ops.swiglu(tmp, out, 64)
+    else:
+        def fn(i):
+            ops.gemm_pair(x, ws[i % copies], out, ops.PAIR_SWIGLU if swiglu else ops.PAIR_PLAIN, None, status)
+    us = _time(fn, a.launches)
+    ops.raise_on_status(status)
+    print(f"gemm-pair {'library' if a.library else 'pairs'} mode={a.mode} tokens={T} out={N} inner={K}: {us:.1f} us  "
+          f"{2.0 * T * N * K / us / 1e6:.1f} TFLOP/s")
+
+
 def attention_decode(a) -> None:
     B, ctx, nh, nkv, hd, page = a.batch, a.context, a.heads, a.kv_heads, a.head_dim, a.page
     one = B * ctx * 2 * nkv * hd * 2
@@ -144,6 +167,10 @@ def main() -> None:
     g.add_argument("--tokens", type=int, default=8); g.add_argument("--out", type=int, default=17920)
     g.add_argument("--inner", type=int, default=1536); g.add_argument("--splits", type=int, default=1)
     g.add_argument("--library", action="store_true"); g.set_defaults(fn=gemm)
+    gp = sub.add_parser("gemm-pair")
+    gp.add_argument("--tokens", type=int, default=2048); gp.add_argument("--out", type=int, default=17920)
+    gp.add_argument("--inner", type=int, default=1536); gp.add_argument("--mode", default="plain", choices=["plain", "swiglu"])
+    gp.add_argument("--library", action="store_true"); gp.set_defaults(fn=gemm_pair)
     f = sub.add_parser("gemm-fused")
     f.add_argument("--tokens", type=int, default=8); f.add_argument("--out", type=int, default=17920)
     f.add_argument("--inner", type=int, default=1536); f.add_argument("--splits", type=int, default=2)
@@ -162,7 +189,7 @@ def main() -> None:
     n = sub.add_parser("norm")
     n.add_argument("--tokens", type=int, default=8); n.add_argument("--width", type=int, default=1536)
     n.add_argument("--parts", type=int, default=1); n.set_defaults(fn=norm)
-    for s in (g, f, d, p, n):
+    for s in (g, gp, f, d, p, n):
         s.add_argument("--launches", type=int, default=20)
     a = ap.parse_args()
     ops.lib()

@@ -45,6 +45,8 @@ _SIGNATURES = {
                        _c_int, _c_void_p],
     "bg_gemm_bf16_tn": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int,
                         _c_int, _c_int, _c_void_p, _c_void_p],
+    "bg_gemm_pair": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int,
+                     _c_void_p, _c_void_p],
     "bg_gemm_fused": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int,
                       _c_void_p, _c_float, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
                       _c_void_p, _c_void_p],
@@ -549,6 +551,30 @@ def gemm_bf16_tn_unchecked(x: torch.Tensor, w_ptr: int, n_out: int, k: int, ldw:
     _check(_lib.bg_gemm_bf16_tn(w_ptr, n_out, k, ldw, x.data_ptr(), x.shape[0], x.stride(0), bias_ptr, out.data_ptr(),
                                 F32 if out.dtype == torch.float32 else BF16, n_out, splits, status_ptr, _stream()),
            "gemm_bf16_tn")
+
+
+PAIR_PLAIN, PAIR_SWIGLU = 0, 1
+
+
+def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = PAIR_PLAIN,
+              bias: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
+    """The product of many rows (prompt portions) with w[N, K]^T by pairs of CTAs on the tcgen05 tensor cores.
+    mode PAIR_PLAIN: out bfloat16 [T, N] = product (+ bias).  mode PAIR_SWIGLU: w's rows are interleaved (64 of
+    gate, then their 64 of up); out bfloat16 [T, N / 2] = silu(gate) * up."""
+    _cuda(x, w, out, bias, status)
+    N, K = w.shape
+    T = x.shape[0]
+    cols = N // 2 if mode == PAIR_SWIGLU else N
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("gemm_pair takes bfloat16 operands and gives a bfloat16 result")
+    if x.shape[1] != K or x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1 or tuple(out.shape) != (T, cols):
+        raise KernelError(f"gemm_pair: shapes x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+    if status is None:
+        raise KernelError("gemm_pair wants a status word (its waits are bounded)")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N or not bias.is_contiguous()):
+        raise KernelError("gemm_pair: bias must be float32 with one value per output feature")
+    _check(lib().bg_gemm_pair(_p(w), N, K, w.stride(0), _p(x), T, x.stride(0), _p(bias), _p(out), out.stride(0), mode,
+                              _p(status), _stream()), "gemm_pair")
 
 
 FUSED_PLAIN, FUSED_RESIDUAL, FUSED_SWIGLU = 0, 1, 2

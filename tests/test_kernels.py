@@ -551,6 +551,43 @@ def test_gemm_fused_swiglu(ops, T, im, K, splits):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("T,N,K,bias", [(256, 256, 64, False), (300, 520, 200, True), (2048, 1536, 1536, True),
+                                        (1000, 1288, 456, False), (65, 8, 72, True), (777, 17920 // 8, 1536, False)])
+def test_gemm_pair_plain(ops, T, N, K, bias):
+    """The product of many rows by pairs of CTAs (tokens on the M side, 256 x 256 tiles, persistent): sizes that
+    do not fill a tile in any direction, more tiles than pairs, a bias."""
+    torch.manual_seed(T + N)
+    x = (torch.randn(T, K) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N) if bias else None
+    want = x.double() @ w.double().t() + (b.double() if bias else 0.0)
+    out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = ops.new_status(DEV)
+    ops.gemm_pair(x.to(DEV), w.to(DEV), out, ops.PAIR_PLAIN, b.to(DEV) if bias else None, status)
+    ops.raise_on_status(status)
+    assert torch.isfinite(out).all()
+    assert (out.double().cpu() - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,im,K", [(256, 128, 64), (300, 320, 200), (2048, 8960 // 4, 1536), (999, 64, 136)])
+def test_gemm_pair_swiglu(ops, T, im, K):
+    """The same with SwiGLU in the epilogue: the weight's rows are gate and up features interleaved in blocks of 64."""
+    torch.manual_seed(T + im)
+    x = (torch.randn(T, K) * 0.5).to(torch.bfloat16)
+    gate = (torch.randn(im, K) * 0.08).to(torch.bfloat16)
+    up = (torch.randn(im, K) * 0.08).to(torch.bfloat16)
+    g, u = x.double() @ gate.double().t(), x.double() @ up.double().t()
+    want = g / (1.0 + torch.exp(-g)) * u
+    out = torch.full((T, im), float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = ops.new_status(DEV)
+    ops.gemm_pair(x.to(DEV), _interleave_gate_up(gate, up).contiguous().to(DEV), out, ops.PAIR_SWIGLU, None, status)
+    ops.raise_on_status(status)
+    assert torch.isfinite(out).all()
+    assert (out.double().cpu() - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("nh,nkv,hd,page,dtype,split", [(4, 2, 64, 16, torch.float32, 32), (6, 2, 128, 64, torch.bfloat16, 32),
                                                         (2, 1, 256, 32, torch.float32, 32), (3, 1, 32, 8, torch.float32, 64)])
 @pytest.mark.parametrize("decode_only", [False, True])
