@@ -577,6 +577,16 @@ def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = P
                               _p(status), _stream()), "gemm_pair")
 
 
+def gemm_pair_unchecked(x: torch.Tensor, w_ptr: int, n_out: int, k: int, ldw: int, out: torch.Tensor, mode: int,
+                        status_ptr) -> None:
+    """gemm_pair for a caller that has checked the weight once (Linear): x bfloat16 [T, k] with contiguous rows,
+    out bfloat16 [T, n_out] or, with PAIR_SWIGLU, [T, n_out / 2]; no bias."""
+    if status_ptr is None:
+        raise KernelError("gemm_pair wants a status word (its waits are bounded)")
+    _check(_lib.bg_gemm_pair(w_ptr, n_out, k, ldw, x.data_ptr(), x.shape[0], x.stride(0), None, out.data_ptr(),
+                             out.stride(0), mode, status_ptr, _stream()), "gemm_pair")
+
+
 FUSED_PLAIN, FUSED_RESIDUAL, FUSED_SWIGLU = 0, 1, 2
 
 

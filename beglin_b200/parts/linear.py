@@ -75,11 +75,17 @@ class Linear:
         not been computed).  Where the fused product runs, the norm is applied to the operand inside it;
         the result is then complete ([T, out], float).  Else as `partial`.  With `swiglu` (the weight's
         rows interleaved in blocks of 64, gate then up) the result is silu(gate) * up, [T, out / 2] in the
-        compute type, or None when this step does not run the fused product."""
+        compute type (from the fused product of few rows or from the product of many rows on pairs of CTAs), or
+        None when this step runs neither."""
         lazy = isinstance(inp, NormedInput)
         T = inp.rows if lazy else inp.shape[0]
         if not self.fuses(T):
-            return None if swiglu else self.partial(inp.tensor() if lazy else inp)
+            if swiglu:
+                if self._tc is None or not self._tc.pairs(T):
+                    return None
+                with ops.phase(self.label):
+                    return self._tc.pair_swiglu(inp.tensor() if lazy else inp)
+            return self.partial(inp.tensor() if lazy else inp)
         fusion = inp.fusable() if lazy else None
         n = self.out_features // 2 if swiglu else self.out_features
         out = torch.empty((T, n), dtype=self.ctx.compute_dtype if swiglu else torch.float32, device=self.weight.device)

@@ -17,6 +17,7 @@ from .context import BuildContext
 
 FEW_TOKENS = 64            # up to this many rows a product is treated as weight-streaming
 FUSED_TOKENS = 16            # steps of up to this many rows run the fused product (measured: it loses from 32 rows on)
+PAIR_TOKENS = 192            # from this many rows on the product with SwiGLU in its epilogue runs on pairs of CTAs
 
 
 class TensorCoreProduct:
@@ -86,6 +87,22 @@ class TensorCoreProduct:
                                  None if norm_weight is None else norm_weight.data_ptr(), eps,
                                  None if bias is None else bias.data_ptr(), ssq_out, s, self._status_ptr)
         return ssq_out
+
+    # ------------------------------------------------------------------ the product of many rows on pairs of CTAs
+    def pairs(self, T: int) -> bool:
+        """Whether a step of T rows runs gate/up with SwiGLU as ONE kernel of CTA pairs (measured at the 1.5B and
+        7B shapes: from 256 rows on it beats the library's product followed by the SwiGLU kernel by 10 to 25 %;
+        at 128 rows it loses by 6 %).  The plain products of many rows stay with the library: their matrices
+        have too few 256 x 256 tiles for the pairs of the device."""
+        return self.ctx.fuse and T >= PAIR_TOKENS and self.n_out % 128 == 0
+
+    def pair_swiglu(self, x: torch.Tensor) -> torch.Tensor:
+        """silu(gate) * up of x's rows, [T, n_out / 2] bfloat16; the weight's rows are interleaved in blocks of 64."""
+        if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.shape[1] != self.k or x.stride(0) % 8:
+            raise ops.KernelError(f"the tcgen05 product takes contiguous bfloat16 rows of {self.k} features")
+        out = torch.empty((x.shape[0], self.n_out // 2), dtype=torch.bfloat16, device=x.device)
+        ops.gemm_pair_unchecked(x, self._w_ptr, self.n_out, self.k, self._ldw, out, ops.PAIR_SWIGLU, self._status_ptr)
+        return out
 
     def __call__(self, x: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype, partial: bool) -> torch.Tensor:
         T = x.shape[0]

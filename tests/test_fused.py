@@ -66,3 +66,30 @@ def test_pages_of_64_positions(model_root, dtype):
     for r in ids:
         assert rel_err(torch.cat(got[r]).cpu(), want[r]) < tol, r
     eng.cache.check()
+
+
+def test_steps_of_many_rows_run_swiglu_inside_the_pair_product(model_root):
+    """From 192 rows on, gate/up and SwiGLU are one kernel of CTA pairs.  A whole prompt of 300 tokens, then a step of
+    a 200-token portion of a second request beside a decoded token of the first, then the rest (under 192 rows: the
+    library's product and the SwiGLU kernel), against the plain implementation and against an engine without fusions."""
+    from beglin_b200 import Engine
+    cfg = dict(TINY["D"][0], intermediate_size=320, num_hidden_layers=3, use_sliding_window=False)
+    folder = make_model(model_root, "pairs", seed=21, dtype=torch.bfloat16, config=cfg, std=0.05, bias_std=0.05)
+    ids = {"a": seeded_ids(301, cfg["vocab_size"], 3), "b": seeded_ids(300, cfg["vocab_size"], 4)}
+    want = {r: plain_logits(folder, ids[r]) for r in ids}
+    outs = {}
+    for fuse in (True, False):
+        eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=1024, max_requests=2, fuse=fuse)
+        rl.poison(eng)
+        ff = eng.model.blocks[0].feed_forward
+        assert ff.block == 64 and ff.gate_up._tc.pairs(192) == fuse and not ff.gate_up._tc.pairs(191)
+        got = {"a": [], "b": []}
+        got["a"].append(eng.step([("a", ids["a"][:300], list(range(300)))]))
+        out = eng.step([("b", ids["b"][:200], list(range(200))), ("a", ids["a"][300:], [0])])
+        got["b"].append(out[:200]); got["a"].append(out[200:])
+        got["b"].append(eng.step([("b", ids["b"][200:], list(range(100)))]))
+        outs[fuse] = {r: torch.cat(got[r]).cpu() for r in ids}
+        for r in ids:
+            assert rel_err(outs[fuse][r], want[r]) < TOL_BF16, (r, fuse)
+    for r in ids:
+        assert rel_err(outs[True][r], outs[False][r]) < TOL_BF16 / 2
