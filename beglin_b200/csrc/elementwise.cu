@@ -111,6 +111,60 @@ __global__ void add_rmsnorm_vec8_kernel(float* __restrict__ x, const TD* __restr
     }
 }
 
+// The same with a WARP per row and the row in registers (ITER chunks of eight features per lane): all loads of a
+// row are on their way at once, the statistics need shuffles only, and no thread waits at a barrier of the block.
+// A row's sum of squares is added up in an order that the width alone fixes, whatever the step's other rows are.
+template <typename TD, typename TW, typename TO, int ITER>
+__global__ void __launch_bounds__(256) add_rmsnorm_warp_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+                                                               const TW* __restrict__ w, float eps, TO* __restrict__ out,
+                                                               const int* __restrict__ rows, int n_rows, int d, int update) {
+    pdl_launch();
+    pdl_wait();
+    const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (r >= n_rows) return;
+    const int s = rows ? rows[r] : r;
+    float* xr = x + (size_t)s * d;
+    const int d8 = d >> 3;
+    float v[ITER][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int c = lane + 32 * i;
+        if (c < d8) {
+            load8(xr + 8 * c, v[i]);
+            if (delta) {
+                float a[8];
+                load8(delta + (size_t)s * d + 8 * c, a);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[i][j] += a[j];
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int c = lane + 32 * i;
+        if (c < d8) {
+            if (update && delta) store8(xr + 8 * c, v[i]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+        }
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    TO* o = out + (size_t)r * d;
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int c = lane + 32 * i;
+        if (c < d8) {
+            float g[8];
+            load8(w + 8 * c, g);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] * inv * g[j];
+            store8(o + 8 * c, v[i]);
+        }
+    }
+}
+
 // For float partial sums and few rows: one float4 per thread, so the loads of all parts of a row are
 // in flight at once across the block (the kernel is a chain of dependent round trips otherwise).
 template <typename TW, typename TO>
@@ -489,6 +543,18 @@ static int add_rmsnorm_launch(float* x, const void* delta, int parts, size_t par
         int threads = d / 4 >= 512 ? 512 : (d / 4 >= 256 ? 384 : 128);
         launch(kern, dim3(n_rows), dim3(threads), smem, stream, x, (const float*)delta, parts, part_stride, (const TW*)w, eps,
                (TO*)out, rows, d, update);
+    } else if (vec && parts <= 1 && d <= 8 * 32 * 16) {
+        // a warp per row; the number of chunks per lane depends on the width alone
+        const int iter = (d / 8 + 31) / 32;
+        const unsigned blocks = (unsigned)((n_rows + 7) / 8);
+#define BG_NORM_WARP(IT)                                                                                            \
+        launch(add_rmsnorm_warp_kernel<TD, TW, TO, IT>, dim3(blocks), dim3(256), 0, stream, x, (const TD*)delta, (const TW*)w, \
+               eps, (TO*)out, rows, n_rows, d, update)
+        if (iter <= 2) BG_NORM_WARP(2);
+        else if (iter <= 4) BG_NORM_WARP(4);
+        else if (iter <= 8) BG_NORM_WARP(8);
+        else BG_NORM_WARP(16);
+#undef BG_NORM_WARP
     } else if (vec) {
         auto kern = add_rmsnorm_vec8_kernel<TD, TW, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

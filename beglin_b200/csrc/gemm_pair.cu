@@ -25,20 +25,24 @@
 namespace bg {
 
 constexpr int GP_BM = 128;                 // tokens per CTA (256 per pair)
-constexpr int GP_BN = 256;                 // output features per tile; a CTA loads 128 rows of the weight
-constexpr int GP_HALF_N = GP_BN / 2;
 constexpr int GP_THREADS = 192;            // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
 constexpr unsigned GP_A_BYTES = GP_BM * TC_BK * 2;
-constexpr unsigned GP_B_BYTES = GP_HALF_N * TC_BK * 2;
-constexpr unsigned GP_STAGE_BYTES = GP_A_BYTES + GP_B_BYTES;          // 32 KB
 constexpr unsigned GP_OUT_BYTES = GP_BM * 128;                        // a staging buffer: 128 rows of 64 bfloat16
 constexpr int GP_MODE_PLAIN = 0;           // out[t, n] (+ bias[n]) as bfloat16
 constexpr int GP_MODE_SWIGLU = 1;          // out[t, j] = silu(gate) * up, the weight's rows interleaved in blocks of 64
+constexpr int GP_MODE_RESIDUAL = 2;        // out (float, the residual stream) [t, n] += product (+ bias[n])
+// A tile is 256 tokens x BN output features, BN = 256, 192 or 128: a CTA loads BN / 2 rows of the weight.  The widest
+// tile that keeps the pairs of the device busy is chosen on the host: a narrow matrix has too few tiles of 256.
+template <int BN> struct GpTile {
+    static constexpr unsigned B_BYTES = (BN / 2) * TC_BK * 2;
+    static constexpr unsigned STAGE_BYTES = GP_A_BYTES + B_BYTES;             // 32, 28 or 24 KB
+    static constexpr unsigned TMEM_COLS = BN <= 128 ? 256 : 512;              // two accumulators of BN columns
+};
 
 struct PairParams {
     const float* bias;      // [n_out] or null
     int n_out, T, K;
-    int tiles_m, tiles_n;   // tiles of 256 tokens and of 256 features
+    int tiles_m, tiles_n;   // tiles of 256 tokens and of BN features
     unsigned* status;
 };
 
@@ -55,6 +59,10 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+                 ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];\n"
                  ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void tc_commit_pair(unsigned long long* bar) {
@@ -90,11 +98,14 @@ __device__ __forceinline__ void stage_store16(unsigned char* buf, int row, int c
     *reinterpret_cast<uint4*>(buf + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
 }
 
-template <int STAGES, int MODE>
+template <int STAGES, int MODE, int BN>
 __global__ void __launch_bounds__(GP_THREADS)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_out, PairParams p) {
     extern __shared__ unsigned char gp_smem_raw[];
+    constexpr unsigned GP_STAGE_BYTES = GpTile<BN>::STAGE_BYTES;
+    constexpr int GP_HALF_N = BN / 2;
+    constexpr int GP_BN = BN;
     unsigned char* tiles = (unsigned char*)(((uintptr_t)gp_smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* staging = tiles + (size_t)STAGES * GP_STAGE_BYTES;
     __shared__ __align__(8) unsigned long long full_bar[STAGES];
@@ -119,7 +130,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(smem_u32(&tmem_base_sh)), "r"(512u) : "memory");
+                     ::"r"(smem_u32(&tmem_base_sh)), "r"(GpTile<BN>::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
     }
     tc_fence_before();
@@ -193,7 +204,43 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             tc_fence_after();
             const unsigned t_addr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(b * GP_BN);
             const int row0 = tm * (2 * GP_BM) + (int)rank * GP_BM;
-            constexpr int CHUNKS = MODE == GP_MODE_SWIGLU ? 2 : 4;
+            if (MODE == GP_MODE_RESIDUAL) {
+                // 32 features of the thread's token at a time go into the staging buffer as floats (a row of 128
+                // bytes), and a TMA reduction adds the buffer to the stream in global memory: the SM never reads
+                // the stream, and every element is added to exactly once
+#pragma unroll 1
+                for (int c = 0; c < GP_BN / 32; ++c, ++q) {
+                    unsigned char* buf = staging + (size_t)(q & 1) * GP_OUT_BYTES;
+                    if (elected) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
+                    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                    unsigned g[32];
+                    tc_ld32(t_addr + (unsigned)(c * 32), g);
+                    tc_wait_ld();
+                    if (c == GP_BN / 32 - 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(acc_empty_first + (unsigned)(b * sizeof(unsigned long long)));
+                    }
+                    const int n0 = tn * GP_BN + c * 32;
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        float o[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            o[j] = __uint_as_float(g[4 * v + j]) + ((p.bias && n0 + 4 * v + j < p.n_out) ? __ldg(p.bias + n0 + 4 * v + j) : 0.0f);
+                        stage_store16(buf, row, v, make_uint4(__float_as_uint(o[0]), __float_as_uint(o[1]), __float_as_uint(o[2]),
+                                                              __float_as_uint(o[3])));
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                    if (elected) {
+                        tma_reduce_add_2d(&map_out, buf, n0, row0);
+                        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                    }
+                }
+                continue;
+            }
+            constexpr int CHUNKS = MODE == GP_MODE_SWIGLU ? GP_BN / 128 : GP_BN / 64;
 #pragma unroll 1
             for (int c = 0; c < CHUNKS; ++c, ++q) {
                 unsigned char* buf = staging + (size_t)(q & 1) * GP_OUT_BYTES;
@@ -249,15 +296,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     cluster_sync_all();                     // neither CTA frees tensor memory or leaves while its peer may still signal it
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(GpTile<BN>::TMEM_COLS) : "memory");
     }
     if (threadIdx.x == 0 && failed && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
 }
 
-template <int STAGES, int MODE>
+template <int STAGES, int MODE, int BN>
 static int gp_launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const PairParams& p, cudaStream_t stream) {
-    auto kern = gemm_pair_kernel<STAGES, MODE>;
-    const size_t smem = (size_t)STAGES * GP_STAGE_BYTES + 2 * GP_OUT_BYTES + 1024;
+    auto kern = gemm_pair_kernel<STAGES, MODE, BN>;
+    const size_t smem = (size_t)STAGES * GpTile<BN>::STAGE_BYTES + 2 * GP_OUT_BYTES + 1024;
     static bool set = false;
     if (!set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -289,40 +336,64 @@ static int gp_launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtenso
     return BG_OK;
 }
 
+// The tile width for a product of T rows with n_out output features: the one whose rounds of tiles over the
+// device's pairs cost least.  A tile's cost is the larger of its MMA time (in proportion to its width) and the
+// time its operands need to reach an SM (16 KB of tokens and 64 bytes per feature, at 64 bytes a cycle): 512, 448
+// and 384 cycles per k-block for 256, 192 and 128 features.  Ties go to the wider tile.
+static int gp_tile_width(int T, int n_out, int mode) {
+    static int forced = [] { const char* e = getenv("BEGLIN_B200_PAIR_BN"); return e ? atoi(e) : 0; }();
+    if (forced == 256 || forced == 128 || (forced == 192 && mode != GP_MODE_SWIGLU)) return forced;
+    const int pairs = sm_count() / 2 > 0 ? sm_count() / 2 : 1;
+    const int tiles_m = (T + 2 * GP_BM - 1) / (2 * GP_BM);
+    const int widths[3] = {256, 192, 128}, cost[3] = {512, 448, 384};
+    int best = 256;
+    long long best_cost = -1;
+    for (int i = 0; i < 3; ++i) {
+        if (widths[i] == 192 && mode == GP_MODE_SWIGLU) continue;         // gate and up come in blocks of 64 + 64
+        const long long tiles = (long long)tiles_m * ((n_out + widths[i] - 1) / widths[i]);
+        const long long c = (tiles + pairs - 1) / pairs * cost[i];
+        if (best_cost < 0 || c < best_cost) { best_cost = c; best = widths[i]; }
+    }
+    return best;
+}
+
 }  // namespace bg
 
 using namespace bg;
 
-// out[t, n] = sum_k X[t, k] W[n, k] (+ bias[n]) as bfloat16 [T, ldo] (mode 0), or, with the rows of W being
-// gate and up features interleaved in blocks of 64 (n_out = 2 * inner), out[t, j] = silu(gate_j) * up_j as
-// bfloat16 [T, ldo] with n_out / 2 columns (mode 1).
-//   W: [n_out, K] bfloat16, row stride ldw; X: [T, K] bfloat16, row stride ldx; strides multiples of 8 elements,
-//   bases 16-byte aligned.  Mode 1 wants n_out a multiple of 128.
+// The product of many rows on pairs of CTAs.
+//   mode 0: out[t, n] = sum_k X[t, k] W[n, k] (+ bias[n]) as bfloat16 [T, ldo];
+//   mode 1: the rows of W are gate and up features interleaved in blocks of 64 (n_out = 2 * inner, a multiple of
+//           128): out[t, j] = silu(gate_j) * up_j as bfloat16 [T, ldo] with n_out / 2 columns; no bias;
+//   mode 2: out is the float residual stream [T, ldo]: out[t, n] += sum_k X[t, k] W[n, k] (+ bias[n]).
+//   W: [n_out, K] bfloat16, row stride ldw; X: [T, K] bfloat16, row stride ldx; strides multiples of 8 elements
+//   (ldo of mode 2: of 4), bases 16-byte aligned.
 extern "C" int bg_gemm_pair(const void* W, int n_out, int K, int ldw, const void* X, int T, int ldx, const float* bias,
                             void* out, int ldo, int mode, unsigned* status, cudaStream_t stream) {
     if (T <= 0 || n_out <= 0) return BG_OK;
     if (K <= 0) return BG_ERR_SHAPE;
-    if ((ldw % 8) || (ldx % 8) || (ldo % 8) || ((uintptr_t)W % 16) || ((uintptr_t)X % 16) || ((uintptr_t)out % 16)) return BG_ERR_ALIGN;
-    if (mode != GP_MODE_PLAIN && mode != GP_MODE_SWIGLU) return BG_ERR_UNSUPPORTED;
+    if (mode != GP_MODE_PLAIN && mode != GP_MODE_SWIGLU && mode != GP_MODE_RESIDUAL) return BG_ERR_UNSUPPORTED;
+    if ((ldw % 8) || (ldx % 8) || ((uintptr_t)W % 16) || ((uintptr_t)X % 16) || ((uintptr_t)out % 16)) return BG_ERR_ALIGN;
+    if (mode == GP_MODE_RESIDUAL ? (ldo % 4) : (ldo % 8)) return BG_ERR_ALIGN;
     if (mode == GP_MODE_SWIGLU && (n_out % 128 || bias)) return BG_ERR_SHAPE;
+    const int bn = gp_tile_width(T, n_out, mode);
     PairParams p;
     p.bias = bias; p.n_out = n_out; p.T = T; p.K = K; p.status = status;
     p.tiles_m = (T + 2 * GP_BM - 1) / (2 * GP_BM);
-    p.tiles_n = (n_out + GP_BN - 1) / GP_BN;
+    p.tiles_n = (n_out + bn - 1) / bn;
     CUtensorMap mw, mx, mo;
-    int rc = weight_map(&mw, W, n_out, K, ldw);
+    int rc = weight_map(&mw, W, n_out, K, ldw, bn / 2);
     if (rc != BG_OK) return rc;
     rc = make_map(&mx, X, T, K, ldx, GP_BM);
     if (rc != BG_OK) return rc;
-    rc = make_map(&mo, out, T, mode == GP_MODE_SWIGLU ? n_out / 2 : n_out, ldo, GP_BM);
+    if (mode == GP_MODE_RESIDUAL) rc = make_map_f32(&mo, out, T, n_out, ldo, GP_BM);
+    else rc = make_map(&mo, out, T, mode == GP_MODE_SWIGLU ? n_out / 2 : n_out, ldo, GP_BM);
     if (rc != BG_OK) return rc;
-    static int stages = [] { const char* e = getenv("BEGLIN_B200_PAIR_STAGES"); return e ? atoi(e) : 6; }();
-    if (mode == GP_MODE_SWIGLU) {
-        if (stages == 4) return gp_launch<4, GP_MODE_SWIGLU>(mx, mw, mo, p, stream);
-        if (stages == 5) return gp_launch<5, GP_MODE_SWIGLU>(mx, mw, mo, p, stream);
-        return gp_launch<6, GP_MODE_SWIGLU>(mx, mw, mo, p, stream);
-    }
-    if (stages == 4) return gp_launch<4, GP_MODE_PLAIN>(mx, mw, mo, p, stream);
-    if (stages == 5) return gp_launch<5, GP_MODE_PLAIN>(mx, mw, mo, p, stream);
-    return gp_launch<6, GP_MODE_PLAIN>(mx, mw, mo, p, stream);
+    if (mode == GP_MODE_SWIGLU)
+        return bn == 256 ? gp_launch<6, GP_MODE_SWIGLU, 256>(mx, mw, mo, p, stream) : gp_launch<8, GP_MODE_SWIGLU, 128>(mx, mw, mo, p, stream);
+    if (mode == GP_MODE_PLAIN)
+        return bn == 256 ? gp_launch<6, GP_MODE_PLAIN, 256>(mx, mw, mo, p, stream)
+             : bn == 192 ? gp_launch<6, GP_MODE_PLAIN, 192>(mx, mw, mo, p, stream) : gp_launch<8, GP_MODE_PLAIN, 128>(mx, mw, mo, p, stream);
+    return bn == 256 ? gp_launch<6, GP_MODE_RESIDUAL, 256>(mx, mw, mo, p, stream)
+         : bn == 192 ? gp_launch<6, GP_MODE_RESIDUAL, 192>(mx, mw, mo, p, stream) : gp_launch<8, GP_MODE_RESIDUAL, 128>(mx, mw, mo, p, stream);
 }

@@ -96,17 +96,27 @@ def gemm_pair(a) -> None:
     ws = [(torch.randn(N, K, device=DEV) * 0.02).to(torch.bfloat16) for _ in range(copies)]
     x = torch.randn(T, K, device=DEV).to(torch.bfloat16)
     status = ops.new_status(DEV)
-    swiglu = a.mode == "swiglu"
-    out = torch.empty((T, N // 2 if swiglu else N), dtype=torch.bfloat16, device=DEV)
+    swiglu, residual = a.mode == "swiglu", a.mode == "residual"
+    out = torch.zeros((T, N // 2 if swiglu else N), dtype=torch.float32 if residual else torch.bfloat16, device=DEV)
     if a.library:
+        # the library's product; with its neighbour as a kernel of its own (SwiGLU, or the residual add with the norm)
         tmp = torch.empty((T, N), dtype=torch.bfloat16, device=DEV)
+        nw = torch.ones(N, dtype=torch.bfloat16, device=DEV)
+        normed = torch.empty((T, N), dtype=torch.bfloat16, device=DEV)
         def fn(i):
             torch.mm(x, ws[i % copies].t(), out=tmp)
             if swiglu:
                 ops.swiglu(tmp, out, 64)
+            elif residual:
+                ops.add_rmsnorm(out, tmp, nw, 1e-6, normed)
     else:
+        mode = ops.PAIR_SWIGLU if swiglu else ops.PAIR_RESIDUAL if residual else ops.PAIR_PLAIN
+        nw = torch.ones(N, dtype=torch.bfloat16, device=DEV)
+        normed = torch.empty((T, N), dtype=torch.bfloat16, device=DEV)
         def fn(i):
-            ops.gemm_pair(x, ws[i % copies], out, ops.PAIR_SWIGLU if swiglu else ops.PAIR_PLAIN, None, status)
+            ops.gemm_pair(x, ws[i % copies], out, mode, None, status)
+            if residual:
+                ops.add_rmsnorm(out, None, nw, 1e-6, normed, update=False)
     us = _time(fn, a.launches)
     ops.raise_on_status(status)
     print(f"gemm-pair {'library' if a.library else 'pairs'} mode={a.mode} tokens={T} out={N} inner={K}: {us:.1f} us  "
@@ -154,6 +164,8 @@ def norm(a) -> None:
     T, d, parts = a.tokens, a.width, a.parts
     x = torch.randn(T, d, device=DEV)
     delta = torch.randn((parts, T, d) if parts > 1 else (T, d), device=DEV)
+    if a.bf16_addend:
+        delta = delta.to(torch.bfloat16)
     w = torch.ones(d, dtype=torch.bfloat16, device=DEV)
     out = torch.empty((T, d), dtype=torch.bfloat16, device=DEV)
     us = _time(lambda i: ops.add_rmsnorm(x, delta, w, 1e-6, out), a.launches)
@@ -169,7 +181,7 @@ def main() -> None:
     g.add_argument("--library", action="store_true"); g.set_defaults(fn=gemm)
     gp = sub.add_parser("gemm-pair")
     gp.add_argument("--tokens", type=int, default=2048); gp.add_argument("--out", type=int, default=17920)
-    gp.add_argument("--inner", type=int, default=1536); gp.add_argument("--mode", default="plain", choices=["plain", "swiglu"])
+    gp.add_argument("--inner", type=int, default=1536); gp.add_argument("--mode", default="plain", choices=["plain", "swiglu", "residual"])
     gp.add_argument("--library", action="store_true"); gp.set_defaults(fn=gemm_pair)
     f = sub.add_parser("gemm-fused")
     f.add_argument("--tokens", type=int, default=8); f.add_argument("--out", type=int, default=17920)
@@ -188,7 +200,8 @@ def main() -> None:
         s.add_argument("--split", type=int, default=256)
     n = sub.add_parser("norm")
     n.add_argument("--tokens", type=int, default=8); n.add_argument("--width", type=int, default=1536)
-    n.add_argument("--parts", type=int, default=1); n.set_defaults(fn=norm)
+    n.add_argument("--parts", type=int, default=1); n.add_argument("--bf16-addend", action="store_true")
+    n.set_defaults(fn=norm)
     for s in (g, gp, f, d, p, n):
         s.add_argument("--launches", type=int, default=20)
     a = ap.parse_args()

@@ -553,20 +553,22 @@ def gemm_bf16_tn_unchecked(x: torch.Tensor, w_ptr: int, n_out: int, k: int, ldw:
            "gemm_bf16_tn")
 
 
-PAIR_PLAIN, PAIR_SWIGLU = 0, 1
+PAIR_PLAIN, PAIR_SWIGLU, PAIR_RESIDUAL = 0, 1, 2
 
 
 def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = PAIR_PLAIN,
               bias: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
     """The product of many rows (prompt portions) with w[N, K]^T by pairs of CTAs on the tcgen05 tensor cores.
     mode PAIR_PLAIN: out bfloat16 [T, N] = product (+ bias).  mode PAIR_SWIGLU: w's rows are interleaved (64 of
-    gate, then their 64 of up); out bfloat16 [T, N / 2] = silu(gate) * up."""
+    gate, then their 64 of up); out bfloat16 [T, N / 2] = silu(gate) * up.  mode PAIR_RESIDUAL: out is the float32
+    residual stream [T, N]: out += product (+ bias)."""
     _cuda(x, w, out, bias, status)
     N, K = w.shape
     T = x.shape[0]
     cols = N // 2 if mode == PAIR_SWIGLU else N
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
-        raise KernelError("gemm_pair takes bfloat16 operands and gives a bfloat16 result")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or \
+            out.dtype != (torch.float32 if mode == PAIR_RESIDUAL else torch.bfloat16):
+        raise KernelError("gemm_pair takes bfloat16 operands and gives a bfloat16 result (adds to a float32 stream)")
     if x.shape[1] != K or x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1 or tuple(out.shape) != (T, cols):
         raise KernelError(f"gemm_pair: shapes x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
     if status is None:
@@ -578,12 +580,12 @@ def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = P
 
 
 def gemm_pair_unchecked(x: torch.Tensor, w_ptr: int, n_out: int, k: int, ldw: int, out: torch.Tensor, mode: int,
-                        status_ptr) -> None:
+                        status_ptr, bias_ptr=None) -> None:
     """gemm_pair for a caller that has checked the weight once (Linear): x bfloat16 [T, k] with contiguous rows,
-    out bfloat16 [T, n_out] or, with PAIR_SWIGLU, [T, n_out / 2]; no bias."""
+    out bfloat16 [T, n_out], with PAIR_SWIGLU [T, n_out / 2], with PAIR_RESIDUAL the float32 stream [T, n_out]."""
     if status_ptr is None:
         raise KernelError("gemm_pair wants a status word (its waits are bounded)")
-    _check(_lib.bg_gemm_pair(w_ptr, n_out, k, ldw, x.data_ptr(), x.shape[0], x.stride(0), None, out.data_ptr(),
+    _check(_lib.bg_gemm_pair(w_ptr, n_out, k, ldw, x.data_ptr(), x.shape[0], x.stride(0), bias_ptr, out.data_ptr(),
                              out.stride(0), mode, status_ptr, _stream()), "gemm_pair")
 
 

@@ -110,5 +110,9 @@ class Linear:
             self._check_rows(x)
             with ops.phase(self.label):
                 stream.updated(self._tc.fused(T, stream.x, ops.FUSED_RESIDUAL, x=x, bias=self.bias_f32, want_ssq=True))
+        elif self._tc_always and T >= tensor_core.PAIR_TOKENS and stream.pending is None and self.out_features % 4 == 0:
+            with ops.phase(self.label):
+                self._tc.pair_residual(x, self.bias_f32, stream.x)
+            stream.updated(None)
         else:
             stream.owe(self.partial(x))

@@ -104,8 +104,25 @@ class TensorCoreProduct:
         ops.gemm_pair_unchecked(x, self._w_ptr, self.n_out, self.k, self._ldw, out, ops.PAIR_SWIGLU, self._status_ptr)
         return out
 
+    def pair_residual(self, x: torch.Tensor, bias: Optional[torch.Tensor], stream_x: torch.Tensor) -> None:
+        """stream_x (float32 [T, n_out]) += x W^T (+ bias) on pairs of CTAs.  Measured slower than the library's
+        product followed by the add-and-norm kernel at the 1.5B and 7B shapes (58 against 50 us for the down
+        product of 2,048 tokens), so only an engine built with gemm="tcgen05" runs it."""
+        if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.shape[1] != self.k or x.stride(0) % 8:
+            raise ops.KernelError(f"the tcgen05 product takes contiguous bfloat16 rows of {self.k} features")
+        ops.gemm_pair_unchecked(x, self._w_ptr, self.n_out, self.k, self._ldw, stream_x, ops.PAIR_RESIDUAL,
+                                self._status_ptr, None if bias is None else bias.data_ptr())
+
     def __call__(self, x: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype, partial: bool) -> torch.Tensor:
         T = x.shape[0]
+        if T >= PAIR_TOKENS and out_dtype == torch.bfloat16:
+            # many rows (this kernel is asked for them only by an engine built with gemm="tcgen05"): pairs of CTAs
+            if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.shape[1] != self.k or x.stride(0) % 8:
+                raise ops.KernelError(f"the tcgen05 product takes contiguous bfloat16 rows of {self.k} features")
+            out = torch.empty((T, self.n_out), dtype=torch.bfloat16, device=x.device)
+            ops.gemm_pair_unchecked(x, self._w_ptr, self.n_out, self.k, self._ldw, out, ops.PAIR_PLAIN, self._status_ptr,
+                                    None if bias is None else bias.data_ptr())
+            return out
         s = self.splits(T) if partial else 1
         if s > 1:
             out = torch.empty((s, T, self.n_out), dtype=torch.float32, device=x.device)

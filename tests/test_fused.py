@@ -93,3 +93,23 @@ def test_steps_of_many_rows_run_swiglu_inside_the_pair_product(model_root):
             assert rel_err(outs[fuse][r], want[r]) < TOL_BF16, (r, fuse)
     for r in ids:
         assert rel_err(outs[True][r], outs[False][r]) < TOL_BF16 / 2
+
+
+def test_an_engine_of_own_products_only(model_root):
+    """gemm="tcgen05": every product of the model on this package's kernels; steps of 192 rows and more then run
+    the products of CTA pairs in all three modes (plain with bias for q/k/v, into the residual stream for the
+    output and down products, SwiGLU for gate/up).  Against the plain implementation and the default engine."""
+    from beglin_b200 import Engine
+    cfg = dict(TINY["D"][0], intermediate_size=320, num_hidden_layers=3, use_sliding_window=False)
+    folder = make_model(model_root, "pairs", seed=21, dtype=torch.bfloat16, config=cfg, std=0.05, bias_std=0.05)
+    ids = seeded_ids(330, cfg["vocab_size"], 9)
+    want = plain_logits(folder, ids)
+    outs = {}
+    for gemm in ("tcgen05", "auto"):
+        eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=512, max_requests=1, gemm=gemm)
+        rl.poison(eng)
+        got = [eng.step([("a", ids[:250], list(range(250)))]), eng.step([("a", ids[250:270], list(range(20)))]),
+               eng.step([("a", ids[270:], list(range(60)))])]
+        outs[gemm] = torch.cat(got).cpu()
+        assert rel_err(outs[gemm], want) < TOL_BF16, gemm
+    assert rel_err(outs["tcgen05"], outs["auto"]) < TOL_BF16 / 2

@@ -552,10 +552,12 @@ def test_gemm_fused_swiglu(ops, T, im, K, splits):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("T,N,K,bias", [(256, 256, 64, False), (300, 520, 200, True), (2048, 1536, 1536, True),
-                                        (1000, 1288, 456, False), (65, 8, 72, True), (777, 17920 // 8, 1536, False)])
+                                        (1000, 1288, 456, False), (65, 8, 72, True), (777, 17920 // 8, 1536, False),
+                                        (2048, 4096, 128, True), (3000, 2600, 72, False)])
 def test_gemm_pair_plain(ops, T, N, K, bias):
-    """The product of many rows by pairs of CTAs (tokens on the M side, 256 x 256 tiles, persistent): sizes that
-    do not fill a tile in any direction, more tiles than pairs, a bias."""
+    """The product of many rows by pairs of CTAs (tokens on the M side, tiles of 256 tokens x 256, 192 or 128
+    features, persistent): sizes that do not fill a tile in any direction, more tiles than pairs, every tile
+    width (the last two shapes take 256, (2048, 1536) takes 192, (1000, 1288) takes 128), a bias."""
     torch.manual_seed(T + N)
     x = (torch.randn(T, K) * 0.5).to(torch.bfloat16)
     w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
@@ -570,7 +572,28 @@ def test_gemm_pair_plain(ops, T, N, K, bias):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("T,im,K", [(256, 128, 64), (300, 320, 200), (2048, 8960 // 4, 1536), (999, 64, 136)])
+@pytest.mark.parametrize("T,N,K,bias", [(256, 256, 64, False), (300, 520, 200, True), (2048, 1536, 1536, False),
+                                        (1000, 1288, 456, True), (65, 8, 72, True), (2048, 4096, 128, True)])
+def test_gemm_pair_residual(ops, T, N, K, bias):
+    """The same adding into the float residual stream: out += product (+ bias), nothing else of the stream touched."""
+    torch.manual_seed(T + N + 1)
+    x = (torch.randn(T, K) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N) if bias else None
+    stream = torch.randn(T + 3, N)
+    want = stream.double().clone()
+    want[:T] += x.double() @ w.double().t() + (b.double() if bias else 0.0)
+    out = stream.to(DEV)
+    status = ops.new_status(DEV)
+    ops.gemm_pair(x.to(DEV), w.to(DEV), out[:T], ops.PAIR_RESIDUAL, b.to(DEV) if bias else None, status)
+    ops.raise_on_status(status)
+    assert (out.double().cpu() - want).abs().max() < 2e-3 * max(1.0, float(want.abs().max()))
+    assert torch.equal(out[T:].cpu(), stream[T:])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,im,K", [(256, 128, 64), (300, 320, 200), (2048, 8960 // 4, 1536), (999, 64, 136),
+                                    (2048, 2048, 72)])
 def test_gemm_pair_swiglu(ops, T, im, K):
     """The same with SwiGLU in the epilogue: the weight's rows are gate and up features interleaved in blocks of 64."""
     torch.manual_seed(T + im)
