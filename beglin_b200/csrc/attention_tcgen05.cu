@@ -42,7 +42,7 @@ inline int at_wide_from() {
 // Keys per tile: 128 for long contexts (an MMA of 64 key columns costs as much as one of 128), 64 for short ones
 // (a block's keys are walked in whole tiles, and with few tiles a tile that is mostly masked weighs more).  A tile
 // is cut into two halves, one for each group of softmax warps.  Stages of the key and value rings: 256 keys each.
-constexpr int AT_THREADS = 384;            // warps 0 and 6: MMA issue; warps 1-4 and 8-11: softmax; warps 5 and 7: loaders
+constexpr int AT_THREADS = 448;            // warps 0 and 6: MMA issue; warps 1-4 and 8-11: softmax; warps 5, 7, 12, 13: loaders
 constexpr unsigned long long AT_WAIT_NS = 1000000000ull;
 constexpr float AT_LOG2E = 1.4426950408889634f;
 
@@ -206,13 +206,16 @@ template <int HD, int AT_BK>
 __global__ void __launch_bounds__(AT_THREADS)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParams p) {
     constexpr int AT_HALF = AT_BK / 2, AT_STAGES = 256 / AT_BK;
+    constexpr int NSB = AT_STAGES;                       // score buffers in tensor memory: tiles whose scores may be under way
     constexpr int CB = HD / 64;                          // 64-feature column blocks of a row
     constexpr int Q_BYTES = CB * AT_BM * 128;
     constexpr int KV_BLOCK = AT_BK * 128;                // one column block of a key or value tile
     constexpr int KV_BYTES = CB * KV_BLOCK;
-    // tensor memory: S in two buffers of 128 columns (columns 0..63 of a buffer are the first group's keys, 64..127
-    // the second group's; a group's P, two bfloat16 a column, takes the first 32 columns of its half), and an
-    // accumulator O of 128 columns for each group
+    // tensor memory: S in NSB buffers of AT_BK columns, 256 in all (the first half of a buffer's columns are the first
+    // group's keys, the second half the second group's; a group's P, two bfloat16 a column, takes the first half of
+    // its half), and an accumulator O of 128 columns for each group.  With tiles of 64 keys four tiles' scores are
+    // under way at once, so that a group's softmax finds its next scores waiting: the chain product -> load ->
+    // exponentials -> store -> product of one tile, with a barrier's latency at every arrow, is hidden behind three others.
     constexpr unsigned TMEM_COLS = 512;
     constexpr unsigned O_COL = 256;
     extern __shared__ unsigned char at_raw[];
@@ -220,8 +223,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
     unsigned char* q_s = base;
     unsigned char* k_s = q_s + Q_BYTES;
     unsigned char* v_s = k_s + AT_STAGES * KV_BYTES;
-    __shared__ __align__(8) unsigned long long k_full[AT_STAGES], k_empty[AT_STAGES], v_full[AT_STAGES], v_empty[AT_STAGES], kv_landed[AT_STAGES];
-    __shared__ __align__(8) unsigned long long s_full[2], p_full[4], pv_done[4], o_ready;    // [buffer], [2 buffer + group]
+    // A commit costs its thread hundreds of cycles, so one commit serves every reader of an event: s_full[b] tells the
+    // softmax warps that the scores of a tile are there AND the key loader that the tile's stage is free (a stage of
+    // the rings and a score buffer have the same number); pv_done[b] tells the score issuer that buffer b may be
+    // overwritten, the softmax warps that O may be rescaled, and the value loader that the stage is free.
+    __shared__ __align__(8) unsigned long long k_full[AT_STAGES], v_full[AT_STAGES], kv_landed[AT_STAGES];
+    __shared__ __align__(8) unsigned long long s_full[NSB], p_full[2 * NSB], pv_done[NSB], o_ready;    // p_full: [2 buffer + group]
     __shared__ float2 ml_other[AT_BM];                   // the second group's running maximum and sum of every row, for the join
     __shared__ unsigned tmem_sh;
     __shared__ int failed;
@@ -233,11 +240,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
     const int kvh = blockIdx.x, qb = (int)gridDim.y - 1 - (int)blockIdx.y;
     if (tid == 0) {
         for (int s = 0; s < AT_STAGES; ++s) {
-            at_mbar_init(&k_full[s], 1); at_mbar_init(&k_empty[s], 1); at_mbar_init(&v_full[s], 1); at_mbar_init(&v_empty[s], 1);
-            at_mbar_init(&kv_landed[s], 1);
+            at_mbar_init(&k_full[s], 1); at_mbar_init(&v_full[s], 1); at_mbar_init(&kv_landed[s], 1);
         }
-        for (int b = 0; b < 2; ++b) at_mbar_init(&s_full[b], 1);
-        for (int b = 0; b < 4; ++b) { at_mbar_init(&p_full[b], 128); at_mbar_init(&pv_done[b], 1); }
+        for (int b = 0; b < NSB; ++b) { at_mbar_init(&s_full[b], 1); at_mbar_init(&pv_done[b], 1); }
+        for (int b = 0; b < 2 * NSB; ++b) at_mbar_init(&p_full[b], 128);
         at_mbar_init(&o_ready, 1);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -291,9 +297,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             // scores: S[b] = Q K(i)^T as soon as the keys have landed and both groups' P of the buffer's last tile
             // have been used up
             for (int i = 0; i < n_tiles && ok; ++i) {
-                const int st = i % AT_STAGES, b = i & 1;
+                const int st = i % AT_STAGES, b = i % NSB;
                 ok = wait_all(&k_full[st], (i / AT_STAGES) & 1);
-                if (ok && i >= 2) ok = wait_all(&pv_done[2 * b], ((i >> 1) - 1) & 1) && wait_all(&pv_done[2 * b + 1], ((i >> 1) - 1) & 1);
+                if (ok && i >= NSB) ok = wait_all(&pv_done[b], ((i / NSB) - 1) & 1);
                 if (!ok) break;
                 at_tc_after();
                 const unsigned k_addr = at_smem(k_s + st * KV_BYTES);
@@ -305,18 +311,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                                at_desc_kmajor(k_addr + (ks >> 2) * KV_BLOCK + off), idesc_qk, ks > 0 ? 1u : 0u);
                     }
                     at_commit(&s_full[b]);
-                    at_commit(&k_empty[st]);
                 }
                 __syncwarp();
             }
         } else {
             // values: O[g] += P(i, g) V(i, g) once group g's softmax warps have written their half of P
             for (int i = 0; i < n_tiles && ok; ++i) {
-                const int st = i % AT_STAGES, b = i & 1;
+                const int st = i % AT_STAGES, b = i % NSB;
                 ok = wait_all(&v_full[st], (i / AT_STAGES) & 1);
                 const unsigned v_addr = at_smem(v_s + st * KV_BYTES);
                 for (int g = 0; g < 2 && ok; ++g) {
-                    ok = wait_all(&p_full[2 * b + g], (i >> 1) & 1);
+                    ok = wait_all(&p_full[2 * b + g], (i / NSB) & 1);
                     if (!ok) break;
                     at_tc_after();
                     if (at_elect()) {
@@ -325,8 +330,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                             at_mma_ts(tmem + O_COL + 128u * (unsigned)g, tmem + (unsigned)b * AT_BK + (unsigned)g * AT_HALF + (unsigned)ks * 8,
                                       at_desc_nmajor(v_addr + (g * (AT_HALF / 16) + ks) * 2048, KV_BLOCK, 1024), idesc_pv,
                                       (i > 0 || ks > 0) ? 1u : 0u);
-                        at_commit(&pv_done[2 * b + g]);
-                        if (g == 1) at_commit(&v_empty[st]);
+                        if (g == 1) at_commit(&pv_done[b]);
                     }
                     __syncwarp();
                 }
@@ -335,7 +339,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             __syncwarp();
         }
         if (!ok && lane == 0) atomicExch(&failed, 1);
-    } else if (warp <= 4 || warp >= 8) {
+    } else if (warp <= 4 || (warp >= 8 && warp <= 11)) {
         // ------------------------------------------------------------------ softmax: one thread per row, in each of two groups;
         // group 0 (warps 1-4) takes the first 64 keys of every tile, group 1 (warps 8-11) the last 64
         const int grp = warp >= 8 ? 1 : 0;
@@ -351,10 +355,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
         for (int i = 0; i < n_tiles && ok; ++i) {
-            const int b = i & 1;
+            const int b = i % NSB;
             const unsigned s_col = (unsigned)b * AT_BK + (unsigned)grp * AT_HALF;     // this group's scores of the tile, and its P
             const int key0 = (tile0 + i) * AT_BK + grp * AT_HALF;
-            ok = at_mbar_wait(&s_full[b], (i >> 1) & 1);
+            ok = at_mbar_wait(&s_full[b], (i / NSB) & 1);
             if (!ok) break;
             at_tc_after();
             float s[AT_HALF];
@@ -395,7 +399,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             m = m_new;
             // rows whose maximum grew: O *= corr, once this group's product of the tile before has landed
             if (i > 0 && grow) {
-                ok = at_mbar_wait(&pv_done[2 * (b ^ 1) + grp], ((i - 1) >> 1) & 1);
+                ok = at_mbar_wait(&pv_done[(i - 1) % NSB], ((i - 1) / NSB) & 1);
                 if (!ok) break;
                 at_tc_after();
 #pragma unroll
@@ -447,14 +451,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             }
         }
     } else {
-        // ------------------------------------------------------------------ loaders: TMA, a tile of 64 keys at a time;
-        // warp 5 brings the keys, warp 7 the values, each through a ring of stages of its own
-        const int which = warp == 7;
+        // ------------------------------------------------------------------ loaders: TMA, a tile of keys at a time;
+        // warps 5 and 12 bring the keys, warps 7 and 13 the values, each pair through a ring of stages of its own.
+        // A loader's turn for one tile (page numbers, the barrier's byte count, the copies: each an operation of a
+        // few hundred cycles, one after the other) takes longer than the tensor cores need for the tile, so two
+        // warps share a ring: one takes the even tiles, the other the odd ones.
+        const int which = (warp == 7 || warp == 13);
+        const int lsub = warp >= 12;
         unsigned char* ring = which ? v_s : k_s;
         unsigned long long* full = which ? v_full : k_full;
-        unsigned long long* empty = which ? v_empty : k_empty;
-        const int ps = p.page_size;
-        const int n_pg = AT_BK / ps;                     // pages per tile (page_size divides 64)
+        unsigned long long* empty = which ? pv_done : s_full;      // AT_STAGES == NSB: stage st is buffer st
+        const int ps = p.page_size, sh = p.page_shift;   // the page size is a power of two
+        const int n_pg = AT_BK >> sh;                    // pages per tile (page_size divides 64)
         bool ok = true;
         unsigned landed_phase = 0;                       // bit s: parity of stage s's "landed" barrier
         constexpr int ROUNDS = AT_BK / 32;               // a lane holds the page of up to ROUNDS of a tile's pages (pages of one key)
@@ -463,15 +471,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
 #pragma unroll
             for (int h = 0; h < ROUNDS; ++h) {
                 const int k = h * 32 + lane;
-                const int pi = key0 / ps + k;
+                const int pi = (key0 >> sh) + k;
                 pg[h] = -1;
                 if (i < n_tiles && k < n_pg && pi < p.max_pages && key0 + k * ps < k_end && key0 + (k + 1) * ps > k_begin)
                     pg[h] = p.block_table[(size_t)req * p.max_pages + pi];
             }
         };
         int pg_next[ROUNDS];
-        fetch_pages(0, pg_next);
-        for (int i = 0; i < n_tiles && ok; ++i) {
+        fetch_pages(lsub, pg_next);
+        for (int i = lsub; i < n_tiles && ok; i += 2) {
             const int st = i % AT_STAGES;
             if (i >= AT_STAGES) {
                 ok = at_mbar_wait(&empty[st], ((i / AT_STAGES) - 1) & 1);
@@ -483,7 +491,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             int pg[ROUNDS];
 #pragma unroll
             for (int h = 0; h < ROUNDS; ++h) pg[h] = pg_next[h];
-            fetch_pages(i + 1, pg_next);
+            fetch_pages(i + 2, pg_next);
             unsigned have[ROUNDS];
             int n_have = 0;
 #pragma unroll
@@ -519,7 +527,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                 }
                 for (int idx = lane; idx < AT_BK * (HD / 8); idx += 32) {
                     const int jrow = idx / (HD / 8), c = idx - jrow * (HD / 8);
-                    const int key = key0 + jrow, k = jrow / ps;
+                    const int key = key0 + jrow, k = jrow >> sh;
                     unsigned mask = have[0];
 #pragma unroll
                     for (int h = 1; h < ROUNDS; ++h) mask = (k >> 5) == h ? have[h] : mask;
