@@ -35,8 +35,8 @@ namespace bg {
 
 constexpr int AT_BM = 128;                 // rows per CTA
 // From this many keys on, tiles of 128 keys (BEGLIN_B200_ATTN_WIDE_FROM overrides the measured default).
-inline int at_wide_from() {
-    static int v = [] { const char* e = getenv("BEGLIN_B200_ATTN_WIDE_FROM"); return (e && atoi(e) > 0) ? atoi(e) : 5120; }();
+inline int& at_wide_from() {
+    static int v = [] { const char* e = getenv("BEGLIN_B200_ATTN_WIDE_FROM"); return (e && atoi(e) > 0) ? atoi(e) : 12288; }();
     return v;
 }
 // Keys per tile: 128 for long contexts (an MMA of 64 key columns costs as much as one of 128), 64 for short ones
@@ -207,6 +207,12 @@ __global__ void __launch_bounds__(AT_THREADS)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParams p) {
     constexpr int AT_HALF = AT_BK / 2, AT_STAGES = 256 / AT_BK;
     constexpr int NSB = AT_STAGES;                       // score buffers in tensor memory: tiles whose scores may be under way
+    // How the two groups of softmax warps share the keys.  Tiles of 128 keys: every tile is cut in two halves, one for
+    // each group.  Tiles of 64 keys: the groups take turns, the first the even tiles and the second the odd ones, so a
+    // group's turn (the load of the scores, the store of P, the barriers: a few hundred cycles that do not depend on
+    // the number of keys) comes once per 128 keys in both arrangements.
+    constexpr bool ALT = AT_BK == 64;
+    constexpr int GK = ALT ? AT_BK : AT_HALF;            // keys of a tile that one group takes
     constexpr int CB = HD / 64;                          // 64-feature column blocks of a row
     constexpr int Q_BYTES = CB * AT_BM * 128;
     constexpr int KV_BLOCK = AT_BK * 128;                // one column block of a key or value tile
@@ -243,7 +249,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             at_mbar_init(&k_full[s], 1); at_mbar_init(&v_full[s], 1); at_mbar_init(&kv_landed[s], 1);
         }
         for (int b = 0; b < NSB; ++b) { at_mbar_init(&s_full[b], 1); at_mbar_init(&pv_done[b], 1); }
-        for (int b = 0; b < 2 * NSB; ++b) at_mbar_init(&p_full[b], 128);
+        for (int b = 0; b < 2 * NSB; ++b) at_mbar_init(&p_full[b], 4);       // one arrival per softmax warp of a group
         at_mbar_init(&o_ready, 1);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -320,6 +326,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                 const int st = i % AT_STAGES, b = i % NSB;
                 ok = wait_all(&v_full[st], (i / AT_STAGES) & 1);
                 const unsigned v_addr = at_smem(v_s + st * KV_BYTES);
+                if constexpr (ALT) {
+                    const int g = i & 1;
+                    if (ok) ok = wait_all(&p_full[b], (i / NSB) & 1);
+                    if (!ok) break;
+                    at_tc_after();
+                    if (at_elect()) {
+#pragma unroll
+                        for (int ks = 0; ks < AT_BK / 16; ++ks)
+                            at_mma_ts(tmem + O_COL + 128u * (unsigned)g, tmem + (unsigned)b * AT_BK + (unsigned)ks * 8,
+                                      at_desc_nmajor(v_addr + ks * 2048, KV_BLOCK, 1024), idesc_pv, (i >= 2 || ks > 0) ? 1u : 0u);
+                        at_commit(&pv_done[b]);
+                    }
+                    __syncwarp();
+                } else {
                 for (int g = 0; g < 2 && ok; ++g) {
                     ok = wait_all(&p_full[2 * b + g], (i / NSB) & 1);
                     if (!ok) break;
@@ -333,6 +353,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                         if (g == 1) at_commit(&pv_done[b]);
                     }
                     __syncwarp();
+                }
                 }
             }
             if (ok) { if (at_elect()) at_commit(&o_ready); }
@@ -354,41 +375,42 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
         const int warp_lo_max = __reduce_max_sync(0xffffffffu, lo);
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
-        for (int i = 0; i < n_tiles && ok; ++i) {
+        const int i_first = ALT ? grp : 0;                   // this group's first tile
+        for (int i = i_first; i < n_tiles && ok; i += (ALT ? 2 : 1)) {
             const int b = i % NSB;
-            const unsigned s_col = (unsigned)b * AT_BK + (unsigned)grp * AT_HALF;     // this group's scores of the tile, and its P
-            const int key0 = (tile0 + i) * AT_BK + grp * AT_HALF;
+            const unsigned s_col = (unsigned)b * AT_BK + (ALT ? 0u : (unsigned)grp * AT_HALF);    // this group's scores of the tile, and its P
+            const int key0 = (tile0 + i) * AT_BK + (ALT ? 0 : grp * AT_HALF);
             ok = at_mbar_wait(&s_full[b], (i / NSB) & 1);
             if (!ok) break;
             at_tc_after();
-            float s[AT_HALF];
-            if constexpr (AT_HALF == 64) at_ld64(tmem + lane_addr + s_col, s);
+            float s[GK];
+            if constexpr (GK == 64) at_ld64(tmem + lane_addr + s_col, s);
             else at_ld32(tmem + lane_addr + s_col, s);
             // only a half that some row of the warp sees in part is masked element by element
             float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            if (key0 + AT_HALF - 1 > warp_pos_min || key0 < warp_lo_max) {
+            if (key0 + GK - 1 > warp_pos_min || key0 < warp_lo_max) {
 #pragma unroll
-                for (int q = 0; q < AT_HALF; ++q) {
+                for (int q = 0; q < GK; ++q) {
                     const int key = key0 + q;
                     s[q] = (key <= pos && key >= lo) ? s[q] : -INFINITY;
                     tm[q & 3] = fmaxf(tm[q & 3], s[q]);
                 }
             } else {
 #pragma unroll
-                for (int q = 0; q < AT_HALF; ++q) tm[q & 3] = fmaxf(tm[q & 3], s[q]);
+                for (int q = 0; q < GK; ++q) tm[q & 3] = fmaxf(tm[q & 3], s[q]);
             }
             const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3])) * p.scale_log2;   // the scale is positive
             // The reference maximum m moves only when some row of the warp outgrows it by more than 8 (a factor
             // of 256, harmless in float and bfloat16): then the rows' O and l are rescaled; otherwise the
             // exponentials keep the old reference and nothing that was accumulated needs touching.
-            const bool grow = __any_sync(0xffffffffu, tmax > m + 8.0f) || (i == 0);
+            const bool grow = __any_sync(0xffffffffu, tmax > m + 8.0f) || (i == i_first);
             const float m_new = grow ? fmaxf(m, tmax) : m;
             const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
             const float corr = grow ? at_ex2(m - m_use) : 1.0f;
             float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            float pk[AT_HALF / 2];                       // P: two keys a column
+            float pk[GK / 2];                            // P: two keys a column
 #pragma unroll
-            for (int c = 0; c < AT_HALF / 2; ++c) {
+            for (int c = 0; c < GK / 2; ++c) {
                 const float e0 = at_ex2(fmaf(s[2 * c], p.scale_log2, -m_use)), e1 = at_ex2(fmaf(s[2 * c + 1], p.scale_log2, -m_use));
                 sums[c & 3] += e0 + e1;
                 const __nv_bfloat162 h2 = __floats2bfloat162_rn(e0, e1);
@@ -397,9 +419,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
             l = l * corr + sum;
             m = m_new;
-            // rows whose maximum grew: O *= corr, once this group's product of the tile before has landed
-            if (i > 0 && grow) {
-                ok = at_mbar_wait(&pv_done[(i - 1) % NSB], ((i - 1) / NSB) & 1);
+            // rows whose maximum grew: O *= corr, once this group's product before this one has landed
+            const int prev = ALT ? i - 2 : i - 1;
+            if (prev >= 0 && grow) {
+                ok = at_mbar_wait(&pv_done[prev % NSB], (prev / NSB) & 1);
                 if (!ok) break;
                 at_tc_after();
 #pragma unroll
@@ -411,11 +434,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                     at_st32(tmem + lane_addr + o_col + c0, t);
                 }
             }
-            if constexpr (AT_HALF == 64) at_st32(tmem + lane_addr + s_col, pk);       // over the first half of the scores it came from
+            if constexpr (GK == 64) at_st32(tmem + lane_addr + s_col, pk);       // over the first half of the scores it came from
             else at_st16(tmem + lane_addr + s_col, pk);
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             at_tc_before();
-            at_mbar_arrive(&p_full[2 * b + grp]);
+            __syncwarp();                                // every lane's P has been stored: one arrival for the warp
+            if (lane == 0) at_mbar_arrive(&p_full[ALT ? b : 2 * b + grp]);
         }
         if (ok && n_tiles > 0) ok = at_mbar_wait(&o_ready, 0);
         if (!ok) atomicExch(&failed, 1);
@@ -432,6 +456,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             const float l_all = l * a0 + other.y * a1;
             const float inv = (real && l_all > 0.0f) ? 1.0f / l_all : 0.0f;
             const float w0 = a0 * inv, w1 = a1 * inv;
+            const bool has1 = !ALT || n_tiles > 1;       // with one tile the second group's accumulator was never written
             const int qi = real ? r / group : 0, g = real ? r - qi * group : 0;
             __nv_bfloat16* o = p.out + (size_t)(row0 + qi) * p.out_stride + (size_t)(kvh * group + g) * HD;
 #pragma unroll
@@ -444,7 +469,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                     for (int q = 0; q < 32; q += 8) {
                         float v8[8];
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) v8[k] = t[q + k] * w0 + u[q + k] * w1;
+                        for (int k = 0; k < 8; ++k) v8[k] = t[q + k] * w0 + (has1 ? u[q + k] * w1 : 0.0f);
                         store8(o + c0 + q, v8);
                     }
                 }
@@ -566,6 +591,13 @@ static int at_launch(const CUtensorMap& map, const AttnTcParams& p, int n_qblk, 
 }  // namespace bg
 
 using namespace bg;
+
+// Sets the number of keys from which tiles of 128 keys are walked (0 or less: leaves it) and returns the old one.
+extern "C" int bg_attention_tc_wide_from(int keys) {
+    const int old = at_wide_from();
+    if (keys > 0) at_wide_from() = keys;
+    return old;
+}
 
 // Rows (tokens) per query block for these sizes, or BG_ERR_UNSUPPORTED.
 extern "C" int bg_attention_tc_plan(int group, int hd, int page_size, int* bq_out) {

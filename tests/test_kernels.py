@@ -251,7 +251,7 @@ def _attention_case(ops, nh, nkv, hd, page, dtype, window, seed, split=64, prefe
         ctx = [(37, 1), (150, 1), (0, 1), (63, 1), (64, 1), (127, 1), (200, 1)]
     if long:                                         # many key tiles: every pipeline stage is reused several times
         ctx = [(517, 90), (1000, 1), (0, 333)] if not decode_only else [(517, 1), (1000, 1), (0, 1), (2100, 1), (4400, 1)]
-    if long == "wide":                               # beyond 5,120 keys the tcgen05 kernel walks tiles of 128 keys
+    if long == "wide":                               # thousands of keys: the tcgen05 kernel in either arrangement of its tiles
         ctx = [(6144, 2048), (5300, 1), (0, 333)]
     total = [c + n for c, n in ctx]
     n_pages_each = [-(-t // page) for t in total]
@@ -365,12 +365,18 @@ def test_attention_long_contexts(ops, prefer, decode_only, nh, nkv, hd, page, wi
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page,window", [(2, 1, 128, 64, None), (3, 1, 64, 16, None), (2, 2, 128, 32, 700)])
-def test_attention_tcgen05_wide_tiles(ops, nh, nkv, hd, page, window):
+@pytest.mark.parametrize("tile_keys", [128, 64])
+def test_attention_tcgen05_long_prompts(ops, nh, nkv, hd, page, window, tile_keys):
     """2,048 rows on top of 6,144 positions of context (8,192 keys), a decoded token at 5,300 and a fresh prompt, in
-    one step: with this many keys the kernel walks tiles of 128 keys, each cut between its two groups of softmax
-    warps, whose accumulators are joined at the end.  Against the plain attention."""
-    got, want = _attention_case(ops, nh, nkv, hd, page, torch.bfloat16, window, seed=17, split=256, prefer="tcgen05",
-                                long="wide")
+    one step, in both arrangements of the kernel: tiles of 128 keys, each cut between the two groups of softmax
+    warps, and tiles of 64 keys that the groups take in turns (the kernel picks by the number of keys; the test
+    moves the limit).  The groups' accumulators are joined at the end.  Against the plain attention."""
+    old = ops.attention_wide_from(4096 if tile_keys == 128 else 1 << 30)
+    try:
+        got, want = _attention_case(ops, nh, nkv, hd, page, torch.bfloat16, window, seed=17, split=256, prefer="tcgen05",
+                                    long="wide")
+    finally:
+        ops.attention_wide_from(old)
     assert torch.isfinite(got).all()
     assert (got - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
 
