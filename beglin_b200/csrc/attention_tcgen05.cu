@@ -1,31 +1,33 @@
 // Attention of prompt portions on the fifth-generation tensor cores (bfloat16, head size 64 or 128).
 //
 // One CTA takes a query block of up to 128 rows (consecutive tokens of one request x the query heads
-// of one kv head) and walks all keys the block sees, 128 at a time:
-//   S = Q K^T      tcgen05.mma with 128 key columns (an MMA of 64 columns costs its issuer and the tensor
-//                  cores as much as one of 128), Q and the key tile in shared memory (K-major, 128-byte
-//                  swizzle), S in tensor memory (128 columns);
-//   softmax        one thread per row, the tile's scores in two halves of 64: tcgen05.ld of the row's 64
-//                  scores, scale, mask, running maximum and sum in float, P = exp2(S - m) as bfloat16
-//                  into shared memory;
-//   O += P V       tcgen05.mma, one half at a time: P K-major, the value tile as it lies in the cache
-//                  (N-major), O in tensor memory (head_dim columns); when a row's maximum grows, its O is
-//                  rescaled by tcgen05.ld / tcgen05.st before the product is issued.
-// The softmax of a tile is a chain of latencies (the load from tensor memory, the maximum, the
-// exponentials, the store of P) that one warp per SM sub-partition cannot hide, and it is what a tile
-// waits for.  So the key tiles are dealt to TWO groups of four softmax warps, the even tiles to one
-// and the odd tiles to the other: each group has a score buffer, keeps a running maximum, a sum and an accumulator O in
-// tensor memory of its own, as if the keys had been cut into two interleaved sets, and the two are
-// joined when all tiles are done (O = (O_e 2^(m_e - m) + O_o 2^(m_o - m)) / (l_e 2^(m_e - m) + l_o 2^(m_o - m))).
-// While one group is busy with tile i the other works on tile i + 1, and the tensor cores serve both.
-// Keys and values come from the pages by TMA (cp.async.bulk.tensor over the page pool seen as a 2-D
-// tensor [rows, head_dim], boxes of one page x 64 features, 128-byte swizzle), each through a ring of
-// two stages of 128 keys of its own: the keys' stage is free as soon as the scores are done, the values'
-// only after the second product.  Issuing an asynchronous operation (a copy, an MMA, a commit) costs the
-// issuing thread on the order of a hundred cycles, so the roles are spread over warps: warp 0 issues
-// S = Q K^T, warp 6 issues O += P V, warp 5 copies keys, warp 7 copies values, warps 1-4 are the
-// softmax of the even tiles and warps 8-11 that of the odd tiles.  A tile of values at the ragged end of the keys is completed by its loader (rows that the
-// block must not see are zeroed, so that 0 * garbage cannot be NaN) before it is released.
+// of one kv head) and walks all keys the block sees, a tile of 64 or of 128 keys at a time:
+//   S = Q K^T      tcgen05.mma, Q and the key tile in shared memory (K-major, 128-byte swizzle), S in tensor
+//                  memory: 256 columns hold the scores of four tiles of 64 keys or of two tiles of 128;
+//   softmax        one thread per row: tcgen05.ld of the row's scores, scale, mask, running maximum and sum in
+//                  float, P = exp2(S - m) as bfloat16, written by tcgen05.st over the columns the scores came
+//                  from (two keys a column);
+//   O += P V       tcgen05.mma with P as the left operand IN TENSOR MEMORY and the value tile as it lies in the
+//                  cache (N-major) in shared memory; O in tensor memory.  When a row's maximum has grown by more
+//                  than a factor of 256, its O is rescaled by tcgen05.ld / tcgen05.st before the product is issued.
+// The softmax of a tile is a chain of latencies (the load from tensor memory, the maximum, the exponentials, the
+// store of P) that one warp per SM sub-partition cannot hide.  So there are TWO groups of four softmax warps, each
+// with a running maximum, a sum and an accumulator O in tensor memory of its own, as if the keys had been cut into
+// two sets; the two are joined when all tiles are done
+// (O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m))).  With tiles of 128 keys a tile
+// is cut in two halves, one for each group; with tiles of 64 keys the groups take the tiles in turns.
+// Tiles of 128 keys cost the tensor cores less per key (an MMA of 64 key columns takes as long as one of 128), tiles
+// of 64 have four tiles under way instead of two and waste less on the tile at the diagonal: the narrow ones win up
+// to about 12,000 keys.
+// Keys and values come from the pages by TMA (cp.async.bulk.tensor over the page pool seen as a 2-D tensor
+// [rows, head_dim], boxes of one page x 64 features, 128-byte swizzle), each through a ring of 256 keys of its own:
+// a stage of the keys is free as soon as its scores are done, a stage of the values after the second product.
+// Issuing an asynchronous operation (a copy, an MMA, a commit) costs the issuing thread a few hundred cycles, and a
+// loader's turn for one tile is a chain of such operations that takes longer than the tensor cores need for the
+// tile.  So the roles are spread over fourteen warps: warp 0 issues S = Q K^T, warp 6 issues O += P V, warps 5 and 12
+// copy the keys of the even and the odd tiles, warps 7 and 13 the values, warps 1-4 and 8-11 are the two softmax
+// groups.  A tile of values at the ragged end of the keys is completed by its loader (rows that the block must not
+// see are zeroed, so that 0 * garbage cannot be NaN) before it is released.
 // Every wait on an mbarrier is bounded in time and records BG_STATUS_TIMEOUT.
 //
 // The result is the finished row, out[t, h, :] = O / l, as in attention_mma.cu's rows arrangement.
@@ -39,9 +41,7 @@ inline int& at_wide_from() {
     static int v = [] { const char* e = getenv("BEGLIN_B200_ATTN_WIDE_FROM"); return (e && atoi(e) > 0) ? atoi(e) : 12288; }();
     return v;
 }
-// Keys per tile: 128 for long contexts (an MMA of 64 key columns costs as much as one of 128), 64 for short ones
-// (a block's keys are walked in whole tiles, and with few tiles a tile that is mostly masked weighs more).  A tile
-// is cut into two halves, one for each group of softmax warps.  Stages of the key and value rings: 256 keys each.
+// Stages of the key and value rings: 256 keys each.
 constexpr int AT_THREADS = 448;            // warps 0 and 6: MMA issue; warps 1-4 and 8-11: softmax; warps 5, 7, 12, 13: loaders
 constexpr unsigned long long AT_WAIT_NS = 1000000000ull;
 constexpr float AT_LOG2E = 1.4426950408889634f;
