@@ -160,9 +160,9 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
     // The group fetched here is the one the first keys of this CTA's range lie in when there is no window.
     __shared__ int table_s[AM_TABLE];
     if (tid == 0) {
-        for (int s = 0; s < AM_STAGES; ++s) { pt_mbar_init(&full_bar[s], 1); pt_mbar_init(&empty_bar[s], BY_KEYS ? 1 : AM_THREADS / 32); }
+        for (int s = 0; s < AM_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], BY_KEYS ? 1 : AM_THREADS / 32); }
         gave_up = 0;
-        pt_mbar_init_fence();
+        mbar_init_fence();
     }
     const bool direct = !BY_KEYS && p.out != nullptr;
     const int split = keys_per_split(p.split, pos_last + 1, (int)gridDim.z);
@@ -215,7 +215,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
             const int buf = s % AM_STAGES;
             int page = next_page;
             next_page = page_of(s + 1, p.whole_pages ? lane * PER_PAGE : lane);   // fetched while this stage's copies go out
-            if (s >= AM_STAGES && !pt_mbar_wait(&empty_bar[buf], ((s / AM_STAGES) - 1) & 1, &gave_up)) {
+            if (s >= AM_STAGES && !mbar_wait<4000>(&empty_bar[buf], ((s / AM_STAGES) - 1) & 1, &gave_up)) {
                 if (p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
                 return;
             }
@@ -224,10 +224,10 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
                 if (lane == 0) {
                     if (page >= p.num_pages) { if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE); page = -1; }
                     if (page >= 0) {
-                        pt_expect_tx(&full_bar[buf], BUF_BYTES);
-                        pt_tma_page(kd, &map_page, page * 2 * p.nkv + kvh, &full_bar[buf]);
+                        mbar_expect_tx(&full_bar[buf], BUF_BYTES);
+                        tma_load_5d_last(kd, &map_page, page * 2 * p.nkv + kvh, &full_bar[buf]);
                     } else {
-                        pt_mbar_arrive(&full_bar[buf]);
+                        mbar_arrive(&full_bar[buf]);
                     }
                 }
                 continue;
@@ -237,16 +237,16 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
                 if (h > 0) page = page_of(s, o);
                 if (page >= p.num_pages) { if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE); page = -1; }
                 const unsigned have = __ballot_sync(0xffffffffu, page >= 0);
-                if (lane == 0 && have) pt_expect_only(&full_bar[buf], (unsigned)__popc(have) * ps * 128);
+                if (lane == 0 && have) mbar_expect_only(&full_bar[buf], (unsigned)__popc(have) * ps * 128);
                 __syncwarp();
                 if (page >= 0) {
                     const int k = o / PER_PAGE, rem = o % PER_PAGE, which = rem / (HD / 64), cb = rem % (HD / 64);
-                    pt_tma_2d(kd + which * STAGE_BYTES + cb * (AM_STAGE_KEYS * 128) + k * ps * 128, &map_kv, cb * 64,
+                    tma_load_2d(kd + which * STAGE_BYTES + cb * (AM_STAGE_KEYS * 128) + k * ps * 128, &map_kv, cb * 64,
                               ((page * 2 + which) * p.nkv + kvh) * ps, &full_bar[buf]);
                 }
             }
             __syncwarp();
-            if (lane == 0) pt_mbar_arrive(&full_bar[buf]);   // the one arrival the phase waits for, after every expect_tx
+            if (lane == 0) mbar_arrive(&full_bar[buf]);   // the one arrival the phase waits for, after every expect_tx
         }
         return;
     }
@@ -375,7 +375,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
         if (p.use_tma) {
             // A wait that runs out records it and goes on (with whatever the buffer holds; the host raises on
             // the status): every thread then still reaches the barriers below.
-            if (!pt_mbar_wait(&full_bar[buf], (s / AM_STAGES) & 1, &gave_up) && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
+            if (!mbar_wait<4000>(&full_bar[buf], (s / AM_STAGES) & 1, &gave_up) && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
             if (stage_key0 < k_begin || stage_key0 + AM_STAGE_KEYS > k_end) {      // uniform over the readers
                 // whole pages were copied: rows outside the range of keys become zeros (a value row that no
                 // query sees must not hold garbage, since 0 * NaN is NaN)
@@ -386,7 +386,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
                         *reinterpret_cast<uint4*>(vt + swz_kv(j, c)) = make_uint4(0, 0, 0, 0);
                     }
                 }
-                pt_fence_async();
+                fence_proxy_async();
                 if (BY_KEYS) __syncwarp(); else compute_sync();
             }
         } else if (BY_KEYS) {
@@ -585,7 +585,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
         // the stage's buffer may be refilled
         if (p.use_tma) {
             __syncwarp();
-            if (lane == 0) pt_mbar_arrive(&empty_bar[buf]);
+            if (lane == 0) mbar_arrive(&empty_bar[buf]);
         } else if (!BY_KEYS) {
             compute_sync();
         }

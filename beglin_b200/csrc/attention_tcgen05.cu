@@ -43,7 +43,6 @@ inline int& at_wide_from() {
 }
 // Stages of the key and value rings: 256 keys each.
 constexpr int AT_THREADS = 448;            // warps 0 and 6: MMA issue; warps 1-4 and 8-11: softmax; warps 5, 7, 12, 13: loaders
-constexpr unsigned long long AT_WAIT_NS = 1000000000ull;
 constexpr float AT_LOG2E = 1.4426950408889634f;
 
 struct AttnTcParams {
@@ -62,144 +61,15 @@ struct AttnTcParams {
     unsigned* status;
 };
 
-__device__ __forceinline__ unsigned at_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void at_mbar_init(unsigned long long* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(at_smem(bar)), "r"(count));
-}
-__device__ __forceinline__ void at_mbar_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(at_smem(bar)) : "memory");
-}
-__device__ __forceinline__ bool at_mbar_wait(unsigned long long* bar, unsigned parity) {
-    unsigned addr = at_smem(bar);
-    unsigned long long t0 = 0;
-    for (unsigned it = 0;; ++it) {
-        unsigned done;
-        // the hint lets the hardware park the thread (up to 2 us) instead of polling: polls of many waiting
-        // threads would crowd the shared-memory pipeline that the copies of other warps need
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-        if ((it & 15u) == 15u) {
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > AT_WAIT_NS) return false;
-        }
-    }
-}
-__device__ __forceinline__ void at_expect_tx(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(at_smem(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void at_tma_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-                 ::"r"(at_smem(dst)), "l"(map), "r"(x), "r"(y), "r"(at_smem(bar)) : "memory");
-}
-__device__ __forceinline__ void at_fence_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ bool at_elect() {
     unsigned one;
     asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(one));
     return one != 0;
 }
-__device__ __forceinline__ void at_tc_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void at_tc_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void at_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(at_smem(bar)) : "memory");
-}
-__device__ __forceinline__ void at_mma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc, unsigned acc) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
-}
-// The same with the left operand in tensor memory (row i in lane i, two bfloat16 of consecutive k a column).
-__device__ __forceinline__ void at_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long b, unsigned idesc, unsigned acc) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-                 ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void at_ld32(unsigned taddr, float (&v)[32]) {
-    unsigned r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-// 64 consecutive columns: both loads are on their way before the one wait.
-__device__ __forceinline__ void at_ld64(unsigned taddr, float (&v)[64]) {
-    unsigned r[64];
-#define BG_LD32(base, off)                                                                                                  \
-    asm volatile(                                                                                                           \
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"                   \
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"                                        \
-        : "=r"(r[off + 0]), "=r"(r[off + 1]), "=r"(r[off + 2]), "=r"(r[off + 3]), "=r"(r[off + 4]), "=r"(r[off + 5]),       \
-          "=r"(r[off + 6]), "=r"(r[off + 7]), "=r"(r[off + 8]), "=r"(r[off + 9]), "=r"(r[off + 10]), "=r"(r[off + 11]),     \
-          "=r"(r[off + 12]), "=r"(r[off + 13]), "=r"(r[off + 14]), "=r"(r[off + 15]), "=r"(r[off + 16]), "=r"(r[off + 17]), \
-          "=r"(r[off + 18]), "=r"(r[off + 19]), "=r"(r[off + 20]), "=r"(r[off + 21]), "=r"(r[off + 22]), "=r"(r[off + 23]), \
-          "=r"(r[off + 24]), "=r"(r[off + 25]), "=r"(r[off + 26]), "=r"(r[off + 27]), "=r"(r[off + 28]), "=r"(r[off + 29]), \
-          "=r"(r[off + 30]), "=r"(r[off + 31])                                                                              \
-        : "r"(base))
-    BG_LD32(taddr, 0);
-    BG_LD32(taddr + 32, 32);
-#undef BG_LD32
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void at_st32(unsigned taddr, const float (&v)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
-        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
-          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
-          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
-          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
-          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
-          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
-          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
-        : "memory");
-}
-__device__ __forceinline__ void at_st16(unsigned taddr, const float (&v)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
-        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
-          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
-          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
-        : "memory");
-}
 __device__ __forceinline__ float at_ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
-}
-
-// Operand descriptors, 128-byte swizzle.  K-major: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
-__device__ __forceinline__ unsigned long long at_desc_kmajor(unsigned addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
-    d |= (unsigned long long)(1024u >> 4) << 32;
-    d |= 1ull << 46;
-    d |= 2ull << 61;
-    return d;
-}
-// N-major (the value tile, stored [key][feature]): a swizzle atom is 64 features x 8 keys; `lbo` is the
-// distance between atoms along the features, `sbo` along the keys.
-__device__ __forceinline__ unsigned long long at_desc_nmajor(unsigned addr, unsigned lbo, unsigned sbo) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
-    d |= (unsigned long long)((lbo >> 4) & 0x3FFFu) << 16;
-    d |= (unsigned long long)((sbo >> 4) & 0x3FFFu) << 32;
-    d |= 1ull << 46;
-    d |= 2ull << 61;
-    return d;
-}
-__host__ __device__ constexpr unsigned at_idesc(int m, int n, int b_nmajor) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)b_nmajor << 16) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
 
 template <int HD, int AT_BK>
@@ -246,16 +116,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
     const int kvh = blockIdx.x, qb = (int)gridDim.y - 1 - (int)blockIdx.y;
     if (tid == 0) {
         for (int s = 0; s < AT_STAGES; ++s) {
-            at_mbar_init(&k_full[s], 1); at_mbar_init(&v_full[s], 1); at_mbar_init(&kv_landed[s], 1);
+            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_landed[s], 1);
         }
-        for (int b = 0; b < NSB; ++b) { at_mbar_init(&s_full[b], 1); at_mbar_init(&pv_done[b], 1); }
-        for (int b = 0; b < 2 * NSB; ++b) at_mbar_init(&p_full[b], 4);       // one arrival per softmax warp of a group
-        at_mbar_init(&o_ready, 1);
+        for (int b = 0; b < NSB; ++b) { mbar_init(&s_full[b], 1); mbar_init(&pv_done[b], 1); }
+        for (int b = 0; b < 2 * NSB; ++b) mbar_init(&p_full[b], 4);       // one arrival per softmax warp of a group
+        mbar_init(&o_ready, 1);
         failed = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        mbar_init_fence();
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(at_smem(&tmem_sh)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_sh)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     pdl_wait();
@@ -280,10 +150,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
         const int cb = c >> 3, cc = c & 7;
         *reinterpret_cast<uint4*>(q_s + cb * (AT_BM * 128) + r * 128 + ((cc ^ (r & 7)) << 4)) = v;
     }
-    at_fence_async();
-    at_tc_before();
+    fence_proxy_async();
+    tc_fence_before();
     __syncthreads();
-    at_tc_after();
+    tc_fence_after();
     const unsigned tmem = tmem_sh;
 
     if (warp == 0 || warp == 6) {
@@ -292,12 +162,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
         // uniform registers, which keeps the issue of one small MMA to a few cycles.  P, the left operand of the
         // second product, lies in tensor memory, so that MMA reads only its value tile from shared memory (with
         // both operands there, a 128 x 128 x 16 MMA asks for all of an SM's shared-memory bandwidth).
-        constexpr unsigned idesc_qk = at_idesc(AT_BM, AT_BK, 0);
-        constexpr unsigned idesc_pv = at_idesc(AT_BM, HD, 1);
-        const unsigned q_addr = at_smem(q_s);
+        constexpr unsigned idesc_qk = instr_desc_bf16(AT_BM, AT_BK, 0);
+        constexpr unsigned idesc_pv = instr_desc_bf16(AT_BM, HD, 1);
+        const unsigned q_addr = smem_u32(q_s);
         bool ok = true;
         auto wait_all = [&](unsigned long long* bar, unsigned parity) {
-            return __all_sync(0xffffffffu, at_mbar_wait(bar, parity)) != 0;
+            return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0;
         };
         if (warp == 0) {
             // scores: S[b] = Q K(i)^T as soon as the keys have landed and both groups' P of the buffer's last tile
@@ -307,16 +177,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                 ok = wait_all(&k_full[st], (i / AT_STAGES) & 1);
                 if (ok && i >= NSB) ok = wait_all(&pv_done[b], ((i / NSB) - 1) & 1);
                 if (!ok) break;
-                at_tc_after();
-                const unsigned k_addr = at_smem(k_s + st * KV_BYTES);
+                tc_fence_after();
+                const unsigned k_addr = smem_u32(k_s + st * KV_BYTES);
                 if (at_elect()) {
 #pragma unroll
                     for (int ks = 0; ks < HD / 16; ++ks) {
                         const unsigned off = (ks & 3) * 32;
-                        at_mma(tmem + (unsigned)b * AT_BK, at_desc_kmajor(q_addr + (ks >> 2) * (AT_BM * 128) + off),
-                               at_desc_kmajor(k_addr + (ks >> 2) * KV_BLOCK + off), idesc_qk, ks > 0 ? 1u : 0u);
+                        tc_mma(tmem + (unsigned)b * AT_BK, smem_desc_sw128(q_addr + (ks >> 2) * (AT_BM * 128) + off),
+                               smem_desc_sw128(k_addr + (ks >> 2) * KV_BLOCK + off), idesc_qk, ks > 0 ? 1u : 0u);
                     }
-                    at_commit(&s_full[b]);
+                    tc_commit(&s_full[b]);
                 }
                 __syncwarp();
             }
@@ -325,38 +195,38 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             for (int i = 0; i < n_tiles && ok; ++i) {
                 const int st = i % AT_STAGES, b = i % NSB;
                 ok = wait_all(&v_full[st], (i / AT_STAGES) & 1);
-                const unsigned v_addr = at_smem(v_s + st * KV_BYTES);
+                const unsigned v_addr = smem_u32(v_s + st * KV_BYTES);
                 if constexpr (ALT) {
                     const int g = i & 1;
                     if (ok) ok = wait_all(&p_full[b], (i / NSB) & 1);
                     if (!ok) break;
-                    at_tc_after();
+                    tc_fence_after();
                     if (at_elect()) {
 #pragma unroll
                         for (int ks = 0; ks < AT_BK / 16; ++ks)
-                            at_mma_ts(tmem + O_COL + 128u * (unsigned)g, tmem + (unsigned)b * AT_BK + (unsigned)ks * 8,
-                                      at_desc_nmajor(v_addr + ks * 2048, KV_BLOCK, 1024), idesc_pv, (i >= 2 || ks > 0) ? 1u : 0u);
-                        at_commit(&pv_done[b]);
+                            tc_mma_ts(tmem + O_COL + 128u * (unsigned)g, tmem + (unsigned)b * AT_BK + (unsigned)ks * 8,
+                                      smem_desc_sw128_nmajor(v_addr + ks * 2048, KV_BLOCK, 1024), idesc_pv, (i >= 2 || ks > 0) ? 1u : 0u);
+                        tc_commit(&pv_done[b]);
                     }
                     __syncwarp();
                 } else {
                 for (int g = 0; g < 2 && ok; ++g) {
                     ok = wait_all(&p_full[2 * b + g], (i / NSB) & 1);
                     if (!ok) break;
-                    at_tc_after();
+                    tc_fence_after();
                     if (at_elect()) {
 #pragma unroll
                         for (int ks = 0; ks < AT_HALF / 16; ++ks)
-                            at_mma_ts(tmem + O_COL + 128u * (unsigned)g, tmem + (unsigned)b * AT_BK + (unsigned)g * AT_HALF + (unsigned)ks * 8,
-                                      at_desc_nmajor(v_addr + (g * (AT_HALF / 16) + ks) * 2048, KV_BLOCK, 1024), idesc_pv,
+                            tc_mma_ts(tmem + O_COL + 128u * (unsigned)g, tmem + (unsigned)b * AT_BK + (unsigned)g * AT_HALF + (unsigned)ks * 8,
+                                      smem_desc_sw128_nmajor(v_addr + (g * (AT_HALF / 16) + ks) * 2048, KV_BLOCK, 1024), idesc_pv,
                                       (i > 0 || ks > 0) ? 1u : 0u);
-                        if (g == 1) at_commit(&pv_done[b]);
+                        if (g == 1) tc_commit(&pv_done[b]);
                     }
                     __syncwarp();
                 }
                 }
             }
-            if (ok) { if (at_elect()) at_commit(&o_ready); }
+            if (ok) { if (at_elect()) tc_commit(&o_ready); }
             __syncwarp();
         }
         if (!ok && lane == 0) atomicExch(&failed, 1);
@@ -380,12 +250,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             const int b = i % NSB;
             const unsigned s_col = (unsigned)b * AT_BK + (ALT ? 0u : (unsigned)grp * AT_HALF);    // this group's scores of the tile, and its P
             const int key0 = (tile0 + i) * AT_BK + (ALT ? 0 : grp * AT_HALF);
-            ok = at_mbar_wait(&s_full[b], (i / NSB) & 1);
+            ok = mbar_wait(&s_full[b], (i / NSB) & 1);
             if (!ok) break;
-            at_tc_after();
+            tc_fence_after();
             float s[GK];
-            if constexpr (GK == 64) at_ld64(tmem + lane_addr + s_col, s);
-            else at_ld32(tmem + lane_addr + s_col, s);
+            if constexpr (GK == 64) tc_ld64(tmem + lane_addr + s_col, s);
+            else tc_ld32(tmem + lane_addr + s_col, s);
             // only a half that some row of the warp sees in part is masked element by element
             float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (key0 + GK - 1 > warp_pos_min || key0 < warp_lo_max) {
@@ -422,33 +292,33 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             // rows whose maximum grew: O *= corr, once this group's product before this one has landed
             const int prev = ALT ? i - 2 : i - 1;
             if (prev >= 0 && grow) {
-                ok = at_mbar_wait(&pv_done[prev % NSB], (prev / NSB) & 1);
+                ok = mbar_wait(&pv_done[prev % NSB], (prev / NSB) & 1);
                 if (!ok) break;
-                at_tc_after();
+                tc_fence_after();
 #pragma unroll
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     float t[32];
-                    at_ld32(tmem + lane_addr + o_col + c0, t);
+                    tc_ld32(tmem + lane_addr + o_col + c0, t);
 #pragma unroll
                     for (int q = 0; q < 32; ++q) t[q] *= corr;
-                    at_st32(tmem + lane_addr + o_col + c0, t);
+                    tc_st32(tmem + lane_addr + o_col + c0, t);
                 }
             }
-            if constexpr (GK == 64) at_st32(tmem + lane_addr + s_col, pk);       // over the first half of the scores it came from
-            else at_st16(tmem + lane_addr + s_col, pk);
-            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-            at_tc_before();
+            if constexpr (GK == 64) tc_st32(tmem + lane_addr + s_col, pk);       // over the first half of the scores it came from
+            else tc_st16(tmem + lane_addr + s_col, pk);
+            tc_wait_st();
+            tc_fence_before();
             __syncwarp();                                // every lane's P has been stored: one arrival for the warp
-            if (lane == 0) at_mbar_arrive(&p_full[ALT ? b : 2 * b + grp]);
+            if (lane == 0) mbar_arrive(&p_full[ALT ? b : 2 * b + grp]);
         }
-        if (ok && n_tiles > 0) ok = at_mbar_wait(&o_ready, 0);
+        if (ok && n_tiles > 0) ok = mbar_wait(&o_ready, 0);
         if (!ok) atomicExch(&failed, 1);
         // the join of the two groups: the second hands its maximum and sum over, the first group's thread of the
         // same row (the same lanes of tensor memory) reads both accumulators
         if (grp == 1) ml_other[r] = make_float2(m, l);
         asm volatile("bar.sync 1, 256;\n" ::: "memory");
         if (grp == 0 && ok && n_tiles > 0) {
-            at_tc_after();
+            tc_fence_after();
             const float2 other = ml_other[r];
             const float m_all = fmaxf(m, other.x);
             const float m_ref = (m_all == -INFINITY) ? 0.0f : m_all;
@@ -462,8 +332,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
 #pragma unroll
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 float t[32], u[32];
-                at_ld32(tmem + lane_addr + O_COL + c0, t);        // all lanes take part; only real rows store
-                at_ld32(tmem + lane_addr + O_COL + 128u + c0, u);
+                tc_ld32(tmem + lane_addr + O_COL + c0, t);        // all lanes take part; only real rows store
+                tc_ld32(tmem + lane_addr + O_COL + 128u + c0, u);
                 if (real) {
 #pragma unroll
                     for (int q = 0; q < 32; q += 8) {
@@ -507,7 +377,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
         for (int i = lsub; i < n_tiles && ok; i += 2) {
             const int st = i % AT_STAGES;
             if (i >= AT_STAGES) {
-                ok = at_mbar_wait(&empty[st], ((i / AT_STAGES) - 1) & 1);
+                ok = mbar_wait(&empty[st], ((i / AT_STAGES) - 1) & 1);
                 if (!ok) break;
             }
             const int key0 = (tile0 + i) * AT_BK;
@@ -531,8 +401,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             const bool direct = !which || (n_have == n_pg && key0 >= k_begin && key0 + AT_BK <= k_end);
             unsigned long long* bar = direct ? &full[st] : &kv_landed[st];
             if (lane == 0) {
-                if (n_have > 0) at_expect_tx(bar, (unsigned)n_have * ps * HD * 2);
-                else if (direct) at_mbar_arrive(bar);
+                if (n_have > 0) mbar_expect_tx(bar, (unsigned)n_have * ps * HD * 2);
+                else if (direct) mbar_arrive(bar);
             }
             __syncwarp();
 #pragma unroll
@@ -541,12 +411,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                     const int row = ((pg[h] * 2 + which) * p.nkv + kvh) * ps;
 #pragma unroll
                     for (int cb = 0; cb < CB; ++cb)
-                        at_tma_2d(dst + cb * KV_BLOCK + (h * 32 + lane) * ps * 128, &map_kv, cb * 64, row, bar);
+                        tma_load_2d(dst + cb * KV_BLOCK + (h * 32 + lane) * ps * 128, &map_kv, cb * 64, row, bar);
                 }
             }
             if (!direct) {
                 if (n_have > 0) {
-                    ok = at_mbar_wait(&kv_landed[st], (landed_phase >> st) & 1);
+                    ok = mbar_wait(&kv_landed[st], (landed_phase >> st) & 1);
                     landed_phase ^= 1u << st;
                     if (!ok) break;
                 }
@@ -560,17 +430,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
                     if (!held || key < k_begin || key >= k_end)
                         *reinterpret_cast<uint4*>(dst + (c >> 3) * KV_BLOCK + jrow * 128 + (((c & 7) ^ (jrow & 7)) << 4)) = make_uint4(0, 0, 0, 0);
                 }
-                at_fence_async();
+                fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) at_mbar_arrive(&full[st]);
+                if (lane == 0) mbar_arrive(&full[st]);
             }
         }
         if (!ok) atomicExch(&failed, 1);
     }
-    at_tc_before();
+    tc_fence_before();
     __syncthreads();
     if (warp == 0) {
-        at_tc_after();
+        tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
     if (tid == 0 && failed && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);

@@ -57,14 +57,6 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
         ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr) : "memory");
 }
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
-                 ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
-    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];\n"
-                 ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
-}
 __device__ __forceinline__ void tc_commit_pair(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
                  ::"r"(smem_u32(bar)), "h"((unsigned short)3) : "memory");
@@ -78,17 +70,6 @@ __device__ __forceinline__ void tc_mma_pair(unsigned tmem_d, unsigned long long 
 __device__ __forceinline__ void mbar_arrive_cluster(unsigned bar_cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(bar_cluster_addr) : "memory");
 }
-__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -214,7 +195,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     if (elected) asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory");
                     asm volatile("bar.sync 1, 128;\n" ::: "memory");
                     unsigned g[32];
-                    tc_ld32(t_addr + (unsigned)(c * 32), g);
+                    tc_ld32_nowait(t_addr + (unsigned)(c * 32), g);
                     tc_wait_ld();
                     if (c == GP_BN / 32 - 1) {
                         tc_fence_before();
@@ -251,8 +232,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     unsigned g[32], u[32];
                     float o[32];
                     if (MODE == GP_MODE_SWIGLU) {
-                        tc_ld32(t_addr + (unsigned)(c * 128 + h * 32), g);
-                        tc_ld32(t_addr + (unsigned)(c * 128 + 64 + h * 32), u);
+                        tc_ld32_nowait(t_addr + (unsigned)(c * 128 + h * 32), g);
+                        tc_ld32_nowait(t_addr + (unsigned)(c * 128 + 64 + h * 32), u);
                         tc_wait_ld();
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
@@ -260,7 +241,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             o[j] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
                         }
                     } else {
-                        tc_ld32(t_addr + (unsigned)(c * 64 + h * 32), g);
+                        tc_ld32_nowait(t_addr + (unsigned)(c * 64 + h * 32), g);
                         tc_wait_ld();
                         const int n0 = tn * GP_BN + c * 64 + h * 32;
 #pragma unroll
