@@ -9,11 +9,11 @@
 namespace bg {
 
 // ---------------------------------------------------------------------------------------------
-// x[t, :] = table[ids[t], :]   (qwen_infer.c:1438-1439).  An id outside the table sets a status
-// bit and yields a row of zeros.
+// x[t, :] = table[ids[t], :] * scale   (qwen_infer.c:1438-1439, where the scale is 1).  An id outside the
+// table sets a status bit and yields a row of zeros.
 template <typename TT>
 __global__ void embed_gather_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int d, int vocab, unsigned* status) {
+                                    float* __restrict__ out, int d, int vocab, float scale, unsigned* status) {
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
@@ -25,7 +25,15 @@ __global__ void embed_gather_kernel(const TT* __restrict__ table, const int* __r
         return;
     }
     const TT* row = table + (size_t)id * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_float(row[i]) * scale;
+}
+
+// x = cap * tanh(x / cap): a cap on the logits of architectures that have one.
+__global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
+    pdl_launch();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -522,10 +530,18 @@ __global__ void rope_kv_append_heads_kernel(const TS* __restrict__ src, int src_
 using namespace bg;
 
 extern "C" int bg_embed_gather(const void* table, int table_dtype, const int* ids, float* out, int T,
-                               int d, int vocab, unsigned* status, cudaStream_t stream) {
+                               int d, int vocab, float scale, unsigned* status, cudaStream_t stream) {
     if (T <= 0) return BG_OK;
     BG_DISPATCH_DTYPE(table_dtype, TT, launch(embed_gather_kernel<TT>, dim3(T), dim3(256), 0, stream,
-        (const TT*)table, ids, out, d, vocab, status));
+        (const TT*)table, ids, out, d, vocab, scale, status));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return BG_OK;
+    if (!(cap > 0.0f)) return BG_ERR_SHAPE;
+    launch(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, cap);
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

@@ -19,7 +19,8 @@ STATUS_BAD_TOKEN, STATUS_BAD_PAGE, STATUS_TIMEOUT = 1, 2, 4
 _c_int, _c_float, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
 _SIGNATURES = {
-    "bg_embed_gather": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "bg_embed_gather": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+    "bg_softcap": [_c_void_p, _c_ll, _c_float, _c_void_p],
     "bg_add_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_float, _c_void_p, _c_int,
                        _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "bg_add_residual": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
@@ -240,15 +241,25 @@ def raise_on_status(status: torch.Tensor) -> None:
 
 
 # ------------------------------------------------------------------------------------------------
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor]) -> None:
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor],
+                 scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale as float32; an id outside the table sets BG_STATUS_BAD_TOKEN."""
     _cuda(table, ids, out)
     _i32(ids, "ids")
     T, d = ids.numel(), table.shape[1]
     if out.dtype != torch.float32 or tuple(out.shape) != (T, d) or not out.is_contiguous() or not table.is_contiguous():
         raise KernelError("embed_gather: out must be contiguous float32 [T, d] and the table contiguous")
     with phase("emb_gather"):
-        _check(lib().bg_embed_gather(_p(table), _dt(table), _p(ids), _p(out), T, d, table.shape[0], _p(status), _stream()),
-               "embed_gather")
+        _check(lib().bg_embed_gather(_p(table), _dt(table), _p(ids), _p(out), T, d, table.shape[0], float(scale), _p(status),
+                                     _stream()), "embed_gather")
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x = cap * tanh(x / cap) in place; x contiguous float32 (logits)."""
+    _cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not cap > 0.0:
+        raise KernelError("softcap: contiguous float32 values and a positive cap")
+    _check(lib().bg_softcap(_p(x), x.numel(), float(cap), _stream()), "softcap")
 
 
 def _parts(t: torch.Tensor, what: str):

@@ -37,10 +37,11 @@ class DecoderModel:
             self.blocks.append(registry.block_class(layer.block)(**parts))
         self.final_norm = registry.norm_class(spec.final_norm.kind)(
             spec.final_norm, {"weight": tensors[spec.final_norm_name]}, ctx)
+        head_bias = None if spec.head_bias_name is None else tensors[spec.head_bias_name]
         if spec.head_name is None:
-            self.head = Linear(self.embed, None, ctx, label="head_gemv")      # ctx.matrix is a no-op on the table: one copy
+            self.head = Linear(self.embed, head_bias, ctx, label="head_gemv")     # ctx.matrix is a no-op on the table: one copy
         else:
-            self.head = Linear(tensors[spec.head_name], None, ctx, label="head_gemv")
+            self.head = Linear(tensors[spec.head_name], head_bias, ctx, label="head_gemv")
 
     # ------------------------------------------------------------------ cache
     def cache_needs(self) -> List[Optional[object]]:
@@ -87,7 +88,7 @@ class DecoderModel:
         [wanted rows, vocab], or None when no row's logits are wanted (the head is skipped then, as
         qwen_infer.c:2145 skips it)."""
         x = torch.empty((batch.n_rows, self.spec.hidden), dtype=torch.float32, device=self.ctx.device)
-        ops.embed_gather(self.embed, batch.token_ids, x, self.ctx.status)
+        ops.embed_gather(self.embed, batch.token_ids, x, self.ctx.status, scale=self.spec.embed_scale)
         stream = ResidualStream(x)
         for si, stage in enumerate(self.spec.order):
             owner = si if stage.cache is None else stage.cache
@@ -96,4 +97,7 @@ class DecoderModel:
         if batch.n_logit_rows == 0:
             return None
         h = self.final_norm.add_norm(stream.x, stream.pending, rows=batch.logit_rows, update=False)
-        return self.head(h, out_dtype=torch.float32)
+        logits = self.head(h, out_dtype=torch.float32)
+        if self.spec.logit_softcap > 0.0:
+            ops.softcap(logits, self.spec.logit_softcap)
+        return logits

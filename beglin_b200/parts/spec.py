@@ -129,5 +129,8 @@ class ModelSpec:
     final_norm_name: str
     head_name: Optional[str]              # None: the head is the embedding table (tied)
     max_positions: Optional[int] = None
+    embed_scale: float = 1.0              # the embedded rows are multiplied by this (1: as they are)
+    head_bias_name: Optional[str] = None  # a bias [vocab] added to the logits
+    logit_softcap: float = 0.0            # c > 0: logits = c * tanh(logits / c)
     eos_ids: Tuple[int, ...] = ()
     extra: Dict[str, object] = field(default_factory=dict)

@@ -59,6 +59,8 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorRole]:
         out[spec.final_norm_name if role.name == "weight" else f"{spec.final_norm_name}.{role.name}"] = role
     if spec.head_name is not None:
         out[spec.head_name] = TensorRole(spec.head_name, (spec.vocab, spec.hidden), True, True)
+    if spec.head_bias_name is not None:
+        out[spec.head_bias_name] = TensorRole(spec.head_bias_name, (spec.vocab,), True, False, role="bias")
     return out
 
 

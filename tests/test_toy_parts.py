@@ -322,3 +322,42 @@ def test_toy_blocks_with_other_slots():
     ids = {"a": seeded_ids(41, 384, 7), "b": seeded_ids(22, 384, 8)}
     want = {r: plain_toy_blocks_forward(TINY_B, w, ids[r]) for r in ids}
     whole_and_cut(eng, ids, want, TOL_F32)
+
+
+# ------------------------------------------------------------------------------------------------
+# The two ends of the model are the spec's business too: a scale on the embedded rows, a bias on the logits and a
+# cap c * tanh(logits / c).  The architecture here has none of them; a spec with all three is stepped whole and cut.
+def plain_ends_forward(cfg, w, ids, scale, cap):
+    sz = plain.sizes(cfg)
+    x = plain.embed(w["model.embed_tokens.weight"], ids) * scale
+    eps = cfg["rms_norm_eps"]
+    for layer in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{layer}."
+        h = plain.rmsnorm(x, w[p + "input_layernorm.weight"], eps)
+        x = x + plain.attention_block(h, w, p + "self_attn.", sz, cfg["rope_theta"], None, fast=True)
+        h = plain.rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps)
+        x = x + plain.mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    logits = plain.head(x, w, cfg) + w["toy.head_bias"]
+    return cap * torch.tanh(logits / cap)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", TOL_F32), ("bfloat16", TOL_BF16)])
+def test_scaled_embedding_head_bias_and_logit_cap(dtype, tol):
+    from beglin_b200 import Engine
+    from beglin_b200.config import load_config
+    from beglin_b200.weights import TensorDict, expected_tensors, random_tensors
+    arch, cfg = load_config(TINY_B)
+    spec = dataclasses.replace(arch.build_spec(cfg), embed_scale=3.0, head_bias_name="toy.head_bias", logit_softcap=2.5)
+    assert expected_tensors(spec)["toy.head_bias"].shape == (384,)
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    tensors = random_tensors(spec, 17, std=0.05, bias_std=0.5, dtype=stored)
+    eng = Engine(spec, TensorDict(tensors), dtype=dtype, max_tokens=256, page_size=16, max_requests=3, kv_split=64)
+    w = {k: v.double() for k, v in tensors.items()}
+    ids = {"a": seeded_ids(41, 384, 7), "b": seeded_ids(22, 384, 8)}
+    want = {r: plain_ends_forward(TINY_B, w, ids[r], 3.0, 2.5) for r in ids}
+    assert float(want["a"].abs().max()) > 1.5                       # the cap bites
+    whole_and_cut(eng, ids, want, tol)
+    plainer = Engine(arch.build_spec(cfg), TensorDict({k: v for k, v in tensors.items() if k != "toy.head_bias"}), dtype=dtype,
+                     max_tokens=256, page_size=16, max_requests=1)
+    base = plainer.step([("a", ids["a"], range(41))])
+    assert rel_err(base, want["a"]) > 0.1                           # and the three options are what makes the difference
