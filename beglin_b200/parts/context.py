@@ -14,7 +14,10 @@ class BuildContext:
     compute_dtype: torch.dtype              # torch.float32 (true 32-bit path) or torch.bfloat16
     cache_dtype: Optional[torch.dtype] = None
     page_size: int = 64
-    kv_split: int = 256                     # keys per attention split; fixed, so results do not depend on load
+    # keys per split of the CUDA-core attention (the float32 path and odd sizes): fixed positions, so a row's result
+    # does not depend on the batch.  The bfloat16 decoding kernel spreads a request's keys over its CTAs by the
+    # step's shapes instead: its rows agree between batches to rounding, not bit for bit.
+    kv_split: int = 256
     gemm: str = "auto"                      # "auto", "library" or "tcgen05" for the bfloat16 products
     attention: str = "auto"                 # "auto", "generic" (CUDA cores) or "mma" (tensor cores) kernel
     fuse: bool = True                       # few-token steps: norms, residual adds and SwiGLU inside the products
