@@ -28,6 +28,31 @@ __global__ void embed_gather_kernel(const TT* __restrict__ table, const int* __r
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_float(row[i]) * scale;
 }
 
+// Random weights on the device: out[i] = mean + std * x(key, first + i), x approximately normal, a function of the
+// key and the element's number alone, of integer operations and two exactly rounded float operations, so that the
+// host's numpy code (weights/counter_random.py) makes the same bits:
+//   h_j = mix64(key + (3 i + j) * GOLDEN), j = 0..2 (splitmix64's finalizer);
+//   x = (the sum of the twelve 16-bit fields of h_0..h_2 - 6 * 65535) / 65536.
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+template <typename TO>
+__global__ void fill_normal_kernel(TO* __restrict__ out, long long n, unsigned long long key, long long first, float mean, float std) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const unsigned long long e = (unsigned long long)(first + i);
+    int total = 0;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+        const unsigned long long h = mix64(key + (e * 3ull + (unsigned long long)j) * 0x9E3779B97F4A7C15ull);
+        total += (int)(h & 0xFFFF) + (int)((h >> 16) & 0xFFFF) + (int)((h >> 32) & 0xFFFF) + (int)(h >> 48);
+    }
+    const float x = __fmul_rn((float)(total - 6 * 65535), 1.0f / 65536.0f);
+    out[i] = from_float<TO>(__fadd_rn(mean, __fmul_rn(std, x)));
+}
+
 // x = cap * tanh(x / cap): a cap on the logits of architectures that have one.
 __global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
     pdl_launch();
@@ -534,6 +559,17 @@ extern "C" int bg_embed_gather(const void* table, int table_dtype, const int* id
     if (T <= 0) return BG_OK;
     BG_DISPATCH_DTYPE(table_dtype, TT, launch(embed_gather_kernel<TT>, dim3(T), dim3(256), 0, stream,
         (const TT*)table, ids, out, d, vocab, scale, status));
+    BG_LAUNCH_CHECK();
+    return BG_OK;
+}
+
+extern "C" int bg_fill_normal(void* out, int out_dtype, long long n, unsigned long long key, long long first, float mean,
+                              float std, cudaStream_t stream) {
+    if (n <= 0) return BG_OK;
+    const unsigned long long blocks = (unsigned long long)(n + 255) / 256;
+    if (blocks > 0x7fffffffull) return BG_ERR_SHAPE;
+    BG_DISPATCH_DTYPE(out_dtype, TO, launch(fill_normal_kernel<TO>, dim3((unsigned)blocks), dim3(256), 0, stream,
+        (TO*)out, n, key, first, mean, std));
     BG_LAUNCH_CHECK();
     return BG_OK;
 }

@@ -17,10 +17,12 @@ F32, BF16 = 0, 1
 STATUS_BAD_TOKEN, STATUS_BAD_PAGE, STATUS_TIMEOUT = 1, 2, 4
 
 _c_int, _c_float, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+_c_ull = ctypes.c_ulonglong
 
 _SIGNATURES = {
     "bg_embed_gather": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     "bg_softcap": [_c_void_p, _c_ll, _c_float, _c_void_p],
+    "bg_fill_normal": [_c_void_p, _c_int, _c_ll, _c_ull, _c_ll, _c_float, _c_float, _c_void_p],
     "bg_add_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_float, _c_void_p, _c_int,
                        _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "bg_add_residual": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
@@ -252,6 +254,16 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stat
     with phase("emb_gather"):
         _check(lib().bg_embed_gather(_p(table), _dt(table), _p(ids), _p(out), T, d, table.shape[0], float(scale), _p(status),
                                      _stream()), "embed_gather")
+
+
+def fill_normal(out: torch.Tensor, key: int, mean: float, std: float, first: int = 0) -> None:
+    """out (contiguous, float32 or bfloat16) = mean + std * x(key, first + i) for its elements i in storage order: the
+    counter-based generator of weights/counter_random.py on the device, with the same bits."""
+    _cuda(out)
+    if not out.is_contiguous():
+        raise KernelError("fill_normal: a contiguous tensor")
+    _check(lib().bg_fill_normal(_p(out), _dt(out), out.numel(), int(key) & ((1 << 64) - 1), int(first), float(mean), float(std),
+                                _stream()), "fill_normal")
 
 
 def softcap(x: torch.Tensor, cap: float) -> None:

@@ -94,12 +94,13 @@ class Engine:
     @classmethod
     def random(cls, config_json: dict, seed: int = 0, *, std: float = 0.02, bias_std: Optional[float] = None,
                norm_std: float = 0.02, **kw) -> "Engine":
-        """Random weights made on the device, for sizes too large to write to disk first."""
+        """Random weights made on the device, for sizes too large to write to disk first: the values of
+        `write_random_model(..., generator="counter")` with the same seed, bit for bit."""
         arch, cfg = load_config(dict(config_json))
         spec = arch.build_spec(cfg)
         dtype = parse_dtype(kw.get("dtype", "bfloat16"))
         device = require_gpu(kw.get("device", "cuda:0"))
-        tensors = random_tensors(spec, seed, std, bias_std, norm_std, dtype=dtype, device=str(device))
+        tensors = random_tensors(spec, seed, std, bias_std, norm_std, dtype=dtype, device=str(device), generator="counter")
         return cls(spec, TensorDict(tensors), config=cfg, origin="random weights", **kw)
 
     # ------------------------------------------------------------------ the step function

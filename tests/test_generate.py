@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import TINY, follows_plain, make_model, plain, plain_logits, plain_model, seeded_ids
+from helpers import TINY, TOL_BF16, TOL_F32, follows_plain, make_model, plain, plain_logits, plain_model, rel_err, seeded_ids
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -243,3 +243,31 @@ def test_command_line_kept_variables(model_root, tmp_path):
     r = subprocess.run(exe + ["greedy"], env=dict(env, QWEN_HF_CONFIG=str(tmp_path / "missing.json")), capture_output=True,
                        text=True, timeout=600)
     assert r.returncode == 1 and "missing.json" in r.stderr and "arch config" in r.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_weights_made_on_the_device_are_the_folder_of_the_same_seed(model_root, dtype):
+    """`Engine.random` fills the weights on the device with the counter-based generator; the folder that the same
+    seed writes on the host holds the same bits, tensor by tensor, and the two engines give the same logits bit for
+    bit (so a model too large to write to disk can still be held to the plain implementation on a host)."""
+    from beglin_b200 import Engine
+    from beglin_b200.config import load_config
+    from beglin_b200.weights import random_tensors, write_random_model
+    import os
+    cfg, init, page = TINY["B"]
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    arch, c = load_config(dict(cfg))
+    spec = arch.build_spec(c)
+    host = random_tensors(spec, 31, dtype=stored, generator="counter", **init)
+    dev = random_tensors(spec, 31, dtype=stored, generator="counter", device="cuda:0", **init)
+    for name in host:
+        assert torch.equal(host[name], dev[name].cpu()), name
+    folder = os.path.join(str(model_root), f"counter_{dtype}")
+    write_random_model(folder, cfg, 31, dtype=stored, generator="counter", **init)
+    ids = seeded_ids(50, cfg["vocab_size"], 2)
+    a = Engine.random(cfg, 31, dtype=dtype, max_tokens=128, page_size=page, max_requests=1, **init)
+    b = Engine.from_folder(folder, dtype=dtype, max_tokens=128, page_size=page, max_requests=1)
+    la, lb = a.step([("r", ids, list(range(50)))]), b.step([("r", ids, list(range(50)))])
+    assert torch.equal(la, lb)
+    assert rel_err(la, plain_logits(folder, ids)) < (TOL_F32 if dtype == "float32" else TOL_BF16)

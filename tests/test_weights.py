@@ -4,6 +4,7 @@ import json
 import os
 import struct
 
+import numpy as np
 import pytest
 import torch
 
@@ -167,3 +168,36 @@ def test_sharded_folder(tmp_path):
     (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wm}))
     with pytest.raises(SafetensorsError, match="shard lacks"):
         Checkpoint(str(tmp_path))
+
+
+def test_counter_generator_is_a_function_of_seed_name_and_element():
+    """The counter-based generator: any part of a tensor can be made alone, tensors do not depend on one another,
+    and the values are what the formula says (checked here with Python integers for a few elements)."""
+    from beglin_b200.weights import counter_random as cr
+    key = cr.tensor_key(5, "model.layers.1.mlp.down_proj.weight")
+    assert key != cr.tensor_key(6, "model.layers.1.mlp.down_proj.weight") != cr.tensor_key(5, "model.layers.1.mlp.up_proj.weight")
+    x = cr.standard(key, 4096)
+    assert np.array_equal(cr.standard(key, 100, start=1234), x[1234:1334])
+    mask = (1 << 64) - 1
+
+    def mix(z):
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+        return z ^ (z >> 31)
+    for i in (0, 1, 77, 4095):
+        total = 0
+        for j in range(3):
+            h = mix((key + (3 * i + j) * cr.GOLDEN) & mask)
+            total += (h & 0xFFFF) + ((h >> 16) & 0xFFFF) + ((h >> 32) & 0xFFFF) + (h >> 48)
+        assert x[i] == np.float32(total - 6 * 65535) * np.float32(1.0 / 65536.0)
+    big = cr.standard(key, 1 << 20)
+    assert abs(float(big.mean())) < 5e-3 and abs(float(big.std()) - 1.0) < 5e-3 and float(np.abs(big).max()) <= 6.0
+    spec = spec_of(TINY_A)
+    a = random_tensors(spec, 7, std=0.02, bias_std=0.3, norm_std=0.02, dtype=torch.float32, generator="counter")
+    b = random_tensors(spec, 7, std=0.02, bias_std=0.3, norm_std=0.02, dtype=torch.float32, generator="counter")
+    assert all(torch.equal(a[k], b[k]) for k in a)
+    assert abs(float(a["model.norm.weight"].mean()) - 1.0) < 0.02
+    assert 0.2 < float(a["model.layers.0.self_attn.q_proj.bias"].std()) < 0.4
+    assert 0.015 < float(a["model.layers.0.mlp.up_proj.weight"].std()) < 0.025
+    with pytest.raises(ValueError, match="generator"):
+        random_tensors(spec, 7, generator="dice")
