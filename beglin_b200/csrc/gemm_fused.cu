@@ -48,6 +48,27 @@ struct FusedParams {
     unsigned* status;
 };
 
+// The sum of the S ranks' parts of one value, in rank order (S is 1, 2, 4, 8 or 16; the loads of a sum go out together).
+template <int S_>
+__device__ __forceinline__ float ranks_sum_of(const float* rp, int part) {
+    float a[S_];
+#pragma unroll
+    for (int s = 0; s < S_; ++s) a[s] = rp[s * part];
+    float v = a[0];
+#pragma unroll
+    for (int s = 1; s < S_; ++s) v += a[s];
+    return v;
+}
+__device__ __forceinline__ float ranks_sum(const float* rp, int part, int S) {
+    switch (S) {
+        case 1: return rp[0];
+        case 2: return ranks_sum_of<2>(rp, part);
+        case 4: return ranks_sum_of<4>(rp, part);
+        case 8: return ranks_sum_of<8>(rp, part);
+        default: return ranks_sum_of<16>(rp, part);
+    }
+}
+
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }   // warps 2..5
 
 template <int BN, int STAGES>
@@ -297,16 +318,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         const int c0 = te / rows_per;
         const int part = BN * rows_per;                                    // floats between two ranks' parts
         // the sum over the ranks, in rank order (the loads go out together; S is 1, 2, 4, 8 or 16)
-        auto total = [&](int c) {
-            const float* rp = recv + c * rows_per + rl;
-            float a[16];
-#pragma unroll
-            for (int s = 0; s < 16; ++s) a[s] = s < S ? rp[s * part] : 0.0f;
-            float v = a[0];
-#pragma unroll
-            for (int s = 1; s < 16; ++s) v += a[s];
-            return v + bias;
-        };
+        auto total = [&](int c) { return ranks_sum(recv + c * rows_per + rl, part, S) + bias; };
         if (p.mode == GF_PLAIN) {
             if (n < p.n_out) {
                 if (p.out_dtype == BG_DTYPE_F32) {
