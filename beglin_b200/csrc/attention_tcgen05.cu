@@ -109,7 +109,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
     __shared__ unsigned tmem_sh;
     __shared__ int failed;
 
-    pdl_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     // the blocks with the most keys (the last ones of a prompt) are handed out first, for every kv head, so that
     // the short ones fill the machine's last wave
@@ -155,6 +154,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = tmem_sh;
+    // The kernel behind this one may be scheduled only now that this CTA holds its tensor memory: it takes all 512
+    // columns, and a CTA of the successor that came to the same SM first and allocated a few would then wait for
+    // this kernel to end while this CTA waits for its columns.
+    pdl_launch();
 
     if (warp == 0 || warp == 6) {
         // ------------------------------------------------------------------ MMA issuers: warp 0 the scores, warp 6 the values
