@@ -1,17 +1,21 @@
 // out[t, n] = sum_k X[t, k] * W[n, k] for steps of many tokens (prompt portions), on the fifth-generation tensor
 // cores with PAIRS of CTAs: a persistent kernel, one pair (a thread block cluster of two, on the two SMs of a
-// TPC) per tile of 256 tokens x 256 output features.
+// TPC) per tile of 256 tokens x 256 (or 192, or 128) output features.
 //
 //   tokens are the M side here and the weights the N side (the reverse of gemm_tcgen05.cu, which streams the
 //   weights once for a handful of tokens): a thread of the epilogue then owns a token's row of consecutive
 //   features, so SwiGLU (gate and up features interleaved in blocks of 64 rows of the weight) is a thread's own
 //   business, and rows go out as whole 128-byte lines.
-//   One thread of the pair's first CTA issues tcgen05.mma.cta_group::2 (M = 256, N = 256): each CTA brings its own
-//   128 tokens and HALF of the tile's weight rows into its shared memory (32 KB a stage instead of 48), the
-//   instruction reads both halves, and each CTA's tensor memory receives the accumulator of its own 128 tokens.
-//   That halving of the shared-memory traffic per flop is what lets the tensor pipe run near its peak.
-//   The accumulator is double-buffered in tensor memory (2 x 256 columns): the four epilogue warps of each CTA
-//   drain tile i (tcgen05.ld, convert, stage in shared memory, TMA store) while the MMAs of tile i + 1 run.
+//   One thread of the pair's first CTA issues tcgen05.mma.cta_group::2 (M = 256, N = the tile's width): each CTA
+//   brings its own 128 tokens and HALF of the tile's weight rows into its shared memory (32 KB a stage instead of 48
+//   for 256 features), the instruction reads both halves, and each CTA's tensor memory receives the accumulator of
+//   its own 128 tokens.  That halving of the operand traffic per flop is what lets the tensor pipe run near its
+//   peak: an SM fetches its operands at 64 bytes a cycle, which is just what a tile of 256 x 256 needs.
+//   The accumulator is double-buffered in tensor memory (two buffers of the tile's width): the four epilogue warps
+//   of each CTA drain tile i (tcgen05.ld, convert, stage in shared memory, TMA store or TMA reduction) while the
+//   MMAs of tile i + 1 run.
+//   Epilogues: plain (+ bias) as bfloat16; SwiGLU; or added into the float residual stream by
+//   cp.reduce.async.bulk.tensor ... add, so that the SM never reads the stream.
 //
 // Barriers (mbarriers; a wait is bounded and records BG_STATUS_TIMEOUT):
 //   full[s]       in the first CTA: one arrival (its producer's expect_tx of BOTH CTAs' bytes) + the bytes; the second
