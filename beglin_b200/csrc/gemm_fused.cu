@@ -45,6 +45,7 @@ struct FusedParams {
     float* ssq_out;                 // residual: [tiles * splits][ssq_out_stride]
     int ssq_out_stride;
     int n_out, T, K, kb_per_split, splits;
+    int log_splits;                 // splits is a power of two: divisions by it and by the rows of a rank are shifts
     unsigned* status;
 };
 
@@ -247,7 +248,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             }
         }
         {
-            const int S = p.splits, rows_per = TC_BM / S, half = rows_per / 2;
+            const int S = p.splits, rows_per = TC_BM >> p.log_splits, half = rows_per >> 1;
             const int rl = te & (rows_per - 1);
             const int row = p.mode == GF_SWIGLU ? (rl < half ? split * half + rl : 64 + split * half + (rl - half)) : split * rows_per + rl;
             const int n = tile_m * TC_BM + row;
@@ -256,7 +257,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 const int t_real = min(BN, p.T - tile_n * BN);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int c = te / rows_per + i * S;
+                    const int c = (te >> (7 - p.log_splits)) + i * S;
                     if (c < t_real) pre_x[i] = ((const float*)p.out)[(size_t)(tile_n * BN + c) * p.ldo + n];
                 }
             }
@@ -269,14 +270,14 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         // Row m of this CTA's accumulator goes to the rank that owns it, into that rank's recv[my rank][token][row
         // of its share].  (swiglu: a rank owns rows of the gate and the rows of up that belong to them.)
         const int S = p.splits, rank = split;
-        const int rows_per = TC_BM / S, half = rows_per / 2;               // powers of two
+        const int rows_per = TC_BM >> p.log_splits, half = rows_per >> 1;  // powers of two
         const int m_local = quarter * 32 + lane;
         int owner, rl;
         if (p.mode == GF_SWIGLU) {
             const int m = m_local & 63;
-            owner = m / half; rl = (m_local >> 6) * half + (m & (half - 1));
+            owner = m >> (6 - p.log_splits); rl = (m_local >> 6) * half + (m & (half - 1));
         } else {
-            owner = m_local / rows_per; rl = m_local & (rows_per - 1);
+            owner = m_local >> (7 - p.log_splits); rl = m_local & (rows_per - 1);
         }
         const int t_real = min(BN, p.T - tile_n * BN);                     // columns beyond it are padding
         if (S > 1) cluster_wait();                                         // the peers run (first use of the barrier)
@@ -308,14 +309,14 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     if (warp >= 2) {
         const int te = threadIdx.x - 64;
         const int S = p.splits, rank = split;
-        const int rows_per = TC_BM / S, half = rows_per / 2;
+        const int rows_per = TC_BM >> p.log_splits, half = rows_per >> 1;
         const int t_real = min(BN, p.T - tile_n * BN);
         // thread te: row te % rows_per of this rank's share, tokens te / rows_per, + S, + 2 S, ...
         const int rl = te & (rows_per - 1);
         const int row = p.mode == GF_SWIGLU ? (rl < half ? rank * half + rl : 64 + rank * half + (rl - half)) : rank * rows_per + rl;
         const int n = tile_m * TC_BM + row;
         const float bias = pre_bias;
-        const int c0 = te / rows_per;
+        const int c0 = te >> (7 - p.log_splits);
         const int part = BN * rows_per;                                    // floats between two ranks' parts
         // the sum over the ranks, in rank order (the loads go out together; S is 1, 2, 4, 8 or 16)
         auto total = [&](int c) { return ranks_sum(recv + c * rows_per + rl, part, S) + bias; };
@@ -368,10 +369,10 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             }
         } else if (p.mode == GF_SWIGLU) {
             const int i = te & (half - 1);
-            for (int c = te / half; c < t_real; c += 128 / half) {
+            for (int c = te >> (6 - p.log_splits); c < t_real; c += 2 << p.log_splits) {
                 const float g = sq[c * rows_per + i], u = sq[c * rows_per + half + i];
                 ((__nv_bfloat16*)p.out)[(size_t)(tile_n * BN + c) * p.ldo + tile_m * 64 + rank * half + i] =
-                    __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+                    __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);   // as the SwiGLU kernel does for a bfloat16 result
             }
         }
     }
@@ -446,6 +447,8 @@ extern "C" int bg_gemm_fused(const void* W, int n_out, int K, int ldw, const voi
     p.ssq_out = ssq_out; p.ssq_out_stride = ssq_out_stride;
     p.n_out = n_out; p.T = T; p.K = K; p.splits = splits;
     p.kb_per_split = (n_kb + splits - 1) / splits;
+    p.log_splits = 0;
+    while ((1 << p.log_splits) < splits) ++p.log_splits;
     p.status = status;
     if ((long long)(splits - 1) * p.kb_per_split >= n_kb) return BG_ERR_SHAPE;      // an empty range of K
     const int bn = T <= 16 ? 16 : T <= 32 ? 32 : 64;
