@@ -333,44 +333,61 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 }
             }
         } else if (p.mode == GF_RESIDUAL) {
+            // x += product; the squares of a token's new values over this rank's rows are added up by the lanes that
+            // hold them (shuffles, when a rank's rows fit a warp: four ranks and more) or through shared memory
+            const bool by_lanes = rows_per <= 32;
             float* po = (float*)p.out + (size_t)(tile_n * BN + c0) * p.ldo + n;
+            auto leave = [&](int c, bool have, float x) {
+                float v = x * x;
+                if (by_lanes) {
+                    for (int m = rows_per >> 1; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+                    if (rl == 0 && have && p.ssq_out)
+                        p.ssq_out[(size_t)(tile_m * S + rank) * p.ssq_out_stride + tile_n * BN + c] = v;
+                } else if (have) {
+                    sq[c * rows_per + rl] = v;
+                }
+            };
 #pragma unroll
             for (int i = 0; i < 4; ++i) {                                  // the values asked for ahead
                 const int c = c0 + i * S;
-                if (c < t_real) {
+                const bool have = c < t_real;
+                if (by_lanes ? __any_sync(0xffffffffu, have) != 0 : have) {
                     float x = 0.0f;
-                    if (n < p.n_out) {
+                    if (have && n < p.n_out) {
                         x = pre_x[i] + total(c);
                         po[(size_t)i * S * p.ldo] = x;
                     }
-                    sq[c * rows_per + rl] = x * x;
+                    leave(c, have, x);
                 }
             }
             po += (size_t)4 * S * p.ldo;
-            for (int c = c0 + 4 * S; c < t_real; c += S, po += (size_t)S * p.ldo) {
+            for (int c = c0 + 4 * S;; c += S, po += (size_t)S * p.ldo) {
+                const bool have = c < t_real;
+                if (!(by_lanes ? __any_sync(0xffffffffu, have) != 0 : have)) break;
                 float x = 0.0f;
-                if (n < p.n_out) {
+                if (have && n < p.n_out) {
                     x = *po + total(c);
                     *po = x;
                 }
-                sq[c * rows_per + rl] = x * x;
+                leave(c, have, x);
+            }
+            if (!by_lanes) {
+                epilogue_sync();
+                // the sum of squares of this rank's rows, token by token, in row order
+                if (te < t_real) {
+                    float acc = 0.0f;
+                    for (int i = 0; i < rows_per; ++i) acc += sq[te * rows_per + i];
+                    if (p.ssq_out) p.ssq_out[(size_t)(tile_m * S + rank) * p.ssq_out_stride + tile_n * BN + te] = acc;
+                }
             }
         } else {
-#pragma unroll 4
-            for (int c = c0; c < t_real; c += S) sq[c * rows_per + rl] = total(c);
-        }
-        epilogue_sync();
-        if (p.mode == GF_RESIDUAL) {
-            // the sum of squares of this rank's rows, token by token, in row order
-            if (te < t_real) {
-                float acc = 0.0f;
-                for (int i = 0; i < rows_per; ++i) acc += sq[te * rows_per + i];
-                if (p.ssq_out) p.ssq_out[(size_t)(tile_m * S + rank) * p.ssq_out_stride + tile_n * BN + te] = acc;
-            }
-        } else if (p.mode == GF_SWIGLU) {
+            // SwiGLU: a thread adds up a gate value and its up value over the ranks and writes the result
             const int i = te & (half - 1);
+            const int n_gate = tile_m * TC_BM + rank * half + i;           // the gate's row of the weight; its up row is 64 on
+            const float bias_g = p.bias ? p.bias[n_gate] : 0.0f, bias_u = p.bias ? p.bias[n_gate + 64] : 0.0f;
             for (int c = te >> (6 - p.log_splits); c < t_real; c += 2 << p.log_splits) {
-                const float g = sq[c * rows_per + i], u = sq[c * rows_per + half + i];
+                const float g = ranks_sum(recv + c * rows_per + i, part, S) + bias_g;
+                const float u = ranks_sum(recv + c * rows_per + half + i, part, S) + bias_u;
                 ((__nv_bfloat16*)p.out)[(size_t)(tile_n * BN + c) * p.ldo + tile_m * 64 + rank * half + i] =
                     __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);   // as the SwiGLU kernel does for a bfloat16 result
             }

@@ -541,17 +541,20 @@ def test_gemm_fused_norm_prologue(ops, T, N, K, splits, parts):
 @pytest.mark.gpu
 @pytest.mark.parametrize("T,im,K,splits", [(8, 128, 512, 1), (8, 896, 1536, 2), (20, 64, 264, 1), (50, 256, 1024, 8),
                                            (3, 192, 640, 4)])
-def test_gemm_fused_swiglu(ops, T, im, K, splits):
+@pytest.mark.parametrize("bias", [False, True])
+def test_gemm_fused_swiglu(ops, T, im, K, splits, bias):
     torch.manual_seed(im + K)
     x = (torch.randn(T, K) * 0.5).to(torch.bfloat16)
     gate = (torch.randn(im, K) * 0.08).to(torch.bfloat16)
     up = (torch.randn(im, K) * 0.08).to(torch.bfloat16)
-    gv, uv = x.double() @ gate.double().t(), x.double() @ up.double().t()
+    bg, bu = (torch.randn(im), torch.randn(im)) if bias else (torch.zeros(im), torch.zeros(im))
+    gv, uv = x.double() @ gate.double().t() + bg.double(), x.double() @ up.double().t() + bu.double()
     want = gv / (1.0 + torch.exp(-gv)) * uv
     out = torch.full((T, im), float("nan"), dtype=torch.bfloat16, device=DEV)
     status = ops.new_status(DEV)
+    b = _interleave_gate_up(bg[:, None], bu[:, None]).reshape(-1).contiguous().to(DEV) if bias else None
     ops.gemm_fused(_interleave_gate_up(gate, up).contiguous().to(DEV), out, ops.FUSED_SWIGLU, x=x.to(DEV), splits=splits,
-                   status=status)
+                   bias=b, status=status)
     ops.raise_on_status(status)
     assert (out.double().cpu() - want).abs().max() < 1e-2 * max(1.0, float(want.abs().max()))
 
