@@ -177,8 +177,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             // have been used up
             for (int i = 0; i < n_tiles && ok; ++i) {
                 const int st = i % AT_STAGES, b = i % NSB;
-                ok = wait_all(&k_full[st], (i / AT_STAGES) & 1);
-                if (ok && i >= NSB) ok = wait_all(&pv_done[b], ((i / NSB) - 1) & 1);
+                if (i >= NSB) ok = wait_all(&pv_done[b], ((i / NSB) - 1) & 1);      // (the older event first)
+                if (ok) ok = wait_all(&k_full[st], (i / AT_STAGES) & 1);
                 if (!ok) break;
                 tc_fence_after();
                 const unsigned k_addr = smem_u32(k_s + st * KV_BYTES);
