@@ -18,7 +18,7 @@
 // is cut in two halves, one for each group; with tiles of 64 keys the groups take the tiles in turns.
 // Tiles of 128 keys cost the tensor cores less per key (an MMA of 64 key columns takes as long as one of 128), tiles
 // of 64 have four tiles under way instead of two and waste less on the tile at the diagonal: the narrow ones win up
-// to about 12,000 keys.
+// to about 24,000 keys.
 // Keys and values come from the pages by TMA (cp.async.bulk.tensor over the page pool seen as a 2-D tensor
 // [rows, head_dim], boxes of one page x 64 features, 128-byte swizzle), each through a ring of 256 keys of its own:
 // a stage of the keys is free as soon as its scores are done, a stage of the values after the second product.
@@ -38,7 +38,7 @@ namespace bg {
 constexpr int AT_BM = 128;                 // rows per CTA
 // From this many keys on, tiles of 128 keys (BEGLIN_B200_ATTN_WIDE_FROM overrides the measured default).
 inline int& at_wide_from() {
-    static int v = [] { const char* e = getenv("BEGLIN_B200_ATTN_WIDE_FROM"); return (e && atoi(e) > 0) ? atoi(e) : 12288; }();
+    static int v = [] { const char* e = getenv("BEGLIN_B200_ATTN_WIDE_FROM"); return (e && atoi(e) > 0) ? atoi(e) : 24576; }();
     return v;
 }
 // Stages of the key and value rings: 256 keys each.
@@ -177,8 +177,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, AttnTcParam
             // have been used up
             for (int i = 0; i < n_tiles && ok; ++i) {
                 const int st = i % AT_STAGES, b = i % NSB;
-                if (i >= NSB) ok = wait_all(&pv_done[b], ((i / NSB) - 1) & 1);      // (the older event first)
-                if (ok) ok = wait_all(&k_full[st], (i / AT_STAGES) & 1);
+                // (which of the two waits comes first is measured: with four score buffers the older event, the
+                // buffer's release, first: 234 -> 227 us at 8,192 tokens; with two buffers the keys first: 812
+                // against 864 us at 16,384 tokens)
+                if (ALT) {
+                    if (i >= NSB) ok = wait_all(&pv_done[b], ((i / NSB) - 1) & 1);
+                    if (ok) ok = wait_all(&k_full[st], (i / AT_STAGES) & 1);
+                } else {
+                    ok = wait_all(&k_full[st], (i / AT_STAGES) & 1);
+                    if (ok && i >= NSB) ok = wait_all(&pv_done[b], ((i / NSB) - 1) & 1);
+                }
                 if (!ok) break;
                 tc_fence_after();
                 const unsigned k_addr = smem_u32(k_s + st * KV_BYTES);

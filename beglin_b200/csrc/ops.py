@@ -381,7 +381,7 @@ def rope_kv_append(src: torch.Tensor, q_out: torch.Tensor, n_rows: int, nh: int,
 # choices of `prefer` under which prompt portions run the tcgen05 kernel
 def attention_wide_from(keys: int = 0) -> int:
     """The number of keys from which the tcgen05 prompt attention walks tiles of 128 keys instead of 64 (measured
-    default 12,288; BEGLIN_B200_ATTN_WIDE_FROM overrides it).  A positive `keys` sets it; the old value is returned."""
+    default 24,576; BEGLIN_B200_ATTN_WIDE_FROM overrides it).  A positive `keys` sets it; the old value is returned."""
     fn = lib().bg_attention_tc_wide_from
     fn.argtypes, fn.restype = [_c_int], _c_int
     return int(fn(int(keys)))
