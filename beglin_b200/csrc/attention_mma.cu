@@ -628,7 +628,6 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
         constexpr int HP = HD + 4;                                 // rows four floats apart from a multiple of 128 bytes:
         float* o_sh = reinterpret_cast<float*>(k_s);               // [4][16][HP]  the stores below meet no bank twice
         float* ml_sh = o_sh + 4 * 16 * HP;                         // [4][16][2]
-        float* fac_sh = ml_sh + 4 * 16 * 2;                        // [16][4] weights of the warps' parts, then [16][2] m and l
         if (SWAP) {
             const int r0 = 2 * (lane & 3);
 #pragma unroll
@@ -656,38 +655,28 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const __grid_co
         const int pos = pos_first;
         const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
         if (!(pos < sp * split || lo >= (sp + 1) * split)) {
-            // the weights of the four warps' parts, row by row (16 threads), then every thread one feature of all rows
-            if (tid < n_rows) {
-                const int r = tid;
-                float m = -INFINITY;
-#pragma unroll
-                for (int w = 0; w < 4; ++w) m = fmaxf(m, ml_sh[(w * 16 + r) * 2]);
-                float l = 0.0f;
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const float mw = ml_sh[(w * 16 + r) * 2];
-                    const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
-                    fac_sh[r * 4 + w] = f;
-                    l = fmaf(ml_sh[(w * 16 + r) * 2 + 1], f, l);
-                }
-                fac_sh[64 + r * 2 + 0] = m;
-                fac_sh[64 + r * 2 + 1] = l;
-            }
-            compute_sync();
+            // every thread takes one feature of all rows and works out the weights of the four warps' parts itself
+            // (four exponentials a row: cheaper than a third barrier and a round through shared memory)
             if (tid < HD) {
                 const int d = tid;
-#pragma unroll 4
+#pragma unroll 2
                 for (int r = 0; r < n_rows; ++r) {
-                    float acc = 0.0f;
+                    float mw[4], m = -INFINITY;
 #pragma unroll
-                    for (int w = 0; w < 4; ++w) acc = fmaf(o_sh[((size_t)w * 16 + r) * HP + d], fac_sh[r * 4 + w], acc);
+                    for (int w = 0; w < 4; ++w) { mw[w] = ml_sh[(w * 16 + r) * 2]; m = fmaxf(m, mw[w]); }
+                    float acc = 0.0f, l = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        const float f = (mw[w] == -INFINITY) ? 0.0f : exp2f(mw[w] - m);
+                        acc = fmaf(o_sh[((size_t)w * 16 + r) * HP + d], f, acc);
+                        l = fmaf(ml_sh[(w * 16 + r) * 2 + 1], f, l);
+                    }
                     if (p.out) {                               // the only range of its request: the finished row
-                        p.out[(size_t)row0 * p.out_stride + (size_t)(kvh * group + r) * HD + d] =
-                            __float2bfloat16_rn(acc / fac_sh[64 + r * 2 + 1]);
+                        p.out[(size_t)row0 * p.out_stride + (size_t)(kvh * group + r) * HD + d] = __float2bfloat16_rn(acc / l);
                     } else {
                         const size_t prow = ((size_t)row0 * p.nh + (size_t)kvh * group + r) * p.max_splits + sp;
                         p.part_o[prow * HD + d] = acc;
-                        if (d == 0) { p.part_ml[prow * 2 + 0] = fac_sh[64 + r * 2] * AM_LN2; p.part_ml[prow * 2 + 1] = fac_sh[64 + r * 2 + 1]; }
+                        if (d == 0) { p.part_ml[prow * 2 + 0] = m * AM_LN2; p.part_ml[prow * 2 + 1] = l; }
                     }
                 }
             }
