@@ -330,21 +330,28 @@ extern "C" int bg_attention_partial(const void* q, int q_dtype, int q_stride, co
     return BG_OK;
 }
 
-// The same for at most NS (8 or 16) splits and head_dim <= 128 (decoding): the position, the maxima and sums, and the
-// partial outputs of ALL splits are asked for at once, and what lies outside the row's range is dropped when
-// the position has arrived, so the kernel is one round trip to memory instead of three.
+// The same for at most NS (8 or 16) splits and head_dim <= 128 (decoding): the maxima and sums and the partial outputs
+// of ALL splits are asked for at once, and what lies outside the row's range is dropped, so the kernel is one round
+// trip to memory instead of three.  The row's range of splits comes from its position alone, which no kernel of the
+// step writes: it is worked out before the wait for the kernel ahead.
 template <typename TO, int NS>
 __global__ void attention_merge_few_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            const int* __restrict__ positions, TO* __restrict__ out, int out_stride,
                                            int T, int nh, int hd, int max_splits, int split_arg, int window) {
     pdl_launch();
-    pdl_wait();
     const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    if (w >= T * nh) return;
-    const int t = w / nh, h = w - t * nh;
+    const bool idle = w >= T * nh;
+    const int t = idle ? 0 : w / nh, h = w - t * nh;
     const size_t prow = (size_t)w * max_splits;
+    // the row's position is written by no kernel of the step: its range of splits (three integer divisions) is
+    // worked out while the kernel ahead still runs
     const int pos = positions[t];
+    const int split = keys_per_split(split_arg, pos + 1, max_splits);
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int s_lo = lo / split, s_hi = pos / split;
+    pdl_wait();
+    if (idle) return;                  // (not before the wait: with warps of a CTA gone before it, rows came out wrong)
     float ms[NS], ls[NS], v[NS][4];
 #pragma unroll
     for (int s = 0; s < NS; ++s) {
@@ -357,9 +364,6 @@ __global__ void attention_merge_few_kernel(const float* __restrict__ part_o, con
             v[s][i] = (have && d < hd) ? part_o[(prow + s) * hd + d] : 0.0f;
         }
     }
-    const int split = keys_per_split(split_arg, pos + 1, max_splits);
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int s_lo = lo / split, s_hi = pos / split;
     float m = -INFINITY;
 #pragma unroll
     for (int s = 0; s < NS; ++s) {

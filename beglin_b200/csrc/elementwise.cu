@@ -515,7 +515,6 @@ __global__ void rope_kv_append_heads_kernel(const TS* __restrict__ src, int src_
                                             int nh, int nkv, int hd, int rot, int interleaved, unsigned* status) {
     pdl_launch();
     const int t = blockIdx.x, h = blockIdx.y, i = threadIdx.x;
-    if (i >= hd) return;
     const int half = rot >> 1;
     const bool is_v = h >= nh + nkv;
     const TS* head = src + (size_t)t * src_stride + (size_t)h * hd;
@@ -528,6 +527,7 @@ __global__ void rope_kv_append_heads_kernel(const TS* __restrict__ src, int src_
         slot = pos % page_size;
     }
     pdl_wait();
+    if (i >= hd) return;               // (threads leave after the wait, not before it)
     float val = sum_parts(head + i, parts, part_stride);
     if (!is_v && i < rot) {
         int pi, partner;
