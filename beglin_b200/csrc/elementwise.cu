@@ -275,14 +275,16 @@ template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, int parts, size_t part_stride, TO* __restrict__ out,
                               int rows, int im, int block) {
     pdl_launch();
-    pdl_wait();
+    // where this thread's values lie is integer arithmetic (divisions) on the grid alone: done before the wait
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t total = (size_t)rows * im;
-    if (idx >= total) return;
-    size_t t = idx / im;
-    int i = (int)(idx - t * im);
+    const bool idle = idx >= total;
+    size_t t = idle ? 0 : idx / im;
+    int i = idle ? 0 : (int)(idx - t * im);
     const int col = block > 0 ? (i / block) * 2 * block + i % block : i;
     const TI* gp = gu + t * 2 * (size_t)im + col;
+    pdl_wait();
+    if (idle) return;
     float g = sum_parts(gp, parts, part_stride);
     float u = sum_parts(gp + (block > 0 ? block : im), parts, part_stride);
     out[idx] = from_float<TO>(silu_mul<TO>(g, u));
@@ -294,18 +296,19 @@ template <typename TO>
 __global__ void swiglu_parts_vec4_kernel(const float* __restrict__ gu, int parts, size_t part_stride, TO* __restrict__ out,
                                          int rows, int im, int block) {
     pdl_launch();
-    pdl_wait();
     const int im4 = im >> 2;
-    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)rows * im4) return;
-    size_t t = idx / im4;
-    const int i = 4 * (int)(idx - t * im4);
+    const unsigned idx = blockIdx.x * blockDim.x + threadIdx.x;          // (the launcher keeps rows * im / 4 under 2^32)
+    const bool idle = idx >= (unsigned)rows * (unsigned)im4;
+    const unsigned t = idle ? 0u : idx / (unsigned)im4;
+    const int i = idle ? 0 : 4 * (int)(idx - t * (unsigned)im4);
     const int col = block > 0 ? (i / block) * 2 * block + i % block : i;
-    const float4* gp = reinterpret_cast<const float4*>(gu + t * 2 * (size_t)im + col);
+    const float4* gp = reinterpret_cast<const float4*>(gu + (size_t)t * 2 * (size_t)im + col);
+    pdl_wait();
+    if (idle) return;
     const float4 g = sum_parts4(gp, parts, part_stride / 4);
     const float4 u = sum_parts4(gp + (block > 0 ? block : im) / 4, parts, part_stride / 4);
     const float r[4] = {silu_mul<TO>(g.x, u.x), silu_mul<TO>(g.y, u.y), silu_mul<TO>(g.z, u.z), silu_mul<TO>(g.w, u.w)};
-    TO* o = out + t * (size_t)im + i;
+    TO* o = out + (size_t)t * (size_t)im + i;
     if constexpr (std::is_same<TO, float>::value) {
         *reinterpret_cast<float4*>(o) = make_float4(r[0], r[1], r[2], r[3]);
     } else {
@@ -321,14 +324,15 @@ __global__ void swiglu_parts_vec4_kernel(const float* __restrict__ gu, int parts
 template <typename TI, typename TO>
 __global__ void swiglu_vec8_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int rows, int im, int block) {
     pdl_launch();
-    pdl_wait();
     const int im8 = im >> 3;
-    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)rows * im8) return;
-    size_t t = idx / im8;
-    int c = (int)(idx - t * im8);
+    const unsigned idx = blockIdx.x * blockDim.x + threadIdx.x;          // (the launcher keeps rows * im / 8 under 2^32)
+    const bool idle = idx >= (unsigned)rows * (unsigned)im8;
+    const size_t t = idle ? 0u : idx / (unsigned)im8;
+    const int c = idle ? 0 : (int)(idx - (unsigned)t * (unsigned)im8);
     const int i = 8 * c;                                     // block is a multiple of 8 here
     const int col = block > 0 ? (i / block) * 2 * block + i % block : i;
+    pdl_wait();
+    if (idle) return;
     float g[8], u[8];
     load8(gu + t * 2 * (size_t)im + col, g);
     load8(gu + t * 2 * (size_t)im + col + (block > 0 ? block : im), u);
@@ -663,13 +667,14 @@ extern "C" int bg_add_residual(float* x, const void* delta, int delta_dtype, lon
 template <typename TI>
 static int swiglu_in(const void* gu, int parts, size_t part_stride, void* out, int out_dtype, int rows, int im, int block,
                      cudaStream_t stream) {
-    const bool vec = parts == 1 && (im % 8 == 0) && (block % 8 == 0) && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    const bool small = (size_t)rows * (size_t)im < (1ull << 32);          // the vector kernels count their pieces in 32 bits
+    const bool vec = small && parts == 1 && (im % 8 == 0) && (block % 8 == 0) && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0);
     if (vec) {
         size_t total = (size_t)rows * (im / 8);
         unsigned blocks = (unsigned)((total + 255) / 256);
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(swiglu_vec8_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream,
             (const TI*)gu, (TO*)out, rows, im, block));
-    } else if (std::is_same<TI, float>::value && (im % 4 == 0) && (block % 4 == 0) && (part_stride % 4 == 0) &&
+    } else if (small && std::is_same<TI, float>::value && (im % 4 == 0) && (block % 4 == 0) && (part_stride % 4 == 0) &&
                ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
         size_t total = (size_t)rows * (im / 4);
         unsigned blocks = (unsigned)((total + 255) / 256);

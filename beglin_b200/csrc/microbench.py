@@ -2,6 +2,7 @@
 
     python -m beglin_b200.csrc.microbench gemm --tokens 8 --out 17920 --inner 1536 --splits 2
     python -m beglin_b200.csrc.microbench gemm-fused --tokens 8 --out 17920 --inner 1536 --splits 2 --norm --mode swiglu
+    python -m beglin_b200.csrc.microbench gemm-pair --tokens 2048 --out 17920 --inner 1536 --mode swiglu [--library]
     python -m beglin_b200.csrc.microbench attention-decode --batch 8 --context 4096
     python -m beglin_b200.csrc.microbench attention-prefill --tokens 2048
     python -m beglin_b200.csrc.microbench norm --tokens 8 --width 1536 --parts 12
