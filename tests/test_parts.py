@@ -80,6 +80,33 @@ def test_norm_linear_and_feed_forward_parts(dtype, tol):
     assert rel_err(ff.forward(xin, None), want) < tol * 2
 
 
+@pytest.mark.parametrize("rows", [1, 8, 17, 64, 200])
+@pytest.mark.parametrize("k,n", [(255, 176), (144, 255), (254, 720), (360, 255), (255, 1000), (4094, 48), (1536, 256),
+                                 (8960, 64)])
+def test_products_add_up_in_32_bit(rows, k, n):
+    """A product whose halves along the inner size are large and cancel: x = [u, -u], w = [v, v + d] with small
+    integers u, v and d in sixteenths, so that every product and every float sum is exact and the result is
+    -sum(u d).  Whatever kernel or library routine the row count selects, one rounding to bfloat16 is all that
+    may be lost; a sum of parts kept in bfloat16 on the way is wrong by whole units."""
+    from beglin_b200.parts import Linear
+    ctx = ctx_for(torch.bfloat16)
+    g = torch.Generator().manual_seed(k * 1000 + n + rows)
+    half = k // 2
+    u = torch.randint(-8, 9, (rows, half), generator=g).float()
+    v = torch.randint(-7, 8, (n, half), generator=g).float()
+    d = torch.randint(-3, 4, (n, half), generator=g).float() / 16
+    x = torch.cat([u, -u] + [torch.zeros(rows, 1)] * (k % 2), 1)          # an odd inner size: one column of zeros
+    w = torch.cat([v, v + d] + [torch.ones(n, 1)] * (k % 2), 1)
+    assert (w.to(torch.bfloat16).float() == w).all() and (x.to(torch.bfloat16).float() == x).all()
+    want = -(u.double() @ d.double().t())
+    lin = Linear(w, None, ctx)
+    xin = x.to(torch.bfloat16).to(DEV)
+    for out_dtype, lost in ((torch.float32, 0.0), (torch.bfloat16, 2.0 ** -8)):
+        got = lin(xin, out_dtype=out_dtype).double().cpu()
+        excess = ((got - want).abs() - lost * want.abs()).max()
+        assert excess <= 1e-6, (out_dtype, float(excess), float(want.abs().max()))
+
+
 def test_position_part_table_and_pairing():
     from beglin_b200.parts import PositionSpec
     from beglin_b200.parts.rope import shared_position
