@@ -24,6 +24,11 @@
 #define BG_STATUS_BAD_PAGE 2u       // a block-table entry outside [0, num_pages)
 #define BG_STATUS_TIMEOUT 4u        // a bounded wait ran out
 
+// Dynamic shared memory from which a kernel asks for more than the default: the default limit of 48 KB holds for
+// a kernel's static and dynamic shared memory together, so a request of exactly 48 KB beside a few static
+// words is refused at launch unless the larger limit was asked for.
+#define BG_SMEM_OPT_IN (40 * 1024)
+
 #define BG_LAUNCH_CHECK() \
     do { cudaError_t e_ = cudaGetLastError(); if (e_ != cudaSuccess) return (int)e_; } while (0)
 

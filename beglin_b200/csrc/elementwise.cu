@@ -595,7 +595,7 @@ static int add_rmsnorm_launch(float* x, const void* delta, int parts, size_t par
                      ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
     if (vec && std::is_same<TD, float>::value && parts > 1) {
         auto kern = add_rmsnorm_parts_kernel<TW, TO>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > BG_SMEM_OPT_IN) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         int threads = d / 4 >= 512 ? 512 : (d / 4 >= 256 ? 384 : 128);
         launch(kern, dim3(n_rows), dim3(threads), smem, stream, x, (const float*)delta, parts, part_stride, (const TW*)w, eps,
                (TO*)out, rows, d, update);
@@ -616,7 +616,7 @@ static int add_rmsnorm_launch(float* x, const void* delta, int parts, size_t par
 #undef BG_NORM_WARP
     } else if (vec) {
         auto kern = add_rmsnorm_vec8_kernel<TD, TW, TO>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > BG_SMEM_OPT_IN) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         // as few trips through a row as 512 threads allow, and no thread without a chunk in the last trip
         const int d8 = d / 8, trips = (d8 + 511) / 512;
         int threads = (((d8 + trips - 1) / trips) + 31) / 32 * 32;
@@ -625,7 +625,7 @@ static int add_rmsnorm_launch(float* x, const void* delta, int parts, size_t par
                                                 rows, d, update);
     } else {
         auto kern = add_rmsnorm_kernel<TD, TW, TO>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem > BG_SMEM_OPT_IN) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         launch(kern, dim3(n_rows), dim3(256), smem, stream, x, (const TD*)delta, parts, part_stride, (const TW*)w, eps, (TO*)out, rows,
                                             d, update);
     }
@@ -725,7 +725,7 @@ static int rope_kv_cache(const void* src, int src_stride, int parts, size_t part
         BG_LAUNCH_CHECK();
         return BG_OK;
     }
-    if (smem > 48 * 1024) {
+    if (smem > BG_SMEM_OPT_IN) {
         BG_DISPATCH_DTYPE(cache_dtype, TC, cudaFuncSetAttribute(rope_kv_append_kernel<TS, TQ, TC>,
             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     }

@@ -43,7 +43,7 @@ def test_embed_gather(ops, dtype):
     assert torch.equal(out2[1], torch.zeros(72, device=DEV))
 
 
-@pytest.mark.parametrize("d", [64, 1536, 100, 5000])
+@pytest.mark.parametrize("d", [64, 1536, 100, 5000, 12288, 16392])      # 12,288: a row of exactly 48 KB in shared memory
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(ops, d, out_dtype):
     T, eps = 7, 1e-5
@@ -201,10 +201,10 @@ def test_rope_table_and_kv_append(ops, interleaved, dtype, hd, rot):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("nh,nkv,hd,dtype", [(5, 1, 48, torch.float32), (48, 3, 256, torch.float32), (64, 4, 256, torch.float32),
-                                             (200, 4, 256, torch.float32), (12, 2, 128, torch.bfloat16), (48, 3, 256, torch.bfloat16)])
+@pytest.mark.parametrize("nh,nkv,hd,dtype", [(5, 1, 48, torch.float32), (40, 4, 256, torch.float32), (48, 3, 256, torch.float32),
+                                             (64, 4, 256, torch.float32), (200, 4, 256, torch.float32), (12, 2, 128, torch.bfloat16), (48, 3, 256, torch.bfloat16)])
 def test_rope_and_kv_append_of_many_tokens(ops, nh, nkv, hd, dtype):
-    """A portion of 100 tokens (one block per token, its q/k/v row staged in shared memory): rows of up to 48 KB, rows that
+    """A portion of 100 tokens (one block per token, its q/k/v row staged in shared memory): rows of up to 48 KB (and of 48 KB to the byte), rows that
     need the larger shared-memory carve-out (55 and 73 KB) and a row that fits no SM (213 KB: head by head)."""
     T, page, rot = 100, 16, hd
     positions = torch.arange(3, 3 + T, dtype=torch.int32, device=DEV)
