@@ -18,15 +18,22 @@
 //                       of the new x over the CTA's rows go to ssq_out[part][t] (for the next norm);
 //             swiglu:   W's rows are interleaved, 64 of the gate then the 64 of up that belong to them:
 //                       h[t, 64 * tile + i] = silu(acc[i]) * acc[64 + i] as bfloat16
-//                       (qwen_infer.c:727-733), so gate_up never reaches global memory.
+//                       (qwen_infer.c:727-733), so gate_up never reaches global memory;
+//             rope:     W's rows are [query heads | key heads | value heads] of hd features (hd 32, 64 or 128):
+//                       queries and keys are rotated by their token's angles (feature d with d + hd / 2,
+//                       qwen_infer.c:1078-1101), queries go to q[t, :] as bfloat16, keys and values into the
+//                       cache page and slot of their token's position, so q/k/v never reach global memory
+//                       as one row and the step has no kernel for rotation and append.
 //
 // Every wait on an mbarrier is bounded and records BG_STATUS_TIMEOUT; a CTA that gave up still goes
 // through the cluster's barriers, so its peers do not wait for it.
+#include <type_traits>
+
 #include "tc_common.cuh"
 
 namespace bg {
 
-constexpr int GF_PLAIN = 0, GF_RESIDUAL = 1, GF_SWIGLU = 2;
+constexpr int GF_PLAIN = 0, GF_RESIDUAL = 1, GF_SWIGLU = 2, GF_ROPE = 3;
 constexpr int SSQ_AHEAD = 24;        // partial sums of squares that a thread of the norm prologue asks for at a time
 
 struct FusedParams {
@@ -46,8 +53,28 @@ struct FusedParams {
     int ssq_out_stride;
     int n_out, T, K, kb_per_split, splits;
     int log_splits;                 // splits is a power of two: divisions by it and by the rows of a rank are shifts
+    // swiglu and rope work on pairs of rows of the tile, 1 << pair_log apart (gate i and up 64 + i; feature d of a
+    // head and d + hd / 2): a rank owns both rows of its 64 / splits pairs
+    int pair_log;
     unsigned* status;
 };
+
+// What the rope mode needs beside: out is q [T][ldo] bfloat16.  (A parameter of its own, which the kernels of the other
+// modes do not carry.)
+struct RopeParams {
+    const float2* cos_sin;          // [T][hd / 2] (cos, sin) of each row's position
+    const int* positions;           // [T]
+    const int* row_req;             // [T] row of the block table
+    const int* block_table;         // [requests][max_pages]
+    __nv_bfloat16* kv_pool;         // [num_pages][2][nkv][page_size][hd]
+    int max_pages, num_pages, page_size, nh, nkv;
+};
+struct NoRope {};
+
+// Pair j of a tile is rows row_of_pair(j) and row_of_pair(j) + (1 << pair_log).
+__device__ __forceinline__ int pair_of_row(int m, int pair_log) { return ((m >> (pair_log + 1)) << pair_log) | (m & ((1 << pair_log) - 1)); }
+__device__ __forceinline__ int side_of_row(int m, int pair_log) { return (m >> pair_log) & 1; }
+__device__ __forceinline__ int row_of_pair(int j, int pair_log) { return ((j >> pair_log) << (pair_log + 1)) | (j & ((1 << pair_log) - 1)); }
 
 // The sum of the S ranks' parts of one value, in rank order (S is 1, 2, 4, 8 or 16; the loads of a sum go out together).
 template <int S_>
@@ -72,9 +99,12 @@ __device__ __forceinline__ float ranks_sum(const float* rp, int part, int S) {
 
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }   // warps 2..5
 
-template <int BN, int STAGES>
+// ROPE: the kernel of the rope mode is an instance of its own, so that the other modes' code (and what the compiler
+// makes of it) does not change with it.
+template <int BN, int STAGES, bool ROPE>
 __global__ void __launch_bounds__(TC_THREADS)
-gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, FusedParams p) {
+gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, FusedParams p,
+                  typename std::conditional<ROPE, RopeParams, NoRope>::type r) {
     constexpr unsigned A_BYTES = TC_BM * TC_BK * 2;
     constexpr unsigned B_BYTES = BN * TC_BK * 2;
     constexpr unsigned STAGE_BYTES = A_BYTES + B_BYTES;
@@ -121,7 +151,10 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 
     // What the reduction at the end adds to the product (the bias of this thread's row; in residual mode the
     // stream's values that it will update) is asked for while the main loop still runs: up to four values.
+    // (rope: the two biases and the angle's cosine and sine for the thread's first token, and where that token's key
+    // or value goes)
     float pre_bias = 0.0f, pre_x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    int pre_page = 0, pre_slot = 0;
 
     if (warp == 0) {
         // ---------------- TMA producer: the weights (requested before the kernel ahead has finished) and,
@@ -252,8 +285,25 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             const int rl = te & (rows_per - 1);
             const int row = p.mode == GF_SWIGLU ? (rl < half ? split * half + rl : 64 + split * half + (rl - half)) : split * rows_per + rl;
             const int n = tile_m * TC_BM + row;
-            if (p.bias && n < p.n_out) pre_bias = p.bias[n];
-            if (p.mode == GF_RESIDUAL && n < p.n_out) {
+            if (!ROPE && p.bias && n < p.n_out) pre_bias = p.bias[n];
+            if constexpr (ROPE) {
+                const int n_lo = tile_m * TC_BM + row_of_pair(split * half + (te & (half - 1)), p.pair_log);
+                const int t = tile_n * BN + (te >> (6 - p.log_splits));
+                if (n_lo < p.n_out && t < p.T) {
+                    const int dist = 1 << p.pair_log, h = n_lo >> (p.pair_log + 1);
+                    if (p.bias) { pre_x[0] = p.bias[n_lo]; pre_x[1] = p.bias[n_lo + dist]; }
+                    if (h < r.nh + r.nkv) {
+                        const float2 f = r.cos_sin[(size_t)t * dist + (n_lo & (dist - 1))];
+                        pre_x[2] = f.x; pre_x[3] = f.y;
+                    }
+                    if (h >= r.nh) {
+                        const int pos = r.positions[t];
+                        pre_page = r.block_table[(size_t)r.row_req[t] * r.max_pages + pos / r.page_size];
+                        pre_slot = pos % r.page_size;
+                    }
+                }
+            }
+            if (!ROPE && p.mode == GF_RESIDUAL && n < p.n_out) {
                 const int t_real = min(BN, p.T - tile_n * BN);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -273,7 +323,10 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         const int rows_per = TC_BM >> p.log_splits, half = rows_per >> 1;  // powers of two
         const int m_local = quarter * 32 + lane;
         int owner, rl;
-        if (p.mode == GF_SWIGLU) {
+        if constexpr (ROPE) {
+            const int j = pair_of_row(m_local, p.pair_log);
+            owner = j >> (6 - p.log_splits); rl = side_of_row(m_local, p.pair_log) * half + (j & (half - 1));
+        } else if (p.mode == GF_SWIGLU) {
             const int m = m_local & 63;
             owner = m >> (6 - p.log_splits); rl = (m_local >> 6) * half + (m & (half - 1));
         } else {
@@ -320,7 +373,49 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         const int part = BN * rows_per;                                    // floats between two ranks' parts
         // the sum over the ranks, in rank order (the loads go out together; S is 1, 2, 4, 8 or 16)
         auto total = [&](int c) { return ranks_sum(recv + c * rows_per + rl, part, S) + bias; };
-        if (p.mode == GF_PLAIN) {
+        if constexpr (ROPE) {
+            // a thread adds up feature d of a head and feature d + hd / 2 over the ranks, rotates the pair (queries and
+            // keys) and writes both: a query into q, a key or a value into its token's page and slot of the cache
+            const int i = te & (half - 1);
+            const int dist = 1 << p.pair_log, hd = dist << 1;
+            const int n_lo = tile_m * TC_BM + row_of_pair(rank * half + i, p.pair_log);
+            const int h = n_lo >> (p.pair_log + 1), d = n_lo & (dist - 1);
+            const int c_first = te >> (6 - p.log_splits);
+            if (n_lo < p.n_out) {
+                for (int c = c_first; c < t_real; c += 2 << p.log_splits) {
+                    const int t = tile_n * BN + c;
+                    float lo = ranks_sum(recv + c * rows_per + i, part, S) + pre_x[0];
+                    float hi = ranks_sum(recv + c * rows_per + half + i, part, S) + pre_x[1];
+                    if (h < r.nh + r.nkv) {
+                        const float2 f = c == c_first ? make_float2(pre_x[2], pre_x[3]) : r.cos_sin[(size_t)t * dist + d];
+                        const float cross_lo = __fmul_rn(hi, f.y), cross_hi = __fmul_rn(lo, f.y);
+                        const float r_lo = __fmaf_rn(lo, f.x, -cross_lo), r_hi = __fmaf_rn(hi, f.x, cross_hi);
+                        lo = r_lo; hi = r_hi;
+                    }
+                    __nv_bfloat16* dst;
+                    if (h < r.nh) {
+                        dst = (__nv_bfloat16*)p.out + (size_t)t * p.ldo + (size_t)h * hd + d;
+                    } else {
+                        int page = pre_page, slot = pre_slot;
+                        if (c != c_first) {
+                            const int pos = r.positions[t];
+                            page = r.block_table[(size_t)r.row_req[t] * r.max_pages + pos / r.page_size];
+                            slot = pos % r.page_size;
+                        }
+                        if (page < 0 || page >= r.num_pages) {
+                            if (p.status) atomicOr(p.status, BG_STATUS_BAD_PAGE);
+                            continue;
+                        }
+                        const bool is_v = h >= r.nh + r.nkv;
+                        const int kvh = is_v ? h - r.nh - r.nkv : h - r.nh;
+                        dst = r.kv_pool + (((size_t)page * 2 + (is_v ? 1 : 0)) * r.nkv + kvh) * ((size_t)r.page_size * hd) +
+                              (size_t)slot * hd + d;
+                    }
+                    dst[0] = __float2bfloat16_rn(lo);
+                    dst[dist] = __float2bfloat16_rn(hi);
+                }
+            }
+        } else if (p.mode == GF_PLAIN) {
             if (n < p.n_out) {
                 if (p.out_dtype == BG_DTYPE_F32) {
                     float* po = (float*)p.out + (size_t)(tile_n * BN + c0) * p.ldo + n;
@@ -401,9 +496,10 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     if (threadIdx.x == 0 && failed && p.status) atomicOr(p.status, BG_STATUS_TIMEOUT);
 }
 
-template <int BN, int STAGES>
-static int gf_launch_stages(const CUtensorMap& mw, const CUtensorMap& mx, const FusedParams& p, cudaStream_t stream) {
-    auto kern = gemm_fused_kernel<BN, STAGES>;
+template <int BN, int STAGES, bool ROPE>
+static int gf_launch_stages(const CUtensorMap& mw, const CUtensorMap& mx, const FusedParams& p, const RopeParams* rope,
+                            cudaStream_t stream) {
+    auto kern = gemm_fused_kernel<BN, STAGES, ROPE>;
     size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (size_t)BN * TC_BM * 4 + 1024;
     static bool set = false;
     if (!set) {
@@ -414,7 +510,9 @@ static int gf_launch_stages(const CUtensorMap& mw, const CUtensorMap& mx, const 
         set = true;
     }
     dim3 grid((p.n_out + TC_BM - 1) / TC_BM, (p.T + BN - 1) / BN, p.splits);
-    cudaError_t e = launch_cluster(kern, grid, dim3(TC_THREADS), smem, stream, p.splits, mw, mx, p);
+    cudaError_t e;
+    if constexpr (ROPE) e = launch_cluster(kern, grid, dim3(TC_THREADS), smem, stream, p.splits, mw, mx, p, *rope);
+    else e = launch_cluster(kern, grid, dim3(TC_THREADS), smem, stream, p.splits, mw, mx, p, NoRope());
     if (e != cudaSuccess) return (int)e;
     BG_LAUNCH_CHECK();
     return BG_OK;
@@ -423,22 +521,32 @@ static int gf_launch_stages(const CUtensorMap& mw, const CUtensorMap& mx, const 
 // A grid that leaves SMs to spare has a CTA alone on its SM: eight stages then keep enough bytes on their way
 // from HBM (the stream of a few CTAs is bound by what they have in flight); else four, so that two CTAs share an SM.
 template <int BN>
-static int gf_launch(const CUtensorMap& mw, const CUtensorMap& mx, const FusedParams& p, cudaStream_t stream) {
+static int gf_launch(const CUtensorMap& mw, const CUtensorMap& mx, const FusedParams& p, const RopeParams* rope,
+                     cudaStream_t stream) {
     const long long ctas = (long long)((p.n_out + TC_BM - 1) / TC_BM) * ((p.T + BN - 1) / BN) * p.splits;
-    if (BN <= 32 && ctas <= sm_count() && p.kb_per_split > 4) return gf_launch_stages<BN, 8>(mw, mx, p, stream);
-    return gf_launch_stages<BN, 4>(mw, mx, p, stream);
+    if (p.mode == GF_ROPE) {
+        if (BN <= 32 && ctas <= sm_count() && p.kb_per_split > 4) return gf_launch_stages<BN, 8, true>(mw, mx, p, rope, stream);
+        return gf_launch_stages<BN, 4, true>(mw, mx, p, rope, stream);
+    }
+    if (BN <= 32 && ctas <= sm_count() && p.kb_per_split > 4) return gf_launch_stages<BN, 8, false>(mw, mx, p, rope, stream);
+    return gf_launch_stages<BN, 4, false>(mw, mx, p, rope, stream);
 }
 
 }  // namespace bg
 
 using namespace bg;
 
-// See the head of the file.  X (bfloat16 [T, K], row stride ldx) or xf (float [T, K], row stride ldxf, with
-// ssq_in, norm_w and eps) is the left operand; splits is 1, 2, 4, 8 or 16.
-extern "C" int bg_gemm_fused(const void* W, int n_out, int K, int ldw, const void* X, int ldx, const float* xf, int ldxf,
-                             const float* ssq_in, int n_ssq_in, int ssq_in_stride, const void* norm_w, float eps, int T,
-                             const float* bias, int mode, void* out, int out_dtype, int ldo, float* ssq_out,
-                             int ssq_out_stride, int splits, unsigned* status, cudaStream_t stream) {
+struct RopeArgs {
+    const float* cos_sin;
+    const int *positions, *row_req, *block_table;
+    void* kv_pool;
+    int max_pages, num_pages, page_size, nh, nkv, hd;
+};
+
+static int gemm_fused_run(const void* W, int n_out, int K, int ldw, const void* X, int ldx, const float* xf, int ldxf,
+                          const float* ssq_in, int n_ssq_in, int ssq_in_stride, const void* norm_w, float eps, int T,
+                          const float* bias, int mode, void* out, int out_dtype, int ldo, float* ssq_out,
+                          int ssq_out_stride, int splits, const RopeArgs* rope, unsigned* status, cudaStream_t stream) {
     if (T <= 0 || n_out <= 0) return BG_OK;
     if (K <= 0 || T > 64) return BG_ERR_SHAPE;
     if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return BG_ERR_SHAPE;
@@ -446,6 +554,10 @@ extern "C" int bg_gemm_fused(const void* W, int n_out, int K, int ldw, const voi
     if ((X == nullptr) == (xf == nullptr)) return BG_ERR_SHAPE;
     if (X && ((ldx % 8) || ((uintptr_t)X % 16))) return BG_ERR_ALIGN;
     if (xf && ((ldxf % 4) || ((uintptr_t)xf % 16) || ((uintptr_t)norm_w % 16) || !ssq_in || !norm_w || n_ssq_in < 1)) return BG_ERR_ALIGN;
+    FusedParams p;
+    RopeParams rp;
+    memset(&p, 0, sizeof(p));
+    memset(&rp, 0, sizeof(rp));
     if (mode == GF_PLAIN) {
         if (out_dtype != BG_DTYPE_F32 && out_dtype != BG_DTYPE_BF16) return BG_ERR_DTYPE;
     } else if (mode == GF_RESIDUAL) {
@@ -453,11 +565,22 @@ extern "C" int bg_gemm_fused(const void* W, int n_out, int K, int ldw, const voi
     } else if (mode == GF_SWIGLU) {
         if (out_dtype != BG_DTYPE_BF16) return BG_ERR_DTYPE;
         if (n_out % TC_BM) return BG_ERR_SHAPE;
+        p.pair_log = 6;
+    } else if (mode == GF_ROPE) {
+        if (!rope || out_dtype != BG_DTYPE_BF16) return BG_ERR_DTYPE;
+        // whole heads in a tile, so that a feature and its partner meet in one CTA
+        if (rope->hd != 32 && rope->hd != 64 && rope->hd != 128) return BG_ERR_UNSUPPORTED;
+        if (rope->nh < 1 || rope->nkv < 1 || n_out != (rope->nh + 2 * rope->nkv) * rope->hd) return BG_ERR_SHAPE;
+        if (!rope->cos_sin || !rope->positions || !rope->row_req || !rope->block_table || !rope->kv_pool) return BG_ERR_SHAPE;
+        if (rope->page_size < 1 || rope->max_pages < 1 || rope->num_pages < 1 || ((uintptr_t)rope->cos_sin % 8)) return BG_ERR_SHAPE;
+        p.pair_log = rope->hd == 32 ? 4 : rope->hd == 64 ? 5 : 6;
+        rp.cos_sin = (const float2*)rope->cos_sin; rp.positions = rope->positions; rp.row_req = rope->row_req;
+        rp.block_table = rope->block_table; rp.kv_pool = (__nv_bfloat16*)rope->kv_pool; rp.max_pages = rope->max_pages;
+        rp.num_pages = rope->num_pages; rp.page_size = rope->page_size; rp.nh = rope->nh; rp.nkv = rope->nkv;
     } else {
         return BG_ERR_SHAPE;
     }
     const int n_kb = (K + TC_BK - 1) / TC_BK;
-    FusedParams p;
     p.xf = xf; p.ldxf = ldxf; p.ssq_in = ssq_in; p.n_ssq_in = n_ssq_in; p.ssq_in_stride = ssq_in_stride;
     p.norm_w = (const __nv_bfloat16*)norm_w; p.eps = eps;
     p.bias = bias; p.mode = mode; p.out = out; p.out_dtype = out_dtype; p.ldo = ldo;
@@ -479,8 +602,36 @@ extern "C" int bg_gemm_fused(const void* W, int n_out, int K, int ldw, const voi
         memset(&mx, 0, sizeof(mx));
     }
     switch (bn) {
-        case 16: return gf_launch<16>(mw, mx, p, stream);
-        case 32: return gf_launch<32>(mw, mx, p, stream);
-        default: return gf_launch<64>(mw, mx, p, stream);
+        case 16: return gf_launch<16>(mw, mx, p, &rp, stream);
+        case 32: return gf_launch<32>(mw, mx, p, &rp, stream);
+        default: return gf_launch<64>(mw, mx, p, &rp, stream);
     }
+}
+
+// See the head of the file.  X (bfloat16 [T, K], row stride ldx) or xf (float [T, K], row stride ldxf, with
+// ssq_in, norm_w and eps) is the left operand; splits is 1, 2, 4, 8 or 16.
+extern "C" int bg_gemm_fused(const void* W, int n_out, int K, int ldw, const void* X, int ldx, const float* xf, int ldxf,
+                             const float* ssq_in, int n_ssq_in, int ssq_in_stride, const void* norm_w, float eps, int T,
+                             const float* bias, int mode, void* out, int out_dtype, int ldo, float* ssq_out,
+                             int ssq_out_stride, int splits, unsigned* status, cudaStream_t stream) {
+    if (mode == GF_ROPE) return BG_ERR_SHAPE;
+    return gemm_fused_run(W, n_out, K, ldw, X, ldx, xf, ldxf, ssq_in, n_ssq_in, ssq_in_stride, norm_w, eps, T, bias, mode,
+                          out, out_dtype, ldo, ssq_out, ssq_out_stride, splits, nullptr, status, stream);
+}
+
+// The q/k/v product of a step of few tokens with rotation and cache append behind it: W [(nh + 2 nkv) hd, K], the
+// left operand as above; q_out bfloat16 [T][q_stride]; cos_sin [T][hd / 2][2]; the pool of the layer
+// [num_pages][2][nkv][page_size][hd] bfloat16.  Head sizes other than 32, 64 and 128 are refused
+// (BG_ERR_UNSUPPORTED): the caller then runs the product and the rotation as two kernels.
+extern "C" int bg_gemm_fused_rope(const void* W, int K, int ldw, const void* X, int ldx, const float* xf, int ldxf,
+                                  const float* ssq_in, int n_ssq_in, int ssq_in_stride, const void* norm_w, float eps, int T,
+                                  const float* bias, void* q_out, int q_stride, const float* cos_sin, const int* positions,
+                                  const int* row_req, const int* block_table, int max_pages, void* kv_pool, int num_pages,
+                                  int page_size, int nh, int nkv, int hd, int splits, unsigned* status, cudaStream_t stream) {
+    RopeArgs r;
+    r.cos_sin = cos_sin; r.positions = positions; r.row_req = row_req; r.block_table = block_table; r.kv_pool = kv_pool;
+    r.max_pages = max_pages; r.num_pages = num_pages; r.page_size = page_size; r.nh = nh; r.nkv = nkv; r.hd = hd;
+    if (nh < 1 || nkv < 1 || hd < 1) return BG_ERR_SHAPE;
+    return gemm_fused_run(W, (nh + 2 * nkv) * hd, K, ldw, X, ldx, xf, ldxf, ssq_in, n_ssq_in, ssq_in_stride, norm_w, eps, T,
+                          bias, GF_ROPE, q_out, BG_DTYPE_BF16, q_stride, nullptr, 0, splits, &r, status, stream);
 }

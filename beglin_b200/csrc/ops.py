@@ -53,6 +53,10 @@ _SIGNATURES = {
     "bg_gemm_fused": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int,
                       _c_void_p, _c_float, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
                       _c_void_p, _c_void_p],
+    "bg_gemm_fused_rope": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int,
+                           _c_void_p, _c_float, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                           _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                           _c_void_p],
     "bg_sample": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "bg_sample_feed": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                        _c_void_p],
@@ -684,6 +688,55 @@ def gemm_fused_unchecked(w_ptr: int, n_out: int, k: int, ldw: int, T: int, out: 
                               F32 if out.dtype == torch.float32 else BF16, out.stride(0),
                               None if ssq_out is None else ssq_out.data_ptr(), 0 if ssq_out is None else ssq_out.stride(0),
                               splits, status_ptr, _stream()), "gemm_fused")
+
+
+def gemm_fused_rope(w: torch.Tensor, x: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                    cos_sin: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor,
+                    kv_pool: torch.Tensor, nh: int, nkv: int, hd: int, splits: int = 1,
+                    status: Optional[torch.Tensor] = None) -> None:
+    """x [T, K] (bfloat16, up to 64 rows) times w [(nh + 2 nkv) hd, K]^T (+ bias), rows [q | k | v]: queries and
+    keys rotated by cos_sin [T, hd / 2, 2] (feature d with d + hd / 2), queries to q_out [T, nh hd], keys and
+    values into kv_pool [pages, 2, nkv, page_size, hd] at positions[t] of request row_req[t].  hd is 32, 64 or 128."""
+    _cuda(w, x, bias, q_out, cos_sin, positions, row_req, block_table, kv_pool, status)
+    N, K = w.shape
+    T = x.shape[0]
+    if w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16:
+        raise KernelError("gemm_fused_rope takes bfloat16 weights, rows, queries and cache")
+    if N != (nh + 2 * nkv) * hd or x.shape[1] != K or w.stride(1) != 1 or x.stride(1) != 1 or T > 64:
+        raise KernelError(f"gemm_fused_rope: w {tuple(w.shape)}, x {tuple(x.shape)} for {nh}/{nkv} heads of {hd}")
+    if q_out.shape[0] < T or q_out.shape[1] < nh * hd or q_out.stride(1) != 1:
+        raise KernelError(f"gemm_fused_rope: q_out is {tuple(q_out.shape)}")
+    if kv_pool.dim() != 5 or tuple(kv_pool.shape[1:3]) != (2, nkv) or kv_pool.shape[4] != hd or not kv_pool.is_contiguous():
+        raise KernelError(f"gemm_fused_rope: the pool is {tuple(kv_pool.shape)}")
+    if cos_sin.dtype != torch.float32 or tuple(cos_sin.shape) != (T, hd // 2, 2) or not cos_sin.is_contiguous():
+        raise KernelError(f"gemm_fused_rope: cos_sin is {tuple(cos_sin.shape)}, expected {(T, hd // 2, 2)} float32")
+    for t in (positions, row_req, block_table):
+        _i32(t, "positions, row_req and block_table")
+    if positions.numel() != T or row_req.numel() != T or block_table.dim() != 2 or not block_table.is_contiguous():
+        raise KernelError("gemm_fused_rope: positions and row_req have one value per row, block_table is [requests, pages]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N or not bias.is_contiguous()):
+        raise KernelError("gemm_fused_rope: bias must be float32 with one value per output feature")
+    gemm_fused_rope_unchecked(w.data_ptr(), K, w.stride(0), T, q_out, x, None, None, None, 0.0,
+                              None if bias is None else bias.data_ptr(), cos_sin, positions, row_req, block_table, kv_pool,
+                              kv_pool.shape[3], nh, nkv, hd, splits, None if status is None else status.data_ptr())
+
+
+def gemm_fused_rope_unchecked(w_ptr: int, k: int, ldw: int, T: int, q_out: torch.Tensor, x, xf, ssq_in, norm_w_ptr,
+                              eps: float, bias_ptr, cos_sin: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor,
+                              block_table: torch.Tensor, kv_pool: torch.Tensor, page_size: int, nh: int, nkv: int, hd: int,
+                              splits: int, status_ptr) -> None:
+    """The q/k/v product of up to 64 rows with rotation and cache append behind it (left operand as gemm_fused):
+    q_out bfloat16 [T, nh hd] receives the rotated queries, kv_pool [pages, 2, nkv, page_size, hd] (bfloat16) the
+    rotated keys and the values at each row's position.  For a caller that has checked the shapes (Attention);
+    head sizes other than 32, 64 and 128 raise."""
+    _check(_lib.bg_gemm_fused_rope(w_ptr, k, ldw, None if x is None else x.data_ptr(), 0 if x is None else x.stride(0),
+                                   None if xf is None else xf.data_ptr(), 0 if xf is None else xf.stride(0),
+                                   None if ssq_in is None else ssq_in.data_ptr(), 0 if ssq_in is None else ssq_in.shape[0],
+                                   0 if ssq_in is None else ssq_in.stride(0), norm_w_ptr, eps, T, bias_ptr,
+                                   q_out.data_ptr(), q_out.stride(0), cos_sin.data_ptr(), positions.data_ptr(),
+                                   row_req.data_ptr(), block_table.data_ptr(), block_table.shape[1], kv_pool.data_ptr(),
+                                   kv_pool.shape[0], page_size, nh, nkv, hd, splits, status_ptr, _stream()),
+           "gemm_fused_rope")
 
 
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],

@@ -69,6 +69,10 @@ class GQAAttention:
         self.plans = {d: ops.attention_plan(self.nh // self.nkv, self.hd, ctx.cache_dtype, d, ctx.attention,
                                             ctx.page_size) for d in (False, True)}
         self.window = int(spec.window) if spec.window else 0
+        # the fused q/k/v product can rotate and append itself: whole heads rotated in halves, a cache of its own
+        # in bfloat16
+        self.rope_in_product = (spec.own_kv and self.position.rotary_dim == self.hd and not self.position.interleaved
+                                and ctx.compute_dtype == torch.bfloat16 and ctx.cache_dtype == torch.bfloat16)
 
     takes_stream = True        # forward takes a NormedInput and may add its result to the stream itself
 
@@ -76,11 +80,17 @@ class GQAAttention:
         """h: the normed rows, or a NormedInput.  With `stream` the result is added to it (or left owed to
         it) and None is returned; without, the addend is returned."""
         T = batch.n_rows
-        qkv = self.qkv.of(h)
-        q = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=qkv.device)
-        ops.rope_kv_append(qkv, q, T, self.nh, self.nkv, self.hd, self.position.rotary_dim, self.position.interleaved,
-                           self.position.table(batch), batch.positions, batch.row_req, cache.block_table,
-                           cache.pool if self.spec.own_kv else None, cache.page_size, self.ctx.status)
+        if self.rope_in_product and self.qkv.rope_fuses(T, self.hd):
+            # a step of few tokens: rotation and cache append inside the q/k/v product
+            q = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=self.ctx.device)
+            self.qkv.of_rope(h, q, (self.position.table(batch), batch.positions, batch.row_req, cache.block_table,
+                                    cache.pool, cache.page_size, self.nh, self.nkv, self.hd))
+        else:
+            qkv = self.qkv.of(h)
+            q = torch.empty((T, self.qd), dtype=self.ctx.compute_dtype, device=qkv.device)
+            ops.rope_kv_append(qkv, q, T, self.nh, self.nkv, self.hd, self.position.rotary_dim, self.position.interleaved,
+                               self.position.table(batch), batch.positions, batch.row_req, cache.block_table,
+                               cache.pool if self.spec.own_kv else None, cache.page_size, self.ctx.status)
         kernel, bq, tile = self.plans[bool(getattr(batch, "decode_only", False))]
         qblk, n_qblk = batch.query_blocks(bq)
         if qblk is None and kernel != "mma_keys":

@@ -107,6 +107,27 @@ class Linear:
                 self._tc.fused(T, out, mode, x=x, bias=self.bias_f32)
         return out
 
+    def rope_fuses(self, T: int, hd: int) -> bool:
+        """Whether a step of T rows runs this (q/k/v) product with rotation and cache append inside it."""
+        return self.fuses(T) and hd in self._tc.ROPE_HEAD_SIZES
+
+    def of_rope(self, inp, q_out: torch.Tensor, rope: tuple) -> None:
+        """The q/k/v product of `inp` (as `of`) with the rotation of queries and keys and the append of keys and
+        values to the cache inside it: q_out [T, nh hd] receives the queries; `rope` is (cos_sin, positions,
+        row_req, block_table, kv_pool, page_size, nh, nkv, hd).  Only where `rope_fuses`."""
+        lazy = isinstance(inp, NormedInput)
+        T = inp.rows if lazy else inp.shape[0]
+        fusion = inp.fusable() if lazy else None
+        with ops.phase(self.label):
+            if fusion is not None:
+                weight, eps = fusion
+                self._tc.fused_rope(T, q_out, rope, xf=inp.stream.x, ssq_in=inp.stream.ssq, norm_weight=weight, eps=eps,
+                                    bias=self.bias_f32)
+            else:
+                x = inp.tensor() if lazy else inp
+                self._check_rows(x)
+                self._tc.fused_rope(T, q_out, rope, x=x, bias=self.bias_f32)
+
     def into(self, x: torch.Tensor, stream: ResidualStream) -> None:
         """stream += x W^T (+ bias).  Where the fused product runs it adds to the stream itself and leaves
         the sums of squares of the new rows for the next norm; else the result is owed to the stream."""

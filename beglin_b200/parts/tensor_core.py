@@ -88,6 +88,17 @@ class TensorCoreProduct:
                                  None if bias is None else bias.data_ptr(), ssq_out, s, self._status_ptr)
         return ssq_out
 
+    ROPE_HEAD_SIZES = (32, 64, 128)      # whole heads in a tile of 128 rows, so that a feature meets its partner
+
+    def fused_rope(self, T: int, q_out: torch.Tensor, rope: tuple, x: Optional[torch.Tensor] = None,
+                   xf: Optional[torch.Tensor] = None, ssq_in: Optional[torch.Tensor] = None,
+                   norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, bias: Optional[torch.Tensor] = None) -> None:
+        """The q/k/v product with rotation and cache append behind it; `rope` is (cos_sin, positions, row_req,
+        block_table, kv_pool, page_size, nh, nkv, hd)."""
+        ops.gemm_fused_rope_unchecked(self._w_ptr, self.k, self._ldw, T, q_out, x, xf, ssq_in,
+                                      None if norm_weight is None else norm_weight.data_ptr(), eps,
+                                      None if bias is None else bias.data_ptr(), *rope, self.fused_splits(T), self._status_ptr)
+
     # ------------------------------------------------------------------ the product of many rows on pairs of CTAs
     def pairs(self, T: int) -> bool:
         """Whether a step of T rows runs gate/up with SwiGLU as ONE kernel of CTA pairs (measured at the 1.5B and

@@ -23,6 +23,8 @@ def test_fused_and_plain_steps_agree(model_root, name):
         layer = eng.model.blocks[0]
         assert layer.mixer.qkv.fuses(4) == fuse and layer.feed_forward.down.fuses(4) == fuse
         assert not layer.mixer.qkv.fuses(17)                       # only few-token steps
+        hd = layer.mixer.hd                                        # rotation and cache append inside the q/k/v product
+        assert (layer.mixer.rope_in_product and layer.mixer.qkv.rope_fuses(4, hd)) == (fuse and hd in (32, 64, 128))
         rows = [eng.step([("r", ids[:20], list(range(20)))])]      # a portion (plain way in both engines)
         for t in range(20, 40, 4):                                 # then four tokens at a time (fused when allowed)
             rows.append(eng.step([("r", ids[t:t + 4], [0, 1, 2, 3])]))

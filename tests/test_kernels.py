@@ -560,6 +560,65 @@ def test_gemm_fused_swiglu(ops, T, im, K, splits, bias):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("nh,nkv,hd,K,splits", [(12, 2, 128, 1536, 8), (3, 1, 32, 96, 1), (6, 2, 64, 192, 2), (5, 1, 64, 264, 2),
+                                                (7, 3, 32, 1024, 16), (1, 1, 128, 128, 1), (28, 4, 128, 512, 2)])
+@pytest.mark.parametrize("T", [1, 7, 16, 40])
+def test_gemm_fused_rope(ops, nh, nkv, hd, K, splits, T):
+    """The q/k/v product with rotation and cache append inside it: tiles that hold whole heads (128), two or four
+    heads of different kinds (a query beside a key, a key beside a value), a last tile that is partly empty; the rows
+    of three requests at scattered positions, pages in shuffled order, everything not written stays poison; one row
+    with a page number outside the pool is reported and writes nothing."""
+    torch.manual_seed(nh * 100 + hd + T)
+    page, n_pages, max_pages = 16, 23, 6
+    N = (nh + 2 * nkv) * hd
+    x = (torch.randn(T, K) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(N) * 0.2
+    row_req = torch.tensor([t % 3 for t in range(T)], dtype=torch.int32)
+    start = [0, 37, 70]
+    positions = torch.tensor([start[t % 3] + t // 3 for t in range(T)], dtype=torch.int32)       # request r: start[r], start[r] + 1, ...
+    perm = torch.randperm(n_pages)[:3 * max_pages].reshape(3, max_pages).to(torch.int32)
+    bt = perm.clone()
+    bad_row = T - 1 if T >= 7 else None
+    if bad_row is not None:                                            # the last row's page: outside the pool
+        positions[bad_row] = 90
+        bt[int(row_req[bad_row]), int(positions[bad_row]) // page] = n_pages + 5
+        for t in range(T):                                             # (no other row may share that page)
+            assert t == bad_row or (int(row_req[t]), int(positions[t]) // page) != (int(row_req[bad_row]), int(positions[bad_row]) // page)
+    inv = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -(2 * torch.arange(hd // 2, dtype=torch.float64)) / hd).float().to(DEV)
+    table = torch.empty((T, hd // 2, 2), device=DEV)
+    ops.rope_table(positions.to(DEV), inv, table)
+    pool = torch.full((n_pages, 2, nkv, page, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    q_out = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = ops.new_status(DEV)
+    ops.gemm_fused_rope(w.to(DEV), x.to(DEV), bias.to(DEV), q_out, table, positions.to(DEV), row_req.to(DEV), bt.to(DEV),
+                        pool, nh, nkv, hd, splits=splits, status=status)
+    torch.cuda.synchronize()
+    word = int(status.item())
+    assert word == (ops.STATUS_BAD_PAGE if bad_row is not None else 0)
+    status.zero_()
+    o = (x.double() @ w.double().t() + bias.double()).reshape(T, nh + 2 * nkv, hd)
+    c, s_ = table[..., 0].double().cpu()[:, None, :], table[..., 1].double().cpu()[:, None, :]
+
+    def rotate(v):
+        a, b = v[..., :hd // 2], v[..., hd // 2:]
+        return torch.cat([a * c - b * s_, b * c + a * s_], dim=-1)
+
+    scale = max(1.0, float(o.abs().max()))
+    assert (q_out.double().cpu().reshape(T, nh, hd) - rotate(o[:, :nh])).abs().max() < 1e-2 * scale
+    k, v = rotate(o[:, nh:nh + nkv]), o[:, nh + nkv:]
+    written = 0
+    for t in range(T):
+        if t == bad_row:
+            continue
+        pg, sl = int(bt[int(row_req[t]), int(positions[t]) // page]), int(positions[t]) % page
+        assert (pool[pg, 0, :, sl].double().cpu() - k[t]).abs().max() < 1e-2 * scale
+        assert (pool[pg, 1, :, sl].double().cpu() - v[t]).abs().max() < 1e-2 * scale
+        written += 1
+    assert int(torch.isfinite(pool.float()).sum()) == written * 2 * nkv * hd       # nothing else was written
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("T,N,K,bias", [(256, 256, 64, False), (300, 520, 200, True), (2048, 1536, 1536, True),
                                         (1000, 1288, 456, False), (65, 8, 72, True), (777, 17920 // 8, 1536, False),
                                         (2048, 4096, 128, True), (3000, 2600, 72, False)])
