@@ -20,7 +20,9 @@ class BuildContext:
     kv_split: int = 256
     gemm: str = "auto"                      # "auto", "library" or "tcgen05" for the bfloat16 products
     attention: str = "auto"                 # "auto", "generic" (CUDA cores) or "mma" (tensor cores) kernel
-    fuse: bool = True                       # few-token steps: norms, residual adds and SwiGLU inside the products
+    # few-token steps: norms, residual adds, SwiGLU, rotation and cache append inside the products.  True: where it was
+    # measured to pay; "all": wherever the sizes allow it (tests of the fused kernels on tiny models); False: nowhere
+    fuse: object = True
     status: Optional[torch.Tensor] = None   # device word in which kernels record bad ids and pages
     shared: Dict[object, object] = field(default_factory=dict)   # parts shared between layers, by spec
 

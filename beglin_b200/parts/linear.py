@@ -108,8 +108,14 @@ class Linear:
         return out
 
     def rope_fuses(self, T: int, hd: int) -> bool:
-        """Whether a step of T rows runs this (q/k/v) product with rotation and cache append inside it."""
-        return self.fuses(T) and hd in self._tc.ROPE_HEAD_SIZES
+        """Whether a step of T rows runs this (q/k/v) product with rotation and cache append inside it: where the
+        fused product runs, the heads fit its tiles, and the product has CTAs for at least half of the SMs (measured
+        in one run each: 1.283 against 1.354 ms a step at the 1.5B sizes with 128 CTAs and 3.69 against 3.71 ms at
+        the 7B sizes with 144, but 0.954 against 0.943 ms at the 0.5B sizes, whose 36 CTAs take 2 us longer for
+        it, as long as the kernel that it saves).  A context built with fuse="all" fuses whatever the sizes allow."""
+        if not self.fuses(T) or hd not in self._tc.ROPE_HEAD_SIZES:
+            return False
+        return self.ctx.fuse == "all" or 2 * self._tc.tiles * self._tc.fused_splits(T) >= self._tc.sms
 
     def of_rope(self, inp, q_out: torch.Tensor, rope: tuple) -> None:
         """The q/k/v product of `inp` (as `of`) with the rotation of queries and keys and the append of keys and

@@ -17,21 +17,25 @@ def test_fused_and_plain_steps_agree(model_root, name):
     ids = seeded_ids(40, cfg["vocab_size"], 5)
     want = plain_logits(folder, ids)
     outs = {}
-    for fuse in (True, False):
+    for fuse in (True, False, "all"):
         eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=256, page_size=page, max_requests=2, fuse=fuse)
         rl.poison(eng)
         layer = eng.model.blocks[0]
-        assert layer.mixer.qkv.fuses(4) == fuse and layer.feed_forward.down.fuses(4) == fuse
+        assert layer.mixer.qkv.fuses(4) == bool(fuse) and layer.feed_forward.down.fuses(4) == bool(fuse)
         assert not layer.mixer.qkv.fuses(17)                       # only few-token steps
-        hd = layer.mixer.hd                                        # rotation and cache append inside the q/k/v product
-        assert (layer.mixer.rope_in_product and layer.mixer.qkv.rope_fuses(4, hd)) == (fuse and hd in (32, 64, 128))
+        # rotation and cache append inside the q/k/v product: for heads that fit its tiles; a product of as few CTAs
+        # as these models' only when everything is fused that can be
+        hd = layer.mixer.hd
+        assert (layer.mixer.rope_in_product and layer.mixer.qkv.rope_fuses(4, hd)) == (fuse == "all" and hd in (32, 64, 128))
         rows = [eng.step([("r", ids[:20], list(range(20)))])]      # a portion (plain way in both engines)
         for t in range(20, 40, 4):                                 # then four tokens at a time (fused when allowed)
             rows.append(eng.step([("r", ids[t:t + 4], [0, 1, 2, 3])]))
         outs[fuse] = torch.cat(rows).cpu()
         assert rel_err(outs[fuse], want) < TOL_BF16, (name, fuse)
     assert rel_err(outs[True], outs[False]) < TOL_BF16 / 2
+    assert rel_err(outs["all"], outs[False]) < TOL_BF16 / 2
     assert torch.equal(outs[True][:20], outs[False][:20])          # the portion ran the same kernels
+    assert torch.equal(outs["all"][:20], outs[False][:20])
 
 
 def test_fused_swiglu_needs_blocks_of_64(model_root):
@@ -115,3 +119,26 @@ def test_an_engine_of_own_products_only(model_root):
         outs[gemm] = torch.cat(got).cpu()
         assert rel_err(outs[gemm], want) < TOL_BF16, gemm
     assert rel_err(outs["tcgen05"], outs["auto"]) < TOL_BF16 / 2
+
+
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_everything_fused_in_a_mixed_replay(model_root, name):
+    """Up to four live requests, portions of some beside decoded tokens of others, a pool so small that pages are
+    used again, with every fusion on that the sizes allow: the rope epilogue of the q/k/v product among them, which
+    products as small as these models' do not get by default.  Heads of 32 (B) and 64 (D)."""
+    from beglin_b200 import Engine
+    cfg, _, page = TINY[name]
+    folder = make_model(model_root, name, seed=17, dtype=torch.bfloat16)
+    lens = [90, 33, 150, 61, 120, 47, 77]
+    reqs = {f"q{i}": seeded_ids(n, cfg["vocab_size"], 300 + i) for i, n in enumerate(lens)}
+    steps, peak = rl.mixed(reqs, seed=5)
+    eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=peak, page_size=page, max_requests=4, fuse="all")
+    mixer = eng.model.blocks[0].mixer
+    assert mixer.rope_in_product and mixer.qkv.rope_fuses(3, mixer.hd)
+    rl.poison(eng)
+    got = rl.run_in_process(eng, steps)
+    for rid, ids in reqs.items():
+        rows = torch.stack([got[(rid, p)] for p in range(len(ids))])
+        assert torch.isfinite(rows).all(), rid
+        assert rel_err(rows, plain_logits(folder, ids)) < TOL_BF16, rid
+    eng.cache.check()
