@@ -2,6 +2,7 @@
 
     python -m beglin_b200.csrc.microbench gemm --tokens 8 --out 17920 --inner 1536 --splits 2
     python -m beglin_b200.csrc.microbench gemm-fused --tokens 8 --out 17920 --inner 1536 --splits 2 --norm --mode swiglu
+    python -m beglin_b200.csrc.microbench gemm-fused --tokens 8 --inner 1536 --splits 8 --norm --mode rope --heads 12 --kv-heads 2
     python -m beglin_b200.csrc.microbench gemm-pair --tokens 2048 --out 17920 --inner 1536 --mode swiglu [--library]
     python -m beglin_b200.csrc.microbench attention-decode --batch 8 --context 4096
     python -m beglin_b200.csrc.microbench attention-prefill --tokens 2048
@@ -61,8 +62,10 @@ def gemm(a) -> None:
 
 def gemm_fused(a) -> None:
     """The fused few-token product: --norm makes the operand from a float residual stream (RMSNorm inside),
-    --mode plain | residual | swiglu picks the epilogue."""
+    --mode plain | residual | swiglu | rope picks the epilogue."""
     T, N, K, S = a.tokens, a.out, a.inner, a.splits
+    if a.mode == "rope":
+        return gemm_fused_rope(a)
     mode = {"plain": ops.FUSED_PLAIN, "residual": ops.FUSED_RESIDUAL, "swiglu": ops.FUSED_SWIGLU}[a.mode]
     copies = max(2, min(48, int(300e6 // (N * K * 2)) + 1))
     ws = [(torch.randn(N, K, device=DEV) * 0.02).to(torch.bfloat16) for _ in range(copies)]
@@ -80,6 +83,35 @@ def gemm_fused(a) -> None:
     ops.raise_on_status(status)
     print(f"gemm-fused tokens={T} out={N} inner={K} splits={S} {'norm -> ' if a.norm else ''}{a.mode}: {us:.1f} us  "
           f"{N * K * 2 / us / 1e3:.0f} GB/s of weights")
+
+
+def gemm_fused_rope(a) -> None:
+    """The q/k/v product of a decoding step with rotation and cache append behind it: --tokens requests at position
+    --context - 1, --heads / --kv-heads of --head-dim (the weight has (heads + 2 kv heads) head_dim rows)."""
+    T, K, S, nh, nkv, hd, page = a.tokens, a.inner, a.splits, a.heads, a.kv_heads, a.head_dim, 64
+    N = (nh + 2 * nkv) * hd
+    copies = max(2, min(48, int(300e6 // (N * K * 2)) + 1))
+    ws = [(torch.randn(N, K, device=DEV) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    x = torch.randn(T, K, device=DEV).to(torch.bfloat16)
+    xf = torch.randn(T, K, device=DEV)
+    g = torch.ones(K, device=DEV, dtype=torch.bfloat16)
+    ssq_in = (xf * xf).sum(1)[None, :].repeat(12, 1) / 12
+    ssq_in = torch.nn.functional.pad(ssq_in, (0, 64 - T)).contiguous()
+    bias = torch.randn(N, device=DEV) * 0.1
+    pool, bt = _filled_cache(T, a.context, nkv, hd, page)
+    positions = torch.full((T,), a.context - 1, dtype=torch.int32, device=DEV)
+    row_req = torch.arange(T, dtype=torch.int32, device=DEV)
+    inv = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -(2 * torch.arange(hd // 2, dtype=torch.float64)) / hd).float().to(DEV)
+    table = torch.empty((T, hd // 2, 2), device=DEV)
+    ops.rope_table(positions, inv, table)
+    q_out = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=DEV)
+    status = ops.new_status(DEV)
+    kw = dict(xf=xf, ssq_in=ssq_in, norm_weight=g, eps=1e-6) if a.norm else {}
+    us = _time(lambda i: ops.gemm_fused_rope(ws[i % copies], None if a.norm else x, bias, q_out, table, positions, row_req, bt,
+                                             pool, nh, nkv, hd, splits=S, status=status, **kw), a.launches)
+    ops.raise_on_status(status)
+    print(f"gemm-fused tokens={T} heads={nh}/{nkv} head_dim={hd} inner={K} splits={S} {'norm -> ' if a.norm else ''}rope: "
+          f"{us:.1f} us  {N * K * 2 / us / 1e3:.0f} GB/s of weights")
 
 
 def _filled_cache(batch: int, context: int, nkv: int, hd: int, page: int):
@@ -187,7 +219,9 @@ def main() -> None:
     f = sub.add_parser("gemm-fused")
     f.add_argument("--tokens", type=int, default=8); f.add_argument("--out", type=int, default=17920)
     f.add_argument("--inner", type=int, default=1536); f.add_argument("--splits", type=int, default=2)
-    f.add_argument("--norm", action="store_true"); f.add_argument("--mode", default="plain", choices=["plain", "residual", "swiglu"])
+    f.add_argument("--norm", action="store_true"); f.add_argument("--mode", default="plain", choices=["plain", "residual", "swiglu", "rope"])
+    f.add_argument("--heads", type=int, default=12); f.add_argument("--kv-heads", type=int, default=2)
+    f.add_argument("--head-dim", type=int, default=128); f.add_argument("--context", type=int, default=4096)
     f.set_defaults(fn=gemm_fused)
     d = sub.add_parser("attention-decode")
     d.add_argument("--batch", type=int, default=8); d.add_argument("--context", type=int, default=4096)

@@ -690,20 +690,35 @@ def gemm_fused_unchecked(w_ptr: int, n_out: int, k: int, ldw: int, T: int, out: 
                               splits, status_ptr, _stream()), "gemm_fused")
 
 
-def gemm_fused_rope(w: torch.Tensor, x: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+def gemm_fused_rope(w: torch.Tensor, x: Optional[torch.Tensor], bias: Optional[torch.Tensor], q_out: torch.Tensor,
                     cos_sin: torch.Tensor, positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor,
                     kv_pool: torch.Tensor, nh: int, nkv: int, hd: int, splits: int = 1,
-                    status: Optional[torch.Tensor] = None) -> None:
-    """x [T, K] (bfloat16, up to 64 rows) times w [(nh + 2 nkv) hd, K]^T (+ bias), rows [q | k | v]: queries and
-    keys rotated by cos_sin [T, hd / 2, 2] (feature d with d + hd / 2), queries to q_out [T, nh hd], keys and
-    values into kv_pool [pages, 2, nkv, page_size, hd] at positions[t] of request row_req[t].  hd is 32, 64 or 128."""
-    _cuda(w, x, bias, q_out, cos_sin, positions, row_req, block_table, kv_pool, status)
+                    status: Optional[torch.Tensor] = None, *, xf: Optional[torch.Tensor] = None,
+                    ssq_in: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+                    eps: float = 0.0) -> None:
+    """x [T, K] (bfloat16, up to 64 rows; or the float32 stream xf with ssq_in, norm_weight and eps, as gemm_fused)
+    times w [(nh + 2 nkv) hd, K]^T (+ bias), rows [q | k | v]: queries and keys rotated by cos_sin [T, hd / 2, 2]
+    (feature d with d + hd / 2), queries to q_out [T, nh hd], keys and values into kv_pool
+    [pages, 2, nkv, page_size, hd] at positions[t] of request row_req[t].  hd is 32, 64 or 128."""
+    _cuda(w, x, xf, ssq_in, norm_weight, bias, q_out, cos_sin, positions, row_req, block_table, kv_pool, status)
     N, K = w.shape
-    T = x.shape[0]
-    if w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16:
-        raise KernelError("gemm_fused_rope takes bfloat16 weights, rows, queries and cache")
-    if N != (nh + 2 * nkv) * hd or x.shape[1] != K or w.stride(1) != 1 or x.stride(1) != 1 or T > 64:
-        raise KernelError(f"gemm_fused_rope: w {tuple(w.shape)}, x {tuple(x.shape)} for {nh}/{nkv} heads of {hd}")
+    if (x is None) == (xf is None):
+        raise KernelError("gemm_fused_rope takes either x (bfloat16) or xf (float32 with ssq_in and norm_weight)")
+    src = x if x is not None else xf
+    T = src.shape[0]
+    if w.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16:
+        raise KernelError("gemm_fused_rope takes bfloat16 weights, queries and cache")
+    if x is not None and x.dtype != torch.bfloat16:
+        raise KernelError("gemm_fused_rope: x must be bfloat16")
+    if xf is not None:
+        if xf.dtype != torch.float32 or ssq_in is None or norm_weight is None:
+            raise KernelError("gemm_fused_rope: xf must be float32 and come with ssq_in and norm_weight")
+        if ssq_in.dtype != torch.float32 or ssq_in.dim() != 2 or ssq_in.shape[1] < T or ssq_in.stride(1) != 1:
+            raise KernelError("gemm_fused_rope: ssq_in must be float32 [parts, >= T]")
+        if norm_weight.dtype != torch.bfloat16 or norm_weight.numel() != K or not norm_weight.is_contiguous():
+            raise KernelError("gemm_fused_rope: norm_weight must be bfloat16 with one value per input feature")
+    if N != (nh + 2 * nkv) * hd or src.shape[1] != K or w.stride(1) != 1 or src.stride(1) != 1 or T > 64:
+        raise KernelError(f"gemm_fused_rope: w {tuple(w.shape)}, rows {tuple(src.shape)} for {nh}/{nkv} heads of {hd}")
     if q_out.shape[0] < T or q_out.shape[1] < nh * hd or q_out.stride(1) != 1:
         raise KernelError(f"gemm_fused_rope: q_out is {tuple(q_out.shape)}")
     if kv_pool.dim() != 5 or tuple(kv_pool.shape[1:3]) != (2, nkv) or kv_pool.shape[4] != hd or not kv_pool.is_contiguous():
@@ -716,7 +731,8 @@ def gemm_fused_rope(w: torch.Tensor, x: torch.Tensor, bias: Optional[torch.Tenso
         raise KernelError("gemm_fused_rope: positions and row_req have one value per row, block_table is [requests, pages]")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N or not bias.is_contiguous()):
         raise KernelError("gemm_fused_rope: bias must be float32 with one value per output feature")
-    gemm_fused_rope_unchecked(w.data_ptr(), K, w.stride(0), T, q_out, x, None, None, None, 0.0,
+    gemm_fused_rope_unchecked(w.data_ptr(), K, w.stride(0), T, q_out, x, xf, ssq_in,
+                              None if norm_weight is None else norm_weight.data_ptr(), float(eps),
                               None if bias is None else bias.data_ptr(), cos_sin, positions, row_req, block_table, kv_pool,
                               kv_pool.shape[3], nh, nkv, hd, splits, None if status is None else status.data_ptr())
 
