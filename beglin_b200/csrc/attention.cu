@@ -405,14 +405,15 @@ attention_merge_block_kernel(const float* __restrict__ part_o, const float* __re
     __shared__ float4 acc_s[MERGE_WARPS][32];
     __shared__ float2 ml_s[MERGE_WARPS];
     pdl_launch();
-    pdl_wait();
     const int w = blockIdx.x;                                   // (row, head)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = w / nh, h = w - t * nh;
+    // (the row's position is written by no kernel of the step: its range of splits is worked out before the wait)
     const int pos = positions[t];
     const int split = keys_per_split(split_arg, pos + 1, max_splits);
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int s_lo = lo / split, s_hi = pos / split;
+    pdl_wait();
     const size_t prow = (size_t)w * max_splits;
     const int d = lane * 4;
     const bool live = d < hd;                                   // hd is a multiple of 4
@@ -484,13 +485,22 @@ extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, con
     if (T <= 0) return BG_OK;
     long long warps = (long long)T * nh;
     unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
-    if (max_splits <= 8 && hd <= 128) {
+    const bool block_fits = hd <= 128 && hd % 4 == 0 && out_dtype == BG_DTYPE_BF16 && warps <= 4096;
+    if (max_splits > 8 && warps <= 128 && block_fits) {
+        // few bfloat16 rows with more than eight splits each (one or two requests): a CTA per (row, head) spreads the
+        // loads over as many SMs as there are rows and heads; a warp per (row, head) keeps them on one or two
+        // (one request at 4,096 positions, 16 splits: the merge cost its step 5.7 us a layer that way and 2.5 to
+        // 5 us this way; the decode step of the 1.5B sizes went from 1.372 to 1.214 ms at batch 1, from 1.225 to
+        // 1.151 ms at batch 2)
+        launch(attention_merge_block_kernel<__nv_bfloat16>, dim3((unsigned)warps), dim3(32 * MERGE_WARPS), 0, stream,
+               part_o, part_ml, positions, (__nv_bfloat16*)out, out_stride, T, nh, hd, max_splits, split, window);
+    } else if (max_splits <= 8 && hd <= 128) {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 8>, dim3(blocks), dim3(256), 0, stream,
             part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
     } else if (max_splits <= 16 && hd <= 128) {
         BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 16>, dim3(blocks), dim3(256), 0, stream,
             part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
-    } else if (hd <= 128 && hd % 4 == 0 && out_dtype == BG_DTYPE_BF16 && warps <= 4096) {
+    } else if (block_fits) {
         // bfloat16 rows of few requests with many splits each (the float path keeps one order of summation for
         // every shape of a step, so that its rows do not depend on the batch)
         launch(attention_merge_block_kernel<__nv_bfloat16>, dim3((unsigned)warps), dim3(32 * MERGE_WARPS), 0, stream,

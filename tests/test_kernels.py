@@ -706,7 +706,8 @@ def test_attention_merge_of_many_ranges_behind_a_window(ops, nh, nkv, hd, page, 
 
 @pytest.mark.parametrize("dtype,page,batch,bound", [(torch.bfloat16, 64, 8, 4095), (torch.bfloat16, 16, 8, 4095),
                                                     (torch.float32, 64, 8, 4095), (torch.bfloat16, 64, 64, 4095),
-                                                    (torch.bfloat16, 32, 3, 4095), (torch.bfloat16, 64, 2, 32767),
+                                                    (torch.bfloat16, 32, 3, 4095), (torch.bfloat16, 64, 4, 4095),
+                                                    (torch.bfloat16, 64, 2, 32767),
                                                     (torch.bfloat16, 64, 1, 20479)])
 def test_decoding_attention_under_a_bound_finds_every_needle(ops, dtype, page, batch, bound):
     """Decoding steps that are replayed as a graph launch the attention for the context limit, not for the
@@ -715,7 +716,8 @@ def test_decoding_attention_under_a_bound_finds_every_needle(ops, dtype, page, b
     (its value row is a marker), and it is moved through the places where a kernel can lose a key: the first and
     the newest, the two sides of a page's edge and of a 256-key stage, the middle.  Every row must come out as
     its marker; the other keys are noise.  Under a bound of tens of thousands of positions a request's keys are
-    spread over dozens of CTAs, whose partial results the wide merge joins."""
+    spread over dozens of CTAs, whose partial results the wide merge joins; so are the 16 ranges of the three and
+    four requests under 4,095 (few rows with more than eight ranges each)."""
     nh, nkv, hd = 12, 2, 128
     lengths = ([40, 700, 1500, 4000, 63, 1023, 255, 2049] * 8)[:batch]
     if batch == 64:
