@@ -485,6 +485,9 @@ extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, con
     if (T <= 0) return BG_OK;
     long long warps = (long long)T * nh;
     unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+    // few rows: a warp per block, so that the rows' loads go out from as many SMs as there are rows and heads
+    const bool spread = warps <= 592;
+    const unsigned few_blocks = spread ? (unsigned)warps : blocks, few_threads = spread ? 32u : 256u;
     const bool block_fits = hd <= 128 && hd % 4 == 0 && out_dtype == BG_DTYPE_BF16 && warps <= 4096;
     if (max_splits > 8 && warps <= 128 && block_fits) {
         // few bfloat16 rows with more than eight splits each (one or two requests): a CTA per (row, head) spreads the
@@ -495,10 +498,10 @@ extern "C" int bg_attention_merge(const float* part_o, const float* part_ml, con
         launch(attention_merge_block_kernel<__nv_bfloat16>, dim3((unsigned)warps), dim3(32 * MERGE_WARPS), 0, stream,
                part_o, part_ml, positions, (__nv_bfloat16*)out, out_stride, T, nh, hd, max_splits, split, window);
     } else if (max_splits <= 8 && hd <= 128) {
-        BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 8>, dim3(blocks), dim3(256), 0, stream,
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 8>, dim3(few_blocks), dim3(few_threads), 0, stream,
             part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
     } else if (max_splits <= 16 && hd <= 128) {
-        BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 16>, dim3(blocks), dim3(256), 0, stream,
+        BG_DISPATCH_DTYPE(out_dtype, TO, launch(attention_merge_few_kernel<TO, 16>, dim3(few_blocks), dim3(few_threads), 0, stream,
             part_o, part_ml, positions, (TO*)out, out_stride, T, nh, hd, max_splits, split, window));
     } else if (block_fits) {
         // bfloat16 rows of few requests with many splits each (the float path keeps one order of summation for
