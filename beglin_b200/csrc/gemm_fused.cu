@@ -21,7 +21,7 @@
 //                       (qwen_infer.c:727-733), so gate_up never reaches global memory;
 //             rope:     W's rows are [query heads | key heads | value heads] of hd features (hd 32, 64 or 128):
 //                       queries and keys are rotated by their token's angles (feature d with d + hd / 2,
-//                       qwen_infer.c:1078-1101), queries go to q[t, :] as bfloat16, keys and values into the
+//                       qwen_infer.c:782-790), queries go to q[t, :] as bfloat16, keys and values into the
 //                       cache page and slot of their token's position, so q/k/v never reach global memory
 //                       as one row and the step has no kernel for rotation and append.
 //
