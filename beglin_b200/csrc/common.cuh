@@ -130,6 +130,25 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Thread block clusters: the cluster-wide barrier (every thread of every CTA arrives) and stores into a
+// peer CTA's shared memory.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+// (nothing that this thread wrote has to be visible to the peers at the first use of the barrier)
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_sync_all() {
+    cluster_arrive();
+    cluster_wait();
+}
+// the address, in the cluster's shared window, of this CTA's shared-memory address in the CTA of the given rank
+__device__ __forceinline__ unsigned peer_addr(unsigned local_addr, unsigned rank) {
+    unsigned a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(a) : "r"(local_addr), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void st_cluster(unsigned addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
+}
 // Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` holds 32 floats.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

@@ -13,25 +13,6 @@ constexpr int TC_BM = 128;                 // output features per CTA (MMA M)
 constexpr int TC_BK = 64;                  // k per stage: 64 bf16 = 128 bytes = one swizzle row
 constexpr int TC_THREADS = 192;            // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
 
-// Thread block clusters: the cluster-wide barrier (every thread of every CTA arrives) and stores into a
-// peer CTA's shared memory.
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
-// (nothing that this thread wrote has to be visible to the peers at the first use of the barrier)
-__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void cluster_sync_all() {
-    cluster_arrive();
-    cluster_wait();
-}
-// the address, in the cluster's shared window, of this CTA's shared-memory address in the CTA of the given rank
-__device__ __forceinline__ unsigned peer_addr(unsigned local_addr, unsigned rank) {
-    unsigned a;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(a) : "r"(local_addr), "r"(rank));
-    return a;
-}
-__device__ __forceinline__ void st_cluster(unsigned addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
-}
 // A [rows, K] bfloat16 matrix with row stride ld (elements), cut into boxes of box_rows x 64.
 inline int make_map(CUtensorMap* map, const void* base, long long rows, int K, long long ld, int box_rows) {
     EncodeTiledFn fn = encode_fn();

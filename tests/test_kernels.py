@@ -78,6 +78,34 @@ def test_add_rmsnorm(ops, d, out_dtype):
     assert (out3.double() - want3).abs().max() < tol * want3.abs().max() and torch.equal(x2, x)
 
 
+@pytest.mark.parametrize("T,d,parts", [(64, 1536, 13), (32, 3584, 5), (20, 5120, 7), (17, 896, 2), (3, 8192, 4), (40, 24, 3)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm_of_partial_sums_for_few_rows(ops, T, d, parts, out_dtype):
+    """The addend as float partial sums of a split-K product, for the row counts of decoding steps of 17 to 64
+    tokens: bfloat16 results come from clusters of 2, 4 or 8 CTAs per row (every cluster size is met here, and a row
+    shorter than the cluster), float results from the block per row; with the stream updated, and with rows picked by
+    a list and the stream left alone."""
+    eps = 1e-6
+    x = rnd(T, d, seed=T)
+    ps = torch.stack([rnd(T, d, seed=100 + i, scale=0.5) for i in range(parts)]).contiguous()
+    w = (1 + 0.1 * rnd(d, seed=4)).to(out_dtype if out_dtype == torch.bfloat16 else torch.float32)
+    want_x = x.double() + ps.double().sum(0)
+    want = plain.rmsnorm(want_x, w.double(), eps)
+    tol = 1e-5 if out_dtype == torch.float32 else 1e-2
+    x1 = x.clone()
+    out = torch.full((T, d), float("nan"), dtype=out_dtype, device=DEV)
+    ops.add_rmsnorm(x1, ps, w, eps, out)
+    assert (x1.double() - want_x).abs().max() < 1e-5
+    assert (out.double() - want).abs().max() < tol * want.abs().max()
+    picked = [T - 1, 0, T // 2, T - 1]
+    rows = torch.tensor(picked, dtype=torch.int32, device=DEV)
+    x2 = x.clone()
+    out2 = torch.full((len(picked), d), float("nan"), dtype=out_dtype, device=DEV)
+    ops.add_rmsnorm(x2, ps, w, eps, out2, rows=rows, update=False)
+    assert torch.equal(x2, x)
+    assert torch.equal(out2, out[rows.long()])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_swiglu(ops, dtype):
     gu = rnd(5, 2 * 203, dtype=dtype, seed=5, scale=3.0)
